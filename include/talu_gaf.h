@@ -1,0 +1,164 @@
+/*
+ * talu_gaf.h - C ABI of libtalu_gaf.so: grouped-affine (gaf4 / gaf8) quantized
+ * matmul for NVIDIA B200 (sm_100a).
+ *
+ * Drop-in for the matmul operator behind talu's linear layers.  The weight
+ * layout is talu's own, unchanged (core/src/converter/grouped_affine.zig:565-593):
+ *
+ *   packed  u32 [N, K/vpw]  value j of a word at bits [j*bits, (j+1)*bits), vpw = 32/bits
+ *   scales  u16 [N, K/G]    bf16 (tag 1) or f16 (tag 0) bit patterns
+ *   biases  u16 [N, K/G]
+ *   w[n,k] = f32(q[n,k]) * f32(scale[n,k/G]) + f32(bias[n,k/G])
+ *   y[m,n] = sum_k x[m,k] * w[n,k]
+ *
+ * Conventions (the ones talu's own C API follows, core/POLICY.md:96-134):
+ *   - every function returns an int32 status, 0 = ok; nothing aborts or throws;
+ *   - out-parameters are zeroed before any work;
+ *   - tgaf_last_error(ctx) gives the text of the last failure on that context;
+ *   - a context is bound to one device and one stream; calls on one context
+ *     are not re-entrant (same rule as the reference's per-backend argument
+ *     pack, core/src/inference/backend/cuda/engine.zig:4435);
+ *   - compute entry points only enqueue work on the context's stream and
+ *     return; tgaf_synchronize or the *_host variants wait for it;
+ *   - there is no CPU fallback: without a CUDA device every compute call fails.
+ */
+#ifndef TALU_GAF_H
+#define TALU_GAF_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TGAF_ABI_VERSION 1
+
+/* status codes */
+#define TGAF_OK 0
+#define TGAF_ERR_INVALID_ARGUMENT 1 /* the reference's error.InvalidArgument */
+#define TGAF_ERR_CUDA 2
+#define TGAF_ERR_OUT_OF_MEMORY 3
+#define TGAF_ERR_NCCL 4
+#define TGAF_ERR_UNSUPPORTED 5
+#define TGAF_ERR_TIMEOUT 6
+#define TGAF_ERR_DEVICE_FLAG 7 /* a kernel's bounded wait ran out and set its error word */
+
+/* scales dtype tags: core/src/compute/cuda/gaffine_u4_matvec.zig:13-14 */
+#define TGAF_SCALES_F16 0u
+#define TGAF_SCALES_BF16 1u
+
+/* how tgaf_weight_upload cuts a weight for tensor parallelism */
+#define TGAF_SHARD_NONE 0u
+#define TGAF_SHARD_COL 1u /* split N (output features): qkv / gate / up; no collective */
+#define TGAF_SHARD_ROW 2u /* split K (input features) on group boundaries: o / down; outputs are partial sums */
+
+/* element types for tgaf_allreduce */
+#define TGAF_DTYPE_F32 0u
+#define TGAF_DTYPE_BF16 1u
+
+typedef struct tgaf_ctx tgaf_ctx;
+typedef struct tgaf_weight tgaf_weight;
+
+int32_t tgaf_abi_version(void);
+const char *tgaf_status_string(int32_t status);
+
+/* ---- context ------------------------------------------------------------
+ * Replaces the device / registry / launch-stream triple a talu CUDA backend
+ * owns (core/src/compute/cuda/device.zig:147-193).  `stream` is a cudaStream_t
+ * (CUstream) the caller owns, or NULL for a stream the context creates. */
+int32_t tgaf_ctx_create(int32_t device_ordinal, void *stream, tgaf_ctx **out_ctx);
+int32_t tgaf_ctx_destroy(tgaf_ctx *ctx);
+int32_t tgaf_ctx_set_stream(tgaf_ctx *ctx, void *stream);
+int32_t tgaf_synchronize(tgaf_ctx *ctx);
+const char *tgaf_last_error(const tgaf_ctx *ctx);
+/* Tuning knobs by name (e.g. "gemv_slices", "gemv_warps", "pdl"); unknown names
+ * are TGAF_ERR_INVALID_ARGUMENT. */
+int32_t tgaf_ctx_set_option(tgaf_ctx *ctx, const char *name, int64_t value);
+
+/* ---- weights ------------------------------------------------------------
+ * tgaf_weight_upload replaces uploadLinearWeightGroupedAffineU4
+ * (core/src/inference/backend/cuda/engine.zig:8209-8273): host pointers in the
+ * canonical layout (they may be unaligned mmap views - they are read as bytes),
+ * copied to device memory the library owns.  N, K are the FULL (unsharded)
+ * sizes; with shard_kind != NONE only this rank's slice is kept:
+ *   COL: rows    [rank*N/P, (rank+1)*N/P)             requires N % P == 0
+ *   ROW: columns [rank*K/P, (rank+1)*K/P)             requires K % (P*lcm(G, vpw)) == 0
+ * Shape rules are the reference's (gaffine_u4_matvec.zig:99-113,
+ * engine.zig:8229-8233, models/load/transforms.zig:158-185):
+ *   bits in {4,8}; K % vpw == 0; G % vpw == 0; K % G == 0; K/G <= 1024 per rank;
+ *   scales dtype in {f16, bf16}. */
+int32_t tgaf_weight_upload(tgaf_ctx *ctx, const void *packed, const void *scales,
+                           const void *biases, uint64_t N, uint64_t K,
+                           uint32_t group_size, uint32_t bits, uint32_t scales_dtype,
+                           uint32_t shard_kind, uint32_t tp_rank, uint32_t tp_size,
+                           tgaf_weight **out_weight);
+/* Same, for the three device buffers a caller already holds (the reference's
+ * GaffineU4LinearWeight, engine.zig:220-292).  No copy; the caller keeps
+ * ownership and must keep them alive.  No sharding. */
+int32_t tgaf_weight_wrap_device(tgaf_ctx *ctx, const void *d_packed, const void *d_scales,
+                                const void *d_biases, uint64_t N, uint64_t K,
+                                uint32_t group_size, uint32_t bits, uint32_t scales_dtype,
+                                tgaf_weight **out_weight);
+int32_t tgaf_weight_free(tgaf_ctx *ctx, tgaf_weight *w);
+/* local (per-rank) sizes of a weight */
+int32_t tgaf_weight_dims(const tgaf_weight *w, uint64_t *n_local, uint64_t *k_local,
+                         uint32_t *group_size, uint32_t *bits);
+
+/* ---- the matmul operator ------------------------------------------------
+ * Replaces the .gaffine_u4 arm of CudaBackend.linearForwardRows
+ * (engine.zig:4431-4474) and, on the CPU side, MatmulFn for
+ * grouped_affine_u4 / u8 (core/src/compute/cpu/matmul_primitives.zig:101-121,
+ * :947-974, :1037-1063).
+ *   x: [M, K_local] row-major, y: [M, N_local] row-major, device pointers.
+ * bf16 variant: bf16 in, fp32 accumulate, bf16 out (round to nearest even).
+ * f32 variant: the reference's f32-in / f32-out contract. */
+int32_t tgaf_linear_bf16(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16,
+                         uint32_t M, void *y_bf16);
+int32_t tgaf_linear_f32(tgaf_ctx *ctx, const tgaf_weight *w, const float *x,
+                        uint32_t M, float *y);
+/* Host-buffer variants: copy x to the device, run, copy y back, wait. */
+int32_t tgaf_linear_bf16_host(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16_host,
+                              uint32_t M, void *y_bf16_host);
+int32_t tgaf_linear_f32_host(tgaf_ctx *ctx, const tgaf_weight *w, const float *x_host,
+                             uint32_t M, float *y_host);
+
+/* Raw-pointer launch with the argument list of the reference's kernel wrapper
+ * compute.cuda.gaffine_u4_matvec.runWithFunction
+ * (core/src/compute/cuda/gaffine_u4_matvec.zig:58-97; kernel
+ * core/src/compute/cuda/kernels/ops/quant_ops.cu:46-57): f32 activations
+ * [batch_rows, in_dim], f32 out [batch_rows, out_dim], all device pointers.
+ * Validation = the wrapper's validateArgs (:99-113). */
+int32_t tgaf_gaffine_u4_matvec_f32(tgaf_ctx *ctx, const float *input, const uint32_t *packed_weight,
+                                   const uint16_t *scales, const uint16_t *biases, float *out,
+                                   uint32_t in_dim, uint32_t out_dim, uint32_t group_size,
+                                   uint32_t scales_dtype_tag, uint32_t batch_rows);
+/* 8-bit counterpart (the reference has no gaf8 CUDA kernel: it dequantizes gaf8
+ * to f32 on the host and calls cuBLAS, engine.zig:8106-8125). */
+int32_t tgaf_gaffine_u8_matvec_f32(tgaf_ctx *ctx, const float *input, const uint32_t *packed_weight,
+                                   const uint16_t *scales, const uint16_t *biases, float *out,
+                                   uint32_t in_dim, uint32_t out_dim, uint32_t group_size,
+                                   uint32_t scales_dtype_tag, uint32_t batch_rows);
+
+/* ---- dequant --------------------------------------------------------------
+ * Replaces decodeGroupedAffineU4Row / U8Row (core/src/compute/cpu/quant_decode.zig:64-130)
+ * and convertToF32 (core/src/models/load/transforms.zig:651-714): out f32
+ * [N_local, K_local], bit-exact fmaf(q, scale, bias). */
+int32_t tgaf_dequant_f32(tgaf_ctx *ctx, const tgaf_weight *w, float *d_out);
+int32_t tgaf_dequant_f32_host(tgaf_ctx *ctx, const tgaf_weight *w, float *h_out);
+
+/* ---- tensor parallel exchange (no counterpart in the reference, which is
+ * single-device): sum of the row-parallel partial outputs over all ranks. ----
+ * The communicator belongs to the context.  Rank 0 makes the id and the host
+ * program hands its bytes to the other ranks by any means it has. */
+#define TGAF_COMM_ID_BYTES 128
+int32_t tgaf_comm_make_id(uint8_t id[TGAF_COMM_ID_BYTES]);
+int32_t tgaf_comm_init(tgaf_ctx *ctx, const uint8_t id[TGAF_COMM_ID_BYTES], uint32_t rank, uint32_t nranks);
+int32_t tgaf_comm_destroy(tgaf_ctx *ctx);
+/* in place, on the context's stream */
+int32_t tgaf_allreduce(tgaf_ctx *ctx, void *d_buf, uint64_t count, uint32_t dtype);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TALU_GAF_H */

@@ -1,0 +1,633 @@
+// C ABI of libtalu_gaf.so (declared in include/talu_gaf.h): context, weight
+// upload / tensor-parallel sharding, dispatch of the matmul operator, NCCL
+// exchange for row-parallel outputs.  No CPU fallback: every compute entry
+// point needs a CUDA device and fails with a status code otherwise.
+#include "../../include/talu_gaf.h"
+#include "gaf_internal.h"
+
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+#include <string>
+
+using namespace tgaf;
+
+// ---------------------------------------------------------------------------
+// NCCL, bound at run time (the library is usable single-GPU without it)
+// ---------------------------------------------------------------------------
+namespace {
+
+struct NcclUniqueId {
+    char internal[TGAF_COMM_ID_BYTES];
+};
+typedef void *NcclComm;
+enum { kNcclSuccess = 0, kNcclSum = 0, kNcclFloat32 = 7, kNcclBfloat16 = 9 };
+
+struct NcclApi {
+    void *handle = nullptr;
+    int (*GetUniqueId)(NcclUniqueId *) = nullptr;
+    int (*CommInitRank)(NcclComm *, int, NcclUniqueId, int) = nullptr;
+    int (*CommDestroy)(NcclComm) = nullptr;
+    int (*AllReduce)(const void *, void *, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
+    const char *(*GetErrorString)(int) = nullptr;
+    bool ok = false;
+    std::string why;
+};
+
+NcclApi &nccl_api() {
+    static NcclApi api;
+    static bool tried = false;
+    if (tried) return api;
+    tried = true;
+    const char *names[] = {"libnccl.so.2", "libnccl.so"};
+    for (const char *n : names) {
+        api.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+        if (api.handle) break;
+    }
+    if (!api.handle) {
+        api.why = "libnccl.so.2 not found";
+        return api;
+    }
+    api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(api.handle, "ncclGetUniqueId"));
+    api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(api.handle, "ncclCommInitRank"));
+    api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(api.handle, "ncclCommDestroy"));
+    api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(api.handle, "ncclAllReduce"));
+    api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(api.handle, "ncclGetErrorString"));
+    api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce && api.GetErrorString;
+    if (!api.ok) api.why = "libnccl is missing a required symbol";
+    return api;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// objects
+// ---------------------------------------------------------------------------
+struct tgaf_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    int sm_count = 148;
+    Scratch scratch = {nullptr, 0, nullptr, 0};
+    GemvTuning tune = {0, 0, 1, 0};
+    // staging for the *_host entry points
+    void *stage_x = nullptr;
+    size_t stage_x_bytes = 0;
+    void *stage_y = nullptr;
+    size_t stage_y_bytes = 0;
+    unsigned int *d_error_word = nullptr;
+    NcclComm comm = nullptr;
+    uint32_t comm_rank = 0, comm_size = 1;
+    char err[512] = {0};
+};
+
+struct tgaf_weight {
+    WeightView v;
+    bool owns = false;
+    uint64_t full_N = 0, full_K = 0;
+    uint32_t shard_kind = 0, tp_rank = 0, tp_size = 1;
+};
+
+namespace {
+
+int32_t fail(tgaf_ctx *ctx, int32_t status, const char *fmt, ...) {
+    if (ctx) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(ctx->err, sizeof ctx->err, fmt, ap);
+        va_end(ap);
+    }
+    return status;
+}
+
+int32_t cuda_fail(tgaf_ctx *ctx, cudaError_t e, const char *what) {
+    const int32_t st = (e == cudaErrorMemoryAllocation) ? TGAF_ERR_OUT_OF_MEMORY : TGAF_ERR_CUDA;
+    return fail(ctx, st, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define TGAF_CUDA(ctx, call)                                  \
+    do {                                                      \
+        cudaError_t e__ = (call);                             \
+        if (e__ != cudaSuccess) return cuda_fail(ctx, e__, #call); \
+    } while (0)
+
+// Shape rules of the reference (gaffine_u4_matvec.zig:99-113, engine.zig:8229-8233,
+// transforms.zig:158-185).
+bool shape_ok(uint64_t N, uint64_t K, uint32_t group, uint32_t bits, uint32_t sdtype) {
+    if (bits != 4 && bits != 8) return false;
+    const uint32_t vpw = 32u / bits;
+    if (N == 0 || K == 0 || group == 0) return false;
+    if (K % vpw != 0 || group % vpw != 0) return false;
+    if (K % group != 0) return false;
+    if (sdtype != TGAF_SCALES_F16 && sdtype != TGAF_SCALES_BF16) return false;
+    if (K / group > 1024) return false;               // MAX_SUPPORTED_GAFFINE_GROUPS
+    if (N > 0x7FFFFFFFull || K > 0x7FFFFFFFull) return false;
+    if (K * bits / 8 > 0xFFFFFFFFull) return false;
+    return true;
+}
+
+int32_t ensure_scratch(tgaf_ctx *ctx, size_t partial_bytes, size_t counters) {
+    if (partial_bytes > ctx->scratch.partial_bytes) {
+        // previous launches may still be using the old buffer
+        TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if (ctx->scratch.partials) cudaFree(ctx->scratch.partials);
+        ctx->scratch.partials = nullptr;
+        ctx->scratch.partial_bytes = 0;
+        size_t want = partial_bytes < (size_t(8) << 20) ? (size_t(8) << 20) : partial_bytes;
+        TGAF_CUDA(ctx, cudaMalloc(&ctx->scratch.partials, want));
+        ctx->scratch.partial_bytes = want;
+    }
+    if (counters > ctx->scratch.counter_count) {
+        TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if (ctx->scratch.counters) cudaFree(ctx->scratch.counters);
+        ctx->scratch.counters = nullptr;
+        ctx->scratch.counter_count = 0;
+        size_t want = counters < 65536 ? 65536 : counters;
+        TGAF_CUDA(ctx, cudaMalloc(&ctx->scratch.counters, want * sizeof(unsigned int)));
+        TGAF_CUDA(ctx, cudaMemsetAsync(ctx->scratch.counters, 0, want * sizeof(unsigned int), ctx->stream));
+        ctx->scratch.counter_count = want;
+    }
+    return TGAF_OK;
+}
+
+int32_t ensure_stage(tgaf_ctx *ctx, void **buf, size_t *have, size_t need) {
+    if (need <= *have) return TGAF_OK;
+    TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (*buf) cudaFree(*buf);
+    *buf = nullptr;
+    *have = 0;
+    size_t want = need < (size_t(1) << 20) ? (size_t(1) << 20) : need;
+    TGAF_CUDA(ctx, cudaMalloc(buf, want));
+    *have = want;
+    return TGAF_OK;
+}
+
+// The operator: picks the kernel for (shape, M) and enqueues it.
+int32_t linear_device(tgaf_ctx *ctx, const WeightView &w, const void *x, uint32_t M, void *y, bool f32) {
+    if (!x || !y) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null activation or output pointer");
+    if (M == 0) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "M must be > 0");
+    const size_t elt = f32 ? 4 : 2;
+
+    if (!f32 && gemm_tc_eligible(w, M)) {
+        cudaError_t e = gemm_tc(w, x, y, M, ctx->stream, ctx->sm_count, ctx->d_error_word);
+        if (e == cudaSuccess) return TGAF_OK;
+        if (e != cudaErrorNotSupported) return cuda_fail(ctx, e, "gemm_tc");
+    }
+
+    if (!ctx->tune.force_generic && gemv_mma_eligible(w, x, y, f32)) {
+        // rows in chunks of 16; each chunk streams the weights once
+        for (uint32_t m0 = 0; m0 < M; m0 += 16u) {
+            const uint32_t mc = (M - m0) < 16u ? (M - m0) : 16u;
+            const size_t need = gemv_mma_scratch_bytes(w, mc, ctx->tune, ctx->sm_count);
+            if (need) {
+                int32_t st = ensure_scratch(ctx, need, (w.N + 15u) / 16u);
+                if (st != TGAF_OK) return st;
+            }
+            const void *xp = static_cast<const uint8_t *>(x) + static_cast<size_t>(m0) * w.K * elt;
+            void *yp = static_cast<uint8_t *>(y) + static_cast<size_t>(m0) * w.N * elt;
+            cudaError_t e = gemv_mma(w, xp, yp, mc, f32, ctx->scratch, ctx->tune, ctx->stream, ctx->sm_count);
+            if (e != cudaSuccess) return cuda_fail(ctx, e, "gemv_mma launch");
+        }
+        return TGAF_OK;
+    }
+    cudaError_t e = gemv_generic(w, x, y, M, f32, ctx->stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "gemv_generic launch");
+    return TGAF_OK;
+}
+
+int32_t linear_host(tgaf_ctx *ctx, const tgaf_weight *w, const void *xh, uint32_t M, void *yh, bool f32) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!w || !xh || !yh || M == 0) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null pointer or M == 0");
+    const size_t elt = f32 ? 4 : 2;
+    const size_t xb = static_cast<size_t>(M) * w->v.K * elt, yb = static_cast<size_t>(M) * w->v.N * elt;
+    int32_t st = ensure_stage(ctx, &ctx->stage_x, &ctx->stage_x_bytes, xb);
+    if (st != TGAF_OK) return st;
+    st = ensure_stage(ctx, &ctx->stage_y, &ctx->stage_y_bytes, yb);
+    if (st != TGAF_OK) return st;
+    TGAF_CUDA(ctx, cudaMemcpyAsync(ctx->stage_x, xh, xb, cudaMemcpyHostToDevice, ctx->stream));
+    st = linear_device(ctx, w->v, ctx->stage_x, M, ctx->stage_y, f32);
+    if (st != TGAF_OK) return st;
+    TGAF_CUDA(ctx, cudaMemcpyAsync(yh, ctx->stage_y, yb, cudaMemcpyDeviceToHost, ctx->stream));
+    TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return TGAF_OK;
+}
+
+int32_t raw_matvec(tgaf_ctx *ctx, uint32_t bits, const float *input, const uint32_t *packed,
+                   const uint16_t *scales, const uint16_t *biases, float *out, uint32_t in_dim,
+                   uint32_t out_dim, uint32_t group_size, uint32_t sdtype, uint32_t batch_rows) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    // validateArgs, core/src/compute/cuda/gaffine_u4_matvec.zig:99-113
+    const uint32_t vpw = 32u / bits;
+    if (in_dim == 0 || out_dim == 0 || group_size == 0 || batch_rows == 0)
+        return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "zero dimension");
+    if (in_dim % vpw != 0 || group_size % vpw != 0)
+        return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "in_dim and group_size must be multiples of %u", vpw);
+    if (in_dim % group_size != 0) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "in_dim %% group_size != 0");
+    if (sdtype != TGAF_SCALES_F16 && sdtype != TGAF_SCALES_BF16)
+        return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "bad scales dtype tag %u", sdtype);
+    if (!input || !packed || !scales || !biases || !out)
+        return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null device pointer");
+    WeightView v;
+    v.packed = reinterpret_cast<const uint8_t *>(packed);
+    v.scales = scales;
+    v.biases = biases;
+    v.N = out_dim;
+    v.K = in_dim;
+    v.group = group_size;
+    v.bits = bits;
+    v.sdtype = sdtype;
+    v.row_bytes = in_dim / vpw * 4u;
+    v.groups = in_dim / group_size;
+    return linear_device(ctx, v, input, batch_rows, out, true);
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// exported functions
+// ---------------------------------------------------------------------------
+extern "C" {
+
+int32_t tgaf_abi_version(void) { return TGAF_ABI_VERSION; }
+
+const char *tgaf_status_string(int32_t status) {
+    switch (status) {
+        case TGAF_OK: return "ok";
+        case TGAF_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case TGAF_ERR_CUDA: return "CUDA error";
+        case TGAF_ERR_OUT_OF_MEMORY: return "out of device memory";
+        case TGAF_ERR_NCCL: return "NCCL error";
+        case TGAF_ERR_UNSUPPORTED: return "unsupported";
+        case TGAF_ERR_TIMEOUT: return "timeout";
+        case TGAF_ERR_DEVICE_FLAG: return "device-side wait ran out";
+        default: return "unknown status";
+    }
+}
+
+int32_t tgaf_ctx_create(int32_t device_ordinal, void *stream, tgaf_ctx **out_ctx) {
+    if (!out_ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    *out_ctx = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) return TGAF_ERR_CUDA;
+    if (device_ordinal < 0 || device_ordinal >= count) return TGAF_ERR_INVALID_ARGUMENT;
+    tgaf_ctx *ctx = new (std::nothrow) tgaf_ctx();
+    if (!ctx) return TGAF_ERR_OUT_OF_MEMORY;
+    ctx->device = device_ordinal;
+    if (cudaSetDevice(device_ordinal) != cudaSuccess) {
+        delete ctx;
+        return TGAF_ERR_CUDA;
+    }
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device_ordinal) != cudaSuccess) {
+        delete ctx;
+        return TGAF_ERR_CUDA;
+    }
+    if (prop.major != 10) {  // the kernels are sm_100a only; nothing else is compiled in
+        delete ctx;
+        return TGAF_ERR_UNSUPPORTED;
+    }
+    ctx->sm_count = prop.multiProcessorCount;
+    if (stream) {
+        ctx->stream = static_cast<cudaStream_t>(stream);
+    } else {
+        if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+            delete ctx;
+            return TGAF_ERR_CUDA;
+        }
+        ctx->owns_stream = true;
+    }
+    if (cudaMalloc(&ctx->d_error_word, sizeof(unsigned int)) != cudaSuccess ||
+        cudaMemsetAsync(ctx->d_error_word, 0, sizeof(unsigned int), ctx->stream) != cudaSuccess) {
+        tgaf_ctx_destroy(ctx);
+        return TGAF_ERR_CUDA;
+    }
+    // split-K scratch up front so that steady-state calls never allocate
+    if (ensure_scratch(ctx, size_t(8) << 20, 65536) != TGAF_OK) {
+        tgaf_ctx_destroy(ctx);
+        return TGAF_ERR_OUT_OF_MEMORY;
+    }
+    *out_ctx = ctx;
+    return TGAF_OK;
+}
+
+int32_t tgaf_ctx_destroy(tgaf_ctx *ctx) {
+    if (!ctx) return TGAF_OK;
+    cudaSetDevice(ctx->device);
+    if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    if (ctx->comm) tgaf_comm_destroy(ctx);
+    if (ctx->scratch.partials) cudaFree(ctx->scratch.partials);
+    if (ctx->scratch.counters) cudaFree(ctx->scratch.counters);
+    if (ctx->stage_x) cudaFree(ctx->stage_x);
+    if (ctx->stage_y) cudaFree(ctx->stage_y);
+    if (ctx->d_error_word) cudaFree(ctx->d_error_word);
+    if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return TGAF_OK;
+}
+
+int32_t tgaf_ctx_set_stream(tgaf_ctx *ctx, void *stream) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!stream) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "stream must not be NULL");
+    TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+    ctx->owns_stream = false;
+    ctx->stream = static_cast<cudaStream_t>(stream);
+    return TGAF_OK;
+}
+
+int32_t tgaf_synchronize(tgaf_ctx *ctx) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    unsigned int flag = 0;
+    TGAF_CUDA(ctx, cudaMemcpy(&flag, ctx->d_error_word, sizeof flag, cudaMemcpyDeviceToHost));
+    if (flag != 0) {
+        cudaMemset(ctx->d_error_word, 0, sizeof flag);
+        return fail(ctx, TGAF_ERR_DEVICE_FLAG, "a kernel gave up a bounded wait (code 0x%x)", flag);
+    }
+    return TGAF_OK;
+}
+
+const char *tgaf_last_error(const tgaf_ctx *ctx) { return ctx ? ctx->err : "null context"; }
+
+int32_t tgaf_ctx_set_option(tgaf_ctx *ctx, const char *name, int64_t value) {
+    if (!ctx || !name) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!strcmp(name, "gemv_slices")) {
+        ctx->tune.slices_target = static_cast<int>(value);
+    } else if (!strcmp(name, "gemv_warps")) {
+        if (value != 0 && value != 4 && value != 8) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "gemv_warps must be 0, 4 or 8");
+        ctx->tune.warps = static_cast<int>(value);
+    } else if (!strcmp(name, "pdl")) {
+        ctx->tune.pdl = value != 0;
+    } else if (!strcmp(name, "force_generic")) {
+        ctx->tune.force_generic = value != 0;
+    } else {
+        return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "unknown option '%s'", name);
+    }
+    return TGAF_OK;
+}
+
+int32_t tgaf_weight_upload(tgaf_ctx *ctx, const void *packed, const void *scales, const void *biases,
+                           uint64_t N, uint64_t K, uint32_t group_size, uint32_t bits,
+                           uint32_t scales_dtype, uint32_t shard_kind, uint32_t tp_rank,
+                           uint32_t tp_size, tgaf_weight **out_weight) {
+    if (!out_weight) return TGAF_ERR_INVALID_ARGUMENT;
+    *out_weight = nullptr;
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!packed || !scales || !biases) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null weight pointer");
+    if (bits != 4 && bits != 8) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "bits must be 4 or 8");
+    if (shard_kind > TGAF_SHARD_ROW) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "bad shard kind %u", shard_kind);
+    if (shard_kind == TGAF_SHARD_NONE) {
+        tp_rank = 0;
+        tp_size = 1;
+    }
+    if (tp_size == 0 || tp_rank >= tp_size) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "bad tp rank %u of %u", tp_rank, tp_size);
+    const uint32_t vpw = 32u / bits;
+    if (group_size == 0 || K == 0 || N == 0 || K % vpw != 0 || group_size % vpw != 0 || K % group_size != 0)
+        return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "bad shape N=%llu K=%llu G=%u bits=%u",
+                    (unsigned long long)N, (unsigned long long)K, group_size, bits);
+
+    uint64_t n_local = N, k_local = K, n0 = 0, k0 = 0;
+    if (shard_kind == TGAF_SHARD_COL) {
+        if (N % tp_size != 0) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "N=%llu not divisible by %u ranks", (unsigned long long)N, tp_size);
+        n_local = N / tp_size;
+        n0 = n_local * tp_rank;
+    } else if (shard_kind == TGAF_SHARD_ROW) {
+        // cut on group boundaries (vpw divides the group)
+        if (K % (static_cast<uint64_t>(tp_size) * group_size) != 0)
+            return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "K=%llu not divisible by ranks*group = %u*%u",
+                        (unsigned long long)K, tp_size, group_size);
+        k_local = K / tp_size;
+        k0 = k_local * tp_rank;
+    }
+    if (!shape_ok(n_local, k_local, group_size, bits, scales_dtype))
+        return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "shape rejected: N=%llu K=%llu G=%u bits=%u sdtype=%u (K/G <= 1024)",
+                    (unsigned long long)n_local, (unsigned long long)k_local, group_size, bits, scales_dtype);
+
+    tgaf_weight *w = new (std::nothrow) tgaf_weight();
+    if (!w) return fail(ctx, TGAF_ERR_OUT_OF_MEMORY, "host allocation failed");
+    w->owns = true;
+    w->full_N = N;
+    w->full_K = K;
+    w->shard_kind = shard_kind;
+    w->tp_rank = tp_rank;
+    w->tp_size = tp_size;
+    WeightView &v = w->v;
+    v.N = static_cast<uint32_t>(n_local);
+    v.K = static_cast<uint32_t>(k_local);
+    v.group = group_size;
+    v.bits = bits;
+    v.sdtype = scales_dtype;
+    v.row_bytes = static_cast<uint32_t>(k_local * bits / 8);
+    v.groups = static_cast<uint32_t>(k_local / group_size);
+
+    const size_t full_row_bytes = K * bits / 8, full_groups = K / group_size;
+    const size_t pbytes = static_cast<size_t>(v.N) * v.row_bytes;
+    const size_t sbytes = static_cast<size_t>(v.N) * v.groups * 2;
+    uint8_t *dp = nullptr, *ds = nullptr, *db = nullptr;
+    cudaSetDevice(ctx->device);
+    cudaError_t e = cudaMalloc(&dp, pbytes);
+    if (e == cudaSuccess) e = cudaMalloc(&ds, sbytes);
+    if (e == cudaSuccess) e = cudaMalloc(&db, sbytes);
+    if (e == cudaSuccess) {
+        // host sources may be unaligned mmap views: they are copied as bytes
+        const uint8_t *hp = static_cast<const uint8_t *>(packed) + n0 * full_row_bytes + k0 * bits / 8;
+        const uint8_t *hs = static_cast<const uint8_t *>(scales) + (n0 * full_groups + k0 / group_size) * 2;
+        const uint8_t *hb = static_cast<const uint8_t *>(biases) + (n0 * full_groups + k0 / group_size) * 2;
+        e = cudaMemcpy2DAsync(dp, v.row_bytes, hp, full_row_bytes, v.row_bytes, v.N, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess)
+            e = cudaMemcpy2DAsync(ds, v.groups * 2, hs, full_groups * 2, v.groups * 2, v.N, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess)
+            e = cudaMemcpy2DAsync(db, v.groups * 2, hb, full_groups * 2, v.groups * 2, v.N, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);  // the host buffers are the caller's again
+    }
+    if (e != cudaSuccess) {
+        if (dp) cudaFree(dp);
+        if (ds) cudaFree(ds);
+        if (db) cudaFree(db);
+        delete w;
+        return cuda_fail(ctx, e, "weight upload");
+    }
+    v.packed = dp;
+    v.scales = reinterpret_cast<uint16_t *>(ds);
+    v.biases = reinterpret_cast<uint16_t *>(db);
+    *out_weight = w;
+    return TGAF_OK;
+}
+
+int32_t tgaf_weight_wrap_device(tgaf_ctx *ctx, const void *d_packed, const void *d_scales, const void *d_biases,
+                                uint64_t N, uint64_t K, uint32_t group_size, uint32_t bits,
+                                uint32_t scales_dtype, tgaf_weight **out_weight) {
+    if (!out_weight) return TGAF_ERR_INVALID_ARGUMENT;
+    *out_weight = nullptr;
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!d_packed || !d_scales || !d_biases) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null weight pointer");
+    if (!shape_ok(N, K, group_size, bits, scales_dtype))
+        return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "shape rejected: N=%llu K=%llu G=%u bits=%u sdtype=%u",
+                    (unsigned long long)N, (unsigned long long)K, group_size, bits, scales_dtype);
+    tgaf_weight *w = new (std::nothrow) tgaf_weight();
+    if (!w) return fail(ctx, TGAF_ERR_OUT_OF_MEMORY, "host allocation failed");
+    w->owns = false;
+    w->full_N = N;
+    w->full_K = K;
+    WeightView &v = w->v;
+    v.packed = static_cast<const uint8_t *>(d_packed);
+    v.scales = static_cast<const uint16_t *>(d_scales);
+    v.biases = static_cast<const uint16_t *>(d_biases);
+    v.N = static_cast<uint32_t>(N);
+    v.K = static_cast<uint32_t>(K);
+    v.group = group_size;
+    v.bits = bits;
+    v.sdtype = scales_dtype;
+    v.row_bytes = static_cast<uint32_t>(K * bits / 8);
+    v.groups = static_cast<uint32_t>(K / group_size);
+    *out_weight = w;
+    return TGAF_OK;
+}
+
+int32_t tgaf_weight_free(tgaf_ctx *ctx, tgaf_weight *w) {
+    if (!w) return TGAF_OK;
+    if (w->owns) {
+        if (ctx) {
+            cudaSetDevice(ctx->device);
+            cudaStreamSynchronize(ctx->stream);
+        }
+        cudaFree(const_cast<uint8_t *>(w->v.packed));
+        cudaFree(const_cast<uint16_t *>(w->v.scales));
+        cudaFree(const_cast<uint16_t *>(w->v.biases));
+    }
+    delete w;
+    return TGAF_OK;
+}
+
+int32_t tgaf_weight_dims(const tgaf_weight *w, uint64_t *n_local, uint64_t *k_local, uint32_t *group_size,
+                         uint32_t *bits) {
+    if (n_local) *n_local = 0;
+    if (k_local) *k_local = 0;
+    if (group_size) *group_size = 0;
+    if (bits) *bits = 0;
+    if (!w) return TGAF_ERR_INVALID_ARGUMENT;
+    if (n_local) *n_local = w->v.N;
+    if (k_local) *k_local = w->v.K;
+    if (group_size) *group_size = w->v.group;
+    if (bits) *bits = w->v.bits;
+    return TGAF_OK;
+}
+
+int32_t tgaf_linear_bf16(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16, uint32_t M, void *y_bf16) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!w) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null weight");
+    return linear_device(ctx, w->v, x_bf16, M, y_bf16, false);
+}
+
+int32_t tgaf_linear_f32(tgaf_ctx *ctx, const tgaf_weight *w, const float *x, uint32_t M, float *y) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!w) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null weight");
+    return linear_device(ctx, w->v, x, M, y, true);
+}
+
+int32_t tgaf_linear_bf16_host(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16_host, uint32_t M,
+                              void *y_bf16_host) {
+    return linear_host(ctx, w, x_bf16_host, M, y_bf16_host, false);
+}
+
+int32_t tgaf_linear_f32_host(tgaf_ctx *ctx, const tgaf_weight *w, const float *x_host, uint32_t M, float *y_host) {
+    return linear_host(ctx, w, x_host, M, y_host, true);
+}
+
+int32_t tgaf_gaffine_u4_matvec_f32(tgaf_ctx *ctx, const float *input, const uint32_t *packed_weight,
+                                   const uint16_t *scales, const uint16_t *biases, float *out, uint32_t in_dim,
+                                   uint32_t out_dim, uint32_t group_size, uint32_t scales_dtype_tag,
+                                   uint32_t batch_rows) {
+    return raw_matvec(ctx, 4, input, packed_weight, scales, biases, out, in_dim, out_dim, group_size,
+                      scales_dtype_tag, batch_rows);
+}
+
+int32_t tgaf_gaffine_u8_matvec_f32(tgaf_ctx *ctx, const float *input, const uint32_t *packed_weight,
+                                   const uint16_t *scales, const uint16_t *biases, float *out, uint32_t in_dim,
+                                   uint32_t out_dim, uint32_t group_size, uint32_t scales_dtype_tag,
+                                   uint32_t batch_rows) {
+    return raw_matvec(ctx, 8, input, packed_weight, scales, biases, out, in_dim, out_dim, group_size,
+                      scales_dtype_tag, batch_rows);
+}
+
+int32_t tgaf_dequant_f32(tgaf_ctx *ctx, const tgaf_weight *w, float *d_out) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!w || !d_out) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null pointer");
+    cudaError_t e = dequant_f32(w->v, d_out, ctx->stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "dequant launch");
+    return TGAF_OK;
+}
+
+int32_t tgaf_dequant_f32_host(tgaf_ctx *ctx, const tgaf_weight *w, float *h_out) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!w || !h_out) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null pointer");
+    const size_t bytes = static_cast<size_t>(w->v.N) * w->v.K * sizeof(float);
+    float *d = nullptr;
+    TGAF_CUDA(ctx, cudaMalloc(&d, bytes));
+    cudaError_t e = dequant_f32(w->v, d, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h_out, d, bytes, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    cudaFree(d);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "dequant to host");
+    return TGAF_OK;
+}
+
+int32_t tgaf_comm_make_id(uint8_t id[TGAF_COMM_ID_BYTES]) {
+    if (!id) return TGAF_ERR_INVALID_ARGUMENT;
+    memset(id, 0, TGAF_COMM_ID_BYTES);
+    NcclApi &api = nccl_api();
+    if (!api.ok) return TGAF_ERR_NCCL;
+    NcclUniqueId uid;
+    if (api.GetUniqueId(&uid) != kNcclSuccess) return TGAF_ERR_NCCL;
+    memcpy(id, uid.internal, TGAF_COMM_ID_BYTES);
+    return TGAF_OK;
+}
+
+int32_t tgaf_comm_init(tgaf_ctx *ctx, const uint8_t id[TGAF_COMM_ID_BYTES], uint32_t rank, uint32_t nranks) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!id || nranks == 0 || rank >= nranks) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "bad rank %u of %u", rank, nranks);
+    if (ctx->comm) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "communicator already initialised");
+    NcclApi &api = nccl_api();
+    if (!api.ok) return fail(ctx, TGAF_ERR_NCCL, "NCCL unavailable: %s", api.why.c_str());
+    NcclUniqueId uid;
+    memcpy(uid.internal, id, TGAF_COMM_ID_BYTES);
+    cudaSetDevice(ctx->device);
+    int rc = api.CommInitRank(&ctx->comm, static_cast<int>(nranks), uid, static_cast<int>(rank));
+    if (rc != kNcclSuccess) {
+        ctx->comm = nullptr;
+        return fail(ctx, TGAF_ERR_NCCL, "ncclCommInitRank: %s", api.GetErrorString(rc));
+    }
+    ctx->comm_rank = rank;
+    ctx->comm_size = nranks;
+    return TGAF_OK;
+}
+
+int32_t tgaf_comm_destroy(tgaf_ctx *ctx) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!ctx->comm) return TGAF_OK;
+    NcclApi &api = nccl_api();
+    if (api.ok) api.CommDestroy(ctx->comm);
+    ctx->comm = nullptr;
+    ctx->comm_size = 1;
+    ctx->comm_rank = 0;
+    return TGAF_OK;
+}
+
+int32_t tgaf_allreduce(tgaf_ctx *ctx, void *d_buf, uint64_t count, uint32_t dtype) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!d_buf || count == 0) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null buffer or zero count");
+    if (dtype != TGAF_DTYPE_F32 && dtype != TGAF_DTYPE_BF16) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "bad dtype %u", dtype);
+    if (!ctx->comm) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "no communicator: call tgaf_comm_init first");
+    NcclApi &api = nccl_api();
+    int rc = api.AllReduce(d_buf, d_buf, count, dtype == TGAF_DTYPE_F32 ? kNcclFloat32 : kNcclBfloat16, kNcclSum,
+                           ctx->comm, ctx->stream);
+    if (rc != kNcclSuccess) return fail(ctx, TGAF_ERR_NCCL, "ncclAllReduce: %s", api.GetErrorString(rc));
+    return TGAF_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,64 @@
+// Internal interface between the C ABI (gaf_api.cu) and the kernel files.
+// Not installed; the public surface is include/talu_gaf.h.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tgaf {
+
+// A weight as the kernels see it: this rank's slice, canonical layout,
+// row pitches in bytes (they differ from the dense pitch only for wrapped
+// buffers; uploaded weights are repacked densely per rank).
+struct WeightView {
+    const uint8_t *packed;   // [N][row_bytes]
+    const uint16_t *scales;  // [N][groups]
+    const uint16_t *biases;  // [N][groups]
+    uint32_t N;              // local output features
+    uint32_t K;              // local input features
+    uint32_t group;          // elements per group
+    uint32_t bits;           // 4 or 8
+    uint32_t sdtype;         // 0 = f16, 1 = bf16
+    uint32_t row_bytes;      // K * bits / 8
+    uint32_t groups;         // K / group
+};
+
+// Split-K scratch owned by a context.
+struct Scratch {
+    float *partials;          // [slices][m_pad][n_pad]
+    size_t partial_bytes;
+    unsigned int *counters;   // one per 16-row block, self-resetting
+    size_t counter_count;
+};
+
+struct GemvTuning {
+    int slices_target;  // wanted number of warp-slices over the whole grid (0 = default)
+    int warps;          // warps per CTA (0 = default)
+    int pdl;            // launch with programmatic stream serialization
+    int force_generic;  // use the shape-agnostic kernel even when the fast path applies
+};
+
+// y[M,N] = x[M,K] * W^T for M <= 16 on the tensor-core GEMV path.
+// x / y are bf16 when x_f32 == 0, f32 otherwise.  Returns cudaSuccess or the
+// launch error; returns cudaErrorNotSupported when the shape is not eligible
+// for the fast path (the caller then uses gemv_generic).
+cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bool x_f32,
+                     const Scratch &scratch, const GemvTuning &tune, cudaStream_t stream,
+                     int sm_count);
+bool gemv_mma_eligible(const WeightView &w, const void *x, const void *y, bool x_f32);
+// scratch bytes the fast path needs for this problem (0 when it does not split K across CTAs)
+size_t gemv_mma_scratch_bytes(const WeightView &w, uint32_t M, const GemvTuning &tune, int sm_count);
+
+// Any shape the reference accepts, any M.  f32 arithmetic, per-element dequant.
+cudaError_t gemv_generic(const WeightView &w, const void *x, void *y, uint32_t M, bool x_f32,
+                         cudaStream_t stream);
+
+// out f32 [N,K] = fmaf(q, scale, bias), bit-exact.
+cudaError_t dequant_f32(const WeightView &w, float *out, cudaStream_t stream);
+
+// Prefill dequant-GEMM on tcgen05 (bf16 in/out).  cudaErrorNotSupported when not eligible.
+cudaError_t gemm_tc(const WeightView &w, const void *x_bf16, void *y_bf16, uint32_t M,
+                    cudaStream_t stream, int sm_count, unsigned int *d_error_word);
+bool gemm_tc_eligible(const WeightView &w, uint32_t M);
+
+}  // namespace tgaf

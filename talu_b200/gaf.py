@@ -1,0 +1,206 @@
+"""Grouped-affine matmul operator: Python host layer over the C ABI.
+
+Names follow the reference: a *weight* is a `grouped_affine_u4/u8` tensor
+`[N, K]` with `GroupedAffineMeta{scales, biases, group_size, scales_dtype}`
+(core/src/dtype.zig:141-146); `linear` is the `MatmulFn` contract
+`out[M,N] = a[M,K] @ b[N,K]^T` (core/src/compute/cpu/matmul_primitives.zig:101).
+torch is used only for device memory and streams.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _capi
+
+SCALES_F16, SCALES_BF16 = 0, 1
+SHARD_NONE, SHARD_COL, SHARD_ROW = 0, 1, 2
+DTYPE_F32, DTYPE_BF16 = 0, 1
+
+_STATUS_INVALID_ARGUMENT = 1
+
+
+class GafError(RuntimeError):
+    """A non-zero status from libtalu_gaf (status 1 = the reference's InvalidArgument)."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"tgaf status {status} ({_capi.load().tgaf_status_string(status).decode()}): {message}")
+        self.status = status
+        self.message = message
+
+    @property
+    def invalid_argument(self) -> bool:
+        return self.status == _STATUS_INVALID_ARGUMENT
+
+
+def _vpw(bits: int) -> int:
+    return 8 if bits == 4 else 4
+
+
+class Context:
+    """One device + one stream (tgaf_ctx).  Not re-entrant."""
+
+    def __init__(self, device: int = 0, stream: int | None = None):
+        self._lib = _capi.load()
+        h = C.c_void_p()
+        st = self._lib.tgaf_ctx_create(int(device), C.c_void_p(stream or 0), C.byref(h))
+        if st != 0:
+            raise GafError(st, "tgaf_ctx_create failed (is a B200 visible?)")
+        self._h = h
+        self.device = int(device)
+
+    def _check(self, st: int) -> None:
+        if st != 0:
+            raise GafError(st, self._lib.tgaf_last_error(self._h).decode())
+
+    def set_stream(self, stream: int) -> None:
+        self._check(self._lib.tgaf_ctx_set_stream(self._h, C.c_void_p(stream)))
+
+    def set_option(self, name: str, value: int) -> None:
+        self._check(self._lib.tgaf_ctx_set_option(self._h, name.encode(), int(value)))
+
+    def synchronize(self) -> None:
+        self._check(self._lib.tgaf_synchronize(self._h))
+
+    # -- tensor-parallel exchange --
+    def comm_init(self, comm_id: bytes, rank: int, nranks: int) -> None:
+        buf = (C.c_uint8 * _capi.COMM_ID_BYTES).from_buffer_copy(comm_id)
+        self._check(self._lib.tgaf_comm_init(self._h, buf, rank, nranks))
+
+    def allreduce(self, t) -> None:
+        """In-place sum over ranks of a torch f32 / bf16 device tensor, on this context's stream."""
+        import torch
+        dt = {torch.float32: DTYPE_F32, torch.bfloat16: DTYPE_BF16}[t.dtype]
+        self._check(self._lib.tgaf_allreduce(self._h, C.c_void_p(t.data_ptr()), t.numel(), dt))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.tgaf_ctx_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def make_comm_id() -> bytes:
+    lib = _capi.load()
+    buf = (C.c_uint8 * _capi.COMM_ID_BYTES)()
+    st = lib.tgaf_comm_make_id(buf)
+    if st != 0:
+        raise GafError(st, "tgaf_comm_make_id failed")
+    return bytes(buf)
+
+
+class Weight:
+    """A gaf weight resident on the device (tgaf_weight)."""
+
+    def __init__(self, ctx: Context, handle, N: int, K: int, group: int, bits: int, keep=None):
+        self.ctx, self._h = ctx, handle
+        self.N, self.K, self.group, self.bits = N, K, group, bits
+        self._keep = keep
+
+    @classmethod
+    def from_host(cls, ctx: Context, packed, scales, biases, group: int, bits: int,
+                  sdtype: int = SCALES_BF16, shard: int = SHARD_NONE, tp_rank: int = 0, tp_size: int = 1):
+        """Upload the canonical layout: packed u32 [N, K/vpw], scales/biases u16 [N, K/G]."""
+        packed = np.ascontiguousarray(packed)
+        scales = np.ascontiguousarray(scales)
+        biases = np.ascontiguousarray(biases)
+        N = packed.shape[0]
+        K = packed.shape[1] * packed.dtype.itemsize * 8 // bits if bits in (4, 8) else 0
+        h = C.c_void_p()
+        st = ctx._lib.tgaf_weight_upload(ctx._h, packed.ctypes.data, scales.ctypes.data, biases.ctypes.data,
+                                         N, K, group, bits, sdtype, shard, tp_rank, tp_size, C.byref(h))
+        ctx._check(st)
+        n, k = C.c_uint64(), C.c_uint64()
+        g, b = C.c_uint32(), C.c_uint32()
+        ctx._check(ctx._lib.tgaf_weight_dims(h, C.byref(n), C.byref(k), C.byref(g), C.byref(b)))
+        return cls(ctx, h, n.value, k.value, g.value, b.value)
+
+    @classmethod
+    def wrap_device(cls, ctx: Context, packed, scales, biases, group: int, bits: int, sdtype: int = SCALES_BF16):
+        """Wrap torch device tensors (int32 packed [N, K/vpw], int16 scales/biases) without copying."""
+        N = packed.shape[0]
+        K = packed.shape[1] * _vpw(bits)
+        h = C.c_void_p()
+        st = ctx._lib.tgaf_weight_wrap_device(ctx._h, C.c_void_p(packed.data_ptr()), C.c_void_p(scales.data_ptr()),
+                                              C.c_void_p(biases.data_ptr()), N, K, group, bits, sdtype, C.byref(h))
+        ctx._check(st)
+        return cls(ctx, h, N, K, group, bits, keep=(packed, scales, biases))
+
+    def free(self) -> None:
+        if getattr(self, "_h", None):
+            self.ctx._lib.tgaf_weight_free(self.ctx._h, self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            if getattr(self.ctx, "_h", None):
+                self.free()
+        except Exception:
+            pass
+
+
+def linear(ctx: Context, w: Weight, x, out=None):
+    """y[M, N] = x[M, K] @ W^T on the device.  x: torch bf16 or f32, contiguous, on ctx's device."""
+    import torch
+    if x.dim() != 2 or x.shape[1] != w.K:
+        raise GafError(_STATUS_INVALID_ARGUMENT, f"x must be [M, {w.K}], got {tuple(x.shape)}")
+    if not x.is_contiguous():
+        x = x.contiguous()
+    M = x.shape[0]
+    if out is None:
+        out = torch.empty((M, w.N), dtype=x.dtype, device=x.device)
+    if x.dtype == torch.bfloat16:
+        st = ctx._lib.tgaf_linear_bf16(ctx._h, w._h, C.c_void_p(x.data_ptr()), M, C.c_void_p(out.data_ptr()))
+    elif x.dtype == torch.float32:
+        st = ctx._lib.tgaf_linear_f32(ctx._h, w._h, C.c_void_p(x.data_ptr()), M, C.c_void_p(out.data_ptr()))
+    else:
+        raise GafError(_STATUS_INVALID_ARGUMENT, f"unsupported activation dtype {x.dtype}")
+    ctx._check(st)
+    return out
+
+
+def linear_host(ctx: Context, w: Weight, x: np.ndarray, out: np.ndarray | None = None) -> np.ndarray:
+    """Same through host buffers: x uint16 (bf16 bit patterns) or float32 [M, K]."""
+    x = np.ascontiguousarray(x)
+    if x.ndim != 2 or x.shape[1] != w.K:
+        raise GafError(_STATUS_INVALID_ARGUMENT, f"x must be [M, {w.K}], got {x.shape}")
+    M = x.shape[0]
+    if out is None:
+        out = np.empty((M, w.N), x.dtype)
+    if x.dtype == np.uint16:
+        st = ctx._lib.tgaf_linear_bf16_host(ctx._h, w._h, x.ctypes.data, M, out.ctypes.data)
+    elif x.dtype == np.float32:
+        st = ctx._lib.tgaf_linear_f32_host(ctx._h, w._h, x.ctypes.data, M, out.ctypes.data)
+    else:
+        raise GafError(_STATUS_INVALID_ARGUMENT, f"unsupported activation dtype {x.dtype}")
+    ctx._check(st)
+    return out
+
+
+def dequant_f32(ctx: Context, w: Weight):
+    import torch
+    out = torch.empty((w.N, w.K), dtype=torch.float32, device=f"cuda:{ctx.device}")
+    ctx._check(ctx._lib.tgaf_dequant_f32(ctx._h, w._h, C.c_void_p(out.data_ptr())))
+    return out
+
+
+def dequant_f32_host(ctx: Context, w: Weight) -> np.ndarray:
+    out = np.empty((w.N, w.K), np.float32)
+    ctx._check(ctx._lib.tgaf_dequant_f32_host(ctx._h, w._h, out.ctypes.data))
+    return out
+
+
+def gaffine_matvec_f32(ctx: Context, bits: int, input, packed, scales, biases, out, in_dim: int, out_dim: int,
+                       group_size: int, scales_dtype_tag: int, batch_rows: int) -> None:
+    """Raw device-pointer launch with the reference wrapper's argument list
+    (core/src/compute/cuda/gaffine_u4_matvec.zig:58-97).  Arguments are torch device tensors."""
+    fn = ctx._lib.tgaf_gaffine_u4_matvec_f32 if bits == 4 else ctx._lib.tgaf_gaffine_u8_matvec_f32
+    ptr = lambda t: C.c_void_p(t.data_ptr() if t is not None else 0)
+    ctx._check(fn(ctx._h, ptr(input), ptr(packed), ptr(scales), ptr(biases), ptr(out), in_dim, out_dim,
+                  group_size, scales_dtype_tag, batch_rows))

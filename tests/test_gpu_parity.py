@@ -1,0 +1,245 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU
+oracle on the same seeded inputs.  Bit-exact for dequantized weights; matmul
+within the stated tolerance (written beside each check)."""
+import json
+
+import numpy as np
+import pytest
+
+from helpers import (TOL_BF16, TOL_F32, bits_from_torch_bf16, make_weights, make_x_bf16, rel_err,
+                     torch_bf16_from_bits)
+
+pytestmark = pytest.mark.gpu
+
+SCHEMES = [(4, 32), (4, 64), (4, 128), (8, 32), (8, 64), (8, 128)]
+
+
+@pytest.fixture(scope="module")
+def gaf():
+    import torch
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    import talu_b200
+    return talu_b200
+
+
+@pytest.fixture(scope="module")
+def ctx(gaf):
+    c = gaf.Context(0)
+    yield c
+    c.close()
+
+
+def _run_bf16(gaf, ctx, oracle, N, K, G, bits, M, seed=0, host=False):
+    import torch
+    p, s, b = make_weights(oracle, N, K, G, bits, seed)
+    xb, xf = make_x_bf16(oracle, M, K, seed + 1)
+    w = gaf.Weight.from_host(ctx, p, s, b, G, bits)
+    if host:
+        y_bits = gaf.linear_host(ctx, w, xb)
+    else:
+        x = torch_bf16_from_bits(xb, "cuda:0")
+        y = gaf.linear(ctx, w, x)
+        ctx.synchronize()
+        y_bits = bits_from_torch_bf16(y)
+    w.free()
+    ref = oracle.matmul_f32(xf, p, s, b, G, bits)
+    ref_bf16 = oracle.bf16_to_f32(oracle.f32_to_bf16_rne(ref))
+    return oracle.bf16_to_f32(y_bits), ref_bf16
+
+
+@pytest.mark.parametrize("bits,G", SCHEMES)
+def test_dequant_bit_exact(gaf, ctx, oracle, bits, G):
+    """Dequantized weights are bit-exact with the reference CPU dequant."""
+    N, K = 257, 16 * G
+    p, s, b = make_weights(oracle, N, K, G, bits, seed=bits + G)
+    w = gaf.Weight.from_host(ctx, p, s, b, G, bits)
+    d_host = gaf.dequant_f32_host(ctx, w)
+    d_dev = gaf.dequant_f32(ctx, w)
+    ctx.synchronize()
+    ref = oracle.dequant_f32(p, s, b, G, bits)
+    assert (d_host.view(np.uint32) == ref.view(np.uint32)).all()
+    assert (d_dev.cpu().numpy().view(np.uint32) == ref.view(np.uint32)).all()
+    w.free()
+
+
+def test_dequant_bit_exact_f16_scales_and_4096(gaf, ctx, oracle):
+    """Scheme sweep shape (K = N = 4096) and f16 scale/bias patterns."""
+    rng = np.random.default_rng(5)
+    for bits, G in SCHEMES:
+        p, s, b = make_weights(oracle, 4096, 4096, G, bits, seed=11)
+        w = gaf.Weight.from_host(ctx, p, s, b, G, bits)
+        d = gaf.dequant_f32_host(ctx, w)
+        ref = oracle.dequant_f32(p, s, b, G, bits)
+        assert (d.view(np.uint32) == ref.view(np.uint32)).all(), (bits, G)
+        w.free()
+    p, _, _ = make_weights(oracle, 64, 256, 64, 4, seed=3)
+    s16 = rng.standard_normal((64, 4)).astype(np.float16).view(np.uint16)
+    b16 = rng.standard_normal((64, 4)).astype(np.float16).view(np.uint16)
+    w = gaf.Weight.from_host(ctx, p, s16, b16, 64, 4, sdtype=gaf.SCALES_F16)
+    d = gaf.dequant_f32_host(ctx, w)
+    ref = oracle.dequant_f32(p, s16, b16, 64, 4, sdtype=oracle.SCALES_F16)
+    assert (d.view(np.uint32) == ref.view(np.uint32)).all()
+    w.free()
+
+
+def test_reference_known_answers_through_c_abi(gaf, ctx, oracle, kats):
+    """The reference's own matmul and CUDA self-test vectors, through the raw
+    f32 entry point that mirrors its kernel wrapper."""
+    import torch
+    from test_oracle_kats import _build_matmul_case, _h
+    for k in kats["matmul"]:
+        x, packed, scales, biases, want = _build_matmul_case(k)
+        dev = "cuda:0"
+        tx = torch.from_numpy(x).to(dev)
+        tp = torch.from_numpy(packed.view(np.int32)).to(dev)
+        ts = torch.from_numpy(scales.view(np.int16)).to(dev)
+        tb = torch.from_numpy(biases.view(np.int16)).to(dev)
+        out = torch.zeros((k["M"], k["N"]), dtype=torch.float32, device=dev)
+        gaf.gaffine_matvec_f32(ctx, k["bits"], tx, tp, ts, tb, out, k["K"], k["N"], k["group"], k["sdtype"], k["M"])
+        ctx.synchronize()
+        assert np.allclose(out.cpu().numpy(), want, atol=k["tol"]), k["src"]
+    for k in kats["cuda_selftest"]:
+        dev = "cuda:0"
+        tx = torch.tensor(k["input"], dtype=torch.float32, device=dev)
+        tp = torch.from_numpy(np.array([_h(w) for w in k["packed"]], np.uint32).view(np.int32)).to(dev)
+        ts = torch.from_numpy(np.array([_h(w) for w in k["scales"]], np.uint16).view(np.int16)).to(dev)
+        tb = torch.from_numpy(np.array([_h(w) for w in k["biases"]], np.uint16).view(np.int16)).to(dev)
+        out = torch.zeros((len(k["input"]), k["out_dim"]), dtype=torch.float32, device=dev)
+        gaf.gaffine_matvec_f32(ctx, 4, tx, tp, ts, tb, out, k["in_dim"], k["out_dim"], k["group"], k["sdtype"],
+                               len(k["input"]))
+        ctx.synchronize()
+        assert np.allclose(out.cpu().numpy(), np.array(k["expect"]), atol=k["tol"]), k["src"]
+
+
+def test_cfg1_gemv_gaf4_64(gaf, ctx, oracle):
+    """N=4096, K=1024, M=1, gaf4_64: the reference's CPU-runnable case.  rel <= 1e-2."""
+    y, ref = _run_bf16(gaf, ctx, oracle, 4096, 1024, 64, 4, 1, seed=0)
+    assert rel_err(y, ref) <= TOL_BF16
+
+
+@pytest.mark.parametrize("bits,G", SCHEMES)
+@pytest.mark.parametrize("M", [1, 8])
+def test_cfg3_scheme_sweep(gaf, ctx, oracle, bits, G, M):
+    """K = N = 4096, M in {1, 8}, every scheme.  rel <= 1e-2."""
+    y, ref = _run_bf16(gaf, ctx, oracle, 4096, 4096, G, bits, M, seed=20 + bits + G)
+    assert rel_err(y, ref) <= TOL_BF16
+
+
+@pytest.mark.parametrize("M", [1, 4, 16])
+@pytest.mark.parametrize("N,K", [(14336, 4096), (4096, 14336)])
+def test_cfg2_llama8b_ffn(gaf, ctx, oracle, N, K, M):
+    """Llama-3-8B FFN shapes (gate/up and down), gaf4_64, M in {1, 4, 16}.  rel <= 1e-2."""
+    y, ref = _run_bf16(gaf, ctx, oracle, N, K, 64, 4, M, seed=N % 97)
+    assert rel_err(y, ref) <= TOL_BF16
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 5, 8, 9, 15, 16, 17, 33])
+def test_ragged_shapes(gaf, ctx, oracle, M):
+    """Row counts around the tile edges, N not a multiple of 16 (and odd)."""
+    for N, K, G, bits in [(3, 256, 64, 4), (17, 512, 32, 4), (1001, 1024, 128, 4), (31, 256, 32, 8), (130, 768, 64, 8)]:
+        y, ref = _run_bf16(gaf, ctx, oracle, N, K, G, bits, M, seed=M)
+        assert rel_err(y, ref) <= TOL_BF16, (N, K, G, bits, M)
+
+
+def test_f32_contract(gaf, ctx, oracle):
+    """The reference's f32-in / f32-out contract, tolerance 1e-3 (its policy for f32 matmul)."""
+    import torch
+    for bits, G, N, K, M in [(4, 64, 1024, 2048, 1), (4, 32, 515, 1024, 7), (8, 64, 512, 1024, 16), (4, 128, 256, 4096, 12)]:
+        p, s, b = make_weights(oracle, N, K, G, bits, seed=G + M)
+        x = np.random.default_rng(M).standard_normal((M, K), dtype=np.float32)
+        w = gaf.Weight.from_host(ctx, p, s, b, G, bits)
+        y = gaf.linear(ctx, w, torch.from_numpy(x).to("cuda:0"))
+        ctx.synchronize()
+        y_host = gaf.linear_host(ctx, w, x)
+        truth = oracle.matmul_f64(x, p, s, b, G, bits)
+        assert rel_err(y.cpu().numpy(), truth) <= TOL_F32, (bits, G, N, K, M)
+        assert (y_host == y.cpu().numpy()).all()
+        w.free()
+
+
+def test_generic_kernel_matches(gaf, ctx, oracle):
+    """Shapes outside the fast path (group 8 / 16, K = one group) and the forced generic path."""
+    for N, K, G, bits, M in [(5, 8, 8, 4, 2), (9, 48, 16, 4, 3), (6, 16, 4, 8, 1), (33, 64, 16, 8, 4)]:
+        y, ref = _run_bf16(gaf, ctx, oracle, N, K, G, bits, M, seed=K)
+        assert rel_err(y, ref) <= TOL_BF16, (N, K, G, bits, M)
+    ctx.set_option("force_generic", 1)
+    try:
+        y, ref = _run_bf16(gaf, ctx, oracle, 300, 1024, 64, 4, 3, seed=8)
+        assert rel_err(y, ref) <= TOL_BF16
+    finally:
+        ctx.set_option("force_generic", 0)
+
+
+def test_host_entry_point_equals_device_entry_point(gaf, ctx, oracle):
+    yd, ref = _run_bf16(gaf, ctx, oracle, 2048, 1024, 64, 4, 4, seed=2)
+    yh, _ = _run_bf16(gaf, ctx, oracle, 2048, 1024, 64, 4, 4, seed=2, host=True)
+    assert (yd == yh).all()
+    assert rel_err(yh, ref) <= TOL_BF16
+
+
+def test_split_k_is_deterministic_and_tunable(gaf, ctx, oracle):
+    """Different K splits (warps per CTA, CTAs along K) agree within tolerance, and a
+    given split gives the same bits on every run (fixed-order reduction)."""
+    import torch
+    p, s, b = make_weights(oracle, 512, 8192, 64, 4, seed=4)
+    xb, xf = make_x_bf16(oracle, 3, 8192, 9)
+    w = gaf.Weight.from_host(ctx, p, s, b, 64, 4)
+    x = torch_bf16_from_bits(xb, "cuda:0")
+    ref = oracle.matmul_f32(xf, p, s, b, 64, 4)
+    outs = []
+    try:
+        for slices, warps in [(0, 0), (32, 4), (512, 8), (4096, 8), (100000, 8)]:
+            ctx.set_option("gemv_slices", slices)
+            ctx.set_option("gemv_warps", warps)
+            y1 = gaf.linear(ctx, w, x).clone()
+            y2 = gaf.linear(ctx, w, x).clone()
+            ctx.synchronize()
+            assert torch.equal(y1, y2)
+            assert rel_err(oracle.bf16_to_f32(bits_from_torch_bf16(y1)), ref) <= TOL_BF16
+            outs.append(y1)
+    finally:
+        ctx.set_option("gemv_slices", 0)
+        ctx.set_option("gemv_warps", 0)
+    w.free()
+
+
+def test_linearity_at_full_size(gaf, ctx, oracle):
+    """Size-independent property at the benchmark's full shape: y(2x) = 2 y(x) exactly
+    (scaling by two is exact in bf16 and in every partial sum)."""
+    import torch
+    N, K = 14336, 4096
+    p, s, b = make_weights(oracle, N, K, 64, 4, seed=6)
+    xb, _ = make_x_bf16(oracle, 4, K, 3)
+    w = gaf.Weight.from_host(ctx, p, s, b, 64, 4)
+    x = torch_bf16_from_bits(xb, "cuda:0")
+    y1 = gaf.linear(ctx, w, x)
+    y2 = gaf.linear(ctx, w, x * 2)
+    ctx.synchronize()
+    assert torch.equal(y1 * 2, y2)
+    w.free()
+
+
+def test_invalid_arguments_are_status_codes(gaf, ctx, oracle):
+    """Host-side validation mirrors the reference wrapper's tests
+    (gaffine_u4_matvec.zig:145-170): bad group alignment, bad dtype tag, zero rows."""
+    import torch
+    dev = "cuda:0"
+    buf = torch.zeros(4096, dtype=torch.float32, device=dev)
+    for args in [(16, 8, 12, 1, 1), (16, 8, 8, 7, 1), (16, 8, 8, 1, 0)]:
+        with pytest.raises(gaf.GafError) as ei:
+            gaf.gaffine_matvec_f32(ctx, 4, buf, buf, buf, buf, buf, *args)
+        assert ei.value.invalid_argument
+    p, s, b = make_weights(oracle, 8, 64, 32, 4)
+    with pytest.raises(gaf.GafError):
+        gaf.Weight.from_host(ctx, p, s, b, 12, 4)            # group not a multiple of 8
+    with pytest.raises(gaf.GafError):
+        gaf.Weight.from_host(ctx, p, s, b, 32, 4, sdtype=5)  # bad scales dtype
+    with pytest.raises(gaf.GafError):
+        gaf.Weight.from_host(ctx, p, s, b, 32, 5)            # bits
+    w = gaf.Weight.from_host(ctx, p, s, b, 32, 4)
+    with pytest.raises(gaf.GafError):
+        gaf.linear(ctx, w, torch.zeros((2, 32), dtype=torch.bfloat16, device=dev))  # wrong K
+    w.free()
+    # the context is still usable after every rejected call
+    y, ref = _run_bf16(gaf, ctx, oracle, 64, 256, 64, 4, 1)
+    assert rel_err(y, ref) <= TOL_BF16
