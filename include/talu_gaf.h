@@ -66,13 +66,15 @@ const char *tgaf_status_string(int32_t status);
 /* ---- context ------------------------------------------------------------
  * Replaces the device / registry / launch-stream triple a talu CUDA backend
  * owns (core/src/compute/cuda/device.zig:147-193).  `stream` is a cudaStream_t
- * (CUstream) the caller owns, or NULL for a stream the context creates. */
+ * (CUstream) the caller owns, or NULL for a non-blocking stream the context
+ * creates.  The default stream is named by its handle cudaStreamLegacy (0x1)
+ * or cudaStreamPerThread (0x2), not by NULL. */
 int32_t tgaf_ctx_create(int32_t device_ordinal, void *stream, tgaf_ctx **out_ctx);
 int32_t tgaf_ctx_destroy(tgaf_ctx *ctx);
 int32_t tgaf_ctx_set_stream(tgaf_ctx *ctx, void *stream);
 int32_t tgaf_synchronize(tgaf_ctx *ctx);
 const char *tgaf_last_error(const tgaf_ctx *ctx);
-/* Tuning knobs by name (e.g. "gemv_slices", "gemv_warps", "pdl"); unknown names
+/* Tuning knobs by name ("gemv_ctas", "pdl", "force_generic"); unknown names
  * are TGAF_ERR_INVALID_ARGUMENT. */
 int32_t tgaf_ctx_set_option(tgaf_ctx *ctx, const char *name, int64_t value);
 

@@ -74,7 +74,7 @@ struct tgaf_ctx {
     bool owns_stream = false;
     int sm_count = 148;
     Scratch scratch = {nullptr, 0, nullptr, 0};
-    GemvTuning tune = {0, 0, 1, 0};
+    GemvTuning tune = {0, 1, 0};
     // staging for the *_host entry points
     void *stage_x = nullptr;
     size_t stage_x_bytes = 0;
@@ -184,13 +184,12 @@ int32_t linear_device(tgaf_ctx *ctx, const WeightView &w, const void *x, uint32_
         for (uint32_t m0 = 0; m0 < M; m0 += 16u) {
             const uint32_t mc = (M - m0) < 16u ? (M - m0) : 16u;
             const size_t need = gemv_mma_scratch_bytes(w, mc, ctx->tune, ctx->sm_count);
-            if (need) {
-                int32_t st = ensure_scratch(ctx, need, (w.N + 15u) / 16u);
-                if (st != TGAF_OK) return st;
-            }
+            int32_t st = ensure_scratch(ctx, need, gemv_mma_counter_count(w));
+            if (st != TGAF_OK) return st;
             const void *xp = static_cast<const uint8_t *>(x) + static_cast<size_t>(m0) * w.K * elt;
             void *yp = static_cast<uint8_t *>(y) + static_cast<size_t>(m0) * w.N * elt;
-            cudaError_t e = gemv_mma(w, xp, yp, mc, f32, ctx->scratch, ctx->tune, ctx->stream, ctx->sm_count);
+            cudaError_t e = gemv_mma(w, xp, yp, mc, f32, ctx->scratch, ctx->tune, ctx->stream, ctx->sm_count,
+                                     ctx->d_error_word);
             if (e != cudaSuccess) return cuda_fail(ctx, e, "gemv_mma launch");
         }
         return TGAF_OK;
@@ -243,6 +242,7 @@ int32_t raw_matvec(tgaf_ctx *ctx, uint32_t bits, const float *input, const uint3
     v.sdtype = sdtype;
     v.row_bytes = in_dim / vpw * 4u;
     v.groups = in_dim / group_size;
+    attach_packed_tmap(v);
     return linear_device(ctx, v, input, batch_rows, out, true);
 }
 
@@ -347,6 +347,8 @@ int32_t tgaf_synchronize(tgaf_ctx *ctx) {
     TGAF_CUDA(ctx, cudaMemcpy(&flag, ctx->d_error_word, sizeof flag, cudaMemcpyDeviceToHost));
     if (flag != 0) {
         cudaMemset(ctx->d_error_word, 0, sizeof flag);
+        // an abandoned launch may have left arrival counters half way
+        if (ctx->scratch.counters) cudaMemset(ctx->scratch.counters, 0, ctx->scratch.counter_count * sizeof(unsigned int));
         return fail(ctx, TGAF_ERR_DEVICE_FLAG, "a kernel gave up a bounded wait (code 0x%x)", flag);
     }
     return TGAF_OK;
@@ -356,11 +358,9 @@ const char *tgaf_last_error(const tgaf_ctx *ctx) { return ctx ? ctx->err : "null
 
 int32_t tgaf_ctx_set_option(tgaf_ctx *ctx, const char *name, int64_t value) {
     if (!ctx || !name) return TGAF_ERR_INVALID_ARGUMENT;
-    if (!strcmp(name, "gemv_slices")) {
-        ctx->tune.slices_target = static_cast<int>(value);
-    } else if (!strcmp(name, "gemv_warps")) {
-        if (value != 0 && value != 4 && value != 8) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "gemv_warps must be 0, 4 or 8");
-        ctx->tune.warps = static_cast<int>(value);
+    if (!strcmp(name, "gemv_ctas")) {
+        if (value < 0 || value > 65535) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "gemv_ctas out of range");
+        ctx->tune.ctas = static_cast<int>(value);
     } else if (!strcmp(name, "pdl")) {
         ctx->tune.pdl = value != 0;
     } else if (!strcmp(name, "force_generic")) {
@@ -455,6 +455,7 @@ int32_t tgaf_weight_upload(tgaf_ctx *ctx, const void *packed, const void *scales
     v.packed = dp;
     v.scales = reinterpret_cast<uint16_t *>(ds);
     v.biases = reinterpret_cast<uint16_t *>(db);
+    attach_packed_tmap(v);
     *out_weight = w;
     return TGAF_OK;
 }
@@ -485,6 +486,7 @@ int32_t tgaf_weight_wrap_device(tgaf_ctx *ctx, const void *d_packed, const void 
     v.sdtype = scales_dtype;
     v.row_bytes = static_cast<uint32_t>(K * bits / 8);
     v.groups = static_cast<uint32_t>(K / group_size);
+    attach_packed_tmap(v);
     *out_weight = w;
     return TGAF_OK;
 }

@@ -9,18 +9,17 @@
 // Arithmetic (same deferred form as the CPU reference, matmul_prefill.zig:163-337):
 //     y[m,n] = sum_g ( s[n,g] * sum_{k in g} q[n,k] x[m,k] + b[n,g] * sum_{k in g} x[m,k] )
 //
-// How the fast kernel spends its instructions.  At HBM rate a B200 SM must
-// retire ~40 weights per clock, which leaves no room for an int->float convert
-// and an FMA per weight on the CUDA cores once M > 1.  So the codes go through
-// the tensor cores as exact small integers:
+// Instruction budget.  At HBM rate a B200 SM must retire ~40 weights per clock,
+// which leaves no room for an int->float convert and an FMA per weight on the
+// CUDA cores.  So the codes go through the tensor cores as exact small integers:
 //   * a packed word is split with four (shift, and, or) steps into bf16x2 pairs
 //     0x4300|q, i.e. the bf16 value 128+q (exact for q < 128);
 //   * warp-level mma.sync m16n8k16 (bf16 x bf16 -> f32) multiplies 16 weight rows
 //     by up to 8 activation rows; the k order inside a fragment is free, so the
-//     canonical [N, K/8] u32 layout is consumed as is, and the activations are
-//     permuted to match with two byte-permutes per word;
-//   * a second MMA with an all-ones A operand yields sum_k x[m,k] per group in the
-//     same register layout as the accumulators;
+//     canonical [N, K/8] u32 layout is consumed as is and the activations are
+//     permuted to match with byte-permutes;
+//   * a second MMA with an all-ones A operand yields sum_k x[m,k] per group in
+//     the accumulators' register layout;
 //   * per group: y += s*acc + (b - 128 s) * xsum, in fp32.
 // 8-bit codes reuse all of it: a byte is two nibbles, q = lo + 16 hi, and 16 x is
 // exact in bf16, so a gaf8 row is a gaf4 row of twice the length against the
@@ -28,18 +27,35 @@
 // f32 activations are split into bf16 hi + lo parts (two MMAs), which keeps ~16
 // mantissa bits of x.
 //
-// Work split: one CTA = one block of 16 weight rows; its NW warps take
-// consecutive K ranges (whole groups); gridDim.y further CTAs split K when there
-// are too few row blocks to fill the machine.  Warps reduce through shared
-// memory; CTAs through an fp32 scratch and a per-row-block arrival counter whose
-// last arriver sums the partials in a fixed order (no spinning anywhere).
+// Data movement.  A persistent grid (one CTA per SM) walks "units" of
+// 128 weight rows x 256 packed bytes.  A producer thread streams each unit into a
+// 3-deep shared-memory ring with two TMA tensor copies (128 rows x 128 bytes each,
+// 128-byte swizzle) that complete on an mbarrier, so the weights never pass
+// through the load/store units on their way in and ~100 KB per SM can be in
+// flight.  Eight consumer warps each own 16 of the 128 rows: they read their rows
+// from the ring with 4/8/16-byte shared loads, take scales / biases for the whole
+// unit with one vector load per row, and read activations through L1.  No warp
+// ever exchanges data with another warp of the CTA.
+// The MMA fixes which lanes hold which row (lane / 4) but not which weight row
+// that is, so each warp permutes its rows such that the lanes of one shared-load
+// wavefront touch rows whose swizzle patterns do not collide (rho below): the
+// fragment loads are bank-conflict free on the swizzled tile.
 //
-// Loads: every quad (4 lanes) reads one group of one row per step, so each
-// lane's load width is a quarter of the group's bytes (8 B for gaf4_64).  Weights
-// are read once (ld.global.nc, no L1 allocation) and prefetched a batch of groups
-// ahead in registers; activations are re-read by every warp and stay in L1.
+// Units are dealt to CTAs as equal contiguous ranges (row group major, K chunk
+// minor), so a row group can be shared by neighbouring CTAs.  Each warp then
+// parks its fp32 partial in a scratch slot and bumps a per-(row group, warp)
+// arrival counter; whoever arrives last adds the slots in slot order and writes
+// y (nobody spins; counters reset themselves).
+//
+// Every wait on an mbarrier has an iteration limit; a warp that runs out sets an
+// error word for the host and leaves.
+//
+// Programmatic dependent launch: the producer starts copying weights at once
+// (they never change), consumers execute griddepcontrol.wait before they touch
+// activations, outputs or scratch, so back-to-back GEMVs overlap tail and head.
 #include "gaf_internal.h"
 
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -50,23 +66,73 @@ constexpr uint32_t kMagic128 = 0x43004300u;  // bf16x2 {128, 128}
 constexpr uint32_t kOnesBf16 = 0x3F803F80u;  // bf16x2 {1, 1}
 constexpr uint32_t kNibMask = 0x000F000Fu;
 
+constexpr int kRows = 128;        // weight rows per unit (8 consumer warps x 16)
+constexpr int kChunkBytes = 256;  // packed bytes per row per unit
+constexpr int kStages = 3;
+constexpr int kConsumerWarps = 8;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr uint32_t kWaitLimit = 1u << 22;  // polls (with back-off) before a wait gives up
+
 struct GemvParams {
     const uint8_t *packed;
     const uint16_t *scales;
     const uint16_t *biases;
     const void *x;
     void *y;
-    float *partials;
-    unsigned int *counters;
+    float *partials;         // [row group][slot][128][MT*8]
+    unsigned int *counters;  // [row group][8]
+    unsigned int *error_word;
     uint32_t N, K, M;
-    uint32_t groups;     // K / G
-    uint32_t row_bytes;  // packed bytes per weight row
-    uint32_t group;      // G
-    uint32_t gpw;        // groups per warp slice
-    uint32_t ks;         // CTAs along K (gridDim.y)
-    uint32_t sdtype;     // 0 f16, 1 bf16
-    uint32_t n_pad;      // gridDim.x * 16
+    uint32_t groups;      // K / G
+    uint32_t row_bytes;   // packed bytes per weight row
+    uint32_t group;       // G
+    uint32_t sdtype;      // 0 f16, 1 bf16
+    uint32_t chunks;      // K chunks per row group
+    uint32_t units;       // row groups * chunks
+    uint32_t max_slots;   // scratch slots per row group
+    uint32_t vec_sb;      // 1: scales / biases of a unit can be read with one aligned vector load
 };
+
+// ---- small PTX wrappers ----------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false (and the error word set) when the limit runs out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int *error_word, uint32_t code) {
+    for (uint32_t it = 0; it < kWaitLimit; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (it > 32) __nanosleep(it > 4096 ? 256 : 32);
+    }
+    atomicOr(error_word, code);
+    return false;
+}
+// one TMA tile: box {128 bytes, 128 rows} of the packed matrix at (byte column c0, row c1)
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tmap, uint32_t c0, uint32_t c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                                uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -82,42 +148,24 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     return r;
 }
 
-// streaming (read-once) global loads: no L1 allocation
-__device__ __forceinline__ uint32_t ldg_stream_u32(const void *p) {
-    uint32_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint2 ldg_stream_u64(const void *p) {
-    uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint4 ldg_stream_u128(const void *p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
-}
-
+// Packed words of one lane for one group and row, from a swizzled panel.
+// `row_addr` = shared address of the row (128 bytes), `chunk` = first 16-byte chunk
+// of the lane's piece, `inner` = byte offset inside the chunk, `xr` = row & 7.
 template <int WPT>
-__device__ __forceinline__ void load_words(const uint8_t *p, uint32_t (&w)[WPT]) {
+__device__ __forceinline__ void lds_words(uint32_t row_addr, uint32_t chunk, uint32_t inner, uint32_t xr,
+                                          uint32_t (&w)[WPT]) {
     if constexpr (WPT == 1) {
-        w[0] = ldg_stream_u32(p);
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[0]) : "r"(row_addr + ((chunk ^ xr) << 4) + inner));
     } else if constexpr (WPT == 2) {
-        uint2 v = ldg_stream_u64(p);
-        w[0] = v.x;
-        w[1] = v.y;
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];"
+                     : "=r"(w[0]), "=r"(w[1])
+                     : "r"(row_addr + ((chunk ^ xr) << 4) + inner));
     } else {
 #pragma unroll
-        for (int i = 0; i < WPT / 4; ++i) {
-            uint4 v = ldg_stream_u128(p + 16 * i);
-            w[4 * i + 0] = v.x;
-            w[4 * i + 1] = v.y;
-            w[4 * i + 2] = v.z;
-            w[4 * i + 3] = v.w;
-        }
+        for (int i = 0; i < WPT / 4; ++i)
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(w[4 * i]), "=r"(w[4 * i + 1]), "=r"(w[4 * i + 2]), "=r"(w[4 * i + 3])
+                         : "r"(row_addr + (((chunk + i) ^ xr) << 4)));
     }
 }
 
@@ -197,57 +245,112 @@ __device__ __forceinline__ void load_x_frags(const void *xrow, uint32_t kx, bool
     }
 }
 
-template <int GB, int BITS, int MT, bool XF32, int NW>
-__global__ void __launch_bounds__(NW * 32)
-gaf_gemv_mma_kernel(const GemvParams p) {
-    constexpr int LW = GB / 4;                      // bytes one lane reads per group and row
-    constexpr int WPT = LW / 4;                     // packed words per lane per group and row
-    constexpr int XPB = 8 / BITS;                   // activations per packed byte
-    constexpr float OFF = BITS == 4 ? 128.f : 2176.f;  // sum of the +128 offsets per unit of x
-    constexpr int U = WPT >= 4 ? 2 : 4;             // groups per prefetch batch
-    constexpr int MROWS = MT * 8;
-    static_assert(WPT >= 1, "group too small for the fast path");
+// contiguous, near-equal unit ranges: the first `rem` CTAs take one unit more
+__device__ __host__ __forceinline__ uint32_t range_begin(uint32_t cta, uint32_t units, uint32_t ctas) {
+    const uint32_t q = units / ctas, rem = units % ctas;
+    return cta * q + (cta < rem ? cta : rem);
+}
+__device__ __host__ __forceinline__ uint32_t unit_owner(uint32_t u, uint32_t units, uint32_t ctas) {
+    const uint32_t q = units / ctas, rem = units % ctas;
+    const uint32_t cut = rem * (q + 1u);
+    return u < cut ? u / (q + 1u) : rem + (u - cut) / q;
+}
 
+constexpr int kPanelBytes = 128;                       // bytes per row in one TMA tile (the swizzle span)
+constexpr int kPanels = kChunkBytes / kPanelBytes;     // TMA tiles per unit
+constexpr int kPanelSize = kRows * kPanelBytes;        // 16 KB
+constexpr int kStageBytes = kPanels * kPanelSize;      // 32 KB
+constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + slack to align the ring to the swizzle atom
+
+template <int GB>
+struct StreamGeom {
+    static constexpr int GPS = kChunkBytes / GB;   // groups per unit
+    static constexpr int GPP = kPanelBytes / GB;   // groups per panel
+    static constexpr int LW = GB / 4;              // bytes one lane reads per group and row
+    static constexpr int WPT = LW / 4;             // packed words per lane per group and row
+};
+
+// Row permutation inside a warp's 16 rows: lane group g (= lane / 4) works on row rho(g)
+// (and rho(g) + 8).  Chosen per load width so that the rows met by one shared-memory
+// wavefront differ in the address bits the 128-byte swizzle XORs into the chunk index.
+template <int LW>
+__device__ __forceinline__ uint32_t rho(uint32_t g) {
+    if constexpr (LW == 8) return ((g & 3u) << 1) | (g >> 2);   // 0 2 4 6 1 3 5 7
+    if constexpr (LW == 16) return ((g & 1u) << 2) | (g >> 1);  // 0 4 1 5 2 6 3 7
+    return g;
+}
+
+template <int GB, int BITS, int MT, bool XF32>
+__global__ void __launch_bounds__(kThreads, 1)
+gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap) {
+    using Geo = StreamGeom<GB>;
+    constexpr int GPS = Geo::GPS, GPP = Geo::GPP, LW = Geo::LW, WPT = Geo::WPT;
+    constexpr int XPB = 8 / BITS;                          // activations per packed byte
+    constexpr float OFF = BITS == 4 ? 128.f : 2176.f;      // what the +128 offsets add per unit of sum(x)
+    constexpr int SBW = GPS * 2 / 4 > 0 ? GPS * 2 / 4 : 1;  // 32-bit words holding one row's scales of a unit
+    static_assert(WPT >= 1 && GPS >= 2, "unsupported group size");
+
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t s_full[kStages];
+    __shared__ __align__(8) uint64_t s_empty[kStages];
+
+    // the ring starts at a 1024-byte boundary (8 rows x 128 bytes, the swizzle atom)
+    const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    const int g = lane >> 2;  // weight row inside the block (and +8); activation row inside a tile
-    const int t = lane & 3;   // position inside the quad: which quarter of the group
 
-    const uint32_t rb = blockIdx.x;
-    const uint32_t n0 = min(rb * 16u + g, p.N - 1u);
-    const uint32_t n1 = min(rb * 16u + g + 8u, p.N - 1u);
-    const uint32_t slice = blockIdx.y * NW + warp;
-    const uint32_t g_begin = min(slice * p.gpw, p.groups);
-    const uint32_t g_end = min(g_begin + p.gpw, p.groups);
-
-    const uint8_t *w0 = p.packed + static_cast<size_t>(n0) * p.row_bytes + t * LW;
-    const uint8_t *w1 = p.packed + static_cast<size_t>(n1) * p.row_bytes + t * LW;
-    const uint16_t *s0p = p.scales + static_cast<size_t>(n0) * p.groups;
-    const uint16_t *s1p = p.scales + static_cast<size_t>(n1) * p.groups;
-    const uint16_t *b0p = p.biases + static_cast<size_t>(n0) * p.groups;
-    const uint16_t *b1p = p.biases + static_cast<size_t>(n1) * p.groups;
-
-    uint32_t cur0[U][WPT], cur1[U][WPT];
-    uint16_t csb[U][4];
-    auto load_batch = [&](uint32_t gi, uint32_t (&a)[U][WPT], uint32_t (&b)[U][WPT], uint16_t (&sb)[U][4]) {
+    if (threadIdx.x == 0) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            if (gi + u < g_end) {
-                load_words<WPT>(w0 + static_cast<size_t>(gi + u) * GB, a[u]);
-                load_words<WPT>(w1 + static_cast<size_t>(gi + u) * GB, b[u]);
-                sb[u][0] = __ldg(s0p + gi + u);
-                sb[u][1] = __ldg(b0p + gi + u);
-                sb[u][2] = __ldg(s1p + gi + u);
-                sb[u][3] = __ldg(b1p + gi + u);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&s_full[s]), 1);
+            mbar_init(smem_u32(&s_empty[s]), kConsumerWarps);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const uint32_t u_begin = range_begin(blockIdx.x, p.units, gridDim.x);
+    const uint32_t u_end = range_begin(blockIdx.x + 1u, p.units, gridDim.x);
+
+    if (warp == kConsumerWarps) {
+        // ------------------------- producer warp (one lane works) -------------------------
+        if (lane != 0) return;
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap)) : "memory");
+        uint32_t issued = 0;
+        bool ok = true;
+        for (uint32_t u = u_begin; u < u_end; ++u, ++issued) {
+            const uint32_t stage = issued % kStages;
+            const uint32_t round = issued / kStages;
+            if (round > 0) ok = mbar_wait(smem_u32(&s_empty[stage]), (round - 1u) & 1u, p.error_word, 0x1u);
+            if (!ok) break;
+            const uint32_t rg = u / p.chunks, kc = u - rg * p.chunks;
+            const uint32_t full = smem_u32(&s_full[stage]);
+            // rows past N and bytes past the row end are zero-filled by the copy engine,
+            // so every unit delivers the same byte count
+            mbar_arrive_expect_tx(full, kStageBytes);
+#pragma unroll
+            for (int pnl = 0; pnl < kPanels; ++pnl)
+                tma_load_2d(ring + stage * kStageBytes + pnl * kPanelSize, &tmap, kc * kChunkBytes + pnl * kPanelBytes,
+                            rg * kRows, full);
+        }
+        if (!ok) {
+            // give copies already in flight a bounded time to land before the CTA's memory is released
+            const uint32_t pending = issued < static_cast<uint32_t>(kStages) ? issued : static_cast<uint32_t>(kStages);
+            for (uint32_t i = 0; i < pending; ++i) {
+                const uint32_t idx = issued - 1u - i;
+                mbar_wait(smem_u32(&s_full[idx % kStages]), (idx / kStages) & 1u, p.error_word, 0x4u);
             }
         }
-    };
+        return;
+    }
 
-    // Weights do not depend on the previous kernel in the stream: start fetching
-    // them, then wait for it (no-op unless launched as a programmatic dependent).
-    if (g_begin < g_end) load_batch(g_begin, cur0, cur1, csb);
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // --------------------------- consumer warps ---------------------------
+    const int g = lane >> 2;  // activation row inside a tile; accumulator row slot
+    const int t = lane & 3;   // quarter of the group this lane holds
+    const uint32_t wr = rho<LW>(g);  // weight row (of the warp's 16) behind accumulator rows g and g + 8
+    const uint8_t *xbase = static_cast<const uint8_t *>(p.x);
+    const size_t x_elt = XF32 ? 4 : 2;
 
     float yacc[MT][4];
 #pragma unroll
@@ -255,56 +358,115 @@ gaf_gemv_mma_kernel(const GemvParams p) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) yacc[mt][i] = 0.f;
 
-    const size_t x_elt = XF32 ? 4 : 2;
-    const uint8_t *xbase = static_cast<const uint8_t *>(p.x);
+    // scales / biases of one unit for this lane's two rows: {s0, b0, s1, b1}[SBW words]
+    uint32_t sb_cur[4][SBW], sb_nxt[4][SBW];
+    auto load_sb = [&](uint32_t u, uint32_t (&dst)[4][SBW]) {
+        const uint32_t rg = u / p.chunks, kc = u - rg * p.chunks;
+        const uint32_t r0 = min(rg * kRows + warp * 16u + wr, p.N - 1u);
+        const uint32_t r1 = min(rg * kRows + warp * 16u + wr + 8u, p.N - 1u);
+        const uint32_t g0 = kc * GPS;
+        const uint16_t *src[4] = {p.scales + static_cast<size_t>(r0) * p.groups + g0,
+                                  p.biases + static_cast<size_t>(r0) * p.groups + g0,
+                                  p.scales + static_cast<size_t>(r1) * p.groups + g0,
+                                  p.biases + static_cast<size_t>(r1) * p.groups + g0};
+        if (p.vec_sb) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if constexpr (SBW == 1) {
+                    dst[i][0] = __ldg(reinterpret_cast<const uint32_t *>(src[i]));
+                } else if constexpr (SBW == 2) {
+                    const uint2 v = __ldg(reinterpret_cast<const uint2 *>(src[i]));
+                    dst[i][0] = v.x, dst[i][1] = v.y;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < SBW / 4; ++j) {
+                        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(src[i]) + j);
+                        dst[i][4 * j] = v.x, dst[i][4 * j + 1] = v.y, dst[i][4 * j + 2] = v.z, dst[i][4 * j + 3] = v.w;
+                    }
+                }
+            }
+        } else {
+            const uint32_t avail = p.groups - g0;  // groups left in the row
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < SBW; ++j) {
+                    const uint32_t lo = 2u * j < avail ? __ldg(src[i] + 2 * j) : 0u;
+                    const uint32_t hi = 2u * j + 1u < avail ? __ldg(src[i] + 2 * j + 1) : 0u;
+                    dst[i][j] = lo | (hi << 16);
+                }
+        }
+    };
+    auto sb_get = [&](const uint32_t (&src)[4][SBW], int which, int gl) -> float {
+        const uint32_t wv = src[which][gl >> 1];
+        return decode_sb(static_cast<uint16_t>((gl & 1) ? (wv >> 16) : (wv & 0xFFFFu)), p.sdtype);
+    };
 
-    for (uint32_t gi = g_begin; gi < g_end; gi += U) {
-        uint32_t nxt0[U][WPT], nxt1[U][WPT];
-        uint16_t nsb[U][4];
-        if (gi + U < g_end) load_batch(gi + U, nxt0, nxt1, nsb);
+    if (u_begin < u_end) load_sb(u_begin, sb_cur);  // weights: legal before the dependency wait
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    uint32_t consumed = 0;
+    for (uint32_t u = u_begin; u < u_end; ++u, ++consumed) {
+        const uint32_t stage = consumed % kStages;
+        const uint32_t rg = u / p.chunks, kc = u - rg * p.chunks;
+        if (u + 1u < u_end) load_sb(u + 1u, sb_nxt);
+
+        if (!mbar_wait(smem_u32(&s_full[stage]), (consumed / kStages) & 1u, p.error_word, 0x2u)) return;
+
+        const uint32_t off = kc * kChunkBytes;
+        const uint32_t bytes = min(static_cast<uint32_t>(kChunkBytes), p.row_bytes - off);
+        const uint32_t ngroups = bytes / GB;
+        const uint32_t srow0 = ring + stage * kStageBytes + (warp * 16u + wr) * kPanelBytes;
+        const uint32_t srow1 = srow0 + 8u * kPanelBytes;
 
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            if (gi + u < g_end) {
+        for (int gl = 0; gl < GPS; ++gl) {
+            if (static_cast<uint32_t>(gl) < ngroups) {
+                uint32_t wa[WPT], wb[WPT];
+                {
+                    const uint32_t pnl = gl / GPP;
+                    const uint32_t ob = (gl % GPP) * GB + t * LW;  // byte offset of the lane's piece in the panel row
+                    lds_words<WPT>(srow0 + pnl * kPanelSize, ob >> 4, ob & 15u, wr, wa);
+                    lds_words<WPT>(srow1 + pnl * kPanelSize, ob >> 4, ob & 15u, wr, wb);
+                }
                 float acc[MT][4], xs[MT][4];
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) acc[mt][i] = xs[mt][i] = 0.f;
-
+                const uint32_t kx0 = (kc * GPS + gl) * p.group + t * LW * XPB;
 #pragma unroll
                 for (int j = 0; j < WPT; ++j) {
-                    const uint32_t kx = (gi + u) * p.group + (t * LW + 4 * j) * XPB;
-                    const uint32_t wa = cur0[u][j], wb = cur1[u][j];
                     uint32_t pa[4], pb[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        pa[i] = ((wa >> (4 * i)) & kNibMask) | kMagic128;
-                        pb[i] = ((wb >> (4 * i)) & kNibMask) | kMagic128;
+                        pa[i] = ((wa[j] >> (4 * i)) & kNibMask) | kMagic128;
+                        pb[i] = ((wb[j] >> (4 * i)) & kNibMask) | kMagic128;
                     }
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
                         const uint32_t m = mt * 8 + g;
                         uint32_t xh[4], xl[4];
-                        load_x_frags<BITS, XF32>(xbase + static_cast<size_t>(m) * p.K * x_elt, kx, m < p.M, xh, xl);
+                        load_x_frags<BITS, XF32>(xbase + static_cast<size_t>(m) * p.K * x_elt, kx0 + 4 * j * XPB,
+                                                 m < p.M, xh, xl);
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
                             // group sums of x: all-ones A (for 8-bit, only the low-nibble slots)
                             mma_bf16_16816(xs[mt], kOnesBf16, kOnesBf16, BITS == 4 ? kOnesBf16 : 0u,
                                            BITS == 4 ? kOnesBf16 : 0u, xh[2 * h], xh[2 * h + 1]);
-                            mma_bf16_16816(acc[mt], pa[2 * h], pb[2 * h], pa[2 * h + 1], pb[2 * h + 1],
-                                           xh[2 * h], xh[2 * h + 1]);
+                            mma_bf16_16816(acc[mt], pa[2 * h], pb[2 * h], pa[2 * h + 1], pb[2 * h + 1], xh[2 * h],
+                                           xh[2 * h + 1]);
                             if constexpr (XF32) {
                                 mma_bf16_16816(xs[mt], kOnesBf16, kOnesBf16, BITS == 4 ? kOnesBf16 : 0u,
                                                BITS == 4 ? kOnesBf16 : 0u, xl[2 * h], xl[2 * h + 1]);
-                                mma_bf16_16816(acc[mt], pa[2 * h], pb[2 * h], pa[2 * h + 1], pb[2 * h + 1],
-                                               xl[2 * h], xl[2 * h + 1]);
+                                mma_bf16_16816(acc[mt], pa[2 * h], pb[2 * h], pa[2 * h + 1], pb[2 * h + 1], xl[2 * h],
+                                               xl[2 * h + 1]);
                             }
                         }
                     }
                 }
-                const float s0 = decode_sb(csb[u][0], p.sdtype), b0 = decode_sb(csb[u][1], p.sdtype);
-                const float s1 = decode_sb(csb[u][2], p.sdtype), b1 = decode_sb(csb[u][3], p.sdtype);
+                const float s0 = sb_get(sb_cur, 0, gl), b0 = sb_get(sb_cur, 1, gl);
+                const float s1 = sb_get(sb_cur, 2, gl), b1 = sb_get(sb_cur, 3, gl);
                 const float b0o = fmaf(-OFF, s0, b0), b1o = fmaf(-OFF, s1, b1);
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
@@ -319,69 +481,80 @@ gaf_gemv_mma_kernel(const GemvParams p) {
                 }
             }
         }
-        if (gi + U < g_end) {
+        // this warp is done with the stage
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&s_empty[stage]));
+
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
+        for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < WPT; ++j) cur0[u][j] = nxt0[u][j], cur1[u][j] = nxt1[u][j];
+            for (int j = 0; j < SBW; ++j) sb_cur[i][j] = sb_nxt[i][j];
+
+        // ---- end of this CTA's share of the row group: write y or park a partial ----
+        const bool last_of_rg = (kc + 1u == p.chunks) || (u + 1u == u_end);
+        if (last_of_rg) {
+            const uint32_t rg_first = rg * p.chunks, rg_last = rg_first + p.chunks - 1u;
+            const uint32_t n0 = rg * kRows + warp * 16u + wr, n1 = n0 + 8u;
+            auto store = [&](uint32_t m, uint32_t n, float val) {
+                if (m < p.M && n < p.N) {
+                    if constexpr (XF32)
+                        static_cast<float *>(p.y)[static_cast<size_t>(m) * p.N + n] = val;
+                    else
+                        static_cast<__nv_bfloat16 *>(p.y)[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(val);
+                }
+            };
+            if (u_begin <= rg_first && rg_last < u_end) {
+                // this CTA saw every chunk of the row group
 #pragma unroll
-                for (int i = 0; i < 4; ++i) csb[u][i] = nsb[u][i];
+                for (int mt = 0; mt < MT; ++mt) {
+                    store(mt * 8 + 2 * t, n0, yacc[mt][0]);
+                    store(mt * 8 + 2 * t + 1, n0, yacc[mt][1]);
+                    store(mt * 8 + 2 * t, n1, yacc[mt][2]);
+                    store(mt * 8 + 2 * t + 1, n1, yacc[mt][3]);
+                }
+            } else {
+                const uint32_t first_cta = unit_owner(rg_first, p.units, gridDim.x);
+                const uint32_t last_cta = unit_owner(rg_last, p.units, gridDim.x);
+                const uint32_t slots = last_cta - first_cta + 1u;
+                const uint32_t slot = blockIdx.x - first_cta;
+                // slot layout [128 rows][MT*8] so that this lane's values are 8-byte pairs
+                float *base = p.partials + (static_cast<size_t>(rg) * p.max_slots + slot) * (kRows * MT * 8);
+                const uint32_t r0 = warp * 16u + wr, r1 = r0 + 8u;
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    *reinterpret_cast<float2 *>(base + r0 * (MT * 8) + mt * 8 + 2 * t) = make_float2(yacc[mt][0], yacc[mt][1]);
+                    *reinterpret_cast<float2 *>(base + r1 * (MT * 8) + mt * 8 + 2 * t) = make_float2(yacc[mt][2], yacc[mt][3]);
+                }
+                __threadfence();
+                __syncwarp();
+                unsigned int ticket = 0;
+                if (lane == 0) ticket = atomicAdd(&p.counters[rg * kConsumerWarps + warp], 1u);
+                ticket = __shfl_sync(0xFFFFFFFFu, ticket, 0);
+                if (ticket == slots - 1u) {
+                    __threadfence();
+                    const float *all = p.partials + static_cast<size_t>(rg) * p.max_slots * (kRows * MT * 8);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        float2 a = make_float2(0.f, 0.f), b = make_float2(0.f, 0.f);
+                        for (uint32_t sidx = 0; sidx < slots; ++sidx) {  // fixed order: reproducible sums
+                            const float *sp = all + static_cast<size_t>(sidx) * (kRows * MT * 8);
+                            const float2 va = __ldcg(reinterpret_cast<const float2 *>(sp + r0 * (MT * 8) + mt * 8 + 2 * t));
+                            const float2 vb = __ldcg(reinterpret_cast<const float2 *>(sp + r1 * (MT * 8) + mt * 8 + 2 * t));
+                            a.x += va.x, a.y += va.y, b.x += vb.x, b.y += vb.y;
+                        }
+                        store(mt * 8 + 2 * t, n0, a.x);
+                        store(mt * 8 + 2 * t + 1, n0, a.y);
+                        store(mt * 8 + 2 * t, n1, b.x);
+                        store(mt * 8 + 2 * t + 1, n1, b.y);
+                    }
+                    if (lane == 0) p.counters[rg * kConsumerWarps + warp] = 0u;  // ready for the next launch
+                }
             }
-        }
-    }
-
-    // ---- reduce the NW warp slices through shared memory ----
-    __shared__ float red[NW][MROWS][17];
-    __shared__ unsigned int s_last;
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-        red[warp][mt * 8 + 2 * t][g] = yacc[mt][0];
-        red[warp][mt * 8 + 2 * t + 1][g] = yacc[mt][1];
-        red[warp][mt * 8 + 2 * t][g + 8] = yacc[mt][2];
-        red[warp][mt * 8 + 2 * t + 1][g + 8] = yacc[mt][3];
-    }
-    __syncthreads();
-
-    const int tid = threadIdx.x;
-    const bool owner = tid < MROWS * 16;
-    const uint32_t m = tid >> 4, nl = tid & 15;
-    const uint32_t n = rb * 16u + nl;
-    float v = 0.f;
-    if (owner) {
+            for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int w = 0; w < NW; ++w) v += red[w][m][nl];
-    }
-
-    auto store = [&](float val) {
-        if (m < p.M && n < p.N) {
-            if constexpr (XF32)
-                static_cast<float *>(p.y)[static_cast<size_t>(m) * p.N + n] = val;
-            else
-                static_cast<__nv_bfloat16 *>(p.y)[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(val);
+                for (int i = 0; i < 4; ++i) yacc[mt][i] = 0.f;
         }
-    };
-
-    if (p.ks == 1) {
-        if (owner) store(v);
-        return;
-    }
-
-    // ---- reduce the gridDim.y CTAs through the fp32 scratch; the last CTA to
-    // arrive at this row block's counter sums all partials in slice order ----
-    if (owner) p.partials[(static_cast<size_t>(blockIdx.y) * MROWS + m) * p.n_pad + n] = v;
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) s_last = (atomicAdd(&p.counters[rb], 1u) == p.ks - 1u) ? 1u : 0u;
-    __syncthreads();
-    if (s_last) {
-        __threadfence();
-        if (owner) {
-            float sum = 0.f;
-            for (uint32_t k = 0; k < p.ks; ++k)
-                sum += __ldcg(&p.partials[(static_cast<size_t>(k) * MROWS + m) * p.n_pad + n]);
-            store(sum);
-        }
-        if (tid == 0) p.counters[rb] = 0u;  // ready for the next launch
     }
 }
 
@@ -472,73 +645,103 @@ gaf_dequant_f32_kernel(const uint8_t *packed, const uint16_t *scales, const uint
 // host-side dispatch
 // ---------------------------------------------------------------------------
 struct GemvPlan {
-    int nw;
-    uint32_t ks;
-    uint32_t gpw;
-    uint32_t rbs;
+    uint32_t rgs, chunks, units, ctas, max_slots;
 };
-
-constexpr uint32_t kMaxKs = 32;
 
 GemvPlan plan_gemv(const WeightView &w, const GemvTuning &tune, int sm_count) {
     GemvPlan pl;
-    pl.rbs = (w.N + 15u) / 16u;
-    const uint32_t target = tune.slices_target > 0 ? static_cast<uint32_t>(tune.slices_target)
-                                                   : static_cast<uint32_t>(sm_count) * 32u;
-    uint32_t s_total = (target + pl.rbs - 1u) / pl.rbs;
-    if (s_total < 1u) s_total = 1u;
-    if (s_total > w.groups) s_total = w.groups;
-    int nw = tune.warps > 0 ? tune.warps : (s_total > 4u ? 8 : 4);
-    if (nw != 4 && nw != 8) nw = 8;
-    pl.nw = nw;
-    uint32_t ks = (s_total + nw - 1u) / nw;
-    if (ks > kMaxKs) ks = kMaxKs;
-    pl.gpw = (w.groups + ks * nw - 1u) / (ks * nw);
-    pl.ks = (w.groups + pl.gpw * nw - 1u) / (pl.gpw * nw);
+    pl.rgs = (w.N + kRows - 1u) / kRows;
+    pl.chunks = (w.row_bytes + kChunkBytes - 1u) / kChunkBytes;
+    pl.units = pl.rgs * pl.chunks;
+    uint32_t ctas = tune.ctas > 0 ? static_cast<uint32_t>(tune.ctas) : static_cast<uint32_t>(sm_count);
+    if (ctas > pl.units) ctas = pl.units;
+    if (ctas < 1u) ctas = 1u;
+    pl.ctas = ctas;
+    // a row group of `chunks` units is cut by at most ceil(chunks / q) + 1 contiguous ranges of >= q units
+    const uint32_t q = pl.units / ctas;
+    pl.max_slots = (pl.chunks + q - 1u) / q + 1u;
     return pl;
 }
 
-template <int GB, int BITS, int MT, bool XF32, int NW>
-cudaError_t launch_gemv(const GemvParams &p, dim3 grid, bool pdl, cudaStream_t stream) {
+template <int GB, int BITS, int MT, bool XF32>
+cudaError_t launch_stream(const GemvParams &p, const CUtensorMap &tmap, uint32_t ctas, bool pdl, cudaStream_t stream) {
+    auto kern = gaf_gemv_stream_kernel<GB, BITS, MT, XF32>;
+    static bool configured = false;  // per instantiation; the attribute belongs to the function, not the stream
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(NW * 32);
-    cfg.dynamicSmemBytes = 0;
+    cfg.gridDim = dim3(ctas);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gaf_gemv_mma_kernel<GB, BITS, MT, XF32, NW>, p);
+    return cudaLaunchKernelEx(&cfg, kern, p, tmap);
 }
 
 template <int GB, int BITS>
-cudaError_t dispatch_gemv(const GemvParams &p, dim3 grid, int mt, bool xf32, int nw, bool pdl,
-                          cudaStream_t stream) {
-#define TGAF_CASE(MTv, XFv, NWv) \
-    if (mt == MTv && xf32 == XFv && nw == NWv) return launch_gemv<GB, BITS, MTv, XFv, NWv>(p, grid, pdl, stream);
-    TGAF_CASE(1, false, 4)
-    TGAF_CASE(1, false, 8)
-    TGAF_CASE(2, false, 4)
-    TGAF_CASE(2, false, 8)
-    TGAF_CASE(1, true, 4)
-    TGAF_CASE(1, true, 8)
-    TGAF_CASE(2, true, 4)
-    TGAF_CASE(2, true, 8)
-#undef TGAF_CASE
+cudaError_t dispatch_stream(const GemvParams &p, const CUtensorMap &tmap, uint32_t ctas, int mt, bool xf32, bool pdl,
+                            cudaStream_t stream) {
+    if (mt == 1 && !xf32) return launch_stream<GB, BITS, 1, false>(p, tmap, ctas, pdl, stream);
+    if (mt == 2 && !xf32) return launch_stream<GB, BITS, 2, false>(p, tmap, ctas, pdl, stream);
+    if (mt == 1 && xf32) return launch_stream<GB, BITS, 1, true>(p, tmap, ctas, pdl, stream);
+    if (mt == 2 && xf32) return launch_stream<GB, BITS, 2, true>(p, tmap, ctas, pdl, stream);
     return cudaErrorNotSupported;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
 }
 
 }  // namespace
 
+// Tensor map of the packed matrix as bytes [N][row_bytes], tile 128 rows x 128 bytes, 128-byte swizzle.
+cudaError_t make_packed_tmap(const WeightView &w, CUtensorMap *out) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return cudaErrorNotSupported;
+    if (reinterpret_cast<uintptr_t>(w.packed) % 16u != 0 || w.row_bytes % 16u != 0) return cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {w.row_bytes, w.N};
+    const cuuint64_t strides[1] = {w.row_bytes};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kPanelBytes), static_cast<cuuint32_t>(kRows)};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(w.packed), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+void attach_packed_tmap(WeightView &w) {
+    w.has_tmap = make_packed_tmap(w, &w.tmap) == cudaSuccess;
+}
+
 bool gemv_mma_eligible(const WeightView &w, const void *x, const void *y, bool x_f32) {
+    if (!w.has_tmap) return false;
     const uint32_t gb = w.group * w.bits / 8u;
-    if (gb != 16u && gb != 32u && gb != 64u && gb != 128u) return false;
+    // group sizes 32 / 64 / 128 of either code width (what the converter produces)
+    if (w.bits == 4 ? (gb != 16u && gb != 32u && gb != 64u) : (gb != 32u && gb != 64u && gb != 128u)) return false;
     if (w.row_bytes != w.K * w.bits / 8u) return false;
-    // each lane reads gb/4 bytes at a time (up to 16): row starts and rows must keep that alignment
-    const uint32_t lw = gb / 4u > 16u ? 16u : gb / 4u;
-    if (reinterpret_cast<uintptr_t>(w.packed) % lw != 0 || w.row_bytes % lw != 0) return false;
+    // TMA needs a 16-byte aligned base and row pitch
+    if (reinterpret_cast<uintptr_t>(w.packed) % 16u != 0 || w.row_bytes % 16u != 0) return false;
     if (reinterpret_cast<uintptr_t>(w.scales) % 2u != 0 || reinterpret_cast<uintptr_t>(w.biases) % 2u != 0) return false;
     // activation rows are read 16 bytes at a time
     const size_t xrow = static_cast<size_t>(w.K) * (x_f32 ? 4u : 2u);
@@ -549,21 +752,26 @@ bool gemv_mma_eligible(const WeightView &w, const void *x, const void *y, bool x
 
 size_t gemv_mma_scratch_bytes(const WeightView &w, uint32_t M, const GemvTuning &tune, int sm_count) {
     const GemvPlan pl = plan_gemv(w, tune, sm_count);
-    if (pl.ks <= 1u) return 0;
     const uint32_t mrows = M <= 8u ? 8u : 16u;
-    return static_cast<size_t>(pl.ks) * mrows * (static_cast<size_t>(pl.rbs) * 16u) * sizeof(float);
+    return static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * mrows * sizeof(float);
+}
+
+size_t gemv_mma_counter_count(const WeightView &w) {
+    return static_cast<size_t>((w.N + kRows - 1u) / kRows) * kConsumerWarps;
 }
 
 cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bool x_f32,
-                     const Scratch &scratch, const GemvTuning &tune, cudaStream_t stream, int sm_count) {
+                     const Scratch &scratch, const GemvTuning &tune, cudaStream_t stream, int sm_count,
+                     unsigned int *d_error_word) {
     if (M == 0 || M > 16u) return cudaErrorNotSupported;
     if (!gemv_mma_eligible(w, x, y, x_f32)) return cudaErrorNotSupported;
     const GemvPlan pl = plan_gemv(w, tune, sm_count);
     const int mt = M <= 8u ? 1 : 2;
-    if (pl.ks > 1u) {
-        const size_t need = static_cast<size_t>(pl.ks) * (mt * 8) * (static_cast<size_t>(pl.rbs) * 16u) * sizeof(float);
-        if (need > scratch.partial_bytes || pl.rbs > scratch.counter_count) return cudaErrorMemoryAllocation;
-    }
+    const size_t need = static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * (mt * 8) * sizeof(float);
+    if (need > scratch.partial_bytes || gemv_mma_counter_count(w) > scratch.counter_count)
+        return cudaErrorMemoryAllocation;
+    const uint32_t gb = w.group * w.bits / 8u;
+    const uint32_t gps = kChunkBytes / gb;
     GemvParams p;
     p.packed = w.packed;
     p.scales = w.scales;
@@ -572,27 +780,35 @@ cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bo
     p.y = y;
     p.partials = scratch.partials;
     p.counters = scratch.counters;
+    p.error_word = d_error_word;
     p.N = w.N;
     p.K = w.K;
     p.M = M;
     p.groups = w.groups;
     p.row_bytes = w.row_bytes;
     p.group = w.group;
-    p.gpw = pl.gpw;
-    p.ks = pl.ks;
     p.sdtype = w.sdtype;
-    p.n_pad = pl.rbs * 16u;
-    const dim3 grid(pl.rbs, pl.ks);
+    p.chunks = pl.chunks;
+    p.units = pl.units;
+    p.max_slots = pl.max_slots;
+    // one aligned vector load per row and unit: every unit must be whole and every row start aligned
+    const size_t sbw_bytes = static_cast<size_t>(gps) * 2u;
+    p.vec_sb = (w.groups % gps == 0 && reinterpret_cast<uintptr_t>(w.scales) % sbw_bytes == 0 &&
+                reinterpret_cast<uintptr_t>(w.biases) % sbw_bytes == 0 && sbw_bytes <= 16u)
+                   ? 1u
+                   : 0u;
+    if (sbw_bytes > 16u)  // 32-byte rows of scales: two 16-byte loads, 16-byte alignment is enough
+        p.vec_sb = (w.groups % gps == 0 && reinterpret_cast<uintptr_t>(w.scales) % 16u == 0 &&
+                    reinterpret_cast<uintptr_t>(w.biases) % 16u == 0) ? 1u : 0u;
     const bool pdl = tune.pdl != 0;
-    const uint32_t gb = w.group * w.bits / 8u;
     if (w.bits == 4) {
-        if (gb == 16u) return dispatch_gemv<16, 4>(p, grid, mt, x_f32, pl.nw, pdl, stream);
-        if (gb == 32u) return dispatch_gemv<32, 4>(p, grid, mt, x_f32, pl.nw, pdl, stream);
-        if (gb == 64u) return dispatch_gemv<64, 4>(p, grid, mt, x_f32, pl.nw, pdl, stream);
+        if (gb == 16u) return dispatch_stream<16, 4>(p, w.tmap, pl.ctas, mt, x_f32, pdl, stream);
+        if (gb == 32u) return dispatch_stream<32, 4>(p, w.tmap, pl.ctas, mt, x_f32, pdl, stream);
+        if (gb == 64u) return dispatch_stream<64, 4>(p, w.tmap, pl.ctas, mt, x_f32, pdl, stream);
     } else {
-        if (gb == 32u) return dispatch_gemv<32, 8>(p, grid, mt, x_f32, pl.nw, pdl, stream);
-        if (gb == 64u) return dispatch_gemv<64, 8>(p, grid, mt, x_f32, pl.nw, pdl, stream);
-        if (gb == 128u) return dispatch_gemv<128, 8>(p, grid, mt, x_f32, pl.nw, pdl, stream);
+        if (gb == 32u) return dispatch_stream<32, 8>(p, w.tmap, pl.ctas, mt, x_f32, pdl, stream);
+        if (gb == 64u) return dispatch_stream<64, 8>(p, w.tmap, pl.ctas, mt, x_f32, pdl, stream);
+        if (gb == 128u) return dispatch_stream<128, 8>(p, w.tmap, pl.ctas, mt, x_f32, pdl, stream);
     }
     return cudaErrorNotSupported;
 }

@@ -2,6 +2,7 @@
 // Not installed; the public surface is include/talu_gaf.h.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -21,19 +22,20 @@ struct WeightView {
     uint32_t sdtype;         // 0 = f16, 1 = bf16
     uint32_t row_bytes;      // K * bits / 8
     uint32_t groups;         // K / group
+    CUtensorMap tmap;        // packed matrix as bytes [N][row_bytes] for the streaming GEMV
+    bool has_tmap;           // false: base / pitch not 16-byte aligned (generic kernel only)
 };
 
 // Split-K scratch owned by a context.
 struct Scratch {
-    float *partials;          // [slices][m_pad][n_pad]
+    float *partials;          // [row group][slot][128][8 or 16]
     size_t partial_bytes;
-    unsigned int *counters;   // one per 16-row block, self-resetting
+    unsigned int *counters;   // [row group][8], self-resetting
     size_t counter_count;
 };
 
 struct GemvTuning {
-    int slices_target;  // wanted number of warp-slices over the whole grid (0 = default)
-    int warps;          // warps per CTA (0 = default)
+    int ctas;           // persistent CTAs of the streaming GEMV (0 = one per SM)
     int pdl;            // launch with programmatic stream serialization
     int force_generic;  // use the shape-agnostic kernel even when the fast path applies
 };
@@ -44,10 +46,14 @@ struct GemvTuning {
 // for the fast path (the caller then uses gemv_generic).
 cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bool x_f32,
                      const Scratch &scratch, const GemvTuning &tune, cudaStream_t stream,
-                     int sm_count);
+                     int sm_count, unsigned int *d_error_word);
 bool gemv_mma_eligible(const WeightView &w, const void *x, const void *y, bool x_f32);
-// scratch bytes the fast path needs for this problem (0 when it does not split K across CTAs)
+// fills w.tmap / w.has_tmap from the other fields
+void attach_packed_tmap(WeightView &w);
+cudaError_t make_packed_tmap(const WeightView &w, CUtensorMap *out);
+// scratch the fast path needs for this problem
 size_t gemv_mma_scratch_bytes(const WeightView &w, uint32_t M, const GemvTuning &tune, int sm_count);
+size_t gemv_mma_counter_count(const WeightView &w);
 
 // Any shape the reference accepts, any M.  f32 arithmetic, per-element dequant.
 cudaError_t gemv_generic(const WeightView &w, const void *x, void *y, uint32_t M, bool x_f32,

@@ -34,6 +34,17 @@ class GafError(RuntimeError):
         return self.status == _STATUS_INVALID_ARGUMENT
 
 
+_CUDA_STREAM_LEGACY = 1  # cudaStreamLegacy: the handle of the default stream, usable where NULL means "none"
+
+
+def _torch_current_stream(device: int) -> int:
+    import torch
+    if not torch.cuda.is_available():
+        return 0
+    h = torch.cuda.current_stream(device).cuda_stream
+    return h if h else _CUDA_STREAM_LEGACY
+
+
 def _vpw(bits: int) -> int:
     return 8 if bits == 4 else 4
 
@@ -41,9 +52,14 @@ def _vpw(bits: int) -> int:
 class Context:
     """One device + one stream (tgaf_ctx).  Not re-entrant."""
 
-    def __init__(self, device: int = 0, stream: int | None = None):
+    def __init__(self, device: int = 0, stream: int | None = None, own_stream: bool = False):
+        """`stream`: a cudaStream_t handle.  Default: torch's current stream on `device`, so
+        that calls are ordered with the torch ops around them; own_stream=True asks the
+        library for a private non-blocking stream instead."""
         self._lib = _capi.load()
         h = C.c_void_p()
+        if stream is None and not own_stream:
+            stream = _torch_current_stream(device)
         st = self._lib.tgaf_ctx_create(int(device), C.c_void_p(stream or 0), C.byref(h))
         if st != 0:
             raise GafError(st, "tgaf_ctx_create failed (is a B200 visible?)")
@@ -55,7 +71,7 @@ class Context:
             raise GafError(st, self._lib.tgaf_last_error(self._h).decode())
 
     def set_stream(self, stream: int) -> None:
-        self._check(self._lib.tgaf_ctx_set_stream(self._h, C.c_void_p(stream)))
+        self._check(self._lib.tgaf_ctx_set_stream(self._h, C.c_void_p(stream or _CUDA_STREAM_LEGACY)))
 
     def set_option(self, name: str, value: int) -> None:
         self._check(self._lib.tgaf_ctx_set_option(self._h, name.encode(), int(value)))
