@@ -69,7 +69,8 @@ constexpr uint32_t kNibMask = 0x000F000Fu;
 constexpr int kRows = 128;        // weight rows per unit (8 consumer warps x 16)
 constexpr int kChunkBytes = 256;  // packed bytes per row per unit
 constexpr int kStages = 3;
-constexpr int kConsumerWarps = 8;
+constexpr int kRowBlocks = 8;      // 16-row blocks per unit
+constexpr int kConsumerWarps = 16;  // two K halves x eight row blocks
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr uint32_t kWaitLimit = 1u << 22;  // polls (with back-off) before a wait gives up
 
@@ -149,23 +150,23 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 }
 
 // Packed words of one lane for one group and row, from a swizzled panel.
-// `row_addr` = shared address of the row (128 bytes), `chunk` = first 16-byte chunk
-// of the lane's piece, `inner` = byte offset inside the chunk, `xr` = row & 7.
+// `addr` = shared address of the lane's first piece (swizzle already applied).
+// Pieces wider than one 16-byte chunk continue in the following chunks, whose
+// positions differ from the first by the XOR of the chunk index with `xr` = row & 7.
 template <int WPT>
-__device__ __forceinline__ void lds_words(uint32_t row_addr, uint32_t chunk, uint32_t inner, uint32_t xr,
-                                          uint32_t (&w)[WPT]) {
+__device__ __forceinline__ void lds_row(uint32_t addr, uint32_t xr, uint32_t (&w)[WPT]) {
     if constexpr (WPT == 1) {
-        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[0]) : "r"(row_addr + ((chunk ^ xr) << 4) + inner));
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[0]) : "r"(addr));
     } else if constexpr (WPT == 2) {
-        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];"
-                     : "=r"(w[0]), "=r"(w[1])
-                     : "r"(row_addr + ((chunk ^ xr) << 4) + inner));
+        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[0]), "=r"(w[1]) : "r"(addr));
+    } else if constexpr (WPT == 4) {
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
     } else {
-#pragma unroll
-        for (int i = 0; i < WPT / 4; ++i)
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                         : "=r"(w[4 * i]), "=r"(w[4 * i + 1]), "=r"(w[4 * i + 2]), "=r"(w[4 * i + 3])
-                         : "r"(row_addr + (((chunk + i) ^ xr) << 4)));
+        // two chunks c and c + 1 with c even: their swizzled positions differ in bit 4 only
+        static_assert(WPT == 8, "unsupported load width");
+        (void)xr;
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "r"(addr ^ 16u));
     }
 }
 
@@ -257,17 +258,29 @@ __device__ __host__ __forceinline__ uint32_t unit_owner(uint32_t u, uint32_t uni
 }
 
 constexpr int kPanelBytes = 128;                       // bytes per row in one TMA tile (the swizzle span)
-constexpr int kPanels = kChunkBytes / kPanelBytes;     // TMA tiles per unit
+constexpr int kPanels = kChunkBytes / kPanelBytes;     // TMA tiles per unit (= K halves, one per warp set)
 constexpr int kPanelSize = kRows * kPanelBytes;        // 16 KB
 constexpr int kStageBytes = kPanels * kPanelSize;      // 32 KB
-constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + slack to align the ring to the swizzle atom
+constexpr int kFragItems = 16;                         // (group, word) pairs per unit: 256 B / 16 B
 
 template <int GB>
 struct StreamGeom {
     static constexpr int GPS = kChunkBytes / GB;   // groups per unit
-    static constexpr int GPP = kPanelBytes / GB;   // groups per panel
+    static constexpr int GPP = kPanelBytes / GB;   // groups per panel = groups per warp and unit
     static constexpr int LW = GB / 4;              // bytes one lane reads per group and row
     static constexpr int WPT = LW / 4;             // packed words per lane per group and row
+};
+
+// shared-memory plan after the ring (all offsets from the 1024-byte aligned ring base)
+template <int MT, bool XF32>
+struct SmemPlan {
+    static constexpr int FRAG_BYTES = kFragItems * MT * (XF32 ? 2 : 1) * 512;  // one unit's activation fragments
+    static constexpr int XS_BYTES = 16 * MT * 8 * 4;                           // group sums [<=16 groups][MT*8]
+    static constexpr int FLUSH_BYTES = kRowBlocks * 32 * MT * 4 * 4;           // K-half exchange at a row-group end
+    static constexpr int OFF_FRAG = kStages * kStageBytes;
+    static constexpr int OFF_XS = OFF_FRAG + 2 * FRAG_BYTES;
+    static constexpr int OFF_FLUSH = OFF_XS + 2 * XS_BYTES;
+    static constexpr int TOTAL = OFF_FLUSH + FLUSH_BYTES + 1024;  // + slack to align the ring
 };
 
 // Row permutation inside a warp's 16 rows: lane group g (= lane / 4) works on row rho(g)
@@ -280,19 +293,26 @@ __device__ __forceinline__ uint32_t rho(uint32_t g) {
     return g;
 }
 
+__device__ __forceinline__ void consumer_barrier() {
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
+}
+
 template <int GB, int BITS, int MT, bool XF32>
 __global__ void __launch_bounds__(kThreads, 1)
 gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap) {
     using Geo = StreamGeom<GB>;
+    using Plan = SmemPlan<MT, XF32>;
     constexpr int GPS = Geo::GPS, GPP = Geo::GPP, LW = Geo::LW, WPT = Geo::WPT;
     constexpr int XPB = 8 / BITS;                          // activations per packed byte
     constexpr float OFF = BITS == 4 ? 128.f : 2176.f;      // what the +128 offsets add per unit of sum(x)
-    constexpr int SBW = GPS * 2 / 4 > 0 ? GPS * 2 / 4 : 1;  // 32-bit words holding one row's scales of a unit
-    static_assert(WPT >= 1 && GPS >= 2, "unsupported group size");
+    constexpr int NF = XF32 ? 2 : 1;                       // fragment sets per activation tile (hi, lo)
+    constexpr int SBW = GPP * 2 / 4 > 0 ? GPP * 2 / 4 : 1;  // 32-bit words holding one row's scales of a warp's groups
+    static_assert(WPT >= 1 && GPP >= 1, "unsupported group size");
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t s_full[kStages];
     __shared__ __align__(8) uint64_t s_empty[kStages];
+    __shared__ volatile uint32_t s_abort;  // a consumer warp gave up a wait: everybody leaves at the next barrier
 
     // the ring starts at a 1024-byte boundary (8 rows x 128 bytes, the swizzle atom)
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -300,6 +320,7 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
     const int warp = threadIdx.x >> 5;
 
     if (threadIdx.x == 0) {
+        s_abort = 0u;
 #pragma unroll
         for (int s = 0; s < kStages; ++s) {
             mbar_init(smem_u32(&s_full[s]), 1);
@@ -346,11 +367,25 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
     }
 
     // --------------------------- consumer warps ---------------------------
+    // warp = kh * 8 + rb: row block rb (16 of the unit's 128 rows), K half kh (one 128-byte panel)
+    const int rb = warp & (kRowBlocks - 1);
+    const int kh = warp / kRowBlocks;
     const int g = lane >> 2;  // activation row inside a tile; accumulator row slot
     const int t = lane & 3;   // quarter of the group this lane holds
     const uint32_t wr = rho<LW>(g);  // weight row (of the warp's 16) behind accumulator rows g and g + 8
     const uint8_t *xbase = static_cast<const uint8_t *>(p.x);
     const size_t x_elt = XF32 ? 4 : 2;
+
+    // shared-memory offsets of this lane's pieces of a panel row, one per group of the panel
+    // (swizzle: 16-byte chunk index XOR (row & 7); rows wr and wr + 8 share the XOR term)
+    uint32_t swz[GPP];
+#pragma unroll
+    for (int q = 0; q < GPP; ++q) {
+        const uint32_t ob = q * GB + t * LW;
+        swz[q] = (rb * 16u + wr) * kPanelBytes + kh * kPanelSize + ((((ob >> 4) ^ wr) & 7u) << 4) + (ob & 15u);
+    }
+    const uint32_t frag_lane = ring + Plan::OFF_FRAG + lane * 16u;
+    const uint32_t xs_lane = ring + Plan::OFF_XS + t * 8u;
 
     float yacc[MT][4];
 #pragma unroll
@@ -358,35 +393,39 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
 #pragma unroll
         for (int i = 0; i < 4; ++i) yacc[mt][i] = 0.f;
 
-    // scales / biases of one unit for this lane's two rows: {s0, b0, s1, b1}[SBW words]
+    // scales / biases of this warp's groups of one unit, for this lane's two rows: {s0, b0, s1, b1}[SBW words]
     uint32_t sb_cur[4][SBW], sb_nxt[4][SBW];
     auto load_sb = [&](uint32_t u, uint32_t (&dst)[4][SBW]) {
         const uint32_t rg = u / p.chunks, kc = u - rg * p.chunks;
-        const uint32_t r0 = min(rg * kRows + warp * 16u + wr, p.N - 1u);
-        const uint32_t r1 = min(rg * kRows + warp * 16u + wr + 8u, p.N - 1u);
-        const uint32_t g0 = kc * GPS;
+        const uint32_t r0 = min(rg * kRows + rb * 16u + wr, p.N - 1u);
+        const uint32_t r1 = min(rg * kRows + rb * 16u + wr + 8u, p.N - 1u);
+        const uint32_t g0 = kc * GPS + kh * GPP;
         const uint16_t *src[4] = {p.scales + static_cast<size_t>(r0) * p.groups + g0,
                                   p.biases + static_cast<size_t>(r0) * p.groups + g0,
                                   p.scales + static_cast<size_t>(r1) * p.groups + g0,
                                   p.biases + static_cast<size_t>(r1) * p.groups + g0};
-        if (p.vec_sb) {
+        if (p.vec_sb && g0 >= p.groups) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < SBW; ++j) dst[i][j] = 0u;
+        } else if (p.vec_sb) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                if constexpr (SBW == 1) {
+                if constexpr (GPP == 1) {
+                    dst[i][0] = __ldg(src[i]);
+                } else if constexpr (SBW == 1) {
                     dst[i][0] = __ldg(reinterpret_cast<const uint32_t *>(src[i]));
                 } else if constexpr (SBW == 2) {
                     const uint2 v = __ldg(reinterpret_cast<const uint2 *>(src[i]));
                     dst[i][0] = v.x, dst[i][1] = v.y;
                 } else {
-#pragma unroll
-                    for (int j = 0; j < SBW / 4; ++j) {
-                        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(src[i]) + j);
-                        dst[i][4 * j] = v.x, dst[i][4 * j + 1] = v.y, dst[i][4 * j + 2] = v.z, dst[i][4 * j + 3] = v.w;
-                    }
+                    const uint4 v = __ldg(reinterpret_cast<const uint4 *>(src[i]));
+                    dst[i][0] = v.x, dst[i][1] = v.y, dst[i][2] = v.z, dst[i][3] = v.w;
                 }
             }
         } else {
-            const uint32_t avail = p.groups - g0;  // groups left in the row
+            const uint32_t avail = g0 < p.groups ? p.groups - g0 : 0u;  // groups left in the row
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -397,44 +436,95 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                 }
         }
     };
-    auto sb_get = [&](const uint32_t (&src)[4][SBW], int which, int gl) -> float {
-        const uint32_t wv = src[which][gl >> 1];
-        return decode_sb(static_cast<uint16_t>((gl & 1) ? (wv >> 16) : (wv & 0xFFFFu)), p.sdtype);
+    auto sb_get = [&](const uint32_t (&src)[4][SBW], int which, int q) -> float {
+        const uint32_t wv = src[which][q >> 1];
+        return decode_sb(static_cast<uint16_t>((q & 1) ? (wv >> 16) : (wv & 0xFFFFu)), p.sdtype);
+    };
+
+    // Activation fragments and group sums of one unit, built once per CTA: warp w < GPS takes group w.
+    // frag item (group gl, word j, tile mt, set f) lives at ((gl*WPT + j)*MT + mt)*NF + f, 512 bytes each.
+    auto prep_unit = [&](uint32_t u, uint32_t buf) {
+        if (warp >= GPS) return;
+        const uint32_t kc = u % p.chunks;
+        const uint32_t gi = kc * GPS + warp;
+        float xs[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) xs[mt][i] = 0.f;
+#pragma unroll
+        for (int j = 0; j < WPT; ++j) {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                const uint32_t m = mt * 8 + g;
+                uint32_t xh[4], xl[4];
+                const uint32_t kx = gi * p.group + (t * LW + 4 * j) * XPB;
+                load_x_frags<BITS, XF32>(xbase + static_cast<size_t>(m) * p.K * x_elt, kx, m < p.M && gi < p.groups,
+                                         xh, xl);
+                const uint32_t item = ((warp * WPT + j) * MT + mt) * NF;
+                const uint32_t dst = frag_lane + buf * Plan::FRAG_BYTES + item * 512u;
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(xh[0]), "r"(xh[1]), "r"(xh[2]),
+                             "r"(xh[3])
+                             : "memory");
+                if constexpr (XF32)
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + 512u), "r"(xl[0]), "r"(xl[1]),
+                                 "r"(xl[2]), "r"(xl[3])
+                                 : "memory");
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    // group sums of x: all-ones A (for 8-bit, only the low-nibble slots)
+                    mma_bf16_16816(xs[mt], kOnesBf16, kOnesBf16, BITS == 4 ? kOnesBf16 : 0u, BITS == 4 ? kOnesBf16 : 0u,
+                                   xh[2 * h], xh[2 * h + 1]);
+                    if constexpr (XF32)
+                        mma_bf16_16816(xs[mt], kOnesBf16, kOnesBf16, BITS == 4 ? kOnesBf16 : 0u,
+                                       BITS == 4 ? kOnesBf16 : 0u, xl[2 * h], xl[2 * h + 1]);
+                }
+            }
+        }
+        if (g == 0) {  // every accumulator row holds the same sums
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                const uint32_t dst = xs_lane + buf * Plan::XS_BYTES + (warp * MT * 8 + mt * 8) * 4u;
+                asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(dst), "f"(xs[mt][0]), "f"(xs[mt][1]) : "memory");
+            }
+        }
     };
 
     if (u_begin < u_end) load_sb(u_begin, sb_cur);  // weights: legal before the dependency wait
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (u_begin < u_end) prep_unit(u_begin, 0u);
+    consumer_barrier();
 
     uint32_t consumed = 0;
     for (uint32_t u = u_begin; u < u_end; ++u, ++consumed) {
         const uint32_t stage = consumed % kStages;
+        const uint32_t buf = consumed & 1u;
         const uint32_t rg = u / p.chunks, kc = u - rg * p.chunks;
         if (u + 1u < u_end) load_sb(u + 1u, sb_nxt);
 
-        if (!mbar_wait(smem_u32(&s_full[stage]), (consumed / kStages) & 1u, p.error_word, 0x2u)) return;
+        // A warp must not leave before the consumer barrier below (the others would wait for it
+        // forever): on a timeout it raises s_abort and skips the work of this unit.
+        const bool landed = mbar_wait(smem_u32(&s_full[stage]), (consumed / kStages) & 1u, p.error_word, 0x2u);
+        if (!landed) s_abort = 1u;
 
-        const uint32_t off = kc * kChunkBytes;
-        const uint32_t bytes = min(static_cast<uint32_t>(kChunkBytes), p.row_bytes - off);
-        const uint32_t ngroups = bytes / GB;
-        const uint32_t srow0 = ring + stage * kStageBytes + (warp * 16u + wr) * kPanelBytes;
-        const uint32_t srow1 = srow0 + 8u * kPanelBytes;
+        const uint32_t off = kc * kChunkBytes + kh * kPanelBytes;
+        const uint32_t bytes = off < p.row_bytes ? min(static_cast<uint32_t>(kPanelBytes), p.row_bytes - off) : 0u;
+        const uint32_t ngroups = bytes / GB;  // groups of this warp's panel that exist
+        const uint32_t stage_base = ring + stage * kStageBytes;
+        const uint32_t fragb = frag_lane + buf * Plan::FRAG_BYTES + (kh * GPP * WPT * MT * NF) * 512u;
+        const uint32_t xsb = xs_lane + buf * Plan::XS_BYTES + (kh * GPP * MT * 8) * 4u;
 
 #pragma unroll
-        for (int gl = 0; gl < GPS; ++gl) {
-            if (static_cast<uint32_t>(gl) < ngroups) {
+        for (int q = 0; q < GPP; ++q) {
+            if (landed && static_cast<uint32_t>(q) < ngroups) {
                 uint32_t wa[WPT], wb[WPT];
-                {
-                    const uint32_t pnl = gl / GPP;
-                    const uint32_t ob = (gl % GPP) * GB + t * LW;  // byte offset of the lane's piece in the panel row
-                    lds_words<WPT>(srow0 + pnl * kPanelSize, ob >> 4, ob & 15u, wr, wa);
-                    lds_words<WPT>(srow1 + pnl * kPanelSize, ob >> 4, ob & 15u, wr, wb);
-                }
-                float acc[MT][4], xs[MT][4];
+                lds_row<WPT>(stage_base + swz[q], wr, wa);
+                lds_row<WPT>(stage_base + swz[q] + 8u * kPanelBytes, wr, wb);
+                float acc[MT][4];
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[mt][i] = xs[mt][i] = 0.f;
-                const uint32_t kx0 = (kc * GPS + gl) * p.group + t * LW * XPB;
+                    for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
 #pragma unroll
                 for (int j = 0; j < WPT; ++j) {
                     uint32_t pa[4], pb[4];
@@ -445,39 +535,34 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                     }
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
-                        const uint32_t m = mt * 8 + g;
-                        uint32_t xh[4], xl[4];
-                        load_x_frags<BITS, XF32>(xbase + static_cast<size_t>(m) * p.K * x_elt, kx0 + 4 * j * XPB,
-                                                 m < p.M, xh, xl);
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            // group sums of x: all-ones A (for 8-bit, only the low-nibble slots)
-                            mma_bf16_16816(xs[mt], kOnesBf16, kOnesBf16, BITS == 4 ? kOnesBf16 : 0u,
-                                           BITS == 4 ? kOnesBf16 : 0u, xh[2 * h], xh[2 * h + 1]);
-                            mma_bf16_16816(acc[mt], pa[2 * h], pb[2 * h], pa[2 * h + 1], pb[2 * h + 1], xh[2 * h],
-                                           xh[2 * h + 1]);
-                            if constexpr (XF32) {
-                                mma_bf16_16816(xs[mt], kOnesBf16, kOnesBf16, BITS == 4 ? kOnesBf16 : 0u,
-                                               BITS == 4 ? kOnesBf16 : 0u, xl[2 * h], xl[2 * h + 1]);
-                                mma_bf16_16816(acc[mt], pa[2 * h], pb[2 * h], pa[2 * h + 1], pb[2 * h + 1], xl[2 * h],
-                                               xl[2 * h + 1]);
-                            }
+                        for (int f = 0; f < NF; ++f) {
+                            uint32_t xf[4];
+                            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                         : "=r"(xf[0]), "=r"(xf[1]), "=r"(xf[2]), "=r"(xf[3])
+                                         : "r"(fragb + (((q * WPT + j) * MT + mt) * NF + f) * 512u));
+                            mma_bf16_16816(acc[mt], pa[0], pb[0], pa[1], pb[1], xf[0], xf[1]);
+                            mma_bf16_16816(acc[mt], pa[2], pb[2], pa[3], pb[3], xf[2], xf[3]);
                         }
                     }
                 }
-                const float s0 = sb_get(sb_cur, 0, gl), b0 = sb_get(sb_cur, 1, gl);
-                const float s1 = sb_get(sb_cur, 2, gl), b1 = sb_get(sb_cur, 3, gl);
+                const float s0 = sb_get(sb_cur, 0, q), b0 = sb_get(sb_cur, 1, q);
+                const float s1 = sb_get(sb_cur, 2, q), b1 = sb_get(sb_cur, 3, q);
                 const float b0o = fmaf(-OFF, s0, b0), b1o = fmaf(-OFF, s1, b1);
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
+                    float xs0, xs1;
+                    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];"
+                                 : "=f"(xs0), "=f"(xs1)
+                                 : "r"(xsb + (q * MT * 8 + mt * 8) * 4u));
                     yacc[mt][0] = fmaf(s0, acc[mt][0], yacc[mt][0]);
                     yacc[mt][1] = fmaf(s0, acc[mt][1], yacc[mt][1]);
                     yacc[mt][2] = fmaf(s1, acc[mt][2], yacc[mt][2]);
                     yacc[mt][3] = fmaf(s1, acc[mt][3], yacc[mt][3]);
-                    yacc[mt][0] = fmaf(b0o, xs[mt][0], yacc[mt][0]);
-                    yacc[mt][1] = fmaf(b0o, xs[mt][1], yacc[mt][1]);
-                    yacc[mt][2] = fmaf(b1o, xs[mt][0], yacc[mt][2]);
-                    yacc[mt][3] = fmaf(b1o, xs[mt][1], yacc[mt][3]);
+                    yacc[mt][0] = fmaf(b0o, xs0, yacc[mt][0]);
+                    yacc[mt][1] = fmaf(b0o, xs1, yacc[mt][1]);
+                    yacc[mt][2] = fmaf(b1o, xs0, yacc[mt][2]);
+                    yacc[mt][3] = fmaf(b1o, xs1, yacc[mt][3]);
                 }
             }
         }
@@ -490,64 +575,87 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
 #pragma unroll
             for (int j = 0; j < SBW; ++j) sb_cur[i][j] = sb_nxt[i][j];
 
-        // ---- end of this CTA's share of the row group: write y or park a partial ----
+        // activation fragments of the next unit go to the other buffer
+        if (u + 1u < u_end) prep_unit(u + 1u, buf ^ 1u);
+
+        // ---- end of this CTA's share of the row group: combine the K halves, write y or park a partial ----
         const bool last_of_rg = (kc + 1u == p.chunks) || (u + 1u == u_end);
+        const uint32_t flush_lane = ring + Plan::OFF_FLUSH + (rb * 32u + lane) * (MT * 16u);
+        if (last_of_rg && kh == 1) {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+                asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(flush_lane + mt * 16u), "f"(yacc[mt][0]),
+                             "f"(yacc[mt][1]), "f"(yacc[mt][2]), "f"(yacc[mt][3])
+                             : "memory");
+        }
+        consumer_barrier();  // fragments of the next unit are complete; the K-half partials are visible
+        if (s_abort) return;
         if (last_of_rg) {
-            const uint32_t rg_first = rg * p.chunks, rg_last = rg_first + p.chunks - 1u;
-            const uint32_t n0 = rg * kRows + warp * 16u + wr, n1 = n0 + 8u;
-            auto store = [&](uint32_t m, uint32_t n, float val) {
-                if (m < p.M && n < p.N) {
-                    if constexpr (XF32)
-                        static_cast<float *>(p.y)[static_cast<size_t>(m) * p.N + n] = val;
-                    else
-                        static_cast<__nv_bfloat16 *>(p.y)[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(val);
-                }
-            };
-            if (u_begin <= rg_first && rg_last < u_end) {
-                // this CTA saw every chunk of the row group
+            if (kh == 0) {
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
-                    store(mt * 8 + 2 * t, n0, yacc[mt][0]);
-                    store(mt * 8 + 2 * t + 1, n0, yacc[mt][1]);
-                    store(mt * 8 + 2 * t, n1, yacc[mt][2]);
-                    store(mt * 8 + 2 * t + 1, n1, yacc[mt][3]);
+                    float o0, o1, o2, o3;
+                    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                                 : "=f"(o0), "=f"(o1), "=f"(o2), "=f"(o3)
+                                 : "r"(flush_lane + mt * 16u));
+                    yacc[mt][0] += o0, yacc[mt][1] += o1, yacc[mt][2] += o2, yacc[mt][3] += o3;
                 }
-            } else {
-                const uint32_t first_cta = unit_owner(rg_first, p.units, gridDim.x);
-                const uint32_t last_cta = unit_owner(rg_last, p.units, gridDim.x);
-                const uint32_t slots = last_cta - first_cta + 1u;
-                const uint32_t slot = blockIdx.x - first_cta;
-                // slot layout [128 rows][MT*8] so that this lane's values are 8-byte pairs
-                float *base = p.partials + (static_cast<size_t>(rg) * p.max_slots + slot) * (kRows * MT * 8);
-                const uint32_t r0 = warp * 16u + wr, r1 = r0 + 8u;
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    *reinterpret_cast<float2 *>(base + r0 * (MT * 8) + mt * 8 + 2 * t) = make_float2(yacc[mt][0], yacc[mt][1]);
-                    *reinterpret_cast<float2 *>(base + r1 * (MT * 8) + mt * 8 + 2 * t) = make_float2(yacc[mt][2], yacc[mt][3]);
-                }
-                __threadfence();
-                __syncwarp();
-                unsigned int ticket = 0;
-                if (lane == 0) ticket = atomicAdd(&p.counters[rg * kConsumerWarps + warp], 1u);
-                ticket = __shfl_sync(0xFFFFFFFFu, ticket, 0);
-                if (ticket == slots - 1u) {
-                    __threadfence();
-                    const float *all = p.partials + static_cast<size_t>(rg) * p.max_slots * (kRows * MT * 8);
+                const uint32_t rg_first = rg * p.chunks, rg_last = rg_first + p.chunks - 1u;
+                const uint32_t n0 = rg * kRows + rb * 16u + wr, n1 = n0 + 8u;
+                auto store = [&](uint32_t m, uint32_t n, float val) {
+                    if (m < p.M && n < p.N) {
+                        if constexpr (XF32)
+                            static_cast<float *>(p.y)[static_cast<size_t>(m) * p.N + n] = val;
+                        else
+                            static_cast<__nv_bfloat16 *>(p.y)[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(val);
+                    }
+                };
+                if (u_begin <= rg_first && rg_last < u_end) {
+                    // this CTA saw every chunk of the row group
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
-                        float2 a = make_float2(0.f, 0.f), b = make_float2(0.f, 0.f);
-                        for (uint32_t sidx = 0; sidx < slots; ++sidx) {  // fixed order: reproducible sums
-                            const float *sp = all + static_cast<size_t>(sidx) * (kRows * MT * 8);
-                            const float2 va = __ldcg(reinterpret_cast<const float2 *>(sp + r0 * (MT * 8) + mt * 8 + 2 * t));
-                            const float2 vb = __ldcg(reinterpret_cast<const float2 *>(sp + r1 * (MT * 8) + mt * 8 + 2 * t));
-                            a.x += va.x, a.y += va.y, b.x += vb.x, b.y += vb.y;
-                        }
-                        store(mt * 8 + 2 * t, n0, a.x);
-                        store(mt * 8 + 2 * t + 1, n0, a.y);
-                        store(mt * 8 + 2 * t, n1, b.x);
-                        store(mt * 8 + 2 * t + 1, n1, b.y);
+                        store(mt * 8 + 2 * t, n0, yacc[mt][0]);
+                        store(mt * 8 + 2 * t + 1, n0, yacc[mt][1]);
+                        store(mt * 8 + 2 * t, n1, yacc[mt][2]);
+                        store(mt * 8 + 2 * t + 1, n1, yacc[mt][3]);
                     }
-                    if (lane == 0) p.counters[rg * kConsumerWarps + warp] = 0u;  // ready for the next launch
+                } else {
+                    const uint32_t first_cta = unit_owner(rg_first, p.units, gridDim.x);
+                    const uint32_t last_cta = unit_owner(rg_last, p.units, gridDim.x);
+                    const uint32_t slots = last_cta - first_cta + 1u;
+                    const uint32_t slot = blockIdx.x - first_cta;
+                    // slot layout [128 rows][MT*8] so that this lane's values are 8-byte pairs
+                    float *base = p.partials + (static_cast<size_t>(rg) * p.max_slots + slot) * (kRows * MT * 8);
+                    const uint32_t r0 = rb * 16u + wr, r1 = r0 + 8u;
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        *reinterpret_cast<float2 *>(base + r0 * (MT * 8) + mt * 8 + 2 * t) = make_float2(yacc[mt][0], yacc[mt][1]);
+                        *reinterpret_cast<float2 *>(base + r1 * (MT * 8) + mt * 8 + 2 * t) = make_float2(yacc[mt][2], yacc[mt][3]);
+                    }
+                    __threadfence();
+                    __syncwarp();
+                    unsigned int ticket = 0;
+                    if (lane == 0) ticket = atomicAdd(&p.counters[rg * kRowBlocks + rb], 1u);
+                    ticket = __shfl_sync(0xFFFFFFFFu, ticket, 0);
+                    if (ticket == slots - 1u) {
+                        __threadfence();
+                        const float *all = p.partials + static_cast<size_t>(rg) * p.max_slots * (kRows * MT * 8);
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            float2 a = make_float2(0.f, 0.f), b = make_float2(0.f, 0.f);
+                            for (uint32_t sidx = 0; sidx < slots; ++sidx) {  // fixed order: reproducible sums
+                                const float *sp = all + static_cast<size_t>(sidx) * (kRows * MT * 8);
+                                const float2 va = __ldcg(reinterpret_cast<const float2 *>(sp + r0 * (MT * 8) + mt * 8 + 2 * t));
+                                const float2 vb = __ldcg(reinterpret_cast<const float2 *>(sp + r1 * (MT * 8) + mt * 8 + 2 * t));
+                                a.x += va.x, a.y += va.y, b.x += vb.x, b.y += vb.y;
+                            }
+                            store(mt * 8 + 2 * t, n0, a.x);
+                            store(mt * 8 + 2 * t + 1, n0, a.y);
+                            store(mt * 8 + 2 * t, n1, b.x);
+                            store(mt * 8 + 2 * t + 1, n1, b.y);
+                        }
+                        if (lane == 0) p.counters[rg * kRowBlocks + rb] = 0u;  // ready for the next launch
+                    }
                 }
             }
 #pragma unroll
@@ -668,14 +776,14 @@ cudaError_t launch_stream(const GemvParams &p, const CUtensorMap &tmap, uint32_t
     auto kern = gaf_gemv_stream_kernel<GB, BITS, MT, XF32>;
     static bool configured = false;  // per instantiation; the attribute belongs to the function, not the stream
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemPlan<MT, XF32>::TOTAL);
         if (e != cudaSuccess) return e;
         configured = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas);
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.dynamicSmemBytes = SmemPlan<MT, XF32>::TOTAL;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -757,7 +865,7 @@ size_t gemv_mma_scratch_bytes(const WeightView &w, uint32_t M, const GemvTuning 
 }
 
 size_t gemv_mma_counter_count(const WeightView &w) {
-    return static_cast<size_t>((w.N + kRows - 1u) / kRows) * kConsumerWarps;
+    return static_cast<size_t>((w.N + kRows - 1u) / kRows) * kRowBlocks;
 }
 
 cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bool x_f32,
@@ -771,7 +879,6 @@ cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bo
     if (need > scratch.partial_bytes || gemv_mma_counter_count(w) > scratch.counter_count)
         return cudaErrorMemoryAllocation;
     const uint32_t gb = w.group * w.bits / 8u;
-    const uint32_t gps = kChunkBytes / gb;
     GemvParams p;
     p.packed = w.packed;
     p.scales = w.scales;
@@ -791,15 +898,13 @@ cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bo
     p.chunks = pl.chunks;
     p.units = pl.units;
     p.max_slots = pl.max_slots;
-    // one aligned vector load per row and unit: every unit must be whole and every row start aligned
-    const size_t sbw_bytes = static_cast<size_t>(gps) * 2u;
-    p.vec_sb = (w.groups % gps == 0 && reinterpret_cast<uintptr_t>(w.scales) % sbw_bytes == 0 &&
-                reinterpret_cast<uintptr_t>(w.biases) % sbw_bytes == 0 && sbw_bytes <= 16u)
+    // one aligned vector load per row, unit and K half: a panel's groups must not straddle a row end
+    const uint32_t gpp = kPanelBytes / gb;
+    const size_t sb_bytes = static_cast<size_t>(gpp) * 2u;
+    p.vec_sb = (w.groups % gpp == 0 && reinterpret_cast<uintptr_t>(w.scales) % sb_bytes == 0 &&
+                reinterpret_cast<uintptr_t>(w.biases) % sb_bytes == 0)
                    ? 1u
                    : 0u;
-    if (sbw_bytes > 16u)  // 32-byte rows of scales: two 16-byte loads, 16-byte alignment is enough
-        p.vec_sb = (w.groups % gps == 0 && reinterpret_cast<uintptr_t>(w.scales) % 16u == 0 &&
-                    reinterpret_cast<uintptr_t>(w.biases) % 16u == 0) ? 1u : 0u;
     const bool pdl = tune.pdl != 0;
     if (w.bits == 4) {
         if (gb == 16u) return dispatch_stream<16, 4>(p, w.tmap, pl.ctas, mt, x_f32, pdl, stream);
