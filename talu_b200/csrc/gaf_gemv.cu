@@ -71,7 +71,7 @@ constexpr int kChunkBytes = 256;  // packed bytes per row per unit
 constexpr int kStages = 3;
 constexpr int kRowBlocks = 8;      // 16-row blocks per unit
 constexpr int kConsumerWarps = 16;  // two K halves x eight row blocks
-constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kThreads = (kConsumerWarps + 2) * 32;  // + producer warp + writer warp
 constexpr uint32_t kWaitLimit = 1u << 22;  // polls (with back-off) before a wait gives up
 
 struct GemvParams {
@@ -81,7 +81,7 @@ struct GemvParams {
     const void *x;
     void *y;
     float *partials;         // [row group][slot][128][MT*8]
-    unsigned int *counters;  // [row group][8]
+    unsigned int *counters;  // [row group]
     unsigned int *error_word;
     uint32_t N, K, M;
     uint32_t groups;      // K / G
@@ -91,7 +91,7 @@ struct GemvParams {
     uint32_t chunks;      // K chunks per row group
     uint32_t units;       // row groups * chunks
     uint32_t max_slots;   // scratch slots per row group
-    uint32_t vec_sb;      // 1: scales / biases of a unit can be read with one aligned vector load
+    uint32_t probe;       // measurement aid, bit mask: 1 = skip the arithmetic, 2 = skip the streaming, 4 = skip the write-out
 };
 
 // ---- small PTX wrappers ----------------------------------------------------
@@ -141,6 +141,15 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
         "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// same with a zero accumulator input (first MMA of a group)
+__device__ __forceinline__ void mma_bf16_16816_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                 uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -260,8 +269,9 @@ __device__ __host__ __forceinline__ uint32_t unit_owner(uint32_t u, uint32_t uni
 constexpr int kPanelBytes = 128;                       // bytes per row in one TMA tile (the swizzle span)
 constexpr int kPanels = kChunkBytes / kPanelBytes;     // TMA tiles per unit (= K halves, one per warp set)
 constexpr int kPanelSize = kRows * kPanelBytes;        // 16 KB
-constexpr int kStageBytes = kPanels * kPanelSize;      // 32 KB
+constexpr int kWeightBytes = kPanels * kPanelSize;     // 32 KB of packed codes per unit
 constexpr int kFragItems = 16;                         // (group, word) pairs per unit: 256 B / 16 B
+constexpr int kMaxBlockUnits = 16;                     // units whose activation fragments are built together
 
 template <int GB>
 struct StreamGeom {
@@ -269,18 +279,25 @@ struct StreamGeom {
     static constexpr int GPP = kPanelBytes / GB;   // groups per panel = groups per warp and unit
     static constexpr int LW = GB / 4;              // bytes one lane reads per group and row
     static constexpr int WPT = LW / 4;             // packed words per lane per group and row
+    // scales / biases of one unit: a TMA box of SBOX bytes x 128 rows (16 bytes is the smallest box)
+    static constexpr int SBOX = GPS * 2 > 16 ? GPS * 2 : 16;
+    static constexpr int SB_BYTES = kRows * SBOX;
+    static constexpr int STAGE_BYTES = kWeightBytes + 2 * SB_BYTES;  // multiple of 1024
 };
 
-// shared-memory plan after the ring (all offsets from the 1024-byte aligned ring base)
-template <int MT, bool XF32>
+// shared-memory plan (all offsets from the 1024-byte aligned ring base)
+template <int GB, int MT, bool XF32>
 struct SmemPlan {
-    static constexpr int FRAG_BYTES = kFragItems * MT * (XF32 ? 2 : 1) * 512;  // one unit's activation fragments
-    static constexpr int XS_BYTES = 16 * MT * 8 * 4;                           // group sums [<=16 groups][MT*8]
-    static constexpr int FLUSH_BYTES = kRowBlocks * 32 * MT * 4 * 4;           // K-half exchange at a row-group end
-    static constexpr int OFF_FRAG = kStages * kStageBytes;
-    static constexpr int OFF_XS = OFF_FRAG + 2 * FRAG_BYTES;
-    static constexpr int OFF_FLUSH = OFF_XS + 2 * XS_BYTES;
-    static constexpr int TOTAL = OFF_FLUSH + FLUSH_BYTES + 1024;  // + slack to align the ring
+    static constexpr int NF = XF32 ? 2 : 1;
+    static constexpr int UNIT_FRAG_MAX = kFragItems * MT * NF * 512;            // one unit's fragments, 8 rows per tile
+    static constexpr int FRAG_BUF = UNIT_FRAG_MAX > 16384 ? UNIT_FRAG_MAX : 16384;  // one block of units
+    static constexpr int XS_UNIT = (kChunkBytes / GB) * MT * 8 * 4;             // group sums of one unit
+    static constexpr int XS_BUF = kMaxBlockUnits * XS_UNIT;
+    static constexpr int OUT_BUF = 2 * kRowBlocks * 32 * MT * 4 * 4;           // both K halves of one row group
+    static constexpr int OFF_FRAG = kStages * StreamGeom<GB>::STAGE_BYTES;
+    static constexpr int OFF_XS = OFF_FRAG + 2 * FRAG_BUF;
+    static constexpr int OFF_OUT = OFF_XS + 2 * XS_BUF;
+    static constexpr int TOTAL = OFF_OUT + 2 * OUT_BUF + 1024;  // + slack to align the ring
 };
 
 // Row permutation inside a warp's 16 rows: lane group g (= lane / 4) works on row rho(g)
@@ -297,21 +314,32 @@ __device__ __forceinline__ void consumer_barrier() {
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
 }
 
-template <int GB, int BITS, int MT, bool XF32>
+// scale / bias word (two 16-bit values) -> f32 of the low or high half; SD = 1 bf16, 0 f16
+template <int SD>
+__device__ __forceinline__ float sb_half(uint32_t w, int hi) {
+    if constexpr (SD == 1) return __uint_as_float(hi ? (w & 0xFFFF0000u) : (w << 16));
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(hi ? (w >> 16) : (w & 0xFFFFu))));
+}
+
+// Warp roles: 0..15 consumers (kh * 8 + rb), 16 producer, 17 writer.
+template <int GB, int BITS, int MT, bool XF32, int SD>
 __global__ void __launch_bounds__(kThreads, 1)
-gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap) {
+gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap_w,
+                       const __grid_constant__ CUtensorMap tmap_s, const __grid_constant__ CUtensorMap tmap_b) {
     using Geo = StreamGeom<GB>;
-    using Plan = SmemPlan<MT, XF32>;
+    using Plan = SmemPlan<GB, MT, XF32>;
     constexpr int GPS = Geo::GPS, GPP = Geo::GPP, LW = Geo::LW, WPT = Geo::WPT;
     constexpr int XPB = 8 / BITS;                          // activations per packed byte
     constexpr float OFF = BITS == 4 ? 128.f : 2176.f;      // what the +128 offsets add per unit of sum(x)
-    constexpr int NF = XF32 ? 2 : 1;                       // fragment sets per activation tile (hi, lo)
+    constexpr int NF = Plan::NF;                           // fragment sets per activation tile (hi, lo)
     constexpr int SBW = GPP * 2 / 4 > 0 ? GPP * 2 / 4 : 1;  // 32-bit words holding one row's scales of a warp's groups
     static_assert(WPT >= 1 && GPP >= 1, "unsupported group size");
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t s_full[kStages];
     __shared__ __align__(8) uint64_t s_empty[kStages];
+    __shared__ __align__(8) uint64_t s_out_full[2];   // consumers -> writer: a row group's sums are in the out buffer
+    __shared__ __align__(8) uint64_t s_out_empty[2];  // writer -> consumers: the out buffer may be reused
     __shared__ volatile uint32_t s_abort;  // a consumer warp gave up a wait: everybody leaves at the next barrier
 
     // the ring starts at a 1024-byte boundary (8 rows x 128 bytes, the swizzle atom)
@@ -326,6 +354,11 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
             mbar_init(smem_u32(&s_full[s]), 1);
             mbar_init(smem_u32(&s_empty[s]), kConsumerWarps);
         }
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&s_out_full[s]), kConsumerWarps);
+            mbar_init(smem_u32(&s_out_empty[s]), 1);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -333,27 +366,39 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
 
     const uint32_t u_begin = range_begin(blockIdx.x, p.units, gridDim.x);
     const uint32_t u_end = range_begin(blockIdx.x + 1u, p.units, gridDim.x);
+    if (u_begin >= u_end) return;
+    const uint32_t rg_begin = u_begin / p.chunks;
+    const uint32_t kc_begin = u_begin - rg_begin * p.chunks;
 
     if (warp == kConsumerWarps) {
         // ------------------------- producer warp (one lane works) -------------------------
         if (lane != 0) return;
-        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap)) : "memory");
-        uint32_t issued = 0;
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_s)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_b)) : "memory");
+        uint32_t issued = 0, rg = rg_begin, kc = kc_begin;
         bool ok = true;
         for (uint32_t u = u_begin; u < u_end; ++u, ++issued) {
             const uint32_t stage = issued % kStages;
             const uint32_t round = issued / kStages;
             if (round > 0) ok = mbar_wait(smem_u32(&s_empty[stage]), (round - 1u) & 1u, p.error_word, 0x1u);
             if (!ok) break;
-            const uint32_t rg = u / p.chunks, kc = u - rg * p.chunks;
             const uint32_t full = smem_u32(&s_full[stage]);
-            // rows past N and bytes past the row end are zero-filled by the copy engine,
-            // so every unit delivers the same byte count
-            mbar_arrive_expect_tx(full, kStageBytes);
+            if (p.probe & 2u) {
+                mbar_arrive(full);
+            } else {
+                // rows past N and bytes past a row end are zero-filled by the copy engine,
+                // so every unit delivers the same byte count
+                const uint32_t base = ring + stage * Geo::STAGE_BYTES;
+                mbar_arrive_expect_tx(full, Geo::STAGE_BYTES);
 #pragma unroll
-            for (int pnl = 0; pnl < kPanels; ++pnl)
-                tma_load_2d(ring + stage * kStageBytes + pnl * kPanelSize, &tmap, kc * kChunkBytes + pnl * kPanelBytes,
-                            rg * kRows, full);
+                for (int pnl = 0; pnl < kPanels; ++pnl)
+                    tma_load_2d(base + pnl * kPanelSize, &tmap_w, kc * kChunkBytes + pnl * kPanelBytes, rg * kRows, full);
+                const uint32_t sb_col = (kc * GPS * 2u) & ~15u;  // boxes start on 16-byte columns
+                tma_load_2d(base + kWeightBytes, &tmap_s, sb_col, rg * kRows, full);
+                tma_load_2d(base + kWeightBytes + Geo::SB_BYTES, &tmap_b, sb_col, rg * kRows, full);
+            }
+            if (++kc == p.chunks) kc = 0u, ++rg;
         }
         if (!ok) {
             // give copies already in flight a bounded time to land before the CTA's memory is released
@@ -366,15 +411,151 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
         return;
     }
 
+    const uint32_t g = lane >> 2;  // activation row inside a tile; accumulator row slot
+    const uint32_t t = lane & 3;   // quarter of the group this lane holds
+    const uint32_t wr = rho<LW>(g);  // weight row (of a warp's 16) behind accumulator rows g and g + 8
+
+    if (warp == kConsumerWarps + 1) {
+        // ------------------------- writer warp -------------------------
+        // One round per row group this CTA touches: add the two K halves, then either write y
+        // (the CTA saw the whole row group) or park the partial and take a ticket; the last
+        // ticket holder adds all partials in slot order and writes y.  Nothing here is on the
+        // consumers' critical path.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        const uint32_t rg_last_touched = (u_end - 1u) / p.chunks;
+        uint32_t ob = 0, ophase = 0;
+        for (uint32_t rg = rg_begin; rg <= rg_last_touched; ++rg) {
+            if (!mbar_wait(smem_u32(&s_out_full[ob]), ophase, p.error_word, 0x8u)) return;
+            const uint32_t rg_first = rg * p.chunks, rg_last = rg_first + p.chunks - 1u;
+            const bool whole = u_begin <= rg_first && rg_last < u_end;
+            uint32_t slots = 1u, slot = 0u;
+            if (!whole) {
+                const uint32_t first_cta = unit_owner(rg_first, p.units, gridDim.x);
+                slots = unit_owner(rg_last, p.units, gridDim.x) - first_cta + 1u;
+                slot = blockIdx.x - first_cta;
+            }
+            float *mine = p.partials + (static_cast<size_t>(rg) * p.max_slots + slot) * (kRows * MT * 8);
+            const uint32_t obuf = ring + Plan::OFF_OUT + ob * Plan::OUT_BUF + lane * (MT * 16u);
+            auto store = [&](uint32_t m, uint32_t n, float val) {
+                if (m < p.M && n < p.N) {
+                    if constexpr (XF32)
+                        static_cast<float *>(p.y)[static_cast<size_t>(m) * p.N + n] = val;
+                    else
+                        static_cast<__nv_bfloat16 *>(p.y)[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(val);
+                }
+            };
+            if (!(p.probe & 4u)) {
+#pragma unroll 2
+                for (uint32_t rb = 0; rb < kRowBlocks; ++rb) {
+                    const uint32_t r0 = rb * 16u + wr, r1 = r0 + 8u;
+                    const uint32_t n0 = rg * kRows + r0, n1 = n0 + 8u;
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        float a0, a1, a2, a3, b0, b1, b2, b3;
+                        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                                     : "=f"(a0), "=f"(a1), "=f"(a2), "=f"(a3)
+                                     : "r"(obuf + rb * (32u * MT * 16u) + mt * 16u));
+                        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                                     : "=f"(b0), "=f"(b1), "=f"(b2), "=f"(b3)
+                                     : "r"(obuf + (kRowBlocks + rb) * (32u * MT * 16u) + mt * 16u));
+                        a0 += b0, a1 += b1, a2 += b2, a3 += b3;
+                        if (whole) {
+                            store(mt * 8 + 2 * t, n0, a0);
+                            store(mt * 8 + 2 * t + 1, n0, a1);
+                            store(mt * 8 + 2 * t, n1, a2);
+                            store(mt * 8 + 2 * t + 1, n1, a3);
+                        } else {
+                            // slot layout [128 rows][MT*8]: this lane's values are 8-byte pairs
+                            *reinterpret_cast<float2 *>(mine + r0 * (MT * 8) + mt * 8 + 2 * t) = make_float2(a0, a1);
+                            *reinterpret_cast<float2 *>(mine + r1 * (MT * 8) + mt * 8 + 2 * t) = make_float2(a2, a3);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&s_out_empty[ob]));  // the consumers may refill this buffer
+            if (!whole && !(p.probe & 4u)) {
+                // release the partial (all lanes' stores are ordered before lane 0's atomic by the warp
+                // barrier) and learn whether the other owners of this row group are done
+                unsigned int ticket = 0;
+                if (lane == 0)
+                    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(ticket) : "l"(p.counters + rg) : "memory");
+                ticket = __shfl_sync(0xFFFFFFFFu, ticket, 0);
+                if (ticket == slots - 1u) {
+                    const float *all = p.partials + static_cast<size_t>(rg) * p.max_slots * (kRows * MT * 8);
+                    if (slots == 2u) {
+                        // the usual case: a few row blocks at a time, every load issued before the first use
+                        constexpr uint32_t RBC = MT == 1 ? 4u : 2u;
+#pragma unroll 1
+                        for (uint32_t rb0 = 0; rb0 < kRowBlocks; rb0 += RBC) {
+                            float2 va[RBC][MT][2], vb[RBC][MT][2];
+#pragma unroll
+                            for (uint32_t i = 0; i < RBC; ++i)
+#pragma unroll
+                                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                                    for (int sidx = 0; sidx < 2; ++sidx) {
+                                        const float *sp = all + static_cast<size_t>(sidx) * (kRows * MT * 8);
+                                        const uint32_t r0 = (rb0 + i) * 16u + wr, r1 = r0 + 8u;
+                                        va[i][mt][sidx] = __ldcg(reinterpret_cast<const float2 *>(sp + r0 * (MT * 8) + mt * 8 + 2 * t));
+                                        vb[i][mt][sidx] = __ldcg(reinterpret_cast<const float2 *>(sp + r1 * (MT * 8) + mt * 8 + 2 * t));
+                                    }
+#pragma unroll
+                            for (uint32_t i = 0; i < RBC; ++i) {
+                                const uint32_t n0 = rg * kRows + (rb0 + i) * 16u + wr, n1 = n0 + 8u;
+#pragma unroll
+                                for (int mt = 0; mt < MT; ++mt) {
+                                    store(mt * 8 + 2 * t, n0, va[i][mt][0].x + va[i][mt][1].x);
+                                    store(mt * 8 + 2 * t + 1, n0, va[i][mt][0].y + va[i][mt][1].y);
+                                    store(mt * 8 + 2 * t, n1, vb[i][mt][0].x + vb[i][mt][1].x);
+                                    store(mt * 8 + 2 * t + 1, n1, vb[i][mt][0].y + vb[i][mt][1].y);
+                                }
+                            }
+                        }
+                    } else {
+#pragma unroll 1
+                        for (uint32_t rb = 0; rb < kRowBlocks; ++rb) {
+                            const uint32_t r0 = rb * 16u + wr, r1 = r0 + 8u;
+                            const uint32_t n0 = rg * kRows + r0, n1 = n0 + 8u;
+#pragma unroll
+                            for (int mt = 0; mt < MT; ++mt) {
+                                float2 a = make_float2(0.f, 0.f), b = make_float2(0.f, 0.f);
+                                for (uint32_t sidx = 0; sidx < slots; ++sidx) {  // fixed order: reproducible sums
+                                    const float *sp = all + static_cast<size_t>(sidx) * (kRows * MT * 8);
+                                    const float2 xa = __ldcg(reinterpret_cast<const float2 *>(sp + r0 * (MT * 8) + mt * 8 + 2 * t));
+                                    const float2 xb = __ldcg(reinterpret_cast<const float2 *>(sp + r1 * (MT * 8) + mt * 8 + 2 * t));
+                                    a.x += xa.x, a.y += xa.y, b.x += xb.x, b.y += xb.y;
+                                }
+                                store(mt * 8 + 2 * t, n0, a.x);
+                                store(mt * 8 + 2 * t + 1, n0, a.y);
+                                store(mt * 8 + 2 * t, n1, b.x);
+                                store(mt * 8 + 2 * t + 1, n1, b.y);
+                            }
+                        }
+                    }
+                    if (lane == 0) p.counters[rg] = 0u;  // ready for the next launch
+                }
+            }
+            ob ^= 1u;
+            if (ob == 0u) ophase ^= 1u;
+        }
+        return;
+    }
+
     // --------------------------- consumer warps ---------------------------
     // warp = kh * 8 + rb: row block rb (16 of the unit's 128 rows), K half kh (one 128-byte panel)
-    const int rb = warp & (kRowBlocks - 1);
-    const int kh = warp / kRowBlocks;
-    const int g = lane >> 2;  // activation row inside a tile; accumulator row slot
-    const int t = lane & 3;   // quarter of the group this lane holds
-    const uint32_t wr = rho<LW>(g);  // weight row (of the warp's 16) behind accumulator rows g and g + 8
+    const uint32_t rb = warp & (kRowBlocks - 1);
+    const uint32_t kh = warp / kRowBlocks;
     const uint8_t *xbase = static_cast<const uint8_t *>(p.x);
     const size_t x_elt = XF32 ? 4 : 2;
+
+    // Activation fragments are stored only for the activation rows that exist (one tile: min(M, 8)).
+    const uint32_t mg = MT == 1 ? (p.M < 8u ? p.M : 8u) : 8u;
+    const uint32_t item_bytes = mg * 64u;                                 // one (group, word, tile, set)
+    const uint32_t unit_frag_bytes = kFragItems * MT * NF * item_bytes;   // one unit
+    uint32_t block_units = Plan::FRAG_BUF / unit_frag_bytes;              // units prepared together
+    if (block_units > static_cast<uint32_t>(kMaxBlockUnits)) block_units = kMaxBlockUnits;
+    const bool has_x = g < mg;
 
     // shared-memory offsets of this lane's pieces of a panel row, one per group of the panel
     // (swizzle: 16-byte chunk index XOR (row & 7); rows wr and wr + 8 share the XOR term)
@@ -382,10 +563,13 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
 #pragma unroll
     for (int q = 0; q < GPP; ++q) {
         const uint32_t ob = q * GB + t * LW;
-        swz[q] = (rb * 16u + wr) * kPanelBytes + kh * kPanelSize + ((((ob >> 4) ^ wr) & 7u) << 4) + (ob & 15u);
+        swz[q] = ring + (rb * 16u + wr) * kPanelBytes + kh * kPanelSize + ((((ob >> 4) ^ wr) & 7u) << 4) + (ob & 15u);
     }
-    const uint32_t frag_lane = ring + Plan::OFF_FRAG + lane * 16u;
+    // this lane's rows in the scale / bias boxes of a stage (row pitch SBOX)
+    const uint32_t sb_lane = ring + kWeightBytes + (rb * 16u + wr) * Geo::SBOX + kh * GPP * 2u;
+    const uint32_t frag_lane = ring + Plan::OFF_FRAG + (g * 4u + t) * 16u;
     const uint32_t xs_lane = ring + Plan::OFF_XS + t * 8u;
+    const uint32_t out_lane = ring + Plan::OFF_OUT + ((kh * kRowBlocks + rb) * 32u + lane) * (MT * 16u);
 
     float yacc[MT][4];
 #pragma unroll
@@ -393,138 +577,121 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
 #pragma unroll
         for (int i = 0; i < 4; ++i) yacc[mt][i] = 0.f;
 
-    // scales / biases of this warp's groups of one unit, for this lane's two rows: {s0, b0, s1, b1}[SBW words]
-    uint32_t sb_cur[4][SBW], sb_nxt[4][SBW];
-    auto load_sb = [&](uint32_t u, uint32_t (&dst)[4][SBW]) {
-        const uint32_t rg = u / p.chunks, kc = u - rg * p.chunks;
-        const uint32_t r0 = min(rg * kRows + rb * 16u + wr, p.N - 1u);
-        const uint32_t r1 = min(rg * kRows + rb * 16u + wr + 8u, p.N - 1u);
-        const uint32_t g0 = kc * GPS + kh * GPP;
-        const uint16_t *src[4] = {p.scales + static_cast<size_t>(r0) * p.groups + g0,
-                                  p.biases + static_cast<size_t>(r0) * p.groups + g0,
-                                  p.scales + static_cast<size_t>(r1) * p.groups + g0,
-                                  p.biases + static_cast<size_t>(r1) * p.groups + g0};
-        if (p.vec_sb && g0 >= p.groups) {
+    // ---- activation fragments and group sums for a block of units, built once per CTA ----
+    // (unit ub of the block, group gl) pairs are dealt round-robin to the 16 warps.
+    // fragment (ub, gl, word j, tile mt, set f) -> buf + ub*unit_frag_bytes + (((gl*WPT + j)*MT + mt)*NF + f)*item_bytes
+    auto prep_block = [&](uint32_t kc_first, uint32_t count, uint32_t buf) {
+        for (uint32_t pi = warp; pi < count * GPS; pi += kConsumerWarps) {
+            const uint32_t ub = pi / GPS, gl = pi % GPS;
+            const uint32_t gi = ((kc_first + ub) % p.chunks) * GPS + gl;
+            float xs[MT][4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                for (int j = 0; j < SBW; ++j) dst[i][j] = 0u;
-        } else if (p.vec_sb) {
+                for (int i = 0; i < 4; ++i) xs[mt][i] = 0.f;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                if constexpr (GPP == 1) {
-                    dst[i][0] = __ldg(src[i]);
-                } else if constexpr (SBW == 1) {
-                    dst[i][0] = __ldg(reinterpret_cast<const uint32_t *>(src[i]));
-                } else if constexpr (SBW == 2) {
-                    const uint2 v = __ldg(reinterpret_cast<const uint2 *>(src[i]));
-                    dst[i][0] = v.x, dst[i][1] = v.y;
-                } else {
-                    const uint4 v = __ldg(reinterpret_cast<const uint4 *>(src[i]));
-                    dst[i][0] = v.x, dst[i][1] = v.y, dst[i][2] = v.z, dst[i][3] = v.w;
-                }
-            }
-        } else {
-            const uint32_t avail = g0 < p.groups ? p.groups - g0 : 0u;  // groups left in the row
+            for (int j = 0; j < WPT; ++j) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+                for (int mt = 0; mt < MT; ++mt) {
+                    const uint32_t m = mt * 8 + g;
+                    uint32_t xh[4], xl[4];
+                    const uint32_t kx = gi * p.group + (t * LW + 4 * j) * XPB;
+                    load_x_frags<BITS, XF32>(xbase + static_cast<size_t>(m) * p.K * x_elt, kx, m < p.M && gi < p.groups,
+                                             xh, xl);
+                    if (has_x) {
+                        const uint32_t dst = frag_lane + buf * Plan::FRAG_BUF + ub * unit_frag_bytes +
+                                             (((gl * WPT + j) * MT + mt) * NF) * item_bytes;
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(xh[0]), "r"(xh[1]),
+                                     "r"(xh[2]), "r"(xh[3])
+                                     : "memory");
+                        if constexpr (XF32)
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + item_bytes), "r"(xl[0]),
+                                         "r"(xl[1]), "r"(xl[2]), "r"(xl[3])
+                                         : "memory");
+                    }
 #pragma unroll
-                for (int j = 0; j < SBW; ++j) {
-                    const uint32_t lo = 2u * j < avail ? __ldg(src[i] + 2 * j) : 0u;
-                    const uint32_t hi = 2u * j + 1u < avail ? __ldg(src[i] + 2 * j + 1) : 0u;
-                    dst[i][j] = lo | (hi << 16);
-                }
-        }
-    };
-    auto sb_get = [&](const uint32_t (&src)[4][SBW], int which, int q) -> float {
-        const uint32_t wv = src[which][q >> 1];
-        return decode_sb(static_cast<uint16_t>((q & 1) ? (wv >> 16) : (wv & 0xFFFFu)), p.sdtype);
-    };
-
-    // Activation fragments and group sums of one unit, built once per CTA: warp w < GPS takes group w.
-    // frag item (group gl, word j, tile mt, set f) lives at ((gl*WPT + j)*MT + mt)*NF + f, 512 bytes each.
-    auto prep_unit = [&](uint32_t u, uint32_t buf) {
-        if (warp >= GPS) return;
-        const uint32_t kc = u % p.chunks;
-        const uint32_t gi = kc * GPS + warp;
-        float xs[MT][4];
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) xs[mt][i] = 0.f;
-#pragma unroll
-        for (int j = 0; j < WPT; ++j) {
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                const uint32_t m = mt * 8 + g;
-                uint32_t xh[4], xl[4];
-                const uint32_t kx = gi * p.group + (t * LW + 4 * j) * XPB;
-                load_x_frags<BITS, XF32>(xbase + static_cast<size_t>(m) * p.K * x_elt, kx, m < p.M && gi < p.groups,
-                                         xh, xl);
-                const uint32_t item = ((warp * WPT + j) * MT + mt) * NF;
-                const uint32_t dst = frag_lane + buf * Plan::FRAG_BYTES + item * 512u;
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(xh[0]), "r"(xh[1]), "r"(xh[2]),
-                             "r"(xh[3])
-                             : "memory");
-                if constexpr (XF32)
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + 512u), "r"(xl[0]), "r"(xl[1]),
-                                 "r"(xl[2]), "r"(xl[3])
-                                 : "memory");
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    // group sums of x: all-ones A (for 8-bit, only the low-nibble slots)
-                    mma_bf16_16816(xs[mt], kOnesBf16, kOnesBf16, BITS == 4 ? kOnesBf16 : 0u, BITS == 4 ? kOnesBf16 : 0u,
-                                   xh[2 * h], xh[2 * h + 1]);
-                    if constexpr (XF32)
+                    for (int h = 0; h < 2; ++h) {
+                        // group sums of x: all-ones A (for 8-bit, only the low-nibble slots)
                         mma_bf16_16816(xs[mt], kOnesBf16, kOnesBf16, BITS == 4 ? kOnesBf16 : 0u,
-                                       BITS == 4 ? kOnesBf16 : 0u, xl[2 * h], xl[2 * h + 1]);
+                                       BITS == 4 ? kOnesBf16 : 0u, xh[2 * h], xh[2 * h + 1]);
+                        if constexpr (XF32)
+                            mma_bf16_16816(xs[mt], kOnesBf16, kOnesBf16, BITS == 4 ? kOnesBf16 : 0u,
+                                           BITS == 4 ? kOnesBf16 : 0u, xl[2 * h], xl[2 * h + 1]);
+                    }
                 }
             }
-        }
-        if (g == 0) {  // every accumulator row holds the same sums
+            if (g == 0) {  // every accumulator row holds the same sums
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                const uint32_t dst = xs_lane + buf * Plan::XS_BYTES + (warp * MT * 8 + mt * 8) * 4u;
-                asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(dst), "f"(xs[mt][0]), "f"(xs[mt][1]) : "memory");
+                for (int mt = 0; mt < MT; ++mt) {
+                    const uint32_t dst = xs_lane + buf * Plan::XS_BUF + ub * Plan::XS_UNIT + (gl * MT * 8 + mt * 8) * 4u;
+                    asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(dst), "f"(xs[mt][0]), "f"(xs[mt][1]) : "memory");
+                }
             }
         }
     };
 
-    if (u_begin < u_end) load_sb(u_begin, sb_cur);  // weights: legal before the dependency wait
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (u_begin < u_end) prep_unit(u_begin, 0u);
+    {
+        const uint32_t total = u_end - u_begin;
+        prep_block(kc_begin, total < block_units ? total : block_units, 0u);
+    }
     consumer_barrier();
 
-    uint32_t consumed = 0;
-    for (uint32_t u = u_begin; u < u_end; ++u, ++consumed) {
-        const uint32_t stage = consumed % kStages;
-        const uint32_t buf = consumed & 1u;
-        const uint32_t rg = u / p.chunks, kc = u - rg * p.chunks;
-        if (u + 1u < u_end) load_sb(u + 1u, sb_nxt);
+    uint32_t rg = rg_begin, kc = kc_begin;
+    uint32_t stage = 0, phase = 0;     // ring position
+    uint32_t ub = 0, buf = 0;          // unit inside the fragment block, fragment buffer
+    uint32_t ob = 0, ophase = 0;       // out buffer and its phase
+    bool alive = true;                 // false once this warp gave up a wait
+    for (uint32_t u = u_begin; u < u_end; ++u) {
+        const bool more = u + 1u < u_end;
+        uint32_t kc_n = kc + 1u, rg_n = rg;  // row group / K chunk of the next unit
+        if (kc_n == p.chunks) kc_n = 0u, ++rg_n;
 
-        // A warp must not leave before the consumer barrier below (the others would wait for it
-        // forever): on a timeout it raises s_abort and skips the work of this unit.
-        const bool landed = mbar_wait(smem_u32(&s_full[stage]), (consumed / kStages) & 1u, p.error_word, 0x2u);
-        if (!landed) s_abort = 1u;
+        // A warp must not leave before the barriers below (the others would wait for it forever):
+        // on a timeout it raises s_abort and skips the arithmetic until everybody leaves together.
+        bool landed = false;
+        if (alive) {
+            landed = mbar_wait(smem_u32(&s_full[stage]), phase, p.error_word, 0x2u);
+            if (!landed) alive = false, s_abort = 1u;
+        }
 
         const uint32_t off = kc * kChunkBytes + kh * kPanelBytes;
         const uint32_t bytes = off < p.row_bytes ? min(static_cast<uint32_t>(kPanelBytes), p.row_bytes - off) : 0u;
-        const uint32_t ngroups = bytes / GB;  // groups of this warp's panel that exist
-        const uint32_t stage_base = ring + stage * kStageBytes;
-        const uint32_t fragb = frag_lane + buf * Plan::FRAG_BYTES + (kh * GPP * WPT * MT * NF) * 512u;
-        const uint32_t xsb = xs_lane + buf * Plan::XS_BYTES + (kh * GPP * MT * 8) * 4u;
+        const uint32_t ngroups = (landed && !(p.probe & 1u)) ? bytes / GB : 0u;  // groups of this warp's panel that exist
+        const uint32_t stage_off = stage * Geo::STAGE_BYTES;
+        const uint32_t fragb = frag_lane + buf * Plan::FRAG_BUF + ub * unit_frag_bytes + (kh * GPP * WPT * MT * NF) * item_bytes;
+        const uint32_t xsb = xs_lane + buf * Plan::XS_BUF + ub * Plan::XS_UNIT + (kh * GPP * MT * 8) * 4u;
+
+        // scales / biases of this warp's groups for rows wr and wr + 8: {s0, b0, s1, b1}[SBW words]
+        uint32_t sb[4][SBW];
+        if (ngroups) {
+            const uint32_t a0 = stage_off + sb_lane + ((kc * GPS * 2u) & 15u);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t a = a0 + (i & 1) * Geo::SB_BYTES + (i >> 1) * 8u * Geo::SBOX;
+                if constexpr (GPP == 1) {
+                    uint16_t v;
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+                    sb[i][0] = v;
+                } else if constexpr (SBW == 1) {
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(sb[i][0]) : "r"(a));
+                } else if constexpr (SBW == 2) {
+                    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(sb[i][0]), "=r"(sb[i][1]) : "r"(a));
+                } else {
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(sb[i][0]), "=r"(sb[i][1]), "=r"(sb[i][2]), "=r"(sb[i][3])
+                                 : "r"(a));
+                }
+            }
+        }
 
 #pragma unroll
         for (int q = 0; q < GPP; ++q) {
-            if (landed && static_cast<uint32_t>(q) < ngroups) {
+            if (static_cast<uint32_t>(q) < ngroups) {
                 uint32_t wa[WPT], wb[WPT];
-                lds_row<WPT>(stage_base + swz[q], wr, wa);
-                lds_row<WPT>(stage_base + swz[q] + 8u * kPanelBytes, wr, wb);
+                lds_row<WPT>(stage_off + swz[q], wr, wa);
+                lds_row<WPT>(stage_off + swz[q] + 8u * kPanelBytes, wr, wb);
                 float acc[MT][4];
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
 #pragma unroll
                 for (int j = 0; j < WPT; ++j) {
                     uint32_t pa[4], pb[4];
@@ -537,17 +704,21 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                     for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
                         for (int f = 0; f < NF; ++f) {
-                            uint32_t xf[4];
-                            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                         : "=r"(xf[0]), "=r"(xf[1]), "=r"(xf[2]), "=r"(xf[3])
-                                         : "r"(fragb + (((q * WPT + j) * MT + mt) * NF + f) * 512u));
-                            mma_bf16_16816(acc[mt], pa[0], pb[0], pa[1], pb[1], xf[0], xf[1]);
+                            uint32_t xf[4] = {0u, 0u, 0u, 0u};
+                            if (has_x)
+                                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                             : "=r"(xf[0]), "=r"(xf[1]), "=r"(xf[2]), "=r"(xf[3])
+                                             : "r"(fragb + (((q * WPT + j) * MT + mt) * NF + f) * item_bytes));
+                            if (j == 0 && f == 0)
+                                mma_bf16_16816_z(acc[mt], pa[0], pb[0], pa[1], pb[1], xf[0], xf[1]);
+                            else
+                                mma_bf16_16816(acc[mt], pa[0], pb[0], pa[1], pb[1], xf[0], xf[1]);
                             mma_bf16_16816(acc[mt], pa[2], pb[2], pa[3], pb[3], xf[2], xf[3]);
                         }
                     }
                 }
-                const float s0 = sb_get(sb_cur, 0, q), b0 = sb_get(sb_cur, 1, q);
-                const float s1 = sb_get(sb_cur, 2, q), b1 = sb_get(sb_cur, 3, q);
+                const float s0 = sb_half<SD>(sb[0][q >> 1], q & 1), b0 = sb_half<SD>(sb[1][q >> 1], q & 1);
+                const float s1 = sb_half<SD>(sb[2][q >> 1], q & 1), b1 = sb_half<SD>(sb[3][q >> 1], q & 1);
                 const float b0o = fmaf(-OFF, s0, b0), b1o = fmaf(-OFF, s1, b1);
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
@@ -568,101 +739,41 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
         }
         // this warp is done with the stage
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&s_empty[stage]));
+        if (landed && lane == 0) mbar_arrive(smem_u32(&s_empty[stage]));
+        if (++stage == kStages) stage = 0u, phase ^= 1u;
 
+        // ---- end of this CTA's share of the row group: hand the sums to the writer warp ----
+        if ((kc + 1u == p.chunks) || !more) {
+            if (alive && !mbar_wait(smem_u32(&s_out_empty[ob]), ophase ^ 1u, p.error_word, 0x10u)) alive = false, s_abort = 1u;
+            if (alive) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-            for (int j = 0; j < SBW; ++j) sb_cur[i][j] = sb_nxt[i][j];
-
-        // activation fragments of the next unit go to the other buffer
-        if (u + 1u < u_end) prep_unit(u + 1u, buf ^ 1u);
-
-        // ---- end of this CTA's share of the row group: combine the K halves, write y or park a partial ----
-        const bool last_of_rg = (kc + 1u == p.chunks) || (u + 1u == u_end);
-        const uint32_t flush_lane = ring + Plan::OFF_FLUSH + (rb * 32u + lane) * (MT * 16u);
-        if (last_of_rg && kh == 1) {
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
-                asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(flush_lane + mt * 16u), "f"(yacc[mt][0]),
-                             "f"(yacc[mt][1]), "f"(yacc[mt][2]), "f"(yacc[mt][3])
-                             : "memory");
-        }
-        consumer_barrier();  // fragments of the next unit are complete; the K-half partials are visible
-        if (s_abort) return;
-        if (last_of_rg) {
-            if (kh == 0) {
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    float o0, o1, o2, o3;
-                    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
-                                 : "=f"(o0), "=f"(o1), "=f"(o2), "=f"(o3)
-                                 : "r"(flush_lane + mt * 16u));
-                    yacc[mt][0] += o0, yacc[mt][1] += o1, yacc[mt][2] += o2, yacc[mt][3] += o3;
-                }
-                const uint32_t rg_first = rg * p.chunks, rg_last = rg_first + p.chunks - 1u;
-                const uint32_t n0 = rg * kRows + rb * 16u + wr, n1 = n0 + 8u;
-                auto store = [&](uint32_t m, uint32_t n, float val) {
-                    if (m < p.M && n < p.N) {
-                        if constexpr (XF32)
-                            static_cast<float *>(p.y)[static_cast<size_t>(m) * p.N + n] = val;
-                        else
-                            static_cast<__nv_bfloat16 *>(p.y)[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(val);
-                    }
-                };
-                if (u_begin <= rg_first && rg_last < u_end) {
-                    // this CTA saw every chunk of the row group
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        store(mt * 8 + 2 * t, n0, yacc[mt][0]);
-                        store(mt * 8 + 2 * t + 1, n0, yacc[mt][1]);
-                        store(mt * 8 + 2 * t, n1, yacc[mt][2]);
-                        store(mt * 8 + 2 * t + 1, n1, yacc[mt][3]);
-                    }
-                } else {
-                    const uint32_t first_cta = unit_owner(rg_first, p.units, gridDim.x);
-                    const uint32_t last_cta = unit_owner(rg_last, p.units, gridDim.x);
-                    const uint32_t slots = last_cta - first_cta + 1u;
-                    const uint32_t slot = blockIdx.x - first_cta;
-                    // slot layout [128 rows][MT*8] so that this lane's values are 8-byte pairs
-                    float *base = p.partials + (static_cast<size_t>(rg) * p.max_slots + slot) * (kRows * MT * 8);
-                    const uint32_t r0 = rb * 16u + wr, r1 = r0 + 8u;
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        *reinterpret_cast<float2 *>(base + r0 * (MT * 8) + mt * 8 + 2 * t) = make_float2(yacc[mt][0], yacc[mt][1]);
-                        *reinterpret_cast<float2 *>(base + r1 * (MT * 8) + mt * 8 + 2 * t) = make_float2(yacc[mt][2], yacc[mt][3]);
-                    }
-                    __threadfence();
-                    __syncwarp();
-                    unsigned int ticket = 0;
-                    if (lane == 0) ticket = atomicAdd(&p.counters[rg * kRowBlocks + rb], 1u);
-                    ticket = __shfl_sync(0xFFFFFFFFu, ticket, 0);
-                    if (ticket == slots - 1u) {
-                        __threadfence();
-                        const float *all = p.partials + static_cast<size_t>(rg) * p.max_slots * (kRows * MT * 8);
-#pragma unroll
-                        for (int mt = 0; mt < MT; ++mt) {
-                            float2 a = make_float2(0.f, 0.f), b = make_float2(0.f, 0.f);
-                            for (uint32_t sidx = 0; sidx < slots; ++sidx) {  // fixed order: reproducible sums
-                                const float *sp = all + static_cast<size_t>(sidx) * (kRows * MT * 8);
-                                const float2 va = __ldcg(reinterpret_cast<const float2 *>(sp + r0 * (MT * 8) + mt * 8 + 2 * t));
-                                const float2 vb = __ldcg(reinterpret_cast<const float2 *>(sp + r1 * (MT * 8) + mt * 8 + 2 * t));
-                                a.x += va.x, a.y += va.y, b.x += vb.x, b.y += vb.y;
-                            }
-                            store(mt * 8 + 2 * t, n0, a.x);
-                            store(mt * 8 + 2 * t + 1, n0, a.y);
-                            store(mt * 8 + 2 * t, n1, b.x);
-                            store(mt * 8 + 2 * t + 1, n1, b.y);
-                        }
-                        if (lane == 0) p.counters[rg * kRowBlocks + rb] = 0u;  // ready for the next launch
-                    }
-                }
+                for (int mt = 0; mt < MT; ++mt)
+                    asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(out_lane + ob * Plan::OUT_BUF + mt * 16u),
+                                 "f"(yacc[mt][0]), "f"(yacc[mt][1]), "f"(yacc[mt][2]), "f"(yacc[mt][3])
+                                 : "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&s_out_full[ob]));
             }
+            ob ^= 1u;
+            if (ob == 0u) ophase ^= 1u;
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) yacc[mt][i] = 0.f;
         }
+
+        // ---- end of a fragment block: build the next one in the other buffer, then everybody meets ----
+        if (++ub == block_units) {
+            ub = 0u;
+            if (more) {
+                const uint32_t left = u_end - (u + 1u);
+                prep_block(kc_n, left < block_units ? left : block_units, buf ^ 1u);
+                consumer_barrier();
+                if (s_abort) return;
+                buf ^= 1u;
+            }
+        }
+        kc = kc_n, rg = rg_n;
     }
 }
 
@@ -771,35 +882,42 @@ GemvPlan plan_gemv(const WeightView &w, const GemvTuning &tune, int sm_count) {
     return pl;
 }
 
-template <int GB, int BITS, int MT, bool XF32>
-cudaError_t launch_stream(const GemvParams &p, const CUtensorMap &tmap, uint32_t ctas, bool pdl, cudaStream_t stream) {
-    auto kern = gaf_gemv_stream_kernel<GB, BITS, MT, XF32>;
+template <int GB, int BITS, int MT, bool XF32, int SD>
+cudaError_t launch_stream(const GemvParams &p, const WeightView &w, uint32_t ctas, bool pdl, cudaStream_t stream) {
+    auto kern = gaf_gemv_stream_kernel<GB, BITS, MT, XF32, SD>;
+    using Plan = SmemPlan<GB, MT, XF32>;
     static bool configured = false;  // per instantiation; the attribute belongs to the function, not the stream
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemPlan<MT, XF32>::TOTAL);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::TOTAL);
         if (e != cudaSuccess) return e;
         configured = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas);
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = SmemPlan<MT, XF32>::TOTAL;
+    cfg.dynamicSmemBytes = Plan::TOTAL;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kern, p, tmap);
+    return cudaLaunchKernelEx(&cfg, kern, p, w.tmap, w.tmap_s, w.tmap_b);
 }
 
 template <int GB, int BITS>
-cudaError_t dispatch_stream(const GemvParams &p, const CUtensorMap &tmap, uint32_t ctas, int mt, bool xf32, bool pdl,
+cudaError_t dispatch_stream(const GemvParams &p, const WeightView &tmap, uint32_t ctas, int mt, bool xf32, bool pdl,
                             cudaStream_t stream) {
-    if (mt == 1 && !xf32) return launch_stream<GB, BITS, 1, false>(p, tmap, ctas, pdl, stream);
-    if (mt == 2 && !xf32) return launch_stream<GB, BITS, 2, false>(p, tmap, ctas, pdl, stream);
-    if (mt == 1 && xf32) return launch_stream<GB, BITS, 1, true>(p, tmap, ctas, pdl, stream);
-    if (mt == 2 && xf32) return launch_stream<GB, BITS, 2, true>(p, tmap, ctas, pdl, stream);
+    const bool bf = p.sdtype == 1u;
+#define TGAF_CASE(MTv, XFv)                                                                          \
+    if (mt == MTv && xf32 == XFv)                                                                    \
+        return bf ? launch_stream<GB, BITS, MTv, XFv, 1>(p, tmap, ctas, pdl, stream)                 \
+                  : launch_stream<GB, BITS, MTv, XFv, 0>(p, tmap, ctas, pdl, stream);
+    TGAF_CASE(1, false)
+    TGAF_CASE(2, false)
+    TGAF_CASE(1, true)
+    TGAF_CASE(2, true)
+#undef TGAF_CASE
     return cudaErrorNotSupported;
 }
 
@@ -838,8 +956,29 @@ cudaError_t make_packed_tmap(const WeightView &w, CUtensorMap *out) {
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+// Tensor map of a scale / bias array as bytes [N][groups * 2], tile 128 rows x max(16, groups-per-unit * 2) bytes.
+static cudaError_t make_sb_tmap(const WeightView &w, const uint16_t *base, CUtensorMap *out) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return cudaErrorNotSupported;
+    const uint32_t gb = w.group * w.bits / 8u;
+    if (gb == 0 || kChunkBytes % gb != 0) return cudaErrorNotSupported;
+    const uint32_t gps = kChunkBytes / gb;
+    const uint32_t sbox = gps * 2u > 16u ? gps * 2u : 16u;
+    const uint64_t pitch = static_cast<uint64_t>(w.groups) * 2u;
+    if (reinterpret_cast<uintptr_t>(base) % 16u != 0 || pitch % 16u != 0) return cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {pitch, w.N};
+    const cuuint64_t strides[1] = {pitch};
+    const cuuint32_t box[2] = {sbox, static_cast<cuuint32_t>(kRows)};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint16_t *>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 void attach_packed_tmap(WeightView &w) {
-    w.has_tmap = make_packed_tmap(w, &w.tmap) == cudaSuccess;
+    w.has_tmap = make_packed_tmap(w, &w.tmap) == cudaSuccess && make_sb_tmap(w, w.scales, &w.tmap_s) == cudaSuccess &&
+                 make_sb_tmap(w, w.biases, &w.tmap_b) == cudaSuccess;
 }
 
 bool gemv_mma_eligible(const WeightView &w, const void *x, const void *y, bool x_f32) {
@@ -865,7 +1004,7 @@ size_t gemv_mma_scratch_bytes(const WeightView &w, uint32_t M, const GemvTuning 
 }
 
 size_t gemv_mma_counter_count(const WeightView &w) {
-    return static_cast<size_t>((w.N + kRows - 1u) / kRows) * kRowBlocks;
+    return static_cast<size_t>((w.N + kRows - 1u) / kRows);
 }
 
 cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bool x_f32,
@@ -898,22 +1037,16 @@ cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bo
     p.chunks = pl.chunks;
     p.units = pl.units;
     p.max_slots = pl.max_slots;
-    // one aligned vector load per row, unit and K half: a panel's groups must not straddle a row end
-    const uint32_t gpp = kPanelBytes / gb;
-    const size_t sb_bytes = static_cast<size_t>(gpp) * 2u;
-    p.vec_sb = (w.groups % gpp == 0 && reinterpret_cast<uintptr_t>(w.scales) % sb_bytes == 0 &&
-                reinterpret_cast<uintptr_t>(w.biases) % sb_bytes == 0)
-                   ? 1u
-                   : 0u;
+    p.probe = static_cast<uint32_t>(tune.probe);
     const bool pdl = tune.pdl != 0;
     if (w.bits == 4) {
-        if (gb == 16u) return dispatch_stream<16, 4>(p, w.tmap, pl.ctas, mt, x_f32, pdl, stream);
-        if (gb == 32u) return dispatch_stream<32, 4>(p, w.tmap, pl.ctas, mt, x_f32, pdl, stream);
-        if (gb == 64u) return dispatch_stream<64, 4>(p, w.tmap, pl.ctas, mt, x_f32, pdl, stream);
+        if (gb == 16u) return dispatch_stream<16, 4>(p, w, pl.ctas, mt, x_f32, pdl, stream);
+        if (gb == 32u) return dispatch_stream<32, 4>(p, w, pl.ctas, mt, x_f32, pdl, stream);
+        if (gb == 64u) return dispatch_stream<64, 4>(p, w, pl.ctas, mt, x_f32, pdl, stream);
     } else {
-        if (gb == 32u) return dispatch_stream<32, 8>(p, w.tmap, pl.ctas, mt, x_f32, pdl, stream);
-        if (gb == 64u) return dispatch_stream<64, 8>(p, w.tmap, pl.ctas, mt, x_f32, pdl, stream);
-        if (gb == 128u) return dispatch_stream<128, 8>(p, w.tmap, pl.ctas, mt, x_f32, pdl, stream);
+        if (gb == 32u) return dispatch_stream<32, 8>(p, w, pl.ctas, mt, x_f32, pdl, stream);
+        if (gb == 64u) return dispatch_stream<64, 8>(p, w, pl.ctas, mt, x_f32, pdl, stream);
+        if (gb == 128u) return dispatch_stream<128, 8>(p, w, pl.ctas, mt, x_f32, pdl, stream);
     }
     return cudaErrorNotSupported;
 }

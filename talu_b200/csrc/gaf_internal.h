@@ -23,7 +23,9 @@ struct WeightView {
     uint32_t row_bytes;      // K * bits / 8
     uint32_t groups;         // K / group
     CUtensorMap tmap;        // packed matrix as bytes [N][row_bytes] for the streaming GEMV
-    bool has_tmap;           // false: base / pitch not 16-byte aligned (generic kernel only)
+    CUtensorMap tmap_s;      // scales as bytes [N][groups * 2]
+    CUtensorMap tmap_b;      // biases as bytes [N][groups * 2]
+    bool has_tmap;           // false: a base or a row pitch is not 16-byte aligned (generic kernel only)
 };
 
 // Split-K scratch owned by a context.
@@ -38,6 +40,7 @@ struct GemvTuning {
     int ctas;           // persistent CTAs of the streaming GEMV (0 = one per SM)
     int pdl;            // launch with programmatic stream serialization
     int force_generic;  // use the shape-agnostic kernel even when the fast path applies
+    int probe;          // measurement aid for the streaming GEMV (0 = off); results are wrong when set
 };
 
 // y[M,N] = x[M,K] * W^T for M <= 16 on the tensor-core GEMV path.

@@ -1,0 +1,114 @@
+"""Multi-GPU leg of bench.py: the Llama-3-70B-shaped linear stack in gaf4_64,
+column- / row-sharded over the ranks (one process per GPU), NCCL allreduce on the
+row-parallel outputs.  Strong scaling: the stack is the same at every N."""
+from __future__ import annotations
+
+import json
+import os
+
+import numpy as np
+
+from . import gaf
+from .tp import LLAMA3_70B_LINEARS, SHARD_ROW, shard_slice
+
+GROUP, BITS = 64, 4
+HIDDEN = 8192
+
+
+def _weight_bytes(N, K):
+    return N * K * BITS // 8 + 2 * N * (K // GROUP) * 2
+
+
+def run(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    stream = torch.cuda.Stream()
+    ctx = gaf.Context(local, stream=stream.cuda_stream)
+    if world > 1:
+        ids = [gaf.make_comm_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        ctx.comm_init(ids[0], rank, world)
+
+    layers = args.layers if args.layers != 12 else 4          # distinct layers in the ring (1.9 GB over all ranks)
+    M = 1
+    rng = np.random.default_rng(1234)                          # same seed on every rank: same full weights
+    ws = []
+    for _ in range(layers):
+        for name, (N, K, kind) in LLAMA3_70B_LINEARS.items():
+            sl = shard_slice(N, K, GROUP, BITS, kind, rank, world)
+            # only this rank's slice is generated (timing does not depend on the values)
+            packed = rng.integers(0, 2 ** 32, size=(sl.n, sl.k * BITS // 32), dtype=np.uint32)
+            scales = (np.full((sl.n, sl.k // GROUP), 0.0053, np.float32).view(np.uint32) >> 16).astype(np.uint16)
+            biases = (np.full((sl.n, sl.k // GROUP), -0.04, np.float32).view(np.uint32) >> 16).astype(np.uint16)
+            ws.append((name, kind, gaf.Weight.from_host(ctx, packed, scales, biases, GROUP, BITS)))
+    xs = {k: torch.randn((M, k), device="cuda").to(torch.bfloat16) for k in {w.K for _, _, w in ws}}
+    ys = [torch.empty((M, w.N), dtype=torch.bfloat16, device="cuda") for _, _, w in ws]
+
+    def step():
+        for (name, kind, w), y in zip(ws, ys):
+            gaf.linear(ctx, w, xs[w.K], out=y)
+            if kind == SHARD_ROW and world > 1:
+                ctx.allreduce(y)          # partial sums of the row-parallel output -> full [M, 8192]
+
+    steps, warmup = args.steps, max(3, args.warmup)
+    with torch.cuda.stream(stream):
+        step()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+        for _ in range(warmup):
+            graph.replay()
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            graph.replay()
+        e1.record(stream)
+        stream.synchronize()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+
+    # whole-job algorithmic bytes: the full (unsharded) stack once per step
+    total = 0
+    for _ in range(layers):
+        for name, (N, K, kind) in LLAMA3_70B_LINEARS.items():
+            total += _weight_bytes(N, K) + M * K * 2 + M * N * 2
+    value = total / ms / 1e6
+    if rank == 0:
+        from bench import measured_peak_hbm
+        peak, kind = measured_peak_hbm()
+        per_rank_launches = len(ws)
+        print(json.dumps({
+            "metric": "gaf4_64 decode GEMV HBM GB/s", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 5), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "llama3_70b_stack", "scheme": "gaf4_64", "M": M, "layers": layers,
+                       "parallelism": f"tp{world}", "sharding": "qkv, gate|up column-parallel; o, down row-parallel + NCCL allreduce (bf16)",
+                       "l2": "distinct layers per step, ring larger than L2 on every rank",
+                       "timing": "CUDA graph replay, CUDA events, max over ranks"},
+            "roofline": {"bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s",
+                         "frac": round(value / world / peak, 4), "peak_kind": f"of {kind}", "traffic": None,
+                         "note": "per-GPU share of the aggregate; allreduce time included"},
+            "cpu_baseline": None,
+            "e2e": None,
+            "gpu_launches": per_rank_launches * steps * world,
+        }))
+    if world > 1:
+        ctx._lib.tgaf_comm_destroy(ctx._h)
+        dist.destroy_process_group()

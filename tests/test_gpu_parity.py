@@ -240,3 +240,45 @@ def test_invalid_arguments_are_status_codes(gaf, ctx, oracle):
     # the context is still usable after every rejected call
     y, ref = _run_bf16(gaf, ctx, oracle, 64, 256, 64, 4, 1)
     assert rel_err(y, ref) <= TOL_BF16
+
+
+@pytest.mark.parametrize("P", [2, 4, 8])
+def test_tensor_parallel_shards_on_one_gpu(gaf, ctx, oracle, P):
+    """tgaf_weight_upload's column / row sharding: every rank's shard is uploaded in turn on
+    this one GPU; column-parallel outputs are concatenated, row-parallel partials are summed
+    on the host, and both must match the unsharded oracle.  rel <= 1e-2."""
+    import torch
+    from talu_b200 import tp
+    G, bits, M = 64, 4, 2
+    hidden, ffn = 1024, 2048
+    up = make_weights(oracle, ffn, hidden, G, bits, seed=31)
+    down = make_weights(oracle, hidden, ffn, G, bits, seed=32)
+    xb, xf = make_x_bf16(oracle, M, hidden, seed=33)
+    x = torch_bf16_from_bits(xb, "cuda:0")
+    # column-parallel: rows of `up`
+    h_parts = []
+    for r in range(P):
+        w = gaf.Weight.from_host(ctx, *up, G, bits, shard=gaf.SHARD_COL, tp_rank=r, tp_size=P)
+        assert (w.N, w.K) == (ffn // P, hidden)
+        h_parts.append(gaf.linear(ctx, w, x))
+        ctx.synchronize()
+        w.free()
+    h = torch.cat(h_parts, dim=1)
+    h_ref = oracle.matmul_f32(xf, *up, G, bits)
+    assert rel_err(oracle.bf16_to_f32(bits_from_torch_bf16(h)), h_ref) <= TOL_BF16
+    # row-parallel: columns of `down`, fed with the matching slice of h (f32 entry point: exact partial sums)
+    hf = oracle.bf16_to_f32(bits_from_torch_bf16(h))
+    y = np.zeros((M, hidden), np.float64)
+    for r in range(P):
+        w = gaf.Weight.from_host(ctx, *down, G, bits, shard=gaf.SHARD_ROW, tp_rank=r, tp_size=P)
+        assert (w.N, w.K) == (hidden, ffn // P)
+        sl = tp.shard_slice(hidden, ffn, G, bits, tp.SHARD_ROW, r, P)
+        part = gaf.linear_host(ctx, w, np.ascontiguousarray(hf[:, sl.k0:sl.k1]))
+        y += part
+        w.free()
+    y_ref = oracle.matmul_f64(hf, *down, G, bits)
+    assert rel_err(y, y_ref) <= TOL_F32
+    with pytest.raises(gaf.GafError):
+        gaf.Weight.from_host(ctx, *down, G, bits, shard=gaf.SHARD_ROW, tp_rank=0, tp_size=5)   # K not divisible
+    with pytest.raises(gaf.GafError):
+        gaf.Weight.from_host(ctx, *up, G, bits, shard=gaf.SHARD_COL, tp_rank=3, tp_size=3)     # rank out of range
