@@ -219,7 +219,7 @@ def run_single(args):
     results = {}
     clocks = ClockSampler(dev)
     with clocks:
-        for M in (1, 4, 16):
+        for M in ((1,) if args.quick else (1, 4, 16)):
             xs, ys = make_io(M)
 
             def step():
@@ -230,6 +230,9 @@ def run_single(args):
             nbytes = sum(launch_bytes(w.N, w.K, M) for _, w in weights)
             results[M] = {"ms_per_step": ms, "gbs": nbytes / ms / 1e6, "bytes": nbytes}
 
+        if args.quick:
+            print(json.dumps({"quick": True, "M1_gbs": round(results[1]["gbs"], 2), "ms_per_step": results[1]["ms_per_step"]}))
+            return
         # ---- end to end through the C ABI with host buffers (pinned), M = 1 ----
         M = 1
         hx = {K: torch.randn((M, K)).to(torch.bfloat16).pin_memory() for K in (4096, 14336)}
@@ -296,6 +299,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=12, help="distinct FFN layers in the weight ring")
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="length of the CPU-baseline sample")
+    ap.add_argument("--quick", action="store_true",
+                    help="M = 1 only, no end-to-end and no CPU leg (small case for profilers; not a bench value)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
