@@ -119,6 +119,22 @@ int32_t tgaf_linear_bf16(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16
                          uint32_t M, void *y_bf16);
 int32_t tgaf_linear_f32(tgaf_ctx *ctx, const tgaf_weight *w, const float *x,
                         uint32_t M, float *y);
+/* No counterpart in the reference.  tgaf_linear_bf16 for hosts that must not allocate
+ * while they serve: a backend that gives the rest of the device's memory to its KV cache
+ * at start-up cannot afford a cudaMalloc in the token loop (it synchronises the device
+ * and may fail).  This call allocates nothing - no cudaMalloc / cudaFree, no growth of
+ * the context's scratch: the kernel's split-K scratch is a fixed 8 MiB (+ 8192 counters)
+ * device array inside the library image, present on every GPU that loads the library
+ * until the process exits.  x, y and the weight are the caller's, as in tgaf_linear_bf16.
+ *   - A problem that needs more scratch than that (very many output rows at M > 8) is
+ *     rejected with TGAF_ERR_UNSUPPORTED and a message; nothing is launched.
+ *   - The first call on a device looks the array's device address up; make that call
+ *     before any stream capture.
+ *   - All calls on a device share the array: calls that overlap on the GPU (two streams)
+ *     race.  The counters are cleared on the stream before each launch. */
+int32_t tgaf_linear_bf16_fixed_scratch(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16,
+                                       uint32_t M, void *y_bf16);
+
 /* Host-buffer variants: copy x to the device, run, copy y back, wait. */
 int32_t tgaf_linear_bf16_host(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16_host,
                               uint32_t M, void *y_bf16_host);

@@ -27,6 +27,7 @@ SIGNATURES = {
     "tgaf_weight_dims": (_i32, [_vp, C.POINTER(_u64), C.POINTER(_u64), C.POINTER(_u32), C.POINTER(_u32)]),
     "tgaf_linear_bf16": (_i32, [_vp, _vp, _vp, _u32, _vp]),
     "tgaf_linear_f32": (_i32, [_vp, _vp, _vp, _u32, _vp]),
+    "tgaf_linear_bf16_fixed_scratch": (_i32, [_vp, _vp, _vp, _u32, _vp]),
     "tgaf_linear_bf16_host": (_i32, [_vp, _vp, _vp, _u32, _vp]),
     "tgaf_linear_f32_host": (_i32, [_vp, _vp, _vp, _u32, _vp]),
     "tgaf_gaffine_u4_matvec_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32]),

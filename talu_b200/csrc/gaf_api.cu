@@ -534,6 +534,37 @@ int32_t tgaf_linear_f32(tgaf_ctx *ctx, const tgaf_weight *w, const float *x, uin
     return linear_device(ctx, w->v, x, M, y, true);
 }
 
+int32_t tgaf_linear_bf16_fixed_scratch(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16, uint32_t M,
+                                       void *y_bf16) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!w || !x_bf16 || !y_bf16) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null pointer");
+    if (M == 0) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "M must be > 0");
+    // nothing below allocates: no cudaMalloc / cudaFree, no growth of the context's scratch
+    TGAF_CUDA(ctx, cudaSetDevice(ctx->device));
+    const WeightView &v = w->v;
+    if (ctx->tune.force_generic || !gemv_mma_eligible(v, x_bf16, y_bf16, false)) {
+        // shapes outside the fast path use the kernel that needs no scratch at all
+        cudaError_t e = gemv_generic(v, x_bf16, y_bf16, M, false, ctx->stream);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "gemv_generic launch");
+        return TGAF_OK;
+    }
+    for (uint32_t m0 = 0; m0 < M; m0 += 16u) {
+        const uint32_t mc = (M - m0) < 16u ? (M - m0) : 16u;
+        const void *xp = static_cast<const uint8_t *>(x_bf16) + static_cast<size_t>(m0) * v.K * 2u;
+        void *yp = static_cast<uint8_t *>(y_bf16) + static_cast<size_t>(m0) * v.N * 2u;
+        size_t need = 0;
+        cudaError_t e = gemv_mma_static(v, xp, yp, mc, false, ctx->tune, ctx->stream, ctx->sm_count, ctx->device,
+                                        ctx->d_error_word, &need);
+        if (e == cudaErrorMemoryAllocation)
+            return fail(ctx, TGAF_ERR_UNSUPPORTED,
+                        "this problem needs %zu bytes of split-K scratch (or more than 8192 row groups); the fixed "
+                        "scratch holds %zu bytes - use tgaf_linear_bf16",
+                        need, gemv_static_scratch_capacity());
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "fixed-scratch gemv launch");
+    }
+    return TGAF_OK;
+}
+
 int32_t tgaf_linear_bf16_host(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16_host, uint32_t M,
                               void *y_bf16_host) {
     return linear_host(ctx, w, x_bf16_host, M, y_bf16_host, false);

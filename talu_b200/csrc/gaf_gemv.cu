@@ -1051,6 +1051,65 @@ cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bo
     return cudaErrorNotSupported;
 }
 
+// ---------------------------------------------------------------------------
+// Streaming GEMV on a fixed scratch that lives in the library image.
+//
+// Some hosts must not allocate once they are serving: they hand the rest of the
+// device's memory to their own KV-cache / arena at start-up, and cudaMalloc or
+// cudaFree later would synchronise the whole device in the middle of a token
+// step, or simply fail.  For them the split-K scratch (partial sums + arrival
+// counters) of this variant is a file-scope device array of a fixed size; every
+// GPU that loads the library carries it until the process exits.
+//
+// In host code the array's name is only a stand-in for the symbol, not a device
+// address; the address is looked up once per device, with that device current,
+// by cudaGetSymbolAddress (first call on a device: make it before any stream
+// capture).  All calls on a device share the array and it keeps whatever the
+// last call left: the counters are cleared on the stream before each launch, the
+// partial sums are always written before they are read.  Two calls that overlap
+// on the GPU (different streams) would race on it.
+// ---------------------------------------------------------------------------
+constexpr size_t kStaticPartialBytes = size_t(8) << 20;  // fp32 partial sums
+constexpr size_t kStaticCounters = 8192;                 // one per 128-row group
+constexpr size_t kStaticScratchBytes = kStaticPartialBytes + kStaticCounters * sizeof(unsigned int);
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void *g_static_ptr[kMaxDevices];  // device address of g_static_scratch, per device (0 = not looked up yet)
+
+size_t gemv_static_scratch_capacity() { return kStaticPartialBytes; }
+
+cudaError_t gemv_mma_static(const WeightView &w, const void *x, void *y, uint32_t M, bool x_f32,
+                            const GemvTuning &tune, cudaStream_t stream, int sm_count, int device,
+                            unsigned int *d_error_word, size_t *needed_bytes) {
+    if (needed_bytes) *needed_bytes = 0;
+    if (M == 0 || M > 16u) return cudaErrorNotSupported;
+    if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+    if (!gemv_mma_eligible(w, x, y, x_f32)) return cudaErrorNotSupported;
+    const size_t need = gemv_mma_scratch_bytes(w, M, tune, sm_count);
+    if (needed_bytes) *needed_bytes = need;
+    if (need > kStaticPartialBytes || gemv_mma_counter_count(w) > kStaticCounters) return cudaErrorMemoryAllocation;
+    if (!g_static_ptr[device]) {
+        // set-up, once per device: `device` must be the current device here
+        void *ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess) return e;
+        g_static_ptr[device] = ptr;
+    }
+    unsigned char *base = static_cast<unsigned char *>(g_static_ptr[device]);
+    Scratch sc;
+    sc.partials = reinterpret_cast<float *>(base);
+    sc.partial_bytes = kStaticPartialBytes;
+    sc.counters = reinterpret_cast<unsigned int *>(base + kStaticPartialBytes);
+    sc.counter_count = kStaticCounters;
+    // the counters must start at zero; the previous call (or an abandoned one) may have left anything
+    cudaError_t e = cudaMemsetAsync(sc.counters, 0, gemv_mma_counter_count(w) * sizeof(unsigned int), stream);
+    if (e != cudaSuccess) return e;
+    GemvTuning t = tune;
+    t.pdl = 0;  // the memset before the launch is a full dependency anyway
+    return gemv_mma(w, x, y, M, x_f32, sc, t, stream, sm_count, d_error_word);
+}
+
 cudaError_t gemv_generic(const WeightView &w, const void *x, void *y, uint32_t M, bool x_f32,
                          cudaStream_t stream) {
     if (M == 0) return cudaErrorInvalidValue;

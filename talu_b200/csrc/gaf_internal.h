@@ -58,6 +58,14 @@ cudaError_t make_packed_tmap(const WeightView &w, CUtensorMap *out);
 size_t gemv_mma_scratch_bytes(const WeightView &w, uint32_t M, const GemvTuning &tune, int sm_count);
 size_t gemv_mma_counter_count(const WeightView &w);
 
+// Same kernel on the library's fixed device-resident scratch: allocates nothing.
+// cudaErrorMemoryAllocation: the problem needs more scratch than the fixed array holds
+// (*needed_bytes tells how much); cudaErrorNotSupported: shape not eligible for the fast path.
+cudaError_t gemv_mma_static(const WeightView &w, const void *x, void *y, uint32_t M, bool x_f32,
+                            const GemvTuning &tune, cudaStream_t stream, int sm_count, int device,
+                            unsigned int *d_error_word, size_t *needed_bytes);
+size_t gemv_static_scratch_capacity();
+
 // Any shape the reference accepts, any M.  f32 arithmetic, per-element dequant.
 cudaError_t gemv_generic(const WeightView &w, const void *x, void *y, uint32_t M, bool x_f32,
                          cudaStream_t stream);

@@ -181,6 +181,23 @@ def linear(ctx: Context, w: Weight, x, out=None):
     return out
 
 
+def linear_fixed_scratch(ctx: Context, w: Weight, x, out=None):
+    """`linear` for bf16 activations through tgaf_linear_bf16_fixed_scratch: the library call
+    allocates nothing (its split-K scratch is a fixed array inside the library image).  The
+    output tensor is the caller's; pass `out` to keep this wrapper from allocating one."""
+    import torch
+    if x.dim() != 2 or x.shape[1] != w.K or x.dtype != torch.bfloat16:
+        raise GafError(_STATUS_INVALID_ARGUMENT, f"x must be bf16 [M, {w.K}], got {x.dtype} {tuple(x.shape)}")
+    if not x.is_contiguous():
+        x = x.contiguous()
+    M = x.shape[0]
+    if out is None:
+        out = torch.empty((M, w.N), dtype=x.dtype, device=x.device)
+    ctx._check(ctx._lib.tgaf_linear_bf16_fixed_scratch(ctx._h, w._h, C.c_void_p(x.data_ptr()), M,
+                                                       C.c_void_p(out.data_ptr())))
+    return out
+
+
 def linear_host(ctx: Context, w: Weight, x: np.ndarray, out: np.ndarray | None = None) -> np.ndarray:
     """Same through host buffers: x uint16 (bf16 bit patterns) or float32 [M, K]."""
     x = np.ascontiguousarray(x)
