@@ -282,3 +282,32 @@ def test_tensor_parallel_shards_on_one_gpu(gaf, ctx, oracle, P):
         gaf.Weight.from_host(ctx, *down, G, bits, shard=gaf.SHARD_ROW, tp_rank=0, tp_size=5)   # K not divisible
     with pytest.raises(gaf.GafError):
         gaf.Weight.from_host(ctx, *up, G, bits, shard=gaf.SHARD_COL, tp_rank=3, tp_size=3)     # rank out of range
+
+
+def _prefill_case(gaf, ctx, oracle, M, N, K, G, seed):
+    import torch
+    p, s, b = make_weights(oracle, N, K, G, 4, seed)
+    xb, xf = make_x_bf16(oracle, M, K, seed + 1)
+    w = gaf.Weight.from_host(ctx, p, s, b, G, 4)
+    y = gaf.linear(ctx, w, torch_bf16_from_bits(xb, "cuda:0"))
+    ctx.synchronize()
+    got = oracle.bf16_to_f32(bits_from_torch_bf16(y))
+    w.free()
+    ref = oracle.matmul_f32(xf, p, s, b, G, 4)
+    return got, ref
+
+
+@pytest.mark.parametrize("M,N,K,G", [(256, 256, 128, 64), (128, 512, 1024, 64), (300, 1000, 512, 32),
+                                     (515, 768, 2048, 128), (1024, 2048, 4096, 64)])
+def test_prefill_tensor_core_gemm(gaf, ctx, oracle, M, N, K, G):
+    """Prefill dequant-GEMM (tcgen05 path, M >= 128): full tiles, ragged M and N, every group size.
+    Weights are rounded to bf16 after the affine (one rounding), fp32 accumulate, bf16 out.  rel <= 1e-2."""
+    got, ref = _prefill_case(gaf, ctx, oracle, M, N, K, G, seed=M + N)
+    assert rel_err(got, ref) <= TOL_BF16, (M, N, K, G, rel_err(got, ref))
+
+
+def test_prefill_cfg4_full_size(gaf, ctx, oracle):
+    """The prefill benchmark shape: M=2048, K=4096, N=14336, gaf4_64.  rel <= 1e-2 against the CPU oracle
+    on every one of the 29M outputs."""
+    got, ref = _prefill_case(gaf, ctx, oracle, 2048, 14336, 4096, 64, seed=4)
+    assert rel_err(got, ref) <= TOL_BF16, rel_err(got, ref)
