@@ -193,6 +193,48 @@ def time_graph(ctx, torch, stream, launch_step, steps, warmup):
     return e0.elapsed_time(e1) / steps
 
 
+def measured_peak_tflops():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            j = json.loads(p.read_text())
+            return float(j["bf16_tflops"]), float(j["bf16_tflops_sustained"]), "measured"
+        except Exception:
+            pass
+    return 1590.0, 1400.0, "fallback"
+
+
+def time_prefill(gaf, ctx, torch, stream, rng, iters=20):
+    """gaf4_64 prefill dequant-GEMM: x bf16 [2048, 4096], W [14336, 4096] (tcgen05 path).
+    TFLOP/s = 2*M*N*K / time; the dequant work is not counted."""
+    M, K, N = 2048, 4096, 14336
+    ws = [gaf.Weight.from_host(ctx, *synth_weight(rng, N, K), GROUP, BITS) for _ in range(2)]
+    x = torch.randn((M, K), device="cuda").to(torch.bfloat16)
+    y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            for w in ws:
+                gaf.linear(ctx, w, x, out=y)
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            for w in ws:
+                gaf.linear(ctx, w, x, out=y)
+        e1.record(stream)
+        stream.synchronize()
+    ctx.synchronize()
+    ms = e0.elapsed_time(e1) / (iters * len(ws))
+    tf = 2.0 * M * N * K / ms / 1e9
+    burst, sustained, kind = measured_peak_tflops()
+    for w in ws:
+        w.free()
+    return {"workload": "gaf4_64 prefill M=2048 K=4096 N=14336", "tflops": round(tf, 1), "ms": round(ms, 4),
+            "frac_of_burst_peak": round(tf / burst, 4), "frac_of_sustained_peak": round(tf / sustained, 4),
+            "peak_tflops": {"burst": burst, "sustained": sustained, "kind": f"of {kind}"},
+            "bound": "tensor"}
+
+
 def run_single(args):
     import torch
     import talu_b200 as gaf
@@ -259,6 +301,8 @@ def run_single(args):
     d2h = sum(M * w.N * 2 for _, w in weights)
     e2e_gbs = results[1]["bytes"] / e2e_ms / 1e6
 
+    prefill = time_prefill(gaf, ctx, torch, stream, rng)
+
     peak, peak_kind = measured_peak_hbm()
     launches_per_step = len(weights)
     avg_launch_ms = results[1]["ms_per_step"] / launches_per_step
@@ -285,6 +329,7 @@ def run_single(args):
                          "sample": f"{cpu_n} calls of one gate-shaped matrix [14336 x 4096], M=1, f32 activations ({cpu_per_call * 1e3:.2f} ms each)"},
         "e2e": {"value": round(e2e_gbs, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": round(e2e_ms, 4), "note": "tgaf_linear_bf16_host per launch: pinned host x -> device, kernel, y -> pinned host, stream wait"},
+        "prefill": prefill,
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks.summary(),
     }
