@@ -258,6 +258,9 @@ def run_single(args):
         ys = [torch.empty((M, w.N), dtype=torch.bfloat16, device="cuda") for _, w in weights]
         return xs, ys
 
+    if args.quick and args.case == "prefill":
+        print(json.dumps({"quick": True, "prefill": time_prefill(gaf, ctx, torch, stream, rng, iters=2)}))
+        return
     results = {}
     clocks = ClockSampler(dev)
     with clocks:
@@ -344,6 +347,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=12, help="distinct FFN layers in the weight ring")
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="length of the CPU-baseline sample")
+    ap.add_argument("--case", default="decode", choices=["decode", "prefill"],
+                    help="with --quick: which kernel the small case runs")
     ap.add_argument("--quick", action="store_true",
                     help="M = 1 only, no end-to-end and no CPU leg (small case for profilers; not a bench value)")
     args = ap.parse_args()
