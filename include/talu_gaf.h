@@ -172,6 +172,9 @@ int32_t tgaf_dequant_f32_host(tgaf_ctx *ctx, const tgaf_weight *w, float *h_out)
 #define TGAF_COMM_ID_BYTES 128
 int32_t tgaf_comm_make_id(uint8_t id[TGAF_COMM_ID_BYTES]);
 int32_t tgaf_comm_init(tgaf_ctx *ctx, const uint8_t id[TGAF_COMM_ID_BYTES], uint32_t rank, uint32_t nranks);
+/* Waits for the context's stream, then destroys the communicator.  Release every CUDA graph
+ * that captured tgaf_allreduce first: NCCL waits for them.  tgaf_ctx_destroy aborts a
+ * communicator that is still there instead of waiting. */
 int32_t tgaf_comm_destroy(tgaf_ctx *ctx);
 /* in place, on the context's stream */
 int32_t tgaf_allreduce(tgaf_ctx *ctx, void *d_buf, uint64_t count, uint32_t dtype);

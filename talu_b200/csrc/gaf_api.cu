@@ -33,6 +33,7 @@ struct NcclApi {
     int (*GetUniqueId)(NcclUniqueId *) = nullptr;
     int (*CommInitRank)(NcclComm *, int, NcclUniqueId, int) = nullptr;
     int (*CommDestroy)(NcclComm) = nullptr;
+    int (*CommAbort)(NcclComm) = nullptr;
     int (*AllReduce)(const void *, void *, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
     const char *(*GetErrorString)(int) = nullptr;
     bool ok = false;
@@ -56,6 +57,7 @@ NcclApi &nccl_api() {
     api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(api.handle, "ncclGetUniqueId"));
     api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(api.handle, "ncclCommInitRank"));
     api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(api.handle, "ncclCommDestroy"));
+    api.CommAbort = reinterpret_cast<decltype(api.CommAbort)>(dlsym(api.handle, "ncclCommAbort"));
     api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(api.handle, "ncclAllReduce"));
     api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(api.handle, "ncclGetErrorString"));
     api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce && api.GetErrorString;
@@ -319,7 +321,13 @@ int32_t tgaf_ctx_destroy(tgaf_ctx *ctx) {
     if (!ctx) return TGAF_OK;
     cudaSetDevice(ctx->device);
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
-    if (ctx->comm) tgaf_comm_destroy(ctx);
+    if (ctx->comm) {
+        // tearing a context down must never block (ncclCommDestroy waits for anything that still refers
+        // to the communicator, e.g. a captured graph the caller has not released): abort instead
+        NcclApi &api = nccl_api();
+        if (api.ok && api.CommAbort) api.CommAbort(ctx->comm);
+        ctx->comm = nullptr;
+    }
     if (ctx->scratch.partials) cudaFree(ctx->scratch.partials);
     if (ctx->scratch.counters) cudaFree(ctx->scratch.counters);
     if (ctx->stage_x) cudaFree(ctx->stage_x);
@@ -646,6 +654,7 @@ int32_t tgaf_comm_destroy(tgaf_ctx *ctx) {
     if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
     if (!ctx->comm) return TGAF_OK;
     NcclApi &api = nccl_api();
+    cudaStreamSynchronize(ctx->stream);
     if (api.ok) api.CommDestroy(ctx->comm);
     ctx->comm = nullptr;
     ctx->comm_size = 1;

@@ -26,15 +26,30 @@ def run(args):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    debug = os.environ.get("TGAF_BENCH_DEBUG") == "1"
+
+    def note(msg):
+        if debug:
+            import sys
+            print(f"[rank {rank}] {msg}", file=sys.stderr, flush=True)
+
+    if debug:
+        import faulthandler
+        faulthandler.dump_traceback_later(60, exit=True)   # where are we if nothing moves for a minute
     torch.cuda.set_device(local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # control plane (id hand-over, barriers, max of timings) over gloo; the data path is the
+        # library's own NCCL communicator
+        dist.init_process_group("gloo")
+    note("process group up")
     stream = torch.cuda.Stream()
     ctx = gaf.Context(local, stream=stream.cuda_stream)
     if world > 1:
         ids = [gaf.make_comm_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
+        note("comm id exchanged")
         ctx.comm_init(ids[0], rank, world)
+        note("communicator initialised")
 
     layers = args.layers if args.layers != 12 else 4          # distinct layers in the ring (1.9 GB over all ranks)
     M = 1
@@ -58,15 +73,19 @@ def run(args):
                 ctx.allreduce(y)          # partial sums of the row-parallel output -> full [M, 8192]
 
     steps, warmup = args.steps, max(3, args.warmup)
+    note(f"{len(ws)} weights uploaded")
     with torch.cuda.stream(stream):
         step()
         stream.synchronize()
+        note("eager step done")
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
+        with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
             step()
+        note("graph captured")
         for _ in range(warmup):
             graph.replay()
         stream.synchronize()
+        note("warm-up done")
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
@@ -79,10 +98,11 @@ def run(args):
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
-    ms = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda")
+    ms = torch.tensor([e0.elapsed_time(e1) / steps])
     if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)     # max over ranks (device-timed on every rank)
     ms = float(ms.item())
+    note(f"timed: {ms} ms/step")
 
     # whole-job algorithmic bytes: the full (unsharded) stack once per step
     total = 0
@@ -109,6 +129,14 @@ def run(args):
             "e2e": None,
             "gpu_launches": per_rank_launches * steps * world,
         }))
+    # the captured graph refers to the communicator: release it before the communicator goes
+    del graph
+    torch.cuda.synchronize()
     if world > 1:
+        dist.barrier()
         ctx._lib.tgaf_comm_destroy(ctx._h)
+        note("communicator destroyed")
         dist.destroy_process_group()
+    if debug:
+        import faulthandler
+        faulthandler.cancel_dump_traceback_later()
