@@ -305,6 +305,11 @@ def run_single(args):
     e2e_gbs = results[1]["bytes"] / e2e_ms / 1e6
 
     prefill = time_prefill(gaf, ctx, torch, stream, rng)
+    # the multi-GPU workload on this one GPU, so that the N > 1 lines have their N = 1 reference
+    from talu_b200 import tp_bench
+    st_ms, st_bytes, st_launches, st_layers, *_ = tp_bench.measure(args, existing_ctx=ctx, existing_stream=stream)
+    stack70b = {"workload": "llama3_70b_stack", "layers": st_layers, "ms_per_step": round(st_ms, 5),
+                "gbs": round(st_bytes / st_ms / 1e6, 2), "launches_per_step": st_launches}
 
     peak, peak_kind = measured_peak_hbm()
     launches_per_step = len(weights)
@@ -333,6 +338,7 @@ def run_single(args):
         "e2e": {"value": round(e2e_gbs, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": round(e2e_ms, 4), "note": "tgaf_linear_bf16_host per launch: pinned host x -> device, kernel, y -> pinned host, stream wait"},
         "prefill": prefill,
+        "llama3_70b_stack_1gpu": stack70b,
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks.summary(),
     }

@@ -76,7 +76,7 @@ struct tgaf_ctx {
     bool owns_stream = false;
     int sm_count = 148;
     Scratch scratch = {nullptr, 0, nullptr, 0};
-    GemvTuning tune = {0, 1, 0, 0};
+    GemvTuning tune = {0, 1, 0, 0, 0};
     // staging for the *_host entry points
     void *stage_x = nullptr;
     size_t stage_x_bytes = 0;
@@ -373,6 +373,8 @@ int32_t tgaf_ctx_set_option(tgaf_ctx *ctx, const char *name, int64_t value) {
         ctx->tune.pdl = value != 0;
     } else if (!strcmp(name, "force_generic")) {
         ctx->tune.force_generic = value != 0;
+    } else if (!strcmp(name, "no_dp4a")) {
+        ctx->tune.no_dp4a = value != 0;
     } else if (!strcmp(name, "probe")) {
         ctx->tune.probe = static_cast<int>(value);
     } else {

@@ -778,6 +778,421 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
 }
 
 // ---------------------------------------------------------------------------
+// Streaming GEMV for M <= 2 on the integer dot-product unit.
+//
+// With one or two activation rows the tensor-core formulation above wastes seven
+// of its eight columns and is bound by instruction issue (unpack + fragment
+// bookkeeping per 16 rows).  Here every lane owns whole weight rows instead:
+//   * activations are turned, once per CTA and K block, into 13-bit integers per
+//     group (x ~ xi * 2^(E-12), E from the group's largest |x|, |xi| <= 4095) and
+//     split into two signed bytes xi = 64 * hi + lo;
+//   * a packed word yields its even and odd nibbles as bytes with three integer
+//     ops; four dp4a (u8 x s8 -> s32) per word accumulate sum(q * hi), sum(q * lo)
+//     exactly;
+//   * per group and row: y += s * 2^(E-12) * (64 * acc_hi + acc_lo) + b * sum(x).
+// The quantisation error of x is at most 2^-13 of the group's largest |x| per
+// element (bf16 inputs carry 2^-9 relative), far inside the 1e-2 budget.
+// Same producer / ring / split-K protocol as the tensor-core kernel; warp =
+// (group of the unit, block of rows), lane = row.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+template <int GB, int MD, bool XF32>
+struct DpPlan {
+    static constexpr int GPS = kChunkBytes / GB;           // groups per unit
+    static constexpr int WPG = GB / 4;                     // packed words per group and row
+    static constexpr int XQ_GROUP = WPG * MD * 16;         // quantised activations of one group: 16 bytes per word and row
+    static constexpr int XQ_UNIT = GPS * XQ_GROUP;         // 1 KB per activation row for any group size
+    static constexpr int XI_UNIT = GPS * MD * 8;           // {2^(E-12), sum x} per group and activation row
+    static constexpr int OUT_BUF = GPS * kRows * MD * 4;   // per-group partial sums of one row group
+    static constexpr int OFF_XQ = kStages * StreamGeom<GB>::STAGE_BYTES;
+    static constexpr int OFF_XI = OFF_XQ + 2 * kMaxBlockUnits * XQ_UNIT;
+    static constexpr int OFF_OUT = OFF_XI + 2 * kMaxBlockUnits * XI_UNIT;
+    static constexpr int TOTAL = OFF_OUT + 2 * OUT_BUF + 1024;
+};
+
+template <int GB, int MD, bool XF32, int SD>
+__global__ void __launch_bounds__(kThreads, 1)
+gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap_w,
+                     const __grid_constant__ CUtensorMap tmap_s, const __grid_constant__ CUtensorMap tmap_b) {
+    using Geo = StreamGeom<GB>;
+    using Plan = DpPlan<GB, MD, XF32>;
+    constexpr int GPS = Geo::GPS, WPG = Plan::WPG;
+    constexpr int RW = kRows * GPS / kConsumerWarps;  // rows per warp: 128 (G=32), 64 (G=64), 32 (G=128)
+    constexpr int R = RW / 32;                        // rows per lane
+    constexpr int CH = GB / 16;                       // 16-byte chunks per group and row
+    static_assert(R >= 1 && GPS * (kRows / RW) == kConsumerWarps, "unsupported group size");
+
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t s_full[kStages];
+    __shared__ __align__(8) uint64_t s_empty[kStages];
+    __shared__ __align__(8) uint64_t s_out_full[2];
+    __shared__ __align__(8) uint64_t s_out_empty[2];
+    __shared__ volatile uint32_t s_abort;
+
+    const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0u;
+#pragma unroll
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&s_full[s]), 1);
+            mbar_init(smem_u32(&s_empty[s]), kConsumerWarps);
+        }
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&s_out_full[s]), kConsumerWarps);
+            mbar_init(smem_u32(&s_out_empty[s]), 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const uint32_t u_begin = range_begin(blockIdx.x, p.units, gridDim.x);
+    const uint32_t u_end = range_begin(blockIdx.x + 1u, p.units, gridDim.x);
+    if (u_begin >= u_end) return;
+    const uint32_t rg_begin = u_begin / p.chunks;
+    const uint32_t kc_begin = u_begin - rg_begin * p.chunks;
+
+    if (warp == kConsumerWarps) {
+        // ------------------------- producer warp (one lane works) -------------------------
+        if (lane != 0) return;
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_s)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_b)) : "memory");
+        uint32_t issued = 0, rg = rg_begin, kc = kc_begin;
+        bool ok = true;
+        for (uint32_t u = u_begin; u < u_end; ++u, ++issued) {
+            const uint32_t stage = issued % kStages;
+            const uint32_t round = issued / kStages;
+            if (round > 0) ok = mbar_wait(smem_u32(&s_empty[stage]), (round - 1u) & 1u, p.error_word, 0x1u);
+            if (!ok) break;
+            const uint32_t full = smem_u32(&s_full[stage]);
+            if (p.probe & 2u) {
+                mbar_arrive(full);
+            } else {
+                const uint32_t base = ring + stage * Geo::STAGE_BYTES;
+                mbar_arrive_expect_tx(full, Geo::STAGE_BYTES);
+#pragma unroll
+                for (int pnl = 0; pnl < kPanels; ++pnl)
+                    tma_load_2d(base + pnl * kPanelSize, &tmap_w, kc * kChunkBytes + pnl * kPanelBytes, rg * kRows, full);
+                const uint32_t sb_col = (kc * GPS * 2u) & ~15u;
+                tma_load_2d(base + kWeightBytes, &tmap_s, sb_col, rg * kRows, full);
+                tma_load_2d(base + kWeightBytes + Geo::SB_BYTES, &tmap_b, sb_col, rg * kRows, full);
+            }
+            if (++kc == p.chunks) kc = 0u, ++rg;
+        }
+        if (!ok) {
+            const uint32_t pending = issued < static_cast<uint32_t>(kStages) ? issued : static_cast<uint32_t>(kStages);
+            for (uint32_t i = 0; i < pending; ++i) {
+                const uint32_t idx = issued - 1u - i;
+                mbar_wait(smem_u32(&s_full[idx % kStages]), (idx / kStages) & 1u, p.error_word, 0x4u);
+            }
+        }
+        return;
+    }
+
+    if (warp == kConsumerWarps + 1) {
+        // ------------------------- writer warp -------------------------
+        // lane owns rows lane, lane + 32, lane + 64, lane + 96 of the row group
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        const uint32_t rg_last_touched = (u_end - 1u) / p.chunks;
+        uint32_t ob = 0, ophase = 0;
+        for (uint32_t rg = rg_begin; rg <= rg_last_touched; ++rg) {
+            if (!mbar_wait(smem_u32(&s_out_full[ob]), ophase, p.error_word, 0x8u)) return;
+            const uint32_t rg_first = rg * p.chunks, rg_last = rg_first + p.chunks - 1u;
+            const bool whole = u_begin <= rg_first && rg_last < u_end;
+            uint32_t slots = 1u, slot = 0u;
+            if (!whole) {
+                const uint32_t first_cta = unit_owner(rg_first, p.units, gridDim.x);
+                slots = unit_owner(rg_last, p.units, gridDim.x) - first_cta + 1u;
+                slot = blockIdx.x - first_cta;
+            }
+            // scratch slot layout [128 rows][8]: the same footprint as the tensor-core kernel's single tile
+            float *mine = p.partials + (static_cast<size_t>(rg) * p.max_slots + slot) * (kRows * 8);
+            const uint32_t obuf = ring + Plan::OFF_OUT + ob * Plan::OUT_BUF;
+            auto store = [&](uint32_t m, uint32_t n, float val) {
+                if (m < p.M && n < p.N) {
+                    if constexpr (XF32)
+                        static_cast<float *>(p.y)[static_cast<size_t>(m) * p.N + n] = val;
+                    else
+                        static_cast<__nv_bfloat16 *>(p.y)[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(val);
+                }
+            };
+            float sum[4][MD];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t row = lane + 32u * i;
+#pragma unroll
+                for (int m = 0; m < MD; ++m) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int gq = 0; gq < GPS; ++gq) {  // fixed order over the unit's groups
+                        float v;
+                        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(obuf + ((gq * kRows + row) * MD + m) * 4u));
+                        a += v;
+                    }
+                    sum[i][m] = a;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&s_out_empty[ob]));
+            if (!(p.probe & 4u)) {
+                if (whole) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+#pragma unroll
+                        for (int m = 0; m < MD; ++m) store(m, rg * kRows + lane + 32u * i, sum[i][m]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+#pragma unroll
+                        for (int m = 0; m < MD; ++m) mine[(lane + 32u * i) * 8 + m] = sum[i][m];
+                    __syncwarp();
+                    unsigned int ticket = 0;
+                    if (lane == 0)
+                        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(ticket) : "l"(p.counters + rg) : "memory");
+                    ticket = __shfl_sync(0xFFFFFFFFu, ticket, 0);
+                    if (ticket == slots - 1u) {
+                        const float *all = p.partials + static_cast<size_t>(rg) * p.max_slots * (kRows * 8);
+                        float tot[4][MD];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+#pragma unroll
+                            for (int m = 0; m < MD; ++m) tot[i][m] = 0.f;
+                        for (uint32_t sidx = 0; sidx < slots; ++sidx) {  // fixed order: reproducible sums
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                                for (int m = 0; m < MD; ++m)
+                                    tot[i][m] += __ldcg(all + static_cast<size_t>(sidx) * (kRows * 8) + (lane + 32u * i) * 8 + m);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+#pragma unroll
+                            for (int m = 0; m < MD; ++m) store(m, rg * kRows + lane + 32u * i, tot[i][m]);
+                        if (lane == 0) p.counters[rg] = 0u;
+                    }
+                }
+            }
+            ob ^= 1u;
+            if (ob == 0u) ophase ^= 1u;
+        }
+        return;
+    }
+
+    // --------------------------- consumer warps ---------------------------
+    const uint32_t gq = warp % GPS;          // group of the unit this warp works on
+    const uint32_t rbase = (warp / GPS) * RW;  // first of its rows
+    const uint8_t *xbase = static_cast<const uint8_t *>(p.x);
+    const size_t x_elt = XF32 ? 4 : 2;
+
+    uint32_t block_units = kMaxBlockUnits;
+
+    // shared-memory offsets of this lane's rows: first 16-byte chunk of the group, swizzled
+    uint32_t woff[R], sboff[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        const uint32_t row = rbase + lane + 32u * i;
+        const uint32_t ob = gq * GB;              // byte offset of the group inside the unit's 256 bytes
+        const uint32_t pnl = ob / kPanelBytes, inp = ob % kPanelBytes;
+        woff[i] = ring + pnl * kPanelSize + row * kPanelBytes + ((((inp >> 4) ^ row) & 7u) << 4);
+        sboff[i] = ring + kWeightBytes + row * Geo::SBOX + gq * 2u;
+    }
+    const uint32_t xq_warp = ring + Plan::OFF_XQ + gq * Plan::XQ_GROUP;
+    const uint32_t xi_warp = ring + Plan::OFF_XI + gq * MD * 8u;
+    const uint32_t out_warp = ring + Plan::OFF_OUT + gq * (kRows * MD * 4u);
+
+    float yacc[R][MD];
+#pragma unroll
+    for (int i = 0; i < R; ++i)
+#pragma unroll
+        for (int m = 0; m < MD; ++m) yacc[i][m] = 0.f;
+
+    // ---- quantised activations for a block of units: (unit, group, activation row) triples over the warps ----
+    auto prep_block = [&](uint32_t kc_first, uint32_t count, uint32_t buf) {
+        for (uint32_t pi = warp; pi < count * GPS * MD; pi += kConsumerWarps) {
+            const uint32_t m = pi % MD, gl = (pi / MD) % GPS, ub = pi / (MD * GPS);
+            const uint32_t gi = ((kc_first + ub) % p.chunks) * GPS + gl;
+            constexpr int G = GB * 2;                   // elements per group (4-bit codes)
+            constexpr int PER = G / 32;                 // elements per lane: 1 (G=32), 2, 4
+            float xv[PER];
+            const bool live = m < p.M && gi < p.groups;
+#pragma unroll
+            for (int e = 0; e < PER; ++e) {
+                const size_t idx = static_cast<size_t>(m) * p.K + static_cast<size_t>(gi) * G + lane * PER + e;
+                float v = 0.f;
+                if (live) {
+                    if constexpr (XF32)
+                        v = reinterpret_cast<const float *>(xbase)[idx];
+                    else
+                        v = __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(xbase)[idx]);
+                }
+                xv[e] = v;
+            }
+            float amax = 0.f, ssum = 0.f;
+#pragma unroll
+            for (int e = 0; e < PER; ++e) amax = fmaxf(amax, fabsf(xv[e])), ssum += xv[e];
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) {
+                amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
+                ssum += __shfl_xor_sync(0xFFFFFFFFu, ssum, off);
+            }
+            // 2^(E-1) <= amax < 2^E; xi = rint(x * 2^(12-E)), |xi| <= 4095
+            int E = 0;
+            if (amax > 0.f && amax < 3.0e38f) (void)frexpf(amax, &E);
+            const float up = amax > 0.f ? ldexpf(1.f, 12 - E) : 0.f;
+            const float down = amax > 0.f ? ldexpf(1.f, E - 12) : 0.f;
+            const uint32_t qb = ring + Plan::OFF_XQ + (buf * kMaxBlockUnits + ub) * Plan::XQ_UNIT + gl * Plan::XQ_GROUP;
+#pragma unroll
+            for (int e = 0; e < PER; ++e) {
+                int xi = __float2int_rn(xv[e] * up);
+                xi = max(-4095, min(4095, xi));
+                const int hi = xi >> 6, lo = xi & 63;
+                // element k of the group -> word k/8, even/odd nibble word, byte (k%8)/2
+                const uint32_t k = lane * PER + e;
+                const uint32_t wj = k >> 3, odd = k & 1u, bytepos = (k & 7u) >> 1;
+                // 16 bytes per (word, activation row): {even hi, odd hi, even lo, odd lo} x 4 bytes
+                const uint32_t a = qb + (wj * MD + m) * 16u + odd * 4u + bytepos;
+                asm volatile("st.shared.u8 [%0], %1;" ::"r"(a), "r"(hi & 0xFF) : "memory");
+                asm volatile("st.shared.u8 [%0], %1;" ::"r"(a + 8u), "r"(lo & 0xFF) : "memory");
+            }
+            if (lane == 0) {
+                const uint32_t a = ring + Plan::OFF_XI + (buf * kMaxBlockUnits + ub) * Plan::XI_UNIT + (gl * MD + m) * 8u;
+                asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(a), "f"(down), "f"(ssum) : "memory");
+            }
+        }
+    };
+
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    {
+        const uint32_t total = u_end - u_begin;
+        prep_block(kc_begin, total < block_units ? total : block_units, 0u);
+    }
+    consumer_barrier();
+
+    uint32_t rg = rg_begin, kc = kc_begin;
+    uint32_t stage = 0, phase = 0;
+    uint32_t ub = 0, buf = 0;
+    uint32_t ob = 0, ophase = 0;
+    bool alive = true;
+    for (uint32_t u = u_begin; u < u_end; ++u) {
+        const bool more = u + 1u < u_end;
+        uint32_t kc_n = kc + 1u, rg_n = rg;
+        if (kc_n == p.chunks) kc_n = 0u, ++rg_n;
+
+        bool landed = false;
+        if (alive) {
+            landed = mbar_wait(smem_u32(&s_full[stage]), phase, p.error_word, 0x2u);
+            if (!landed) alive = false, s_abort = 1u;
+        }
+        const bool exists = kc * GPS + gq < p.groups;  // the last K chunk of a row may hold fewer groups
+        if (landed && exists && !(p.probe & 1u)) {
+            const uint32_t stage_off = stage * Geo::STAGE_BYTES;
+            // packed codes of this lane's rows
+            uint32_t w[R][WPG];
+#pragma unroll
+            for (int i = 0; i < R; ++i)
+#pragma unroll
+                for (int c = 0; c < CH; ++c)
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(w[i][4 * c]), "=r"(w[i][4 * c + 1]), "=r"(w[i][4 * c + 2]), "=r"(w[i][4 * c + 3])
+                                 : "r"(stage_off + (woff[i] ^ (static_cast<uint32_t>(c) << 4))));
+            int ahi[R][MD], alo[R][MD];
+#pragma unroll
+            for (int i = 0; i < R; ++i)
+#pragma unroll
+                for (int m = 0; m < MD; ++m) ahi[i][m] = 0, alo[i][m] = 0;
+            const uint32_t xq = xq_warp + (buf * kMaxBlockUnits + ub) * Plan::XQ_UNIT;
+#pragma unroll
+            for (int j = 0; j < WPG; ++j) {
+                uint32_t xe_hi[MD], xo_hi[MD], xe_lo[MD], xo_lo[MD];
+#pragma unroll
+                for (int m = 0; m < MD; ++m)
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(xe_hi[m]), "=r"(xo_hi[m]), "=r"(xe_lo[m]), "=r"(xo_lo[m])
+                                 : "r"(xq + (j * MD + m) * 16u));
+#pragma unroll
+                for (int i = 0; i < R; ++i) {
+                    const uint32_t even = w[i][j] & 0x0F0F0F0Fu, odd = (w[i][j] >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+                    for (int m = 0; m < MD; ++m) {
+                        ahi[i][m] = dp4a_u8s8(even, xe_hi[m], ahi[i][m]);
+                        ahi[i][m] = dp4a_u8s8(odd, xo_hi[m], ahi[i][m]);
+                        alo[i][m] = dp4a_u8s8(even, xe_lo[m], alo[i][m]);
+                        alo[i][m] = dp4a_u8s8(odd, xo_lo[m], alo[i][m]);
+                    }
+                }
+            }
+            float ex[MD], xs[MD];
+            const uint32_t xi = xi_warp + (buf * kMaxBlockUnits + ub) * Plan::XI_UNIT;
+#pragma unroll
+            for (int m = 0; m < MD; ++m)
+                asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(ex[m]), "=f"(xs[m]) : "r"(xi + m * 8u));
+            const uint32_t sbo = (kc * GPS * 2u) & 15u;
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+                uint16_t sraw, braw;
+                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sraw) : "r"(stage_off + sboff[i] + sbo));
+                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(braw) : "r"(stage_off + sboff[i] + sbo + Geo::SB_BYTES));
+                const float s = sb_half<SD>(sraw, 0), b = sb_half<SD>(braw, 0);
+#pragma unroll
+                for (int m = 0; m < MD; ++m) {
+                    const float v = __int2float_rn(ahi[i][m] * 64 + alo[i][m]);
+                    yacc[i][m] = fmaf(v, s * ex[m], yacc[i][m]);
+                    yacc[i][m] = fmaf(b, xs[m], yacc[i][m]);
+                }
+            }
+        }
+        __syncwarp();
+        if (landed && lane == 0) mbar_arrive(smem_u32(&s_empty[stage]));
+        if (++stage == kStages) stage = 0u, phase ^= 1u;
+
+        // ---- end of this CTA's share of the row group: hand the sums to the writer warp ----
+        if ((kc + 1u == p.chunks) || !more) {
+            if (alive && !mbar_wait(smem_u32(&s_out_empty[ob]), ophase ^ 1u, p.error_word, 0x10u)) alive = false, s_abort = 1u;
+            if (alive) {
+#pragma unroll
+                for (int i = 0; i < R; ++i)
+#pragma unroll
+                    for (int m = 0; m < MD; ++m)
+                        asm volatile("st.shared.f32 [%0], %1;" ::"r"(out_warp + ob * Plan::OUT_BUF +
+                                                                        ((rbase + lane + 32u * i) * MD + m) * 4u),
+                                     "f"(yacc[i][m])
+                                     : "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&s_out_full[ob]));
+            }
+            ob ^= 1u;
+            if (ob == 0u) ophase ^= 1u;
+#pragma unroll
+            for (int i = 0; i < R; ++i)
+#pragma unroll
+                for (int m = 0; m < MD; ++m) yacc[i][m] = 0.f;
+        }
+
+        if (++ub == block_units) {
+            ub = 0u;
+            if (more) {
+                const uint32_t left = u_end - (u + 1u);
+                prep_block(kc_n, left < block_units ? left : block_units, buf ^ 1u);
+                consumer_barrier();
+                if (s_abort) return;
+                buf ^= 1u;
+            }
+        }
+        kc = kc_n, rg = rg_n;
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Shape-agnostic kernel: any K % vpw == 0, G % vpw == 0, K % G == 0, any M.
 // One warp per output feature, grid.y = activation row; the arithmetic is the
 // reference CUDA kernel's (quant_ops.cu:78-89): acc = fmaf(x, q*s + b, acc).
@@ -903,6 +1318,43 @@ cudaError_t launch_stream(const GemvParams &p, const WeightView &w, uint32_t cta
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, p, w.tmap, w.tmap_s, w.tmap_b);
+}
+
+template <int GB, int MD, bool XF32, int SD>
+cudaError_t launch_dp4a(const GemvParams &p, const WeightView &w, uint32_t ctas, bool pdl, cudaStream_t stream) {
+    auto kern = gaf_gemv_dp4a_kernel<GB, MD, XF32, SD>;
+    using Plan = DpPlan<GB, MD, XF32>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::TOTAL);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = Plan::TOTAL;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, p, w.tmap, w.tmap_s, w.tmap_b);
+}
+
+template <int GB>
+cudaError_t dispatch_dp4a(const GemvParams &p, const WeightView &w, uint32_t ctas, uint32_t M, bool xf32, bool pdl,
+                          cudaStream_t stream) {
+    const bool bf = p.sdtype == 1u;
+#define TGAF_CASE(MDv, XFv)                                                                    \
+    if (M == MDv && xf32 == XFv)                                                               \
+        return bf ? launch_dp4a<GB, MDv, XFv, 1>(p, w, ctas, pdl, stream)                      \
+                  : launch_dp4a<GB, MDv, XFv, 0>(p, w, ctas, pdl, stream);
+    TGAF_CASE(1, false)
+    TGAF_CASE(2, false)
+#undef TGAF_CASE
+    return cudaErrorNotSupported;
 }
 
 template <int GB, int BITS>
@@ -1039,6 +1491,13 @@ cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bo
     p.max_slots = pl.max_slots;
     p.probe = static_cast<uint32_t>(tune.probe);
     const bool pdl = tune.pdl != 0;
+    if (w.bits == 4 && M <= 2u && !x_f32 && !tune.no_dp4a) {
+        // one or two bf16 activation rows: the integer dot-product formulation (its 13-bit activations
+        // are ample next to bf16 inputs; f32 callers keep the hi + lo tensor-core path and its 1e-3 accuracy)
+        if (gb == 16u) return dispatch_dp4a<16>(p, w, pl.ctas, M, x_f32, pdl, stream);
+        if (gb == 32u) return dispatch_dp4a<32>(p, w, pl.ctas, M, x_f32, pdl, stream);
+        if (gb == 64u) return dispatch_dp4a<64>(p, w, pl.ctas, M, x_f32, pdl, stream);
+    }
     if (w.bits == 4) {
         if (gb == 16u) return dispatch_stream<16, 4>(p, w, pl.ctas, mt, x_f32, pdl, stream);
         if (gb == 32u) return dispatch_stream<32, 4>(p, w, pl.ctas, mt, x_f32, pdl, stream);

@@ -40,6 +40,7 @@ struct GemvTuning {
     int ctas;           // persistent CTAs of the streaming GEMV (0 = one per SM)
     int pdl;            // launch with programmatic stream serialization
     int force_generic;  // use the shape-agnostic kernel even when the fast path applies
+    int no_dp4a;        // keep M <= 2 on the tensor-core formulation (for A/B comparisons)
     int probe;          // measurement aid for the streaming GEMV (0 = off); results are wrong when set
 };
 

@@ -19,7 +19,9 @@ def _weight_bytes(N, K):
     return N * K * BITS // 8 + 2 * N * (K // GROUP) * 2
 
 
-def run(args):
+def measure(args, existing_ctx=None, existing_stream=None):
+    """Runs the stack on this rank (all ranks call it together) and returns (ms per step over ranks,
+    whole-job bytes per step, launches per rank, layers, world)."""
     import torch
     import torch.distributed as dist
 
@@ -36,14 +38,15 @@ def run(args):
     if debug:
         import faulthandler
         faulthandler.dump_traceback_later(60, exit=True)   # where are we if nothing moves for a minute
-    torch.cuda.set_device(local)
+    if existing_ctx is None:
+        torch.cuda.set_device(local)
     if world > 1:
         # control plane (id hand-over, barriers, max of timings) over gloo; the data path is the
         # library's own NCCL communicator
         dist.init_process_group("gloo")
     note("process group up")
-    stream = torch.cuda.Stream()
-    ctx = gaf.Context(local, stream=stream.cuda_stream)
+    stream = existing_stream or torch.cuda.Stream()
+    ctx = existing_ctx or gaf.Context(local, stream=stream.cuda_stream)
     if world > 1:
         ids = [gaf.make_comm_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
@@ -109,11 +112,29 @@ def run(args):
     for _ in range(layers):
         for name, (N, K, kind) in LLAMA3_70B_LINEARS.items():
             total += _weight_bytes(N, K) + M * K * 2 + M * N * 2
+    # the captured graph refers to the communicator: release it before the communicator goes
+    del graph
+    torch.cuda.synchronize()
+    for _, _, w in ws:
+        w.free()
+    if world > 1:
+        dist.barrier()
+        ctx._lib.tgaf_comm_destroy(ctx._h)
+        note("communicator destroyed")
+        dist.destroy_process_group()
+    if debug:
+        import faulthandler
+        faulthandler.cancel_dump_traceback_later()
+    return ms, total, len(ws), layers, world, rank, steps, warmup
+
+
+def run(args):
+    ms, total, per_rank_launches, layers, world, rank, steps, warmup = measure(args)
+    M = 1
     value = total / ms / 1e6
     if rank == 0:
         from bench import measured_peak_hbm
         peak, kind = measured_peak_hbm()
-        per_rank_launches = len(ws)
         print(json.dumps({
             "metric": "gaf4_64 decode GEMV HBM GB/s", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
             "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 5), "higher_is_better": True,
@@ -129,14 +150,3 @@ def run(args):
             "e2e": None,
             "gpu_launches": per_rank_launches * steps * world,
         }))
-    # the captured graph refers to the communicator: release it before the communicator goes
-    del graph
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-        ctx._lib.tgaf_comm_destroy(ctx._h)
-        note("communicator destroyed")
-        dist.destroy_process_group()
-    if debug:
-        import faulthandler
-        faulthandler.cancel_dump_traceback_later()
