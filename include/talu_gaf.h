@@ -165,6 +165,14 @@ int32_t tgaf_gaffine_u8_matvec_f32(tgaf_ctx *ctx, const float *input, const uint
 int32_t tgaf_dequant_f32(tgaf_ctx *ctx, const tgaf_weight *w, float *d_out);
 int32_t tgaf_dequant_f32_host(tgaf_ctx *ctx, const tgaf_weight *w, float *h_out);
 
+/* Embedding rows: out f32 [count, K_local], row i = dequant(weight row token_ids[i]) * multiplier.
+ * Replaces talu_embedding_lookup_gaffine_u4_f32 (core/src/compute/cuda/kernels/ops/quant_ops.cu:12-44,
+ * one token per launch there) and gatherDecodeGroupedAffineU4Rows / U8Rows
+ * (core/src/compute/cpu/quant_decode.zig:133-210).  token_ids is a HOST array, checked before anything
+ * is enqueued: an id >= N is TGAF_ERR_INVALID_ARGUMENT (the reference's error.InvalidTokenId). */
+int32_t tgaf_embedding_lookup_f32(tgaf_ctx *ctx, const tgaf_weight *w, const uint32_t *token_ids,
+                                  uint32_t count, float multiplier, float *d_out);
+
 /* ---- tensor parallel exchange (no counterpart in the reference, which is
  * single-device): sum of the row-parallel partial outputs over all ranks. ----
  * The communicator belongs to the context.  Rank 0 makes the id and the host

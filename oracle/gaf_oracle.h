@@ -75,6 +75,15 @@ int gaf_dequant_f32(const void *packed, const void *scales, const void *biases,
                     int sdtype, size_t N, size_t K, size_t group, int bits,
                     float *out, int nthreads);
 
+/* gatherDecodeGroupedAffineU4Rows / U8Rows, core/src/compute/cpu/quant_decode.zig:133-210, with the
+ * multiplier of the reference's CUDA embedding kernel
+ * (core/src/compute/cuda/kernels/ops/quant_ops.cu:12-44): out[i, :] = dequant(row ids[i]) * multiplier.
+ * Returns GAF_ERR_INVALID_TOKEN when an id is >= N (the reference's error.InvalidTokenId). */
+#define GAF_ERR_INVALID_TOKEN 2
+int gaf_gather_dequant_f32(const void *packed, const void *scales, const void *biases, int sdtype,
+                           size_t N, size_t K, size_t group, int bits, const uint32_t *ids, size_t count,
+                           float multiplier, float *out);
+
 /* matmulGaffineU4Prefill / matmulGaffineU8Prefill,
  * core/src/compute/cpu/matmul_prefill.zig:28-480 and :488-864.
  * a f32 [M,K], out f32 [M,N].  nthreads = 0 picks the reference's policy

@@ -64,6 +64,8 @@ def lib() -> C.CDLL:
     L.gaf_quantize.argtypes = [vp, sz, sz, sz, i32, vp, vp, vp, i32]
     L.gaf_dequant_f32.restype = i32
     L.gaf_dequant_f32.argtypes = [vp, vp, vp, i32, sz, sz, sz, i32, vp, i32]
+    L.gaf_gather_dequant_f32.restype = i32
+    L.gaf_gather_dequant_f32.argtypes = [vp, vp, vp, i32, sz, sz, sz, i32, vp, sz, C.c_float, vp]
     L.gaf_matmul_f32.restype = i32
     L.gaf_matmul_f32.argtypes = [vp, sz, sz, vp, vp, vp, i32, sz, sz, i32, vp, i32]
     L.gaf_matmul_f64.restype = i32
@@ -126,6 +128,28 @@ def dequant_f32(packed, scales, biases, group: int, bits: int, sdtype: int = SCA
     rc = lib().gaf_dequant_f32(_p(packed), _p(scales), _p(biases), sdtype, N, K, group, bits, _p(out), nt)
     if rc != 0:
         raise OracleError(f"gaf_dequant_f32 rc={rc}")
+    return out
+
+
+class InvalidTokenId(OracleError):
+    """A row index is outside the table (the reference's error.InvalidTokenId)."""
+
+
+def gather_dequant_f32(packed, scales, biases, group: int, bits: int, ids, multiplier: float = 1.0,
+                       sdtype: int = SCALES_BF16) -> np.ndarray:
+    packed = _c(packed, np.uint32)
+    scales = _c(scales, np.uint16)
+    biases = _c(biases, np.uint16)
+    ids = _c(ids, np.uint32)
+    N = packed.shape[0]
+    K = packed.shape[1] * vpw(bits)
+    out = np.empty((ids.size, K), np.float32)
+    rc = lib().gaf_gather_dequant_f32(_p(packed), _p(scales), _p(biases), sdtype, N, K, group, bits, _p(ids),
+                                      ids.size, multiplier, _p(out))
+    if rc == 2:
+        raise InvalidTokenId("row index out of range")
+    if rc != 0:
+        raise OracleError(f"gaf_gather_dequant_f32 rc={rc}")
     return out
 
 

@@ -252,6 +252,31 @@ int gaf_dequant_f32(const void *packed, const void *scales, const void *biases,
     return GAF_OK;
 }
 
+int gaf_gather_dequant_f32(const void *packed, const void *scales, const void *biases, int sdtype,
+                           size_t N, size_t K, size_t group, int bits, const uint32_t *ids, size_t count,
+                           float multiplier, float *out) {
+    int rc = gaf_validate_shape(N, K, group, bits, sdtype);
+    if (rc != GAF_OK) return rc;
+    const size_t vpw = bits == 4 ? 8 : 4;
+    const size_t groups = K / group;
+    for (size_t i = 0; i < count; ++i) {
+        if (ids[i] >= N) return GAF_ERR_INVALID_TOKEN;
+        dq_ctx_t c;
+        memset(&c, 0, sizeof c);
+        c.packed = (const uint8_t *)packed + (size_t)ids[i] * (K / vpw) * 4;
+        c.scales = (const uint8_t *)scales + (size_t)ids[i] * groups * 2;
+        c.biases = (const uint8_t *)biases + (size_t)ids[i] * groups * 2;
+        c.sdtype = sdtype;
+        c.K = K;
+        c.group = group;
+        c.bits = bits;
+        c.out_f32 = out + i * K;
+        dequant_rows(0, 1, &c);
+        for (size_t k = 0; k < K; ++k) out[i * K + k] *= multiplier;
+    }
+    return GAF_OK;
+}
+
 /* ------------------------------------------------------------------ */
 /* float64 truth                                                       */
 /* ------------------------------------------------------------------ */

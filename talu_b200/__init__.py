@@ -18,6 +18,7 @@ from .gaf import (  # noqa: F401
     Weight,
     dequant_f32,
     dequant_f32_host,
+    embedding_lookup_f32,
     gaffine_matvec_f32,
     linear,
     linear_fixed_scratch,
@@ -25,6 +26,6 @@ from .gaf import (  # noqa: F401
 )
 
 __all__ = [
-    "Context", "Weight", "GafError", "linear", "linear_fixed_scratch", "linear_host", "dequant_f32", "dequant_f32_host",
+    "Context", "Weight", "GafError", "linear", "linear_fixed_scratch", "linear_host", "dequant_f32", "dequant_f32_host", "embedding_lookup_f32",
     "gaffine_matvec_f32", "SCALES_F16", "SCALES_BF16", "SHARD_NONE", "SHARD_COL", "SHARD_ROW",
 ]

@@ -34,6 +34,7 @@ SIGNATURES = {
     "tgaf_gaffine_u8_matvec_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32]),
     "tgaf_dequant_f32": (_i32, [_vp, _vp, _vp]),
     "tgaf_dequant_f32_host": (_i32, [_vp, _vp, _vp]),
+    "tgaf_embedding_lookup_f32": (_i32, [_vp, _vp, _vp, _u32, C.c_float, _vp]),
     "tgaf_comm_make_id": (_i32, [_vp]),
     "tgaf_comm_init": (_i32, [_vp, _vp, _u32, _u32]),
     "tgaf_comm_destroy": (_i32, [_vp]),

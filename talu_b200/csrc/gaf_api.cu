@@ -76,7 +76,7 @@ struct tgaf_ctx {
     bool owns_stream = false;
     int sm_count = 148;
     Scratch scratch = {nullptr, 0, nullptr, 0};
-    GemvTuning tune = {0, 1, 0, 0, 0};
+    GemvTuning tune = {0, 1, 0, 0, 0, 0};
     // staging for the *_host entry points
     void *stage_x = nullptr;
     size_t stage_x_bytes = 0;
@@ -373,6 +373,8 @@ int32_t tgaf_ctx_set_option(tgaf_ctx *ctx, const char *name, int64_t value) {
         ctx->tune.pdl = value != 0;
     } else if (!strcmp(name, "force_generic")) {
         ctx->tune.force_generic = value != 0;
+    } else if (!strcmp(name, "dp4a_small")) {
+        ctx->tune.dp4a_small = value != 0;
     } else if (!strcmp(name, "no_dp4a")) {
         ctx->tune.no_dp4a = value != 0;
     } else if (!strcmp(name, "probe")) {
@@ -619,6 +621,25 @@ int32_t tgaf_dequant_f32_host(tgaf_ctx *ctx, const tgaf_weight *w, float *h_out)
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
     cudaFree(d);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "dequant to host");
+    return TGAF_OK;
+}
+
+int32_t tgaf_embedding_lookup_f32(tgaf_ctx *ctx, const tgaf_weight *w, const uint32_t *token_ids, uint32_t count,
+                                  float multiplier, float *d_out) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!w || !token_ids || !d_out) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null pointer");
+    if (count == 0) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "count must be > 0");
+    for (uint32_t i = 0; i < count; ++i)
+        if (token_ids[i] >= w->v.N)
+            return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "token id %u at position %u is outside the table of %u rows",
+                        token_ids[i], i, w->v.N);
+    const size_t bytes = static_cast<size_t>(count) * sizeof(uint32_t);
+    int32_t st = ensure_stage(ctx, &ctx->stage_x, &ctx->stage_x_bytes, bytes);
+    if (st != TGAF_OK) return st;
+    TGAF_CUDA(ctx, cudaMemcpyAsync(ctx->stage_x, token_ids, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    cudaError_t e = gather_dequant_f32(w->v, static_cast<const uint32_t *>(ctx->stage_x), count, multiplier, d_out,
+                                       ctx->stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "embedding lookup launch");
     return TGAF_OK;
 }
 

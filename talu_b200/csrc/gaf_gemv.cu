@@ -91,7 +91,8 @@ struct GemvParams {
     uint32_t chunks;      // K chunks per row group
     uint32_t units;       // row groups * chunks
     uint32_t max_slots;   // scratch slots per row group
-    uint32_t probe;       // measurement aid, bit mask: 1 = skip the arithmetic, 2 = skip the streaming, 4 = skip the write-out
+    uint32_t probe;       // measurement aid, bit mask: 1 = skip the arithmetic, 2 = skip the streaming, 4 = skip the write-out,
+                          // 8 = skip the activation block, 32 = return at once (launch cost only)
 };
 
 // ---- small PTX wrappers ----------------------------------------------------
@@ -801,7 +802,7 @@ __device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
     return d;
 }
 
-template <int GB, int MD, bool XF32>
+template <int GB, int MD, bool XF32, int NST, int BU>
 struct DpPlan {
     static constexpr int GPS = kChunkBytes / GB;           // groups per unit
     static constexpr int WPG = GB / 4;                     // packed words per group and row
@@ -809,27 +810,30 @@ struct DpPlan {
     static constexpr int XQ_UNIT = GPS * XQ_GROUP;         // 1 KB per activation row for any group size
     static constexpr int XI_UNIT = GPS * MD * 8;           // {2^(E-12), sum x} per group and activation row
     static constexpr int OUT_BUF = GPS * kRows * MD * 4;   // per-group partial sums of one row group
-    static constexpr int OFF_XQ = kStages * StreamGeom<GB>::STAGE_BYTES;
-    static constexpr int OFF_XI = OFF_XQ + 2 * kMaxBlockUnits * XQ_UNIT;
-    static constexpr int OFF_OUT = OFF_XI + 2 * kMaxBlockUnits * XI_UNIT;
+    static constexpr int OFF_XQ = NST * StreamGeom<GB>::STAGE_BYTES;
+    static constexpr int OFF_XI = OFF_XQ + 2 * BU * XQ_UNIT;
+    static constexpr int OFF_OUT = OFF_XI + 2 * BU * XI_UNIT;
     static constexpr int TOTAL = OFF_OUT + 2 * OUT_BUF + 1024;
 };
 
-template <int GB, int MD, bool XF32, int SD>
-__global__ void __launch_bounds__(kThreads, 1)
+// NCW consumer warps, NST ring stages, BU units per activation block.  The small configuration
+// (8 warps, 2 stages) fits two CTAs on an SM, so one CTA's prologue and write-out tail overlap the
+// other's streaming, and the next launch's CTAs become resident while this one drains.
+template <int GB, int MD, bool XF32, int SD, int NCW, int NST, int BU>
+__global__ void __launch_bounds__((NCW + 2) * 32, NCW == 8 ? 2 : 1)
 gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap_w,
                      const __grid_constant__ CUtensorMap tmap_s, const __grid_constant__ CUtensorMap tmap_b) {
     using Geo = StreamGeom<GB>;
-    using Plan = DpPlan<GB, MD, XF32>;
+    using Plan = DpPlan<GB, MD, XF32, NST, BU>;
     constexpr int GPS = Geo::GPS, WPG = Plan::WPG;
-    constexpr int RW = kRows * GPS / kConsumerWarps;  // rows per warp: 128 (G=32), 64 (G=64), 32 (G=128)
+    constexpr int RW = kRows * GPS / NCW;  // rows per warp: 128 (G=32), 64 (G=64), 32 (G=128)
     constexpr int R = RW / 32;                        // rows per lane
     constexpr int CH = GB / 16;                       // 16-byte chunks per group and row
-    static_assert(R >= 1 && GPS * (kRows / RW) == kConsumerWarps, "unsupported group size");
+    static_assert(R >= 1 && GPS <= NCW && GPS * (kRows / RW) == NCW, "unsupported group size");
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t s_full[kStages];
-    __shared__ __align__(8) uint64_t s_empty[kStages];
+    __shared__ __align__(8) uint64_t s_full[NST];
+    __shared__ __align__(8) uint64_t s_empty[NST];
     __shared__ __align__(8) uint64_t s_out_full[2];
     __shared__ __align__(8) uint64_t s_out_empty[2];
     __shared__ volatile uint32_t s_abort;
@@ -841,13 +845,13 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
     if (threadIdx.x == 0) {
         s_abort = 0u;
 #pragma unroll
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < NST; ++s) {
             mbar_init(smem_u32(&s_full[s]), 1);
-            mbar_init(smem_u32(&s_empty[s]), kConsumerWarps);
+            mbar_init(smem_u32(&s_empty[s]), NCW);
         }
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
-            mbar_init(smem_u32(&s_out_full[s]), kConsumerWarps);
+            mbar_init(smem_u32(&s_out_full[s]), NCW);
             mbar_init(smem_u32(&s_out_empty[s]), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -855,13 +859,14 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
     __syncthreads();
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
+    if (p.probe & 32u) return;
     const uint32_t u_begin = range_begin(blockIdx.x, p.units, gridDim.x);
     const uint32_t u_end = range_begin(blockIdx.x + 1u, p.units, gridDim.x);
     if (u_begin >= u_end) return;
     const uint32_t rg_begin = u_begin / p.chunks;
     const uint32_t kc_begin = u_begin - rg_begin * p.chunks;
 
-    if (warp == kConsumerWarps) {
+    if (warp == NCW) {
         // ------------------------- producer warp (one lane works) -------------------------
         if (lane != 0) return;
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_w)) : "memory");
@@ -870,8 +875,8 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
         uint32_t issued = 0, rg = rg_begin, kc = kc_begin;
         bool ok = true;
         for (uint32_t u = u_begin; u < u_end; ++u, ++issued) {
-            const uint32_t stage = issued % kStages;
-            const uint32_t round = issued / kStages;
+            const uint32_t stage = issued % NST;
+            const uint32_t round = issued / NST;
             if (round > 0) ok = mbar_wait(smem_u32(&s_empty[stage]), (round - 1u) & 1u, p.error_word, 0x1u);
             if (!ok) break;
             const uint32_t full = smem_u32(&s_full[stage]);
@@ -890,16 +895,16 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
             if (++kc == p.chunks) kc = 0u, ++rg;
         }
         if (!ok) {
-            const uint32_t pending = issued < static_cast<uint32_t>(kStages) ? issued : static_cast<uint32_t>(kStages);
+            const uint32_t pending = issued < static_cast<uint32_t>(NST) ? issued : static_cast<uint32_t>(NST);
             for (uint32_t i = 0; i < pending; ++i) {
                 const uint32_t idx = issued - 1u - i;
-                mbar_wait(smem_u32(&s_full[idx % kStages]), (idx / kStages) & 1u, p.error_word, 0x4u);
+                mbar_wait(smem_u32(&s_full[idx % NST]), (idx / NST) & 1u, p.error_word, 0x4u);
             }
         }
         return;
     }
 
-    if (warp == kConsumerWarps + 1) {
+    if (warp == NCW + 1) {
         // ------------------------- writer warp -------------------------
         // lane owns rows lane, lane + 32, lane + 64, lane + 96 of the row group
         asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -994,7 +999,7 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
     const uint8_t *xbase = static_cast<const uint8_t *>(p.x);
     const size_t x_elt = XF32 ? 4 : 2;
 
-    uint32_t block_units = kMaxBlockUnits;
+    constexpr uint32_t block_units = BU;
 
     // shared-memory offsets of this lane's rows: first 16-byte chunk of the group, swizzled
     uint32_t woff[R], sboff[R];
@@ -1017,14 +1022,20 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
         for (int m = 0; m < MD; ++m) yacc[i][m] = 0.f;
 
     // ---- quantised activations for a block of units: (unit, group, activation row) triples over the warps ----
+    // Two passes so that all of a warp's global loads are in flight together.
     auto prep_block = [&](uint32_t kc_first, uint32_t count, uint32_t buf) {
-        for (uint32_t pi = warp; pi < count * GPS * MD; pi += kConsumerWarps) {
+        if (p.probe & 8u) return;
+        constexpr int G = GB * 2;                          // elements per group (4-bit codes)
+        constexpr int PER = G / 32;                        // elements per lane: 1 (G=32), 2, 4
+        constexpr int TPW = (BU * GPS * MD + NCW - 1) / NCW;  // triples per warp, at most
+        float xv[TPW][PER];
+        const uint32_t ntask = count * GPS * MD;
+#pragma unroll
+        for (int tk = 0; tk < TPW; ++tk) {
+            const uint32_t pi = warp + tk * NCW;
             const uint32_t m = pi % MD, gl = (pi / MD) % GPS, ub = pi / (MD * GPS);
             const uint32_t gi = ((kc_first + ub) % p.chunks) * GPS + gl;
-            constexpr int G = GB * 2;                   // elements per group (4-bit codes)
-            constexpr int PER = G / 32;                 // elements per lane: 1 (G=32), 2, 4
-            float xv[PER];
-            const bool live = m < p.M && gi < p.groups;
+            const bool live = pi < ntask && m < p.M && gi < p.groups;
 #pragma unroll
             for (int e = 0; e < PER; ++e) {
                 const size_t idx = static_cast<size_t>(m) * p.K + static_cast<size_t>(gi) * G + lane * PER + e;
@@ -1035,26 +1046,32 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
                     else
                         v = __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(xbase)[idx]);
                 }
-                xv[e] = v;
+                xv[tk][e] = v;
             }
-            float amax = 0.f, ssum = 0.f;
+        }
 #pragma unroll
-            for (int e = 0; e < PER; ++e) amax = fmaxf(amax, fabsf(xv[e])), ssum += xv[e];
+        for (int tk = 0; tk < TPW; ++tk) {
+            const uint32_t pi = warp + tk * NCW;
+            if (pi >= ntask) break;
+            const uint32_t m = pi % MD, gl = (pi / MD) % GPS, ub = pi / (MD * GPS);
+            // largest |x| of the group: non-negative floats order like their bit patterns
+            uint32_t abits = 0u;
 #pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) {
-                amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, off));
-                ssum += __shfl_xor_sync(0xFFFFFFFFu, ssum, off);
-            }
-            // 2^(E-1) <= amax < 2^E; xi = rint(x * 2^(12-E)), |xi| <= 4095
-            int E = 0;
-            if (amax > 0.f && amax < 3.0e38f) (void)frexpf(amax, &E);
-            const float up = amax > 0.f ? ldexpf(1.f, 12 - E) : 0.f;
-            const float down = amax > 0.f ? ldexpf(1.f, E - 12) : 0.f;
-            const uint32_t qb = ring + Plan::OFF_XQ + (buf * kMaxBlockUnits + ub) * Plan::XQ_UNIT + gl * Plan::XQ_GROUP;
+            for (int e = 0; e < PER; ++e) abits = max(abits, __float_as_uint(xv[tk][e]) & 0x7FFFFFFFu);
+            abits = __reduce_max_sync(0xFFFFFFFFu, abits);
+            // amax = 1.f * 2^(eb - 127) < 2^E with E = eb - 126; xi = rint(x * 2^(12-E)), |xi| <= 4095.
+            // Groups whose largest value is below 2^-100 (or not finite) count as zero.
+            const uint32_t eb = abits >> 23;
+            const bool nz = eb >= 27u && eb < 255u;
+            const float up = nz ? __uint_as_float((265u - eb) << 23) : 0.f;    // 2^(12 - E)
+            const float down = nz ? __uint_as_float((eb - 11u) << 23) : 0.f;   // 2^(E - 12)
+            const uint32_t qb = ring + Plan::OFF_XQ + (buf * BU + ub) * Plan::XQ_UNIT + gl * Plan::XQ_GROUP;
+            int isum = 0;
 #pragma unroll
             for (int e = 0; e < PER; ++e) {
-                int xi = __float2int_rn(xv[e] * up);
+                int xi = __float2int_rn(xv[tk][e] * up);
                 xi = max(-4095, min(4095, xi));
+                isum += xi;
                 const int hi = xi >> 6, lo = xi & 63;
                 // element k of the group -> word k/8, even/odd nibble word, byte (k%8)/2
                 const uint32_t k = lane * PER + e;
@@ -1064,8 +1081,12 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
                 asm volatile("st.shared.u8 [%0], %1;" ::"r"(a), "r"(hi & 0xFF) : "memory");
                 asm volatile("st.shared.u8 [%0], %1;" ::"r"(a + 8u), "r"(lo & 0xFF) : "memory");
             }
+            // sum of the quantised activations (exact in integers): the bias term then matches the
+            // dot products, y = sum_k (s q_k + b) * xq_k
+            isum = __reduce_add_sync(0xFFFFFFFFu, isum);
+            const float ssum = static_cast<float>(isum) * down;
             if (lane == 0) {
-                const uint32_t a = ring + Plan::OFF_XI + (buf * kMaxBlockUnits + ub) * Plan::XI_UNIT + (gl * MD + m) * 8u;
+                const uint32_t a = ring + Plan::OFF_XI + (buf * BU + ub) * Plan::XI_UNIT + (gl * MD + m) * 8u;
                 asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(a), "f"(down), "f"(ssum) : "memory");
             }
         }
@@ -1076,7 +1097,7 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
         const uint32_t total = u_end - u_begin;
         prep_block(kc_begin, total < block_units ? total : block_units, 0u);
     }
-    consumer_barrier();
+    asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
 
     uint32_t rg = rg_begin, kc = kc_begin;
     uint32_t stage = 0, phase = 0;
@@ -1110,7 +1131,7 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
             for (int i = 0; i < R; ++i)
 #pragma unroll
                 for (int m = 0; m < MD; ++m) ahi[i][m] = 0, alo[i][m] = 0;
-            const uint32_t xq = xq_warp + (buf * kMaxBlockUnits + ub) * Plan::XQ_UNIT;
+            const uint32_t xq = xq_warp + (buf * BU + ub) * Plan::XQ_UNIT;
 #pragma unroll
             for (int j = 0; j < WPG; ++j) {
                 uint32_t xe_hi[MD], xo_hi[MD], xe_lo[MD], xo_lo[MD];
@@ -1132,7 +1153,7 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
                 }
             }
             float ex[MD], xs[MD];
-            const uint32_t xi = xi_warp + (buf * kMaxBlockUnits + ub) * Plan::XI_UNIT;
+            const uint32_t xi = xi_warp + (buf * BU + ub) * Plan::XI_UNIT;
 #pragma unroll
             for (int m = 0; m < MD; ++m)
                 asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(ex[m]), "=f"(xs[m]) : "r"(xi + m * 8u));
@@ -1153,7 +1174,7 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
         }
         __syncwarp();
         if (landed && lane == 0) mbar_arrive(smem_u32(&s_empty[stage]));
-        if (++stage == kStages) stage = 0u, phase ^= 1u;
+        if (++stage == NST) stage = 0u, phase ^= 1u;
 
         // ---- end of this CTA's share of the row group: hand the sums to the writer warp ----
         if ((kc + 1u == p.chunks) || !more) {
@@ -1183,7 +1204,7 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
             if (more) {
                 const uint32_t left = u_end - (u + 1u);
                 prep_block(kc_n, left < block_units ? left : block_units, buf ^ 1u);
-                consumer_barrier();
+                asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
                 if (s_abort) return;
                 buf ^= 1u;
             }
@@ -1275,6 +1296,34 @@ gaf_dequant_f32_kernel(const uint8_t *packed, const uint16_t *scales, const uint
     }
 }
 
+// Embedding rows: block = one requested row, threads walk its packed words.
+// (quant * scale + bias) * multiplier, as core/src/compute/cuda/kernels/ops/quant_ops.cu:43.
+__global__ void __launch_bounds__(256)
+gaf_gather_dequant_f32_kernel(const uint8_t *packed, const uint16_t *scales, const uint16_t *biases,
+                              const uint32_t *ids, float multiplier, float *out, uint32_t N, uint32_t K,
+                              uint32_t group, uint32_t bits, uint32_t sdtype, uint32_t row_bytes, uint32_t groups) {
+    const uint32_t n = ids[blockIdx.x];
+    if (n >= N) return;  // ids are validated on the host; never read outside the table
+    const uint32_t vpw = 32u / bits;
+    const uint32_t words = K / vpw;
+    const uint32_t mask = bits == 4 ? 0xFu : 0xFFu;
+    float *orow = out + static_cast<size_t>(blockIdx.x) * K;
+    for (uint32_t wi = threadIdx.x; wi < words; wi += blockDim.x) {
+        const uint8_t *bp = packed + static_cast<size_t>(n) * row_bytes + 4u * wi;
+        uint32_t word;
+        if ((reinterpret_cast<uintptr_t>(bp) & 3u) == 0)
+            word = *reinterpret_cast<const uint32_t *>(bp);
+        else
+            word = bp[0] | (bp[1] << 8) | (bp[2] << 16) | (static_cast<uint32_t>(bp[3]) << 24);
+        const uint32_t k0 = wi * vpw;
+        const uint32_t gi = k0 / group;
+        const float s = decode_sb(scales[static_cast<size_t>(n) * groups + gi], sdtype);
+        const float b = decode_sb(biases[static_cast<size_t>(n) * groups + gi], sdtype);
+        for (uint32_t j = 0; j < vpw; ++j)
+            orow[k0 + j] = fmaf(static_cast<float>((word >> (j * bits)) & mask), s, b) * multiplier;
+    }
+}
+
 // ---------------------------------------------------------------------------
 // host-side dispatch
 // ---------------------------------------------------------------------------
@@ -1320,10 +1369,10 @@ cudaError_t launch_stream(const GemvParams &p, const WeightView &w, uint32_t cta
     return cudaLaunchKernelEx(&cfg, kern, p, w.tmap, w.tmap_s, w.tmap_b);
 }
 
-template <int GB, int MD, bool XF32, int SD>
+template <int GB, int MD, bool XF32, int SD, int NCW, int NST, int BU>
 cudaError_t launch_dp4a(const GemvParams &p, const WeightView &w, uint32_t ctas, bool pdl, cudaStream_t stream) {
-    auto kern = gaf_gemv_dp4a_kernel<GB, MD, XF32, SD>;
-    using Plan = DpPlan<GB, MD, XF32>;
+    auto kern = gaf_gemv_dp4a_kernel<GB, MD, XF32, SD, NCW, NST, BU>;
+    using Plan = DpPlan<GB, MD, XF32, NST, BU>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::TOTAL);
@@ -1332,7 +1381,7 @@ cudaError_t launch_dp4a(const GemvParams &p, const WeightView &w, uint32_t ctas,
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas);
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3((NCW + 2) * 32);
     cfg.dynamicSmemBytes = Plan::TOTAL;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -1343,16 +1392,28 @@ cudaError_t launch_dp4a(const GemvParams &p, const WeightView &w, uint32_t ctas,
     return cudaLaunchKernelEx(&cfg, kern, p, w.tmap, w.tmap_s, w.tmap_b);
 }
 
+// small = true: 8 consumer warps, 2 stages, two CTAs per SM (group sizes 64 and 128 only)
 template <int GB>
-cudaError_t dispatch_dp4a(const GemvParams &p, const WeightView &w, uint32_t ctas, uint32_t M, bool xf32, bool pdl,
+cudaError_t dispatch_dp4a(const GemvParams &p, const WeightView &w, uint32_t ctas, uint32_t M, bool small, bool pdl,
                           cudaStream_t stream) {
     const bool bf = p.sdtype == 1u;
-#define TGAF_CASE(MDv, XFv)                                                                    \
-    if (M == MDv && xf32 == XFv)                                                               \
-        return bf ? launch_dp4a<GB, MDv, XFv, 1>(p, w, ctas, pdl, stream)                      \
-                  : launch_dp4a<GB, MDv, XFv, 0>(p, w, ctas, pdl, stream);
-    TGAF_CASE(1, false)
-    TGAF_CASE(2, false)
+    if constexpr (GB >= 32) {
+        if (small) {
+#define TGAF_CASE(MDv)                                                                                   \
+    if (M == MDv)                                                                                        \
+        return bf ? launch_dp4a<GB, MDv, false, 1, 8, 2, 8>(p, w, ctas, pdl, stream)                     \
+                  : launch_dp4a<GB, MDv, false, 0, 8, 2, 8>(p, w, ctas, pdl, stream);
+            TGAF_CASE(1)
+            TGAF_CASE(2)
+#undef TGAF_CASE
+        }
+    }
+#define TGAF_CASE(MDv)                                                                                       \
+    if (M == MDv)                                                                                            \
+        return bf ? launch_dp4a<GB, MDv, false, 1, kConsumerWarps, kStages, kMaxBlockUnits>(p, w, ctas, pdl, stream) \
+                  : launch_dp4a<GB, MDv, false, 0, kConsumerWarps, kStages, kMaxBlockUnits>(p, w, ctas, pdl, stream);
+    TGAF_CASE(1)
+    TGAF_CASE(2)
 #undef TGAF_CASE
     return cudaErrorNotSupported;
 }
@@ -1494,9 +1555,10 @@ cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bo
     if (w.bits == 4 && M <= 2u && !x_f32 && !tune.no_dp4a) {
         // one or two bf16 activation rows: the integer dot-product formulation (its 13-bit activations
         // are ample next to bf16 inputs; f32 callers keep the hi + lo tensor-core path and its 1e-3 accuracy)
-        if (gb == 16u) return dispatch_dp4a<16>(p, w, pl.ctas, M, x_f32, pdl, stream);
-        if (gb == 32u) return dispatch_dp4a<32>(p, w, pl.ctas, M, x_f32, pdl, stream);
-        if (gb == 64u) return dispatch_dp4a<64>(p, w, pl.ctas, M, x_f32, pdl, stream);
+        const bool small = tune.dp4a_small != 0 && gb >= 32u;
+        if (gb == 16u) return dispatch_dp4a<16>(p, w, pl.ctas, M, false, pdl, stream);
+        if (gb == 32u) return dispatch_dp4a<32>(p, w, pl.ctas, M, small, pdl, stream);
+        if (gb == 64u) return dispatch_dp4a<64>(p, w, pl.ctas, M, small, pdl, stream);
     }
     if (w.bits == 4) {
         if (gb == 16u) return dispatch_stream<16, 4>(p, w, pl.ctas, mt, x_f32, pdl, stream);
@@ -1592,6 +1654,14 @@ cudaError_t gemv_generic(const WeightView &w, const void *x, void *y, uint32_t M
         if (e != cudaSuccess) return e;
     }
     return cudaSuccess;
+}
+
+cudaError_t gather_dequant_f32(const WeightView &w, const uint32_t *d_ids, uint32_t count, float multiplier,
+                               float *out, cudaStream_t stream) {
+    if (count == 0) return cudaSuccess;
+    gaf_gather_dequant_f32_kernel<<<count, 256, 0, stream>>>(w.packed, w.scales, w.biases, d_ids, multiplier, out, w.N,
+                                                            w.K, w.group, w.bits, w.sdtype, w.row_bytes, w.groups);
+    return cudaGetLastError();
 }
 
 cudaError_t dequant_f32(const WeightView &w, float *out, cudaStream_t stream) {

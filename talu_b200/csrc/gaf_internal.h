@@ -40,6 +40,7 @@ struct GemvTuning {
     int ctas;           // persistent CTAs of the streaming GEMV (0 = one per SM)
     int pdl;            // launch with programmatic stream serialization
     int force_generic;  // use the shape-agnostic kernel even when the fast path applies
+    int dp4a_small;     // M <= 2 path: 8 consumer warps + 2 stages per CTA (two CTAs fit on an SM)
     int no_dp4a;        // keep M <= 2 on the tensor-core formulation (for A/B comparisons)
     int probe;          // measurement aid for the streaming GEMV (0 = off); results are wrong when set
 };
@@ -73,6 +74,10 @@ cudaError_t gemv_generic(const WeightView &w, const void *x, void *y, uint32_t M
 
 // out f32 [N,K] = fmaf(q, scale, bias), bit-exact.
 cudaError_t dequant_f32(const WeightView &w, float *out, cudaStream_t stream);
+
+// out f32 [count, K]: row i = dequant(row ids[i]) * multiplier; ids on the device, all < N.
+cudaError_t gather_dequant_f32(const WeightView &w, const uint32_t *d_ids, uint32_t count, float multiplier,
+                               float *out, cudaStream_t stream);
 
 // Prefill dequant-GEMM on tcgen05 (bf16 in/out).  cudaErrorNotSupported when not eligible.
 cudaError_t gemm_tc(const WeightView &w, const void *x_bf16, void *y_bf16, uint32_t M,

@@ -229,6 +229,16 @@ def dequant_f32_host(ctx: Context, w: Weight) -> np.ndarray:
     return out
 
 
+def embedding_lookup_f32(ctx: Context, w: Weight, token_ids, multiplier: float = 1.0):
+    """Rows `token_ids` (host integers) of a gaf table, dequantized to f32 and scaled: [count, K] on the device."""
+    import torch
+    ids = np.ascontiguousarray(token_ids, dtype=np.uint32)
+    out = torch.empty((ids.size, w.K), dtype=torch.float32, device=f"cuda:{ctx.device}")
+    ctx._check(ctx._lib.tgaf_embedding_lookup_f32(ctx._h, w._h, ids.ctypes.data, ids.size, multiplier,
+                                                  C.c_void_p(out.data_ptr())))
+    return out
+
+
 def gaffine_matvec_f32(ctx: Context, bits: int, input, packed, scales, biases, out, in_dim: int, out_dim: int,
                        group_size: int, scales_dtype_tag: int, batch_rows: int) -> None:
     """Raw device-pointer launch with the reference wrapper's argument list

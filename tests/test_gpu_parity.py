@@ -311,3 +311,28 @@ def test_prefill_cfg4_full_size(gaf, ctx, oracle):
     on every one of the 29M outputs."""
     got, ref = _prefill_case(gaf, ctx, oracle, 2048, 14336, 4096, 64, seed=4)
     assert rel_err(got, ref) <= TOL_BF16, rel_err(got, ref)
+
+
+def test_embedding_lookup_and_lm_head(gaf, ctx, oracle):
+    """Embedding rows (bit-exact gather-dequant with the multiplier) and the lm_head shape: one GEMV over a
+    vocabulary-sized table."""
+    import torch
+    vocab, hidden, G = 32000, 2048, 64
+    p, s, b = make_weights(oracle, vocab, hidden, G, 4, seed=77)
+    w = gaf.Weight.from_host(ctx, p, s, b, G, 4)
+    ids = np.array([0, 5, 31999, 17, 17, 12345], np.uint32)
+    for mult in (1.0, 45.25):
+        got = gaf.embedding_lookup_f32(ctx, w, ids, mult)
+        ctx.synchronize()
+        ref = oracle.gather_dequant_f32(p, s, b, G, 4, ids, mult)
+        assert (got.cpu().numpy().view(np.uint32) == ref.view(np.uint32)).all()
+    with pytest.raises(gaf.GafError) as ei:
+        gaf.embedding_lookup_f32(ctx, w, [3, vocab])
+    assert ei.value.invalid_argument
+    # lm_head: logits[1, vocab] = h[1, hidden] @ table^T
+    xb, xf = make_x_bf16(oracle, 1, hidden, seed=5)
+    y = gaf.linear(ctx, w, torch_bf16_from_bits(xb, "cuda:0"))
+    ctx.synchronize()
+    ref = oracle.matmul_f32(xf, p, s, b, G, 4)
+    assert rel_err(oracle.bf16_to_f32(bits_from_torch_bf16(y)), ref) <= TOL_BF16
+    w.free()

@@ -157,3 +157,18 @@ def test_validate_shape_rules(oracle):
     assert ok(8, 16, 8, 5, 1) != 0         # bits
     assert ok(4, 32 * 1025, 32, 4, 1) != 0  # more than 1024 groups
     assert ok(4, 32 * 1024, 32, 4, 1) == 0
+
+
+def test_gather_decode_kats(oracle, kats):
+    for k in kats["gather"]:
+        packed = np.array([[_h(w) for w in row] for row in k["packed"]], np.uint32)
+        s = np.array([[_h(w) for w in row] for row in k["scales"]], np.uint16)
+        b = np.array([[_h(w) for w in row] for row in k["biases"]], np.uint16)
+        out = oracle.gather_dequant_f32(packed, s, b, k["group"], k["bits"], k["ids"], sdtype=k["sdtype"])
+        assert np.allclose(out, k["expect_all"], atol=k["tol"]), k["src"]
+    # an index outside the table is the reference's error.InvalidTokenId (quant_decode.zig:155,194)
+    k = kats["gather"][0]
+    packed = np.array([[_h(w) for w in row] for row in k["packed"]], np.uint32)
+    sb = np.zeros((2, 1), np.uint16)
+    with pytest.raises(oracle.InvalidTokenId):
+        oracle.gather_dequant_f32(packed, sb, sb, 8, 4, [2], sdtype=0)
