@@ -1408,13 +1408,15 @@ cudaError_t dispatch_dp4a(const GemvParams &p, const WeightView &w, uint32_t cta
 #undef TGAF_CASE
         }
     }
-#define TGAF_CASE(MDv)                                                                                       \
-    if (M == MDv)                                                                                            \
-        return bf ? launch_dp4a<GB, MDv, false, 1, kConsumerWarps, kStages, kMaxBlockUnits>(p, w, ctas, pdl, stream) \
-                  : launch_dp4a<GB, MDv, false, 0, kConsumerWarps, kStages, kMaxBlockUnits>(p, w, ctas, pdl, stream);
-    TGAF_CASE(1)
-    TGAF_CASE(2)
-#undef TGAF_CASE
+    // Ring depth: four stages for one activation row where shared memory allows (group sizes 64 / 128),
+    // three otherwise.  (Five stages measured no better: the kernel is issue-bound before it is latency-bound.)
+    constexpr int NST1 = GB == 16 ? 3 : 4;
+    if (M == 1)
+        return bf ? launch_dp4a<GB, 1, false, 1, kConsumerWarps, NST1, 8>(p, w, ctas, pdl, stream)
+                  : launch_dp4a<GB, 1, false, 0, kConsumerWarps, NST1, 8>(p, w, ctas, pdl, stream);
+    if (M == 2)
+        return bf ? launch_dp4a<GB, 2, false, 1, kConsumerWarps, 3, 8>(p, w, ctas, pdl, stream)
+                  : launch_dp4a<GB, 2, false, 0, kConsumerWarps, 3, 8>(p, w, ctas, pdl, stream);
     return cudaErrorNotSupported;
 }
 
