@@ -36,9 +36,10 @@ sys.path.insert(0, str(ROOT))
 METRIC = "gaf4_64 decode GEMV HBM GB/s"
 GROUP, BITS = 64, 4
 NOMINAL_HBM_GBS = 8000.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one gate-shaped launch (14336 x 4096, M = 1),
-# from the ncu capture summarised in profiles/gemv_stream_gate_m1.md
-NCU_TRAFFIC_GATE_LAUNCH = 33_083_392
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, averaged over the step's two launch shapes
+# (gate|up 66,773,760 + 477,440 B; down 33,795,840 + 512 B), from the ncu capture summarised in
+# profiles/gemv_dp4a_llama8b_ffn_m1.md
+NCU_TRAFFIC_PER_LAUNCH = (66_773_760 + 477_440 + 33_795_840 + 512) // 2
 
 
 def measured_peak_hbm():
@@ -331,8 +332,8 @@ def run_single(args):
                              "frac_of_nominal_8TBs": round(r["gbs"] / NOMINAL_HBM_GBS, 4)} for m, r in results.items()},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}",
-                     "traffic": NCU_TRAFFIC_GATE_LAUNCH,
-                     "traffic_note": "dram bytes of one 14336x4096 launch (33.03 MB algorithmic); the fused gate|up launch is twice that"},
+                     "traffic": NCU_TRAFFIC_PER_LAUNCH,
+                     "traffic_note": "ncu dram bytes per launch, mean of the step's two shapes (algorithmic mean 49.6 MB)"},
         "cpu_baseline": {"value": round(cpu_gbs, 3), "unit": "GB/s", "cores": cores, "kind": "port",
                          "sample": f"{cpu_n} calls of one gate-shaped matrix [14336 x 4096], M=1, f32 activations ({cpu_per_call * 1e3:.2f} ms each)"},
         "e2e": {"value": round(e2e_gbs, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
