@@ -234,6 +234,8 @@ gaf_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
             for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++ti) {
                 if (ti > 0 && !mbar_wait(smem_u32(&s_acc_empty), (ti - 1u) & 1u, &s_abort, p.error_word, 0x200u)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                // rows 128..255 of the tile exist only when M reaches them (skinny M: half the tensor work)
+                const bool two_halves = (tile % p.m_tiles) * kBM + 128u < p.M;
                 for (uint32_t kb = 0; kb < p.k_blocks; ++kb, ++it) {
                     const uint32_t stage = it % kStagesTc, par = (it / kStagesTc) & 1u;
                     if (!mbar_wait(smem_u32(&s_full[stage]), par, &s_abort, p.error_word, 0x400u) ||
@@ -250,7 +252,7 @@ gaf_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
                         const uint32_t acc = (kb | k16) ? 1u : 0u;
                         // advancing 16 elements (32 bytes) along K inside the swizzle span: +2 in the address field
                         umma_f16(tmem_base, a0 + 2 * k16, bd + 2 * k16, kInstrDesc, acc);
-                        umma_f16(tmem_base + 256u, a1 + 2 * k16, bd + 2 * k16, kInstrDesc, acc);
+                        if (two_halves) umma_f16(tmem_base + 256u, a1 + 2 * k16, bd + 2 * k16, kInstrDesc, acc);
                     }
                     umma_commit(smem_u32(&s_empty[stage]));  // frees the stage once these MMAs have read it
                 }
@@ -396,7 +398,7 @@ EncodeTiledFn encode_fn() {
 }  // namespace
 
 bool gemm_tc_eligible(const WeightView &w, uint32_t M) {
-    if (M < 128u) return false;                                   // below that the tile is mostly padding
+    if (M <= 16u) return false;                                   // the decode GEMV kernels take M <= 16
     if (w.bits != 4u) return false;
     if (w.group != 32u && w.group != 64u && w.group != 128u) return false;
     if (w.K % kBK != 0u || w.groups % 8u != 0u) return false;      // whole K blocks; 16-byte loads of scales

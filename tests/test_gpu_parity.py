@@ -297,10 +297,11 @@ def _prefill_case(gaf, ctx, oracle, M, N, K, G, seed):
     return got, ref
 
 
-@pytest.mark.parametrize("M,N,K,G", [(256, 256, 128, 64), (128, 512, 1024, 64), (300, 1000, 512, 32),
+@pytest.mark.parametrize("M,N,K,G", [(17, 256, 128, 64), (64, 1024, 2048, 64), (100, 300, 512, 128), (129, 256, 256, 32),
+                                     (256, 256, 128, 64), (128, 512, 1024, 64), (300, 1000, 512, 32),
                                      (515, 768, 2048, 128), (1024, 2048, 4096, 64)])
 def test_prefill_tensor_core_gemm(gaf, ctx, oracle, M, N, K, G):
-    """Prefill dequant-GEMM (tcgen05 path, M >= 128): full tiles, ragged M and N, every group size.
+    """Prefill / skinny-M dequant-GEMM (tcgen05 path, M > 16): full tiles, ragged M and N, every group size.
     Weights are rounded to bf16 after the affine (one rounding), fp32 accumulate, bf16 out.  rel <= 1e-2."""
     got, ref = _prefill_case(gaf, ctx, oracle, M, N, K, G, seed=M + N)
     assert rel_err(got, ref) <= TOL_BF16, (M, N, K, G, rel_err(got, ref))
