@@ -269,7 +269,9 @@ def run_single(args):
             xs, ys = make_io(M)
 
             def step():
-                for (_, w), y in zip(weights, ys):
+                # a decoder knows its layer order: each call names the weight the following call streams
+                for i, ((_, w), y) in enumerate(zip(weights, ys)):
+                    gaf.hint_next_weight(ctx, weights[(i + 1) % len(weights)][1])
                     gaf.linear(ctx, w, xs[w.K], out=y)
 
             ms = time_graph(ctx, torch, stream, step, args.steps, args.warmup)

@@ -74,7 +74,7 @@ int32_t tgaf_ctx_destroy(tgaf_ctx *ctx);
 int32_t tgaf_ctx_set_stream(tgaf_ctx *ctx, void *stream);
 int32_t tgaf_synchronize(tgaf_ctx *ctx);
 const char *tgaf_last_error(const tgaf_ctx *ctx);
-/* Tuning knobs by name ("gemv_ctas", "pdl", "force_generic"); unknown names
+/* Tuning knobs by name ("gemv_ctas", "pdl", "force_generic", "prefetch_units"); unknown names
  * are TGAF_ERR_INVALID_ARGUMENT. */
 int32_t tgaf_ctx_set_option(tgaf_ctx *ctx, const char *name, int64_t value);
 
@@ -106,6 +106,17 @@ int32_t tgaf_weight_free(tgaf_ctx *ctx, tgaf_weight *w);
 /* local (per-rank) sizes of a weight */
 int32_t tgaf_weight_dims(const tgaf_weight *w, uint64_t *n_local, uint64_t *k_local,
                          uint32_t *group_size, uint32_t *bits);
+
+/* Names the weight that the NEXT tgaf_linear_* call after the coming one will
+ * stream, i.e. call order: hint(B); linear(A); linear(B).  While A's kernel
+ * drains, its copy warps ask L2 for the first tiles of B, so HBM keeps streaming
+ * across A's write-out, the launch gap and B's prologue.  One-shot: consumed (or
+ * dropped) by the first linear call that follows; NULL clears it.  Results never
+ * depend on it.  `next` must stay alive until that call has run on the GPU.
+ * "prefetch_units" (tgaf_ctx_set_option) bounds how much of B is requested.
+ * No counterpart in the reference, whose decoder issues each linear on its own
+ * (core/src/inference/backend/cuda/engine.zig:4431-4474). */
+int32_t tgaf_hint_next_weight(tgaf_ctx *ctx, const tgaf_weight *next);
 
 /* ---- the matmul operator ------------------------------------------------
  * Replaces the .gaffine_u4 arm of CudaBackend.linearForwardRows

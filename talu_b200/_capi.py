@@ -25,6 +25,7 @@ SIGNATURES = {
     "tgaf_weight_wrap_device": (_i32, [_vp, _vp, _vp, _vp, _u64, _u64, _u32, _u32, _u32, _pp]),
     "tgaf_weight_free": (_i32, [_vp, _vp]),
     "tgaf_weight_dims": (_i32, [_vp, C.POINTER(_u64), C.POINTER(_u64), C.POINTER(_u32), C.POINTER(_u32)]),
+    "tgaf_hint_next_weight": (_i32, [_vp, _vp]),
     "tgaf_linear_bf16": (_i32, [_vp, _vp, _vp, _u32, _vp]),
     "tgaf_linear_f32": (_i32, [_vp, _vp, _vp, _u32, _vp]),
     "tgaf_linear_bf16_fixed_scratch": (_i32, [_vp, _vp, _vp, _u32, _vp]),

@@ -76,7 +76,7 @@ struct tgaf_ctx {
     bool owns_stream = false;
     int sm_count = 148;
     Scratch scratch = {nullptr, 0, nullptr, 0};
-    GemvTuning tune = {0, 1, 0, 0, 0, 0};
+    GemvTuning tune = {0, 1, 0, 0, 0, 0, 2, nullptr};
     // staging for the *_host entry points
     void *stage_x = nullptr;
     size_t stage_x_bytes = 0;
@@ -171,6 +171,9 @@ int32_t ensure_stage(tgaf_ctx *ctx, void **buf, size_t *have, size_t need) {
 
 // The operator: picks the kernel for (shape, M) and enqueues it.
 int32_t linear_device(tgaf_ctx *ctx, const WeightView &w, const void *x, uint32_t M, void *y, bool f32) {
+    // the next-weight hint belongs to exactly one call, whichever kernel that call ends up on
+    const WeightView *hint = ctx->tune.next;
+    ctx->tune.next = nullptr;
     if (!x || !y) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null activation or output pointer");
     if (M == 0) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "M must be > 0");
     const size_t elt = f32 ? 4 : 2;
@@ -190,7 +193,9 @@ int32_t linear_device(tgaf_ctx *ctx, const WeightView &w, const void *x, uint32_
             if (st != TGAF_OK) return st;
             const void *xp = static_cast<const uint8_t *>(x) + static_cast<size_t>(m0) * w.K * elt;
             void *yp = static_cast<uint8_t *>(y) + static_cast<size_t>(m0) * w.N * elt;
-            cudaError_t e = gemv_mma(w, xp, yp, mc, f32, ctx->scratch, ctx->tune, ctx->stream, ctx->sm_count,
+            GemvTuning t = ctx->tune;
+            t.next = m0 + 16u >= M ? hint : nullptr;  // the last chunk is the one the next launch follows
+            cudaError_t e = gemv_mma(w, xp, yp, mc, f32, ctx->scratch, t, ctx->stream, ctx->sm_count,
                                      ctx->d_error_word);
             if (e != cudaSuccess) return cuda_fail(ctx, e, "gemv_mma launch");
         }
@@ -377,6 +382,9 @@ int32_t tgaf_ctx_set_option(tgaf_ctx *ctx, const char *name, int64_t value) {
         ctx->tune.dp4a_small = value != 0;
     } else if (!strcmp(name, "no_dp4a")) {
         ctx->tune.no_dp4a = value != 0;
+    } else if (!strcmp(name, "prefetch_units")) {
+        if (value < 0 || value > 4096) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "prefetch_units out of range");
+        ctx->tune.prefetch_units = static_cast<int>(value);
     } else if (!strcmp(name, "probe")) {
         ctx->tune.probe = static_cast<int>(value);
     } else {
@@ -505,8 +513,15 @@ int32_t tgaf_weight_wrap_device(tgaf_ctx *ctx, const void *d_packed, const void 
     return TGAF_OK;
 }
 
+int32_t tgaf_hint_next_weight(tgaf_ctx *ctx, const tgaf_weight *next) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    ctx->tune.next = next ? &next->v : nullptr;
+    return TGAF_OK;
+}
+
 int32_t tgaf_weight_free(tgaf_ctx *ctx, tgaf_weight *w) {
     if (!w) return TGAF_OK;
+    if (ctx && ctx->tune.next == &w->v) ctx->tune.next = nullptr;
     if (w->owns) {
         if (ctx) {
             cudaSetDevice(ctx->device);
@@ -554,6 +569,7 @@ int32_t tgaf_linear_bf16_fixed_scratch(tgaf_ctx *ctx, const tgaf_weight *w, cons
     // nothing below allocates: no cudaMalloc / cudaFree, no growth of the context's scratch
     TGAF_CUDA(ctx, cudaSetDevice(ctx->device));
     const WeightView &v = w->v;
+    ctx->tune.next = nullptr;  // a pending next-weight hint is dropped: this variant does not prefetch
     if (ctx->tune.force_generic || !gemv_mma_eligible(v, x_bf16, y_bf16, false)) {
         // shapes outside the fast path use the kernel that needs no scratch at all
         cudaError_t e = gemv_generic(v, x_bf16, y_bf16, M, false, ctx->stream);

@@ -91,6 +91,11 @@ struct GemvParams {
     uint32_t chunks;      // K chunks per row group
     uint32_t units;       // row groups * chunks
     uint32_t max_slots;   // scratch slots per row group
+    uint32_t next_units;     // head-of-next-weight L2 prefetch: units of the next weight (0 = no hint)
+    uint32_t next_chunks;    //   its K chunks per row group
+    uint32_t next_ctas;      //   the grid it will run on
+    uint32_t next_gps;       //   its groups per unit
+    uint32_t next_prefetch;  //   units to prefetch at the head of each of its CTA ranges
     uint32_t probe;       // measurement aid, bit mask: 1 = skip the arithmetic, 2 = skip the streaming, 4 = skip the write-out,
                           // 8 = skip the activation block, 32 = return at once (launch cost only)
 };
@@ -134,6 +139,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tma
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
         "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(bar)
         : "memory");
+}
+
+// the same tile as an L2 prefetch (no shared-memory destination, nothing to wait for)
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *tmap, uint32_t c0, uint32_t c1) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(tmap)),
+                 "r"(c0), "r"(c1)
+                 : "memory");
 }
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -323,10 +335,36 @@ __device__ __forceinline__ float sb_half(uint32_t w, int hi) {
 }
 
 // Warp roles: 0..15 consumers (kh * 8 + rb), 16 producer, 17 writer.
+// Head-of-next-weight prefetch.  A decoder knows which weight the following launch streams; the host can
+// name it, and each producer, once its own last tile is requested, asks L2 for the first tiles of the ranges
+// the next launch's CTAs will start on.  Those requests queue behind this launch's reads, so HBM keeps
+// streaming through this launch's write-out tail, the launch gap and the next launch's prologue, which
+// then finds its first tiles in L2.  Nothing waits on a prefetch and it has no destination in this CTA.
+__device__ __forceinline__ void prefetch_next_head(const GemvParams &p, const CUtensorMap *nw, const CUtensorMap *ns,
+                                                   const CUtensorMap *nb) {
+    if (p.next_units == 0u) return;
+    for (uint32_t c = blockIdx.x; c < p.next_ctas; c += gridDim.x) {
+        const uint32_t b = range_begin(c, p.next_units, p.next_ctas);
+        uint32_t e = range_begin(c + 1u, p.next_units, p.next_ctas);
+        if (e > b + p.next_prefetch) e = b + p.next_prefetch;
+        uint32_t rg = b / p.next_chunks, kc = b - rg * p.next_chunks;
+        for (uint32_t u = b; u < e; ++u) {
+#pragma unroll
+            for (int pnl = 0; pnl < kPanels; ++pnl) tma_prefetch_2d(nw, kc * kChunkBytes + pnl * kPanelBytes, rg * kRows);
+            const uint32_t sb_col = (kc * p.next_gps * 2u) & ~15u;
+            tma_prefetch_2d(ns, sb_col, rg * kRows);
+            tma_prefetch_2d(nb, sb_col, rg * kRows);
+            if (++kc == p.next_chunks) kc = 0u, ++rg;
+        }
+    }
+}
+
 template <int GB, int BITS, int MT, bool XF32, int SD>
 __global__ void __launch_bounds__(kThreads, 1)
 gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap_w,
-                       const __grid_constant__ CUtensorMap tmap_s, const __grid_constant__ CUtensorMap tmap_b) {
+                       const __grid_constant__ CUtensorMap tmap_s, const __grid_constant__ CUtensorMap tmap_b,
+                       const __grid_constant__ CUtensorMap next_w, const __grid_constant__ CUtensorMap next_s,
+                       const __grid_constant__ CUtensorMap next_b) {
     using Geo = StreamGeom<GB>;
     using Plan = SmemPlan<GB, MT, XF32>;
     constexpr int GPS = Geo::GPS, GPP = Geo::GPP, LW = Geo::LW, WPT = Geo::WPT;
@@ -408,6 +446,8 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                 const uint32_t idx = issued - 1u - i;
                 mbar_wait(smem_u32(&s_full[idx % kStages]), (idx / kStages) & 1u, p.error_word, 0x4u);
             }
+        } else {
+            prefetch_next_head(p, &next_w, &next_s, &next_b);
         }
         return;
     }
@@ -822,7 +862,9 @@ struct DpPlan {
 template <int GB, int MD, bool XF32, int SD, int NCW, int NST, int BU>
 __global__ void __launch_bounds__((NCW + 2) * 32, NCW == 8 ? 2 : 1)
 gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap_w,
-                     const __grid_constant__ CUtensorMap tmap_s, const __grid_constant__ CUtensorMap tmap_b) {
+                     const __grid_constant__ CUtensorMap tmap_s, const __grid_constant__ CUtensorMap tmap_b,
+                     const __grid_constant__ CUtensorMap next_w, const __grid_constant__ CUtensorMap next_s,
+                     const __grid_constant__ CUtensorMap next_b) {
     using Geo = StreamGeom<GB>;
     using Plan = DpPlan<GB, MD, XF32, NST, BU>;
     constexpr int GPS = Geo::GPS, WPG = Plan::WPG;
@@ -900,6 +942,8 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
                 const uint32_t idx = issued - 1u - i;
                 mbar_wait(smem_u32(&s_full[idx % NST]), (idx / NST) & 1u, p.error_word, 0x4u);
             }
+        } else {
+            prefetch_next_head(p, &next_w, &next_s, &next_b);
         }
         return;
     }
@@ -1160,9 +1204,11 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
             const uint32_t sbo = (kc * GPS * 2u) & 15u;
 #pragma unroll
             for (int i = 0; i < R; ++i) {
-                uint16_t sraw, braw;
-                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sraw) : "r"(stage_off + sboff[i] + sbo));
-                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(braw) : "r"(stage_off + sboff[i] + sbo + Geo::SB_BYTES));
+                uint16_t sraw = 0x3BAE, braw = 0xBD24;
+                if (!(p.probe & 16u)) {
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sraw) : "r"(stage_off + sboff[i] + sbo));
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(braw) : "r"(stage_off + sboff[i] + sbo + Geo::SB_BYTES));
+                }
                 const float s = sb_half<SD>(sraw, 0), b = sb_half<SD>(braw, 0);
 #pragma unroll
                 for (int m = 0; m < MD; ++m) {
@@ -1347,7 +1393,8 @@ GemvPlan plan_gemv(const WeightView &w, const GemvTuning &tune, int sm_count) {
 }
 
 template <int GB, int BITS, int MT, bool XF32, int SD>
-cudaError_t launch_stream(const GemvParams &p, const WeightView &w, uint32_t ctas, bool pdl, cudaStream_t stream) {
+cudaError_t launch_stream(const GemvParams &p, const WeightView &w, const WeightView *next, uint32_t ctas, bool pdl,
+                          cudaStream_t stream) {
     auto kern = gaf_gemv_stream_kernel<GB, BITS, MT, XF32, SD>;
     using Plan = SmemPlan<GB, MT, XF32>;
     static bool configured = false;  // per instantiation; the attribute belongs to the function, not the stream
@@ -1366,11 +1413,13 @@ cudaError_t launch_stream(const GemvParams &p, const WeightView &w, uint32_t cta
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kern, p, w.tmap, w.tmap_s, w.tmap_b);
+    const WeightView &nx = next ? *next : w;
+    return cudaLaunchKernelEx(&cfg, kern, p, w.tmap, w.tmap_s, w.tmap_b, nx.tmap, nx.tmap_s, nx.tmap_b);
 }
 
 template <int GB, int MD, bool XF32, int SD, int NCW, int NST, int BU>
-cudaError_t launch_dp4a(const GemvParams &p, const WeightView &w, uint32_t ctas, bool pdl, cudaStream_t stream) {
+cudaError_t launch_dp4a(const GemvParams &p, const WeightView &w, const WeightView *next, uint32_t ctas, bool pdl,
+                        cudaStream_t stream) {
     auto kern = gaf_gemv_dp4a_kernel<GB, MD, XF32, SD, NCW, NST, BU>;
     using Plan = DpPlan<GB, MD, XF32, NST, BU>;
     static bool configured = false;
@@ -1389,20 +1438,22 @@ cudaError_t launch_dp4a(const GemvParams &p, const WeightView &w, uint32_t ctas,
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kern, p, w.tmap, w.tmap_s, w.tmap_b);
+    const WeightView &nx = next ? *next : w;
+    return cudaLaunchKernelEx(&cfg, kern, p, w.tmap, w.tmap_s, w.tmap_b, nx.tmap, nx.tmap_s, nx.tmap_b);
 }
 
 // small = true: 8 consumer warps, 2 stages, two CTAs per SM (group sizes 64 and 128 only)
 template <int GB>
-cudaError_t dispatch_dp4a(const GemvParams &p, const WeightView &w, uint32_t ctas, uint32_t M, bool small, bool pdl,
+cudaError_t dispatch_dp4a(const GemvParams &p, const WeightView &w, const WeightView *next, uint32_t ctas, uint32_t M,
+                          bool small, bool pdl,
                           cudaStream_t stream) {
     const bool bf = p.sdtype == 1u;
     if constexpr (GB >= 32) {
         if (small) {
 #define TGAF_CASE(MDv)                                                                                   \
     if (M == MDv)                                                                                        \
-        return bf ? launch_dp4a<GB, MDv, false, 1, 8, 2, 8>(p, w, ctas, pdl, stream)                     \
-                  : launch_dp4a<GB, MDv, false, 0, 8, 2, 8>(p, w, ctas, pdl, stream);
+        return bf ? launch_dp4a<GB, MDv, false, 1, 8, 2, 8>(p, w, next, ctas, pdl, stream)                     \
+                  : launch_dp4a<GB, MDv, false, 0, 8, 2, 8>(p, w, next, ctas, pdl, stream);
             TGAF_CASE(1)
             TGAF_CASE(2)
 #undef TGAF_CASE
@@ -1412,22 +1463,23 @@ cudaError_t dispatch_dp4a(const GemvParams &p, const WeightView &w, uint32_t cta
     // three otherwise.  (Five stages measured no better: the kernel is issue-bound before it is latency-bound.)
     constexpr int NST1 = GB == 16 ? 3 : 4;
     if (M == 1)
-        return bf ? launch_dp4a<GB, 1, false, 1, kConsumerWarps, NST1, 8>(p, w, ctas, pdl, stream)
-                  : launch_dp4a<GB, 1, false, 0, kConsumerWarps, NST1, 8>(p, w, ctas, pdl, stream);
+        return bf ? launch_dp4a<GB, 1, false, 1, kConsumerWarps, NST1, 8>(p, w, next, ctas, pdl, stream)
+                  : launch_dp4a<GB, 1, false, 0, kConsumerWarps, NST1, 8>(p, w, next, ctas, pdl, stream);
     if (M == 2)
-        return bf ? launch_dp4a<GB, 2, false, 1, kConsumerWarps, 3, 8>(p, w, ctas, pdl, stream)
-                  : launch_dp4a<GB, 2, false, 0, kConsumerWarps, 3, 8>(p, w, ctas, pdl, stream);
+        return bf ? launch_dp4a<GB, 2, false, 1, kConsumerWarps, 3, 8>(p, w, next, ctas, pdl, stream)
+                  : launch_dp4a<GB, 2, false, 0, kConsumerWarps, 3, 8>(p, w, next, ctas, pdl, stream);
     return cudaErrorNotSupported;
 }
 
 template <int GB, int BITS>
-cudaError_t dispatch_stream(const GemvParams &p, const WeightView &tmap, uint32_t ctas, int mt, bool xf32, bool pdl,
+cudaError_t dispatch_stream(const GemvParams &p, const WeightView &tmap, const WeightView *next, uint32_t ctas, int mt,
+                            bool xf32, bool pdl,
                             cudaStream_t stream) {
     const bool bf = p.sdtype == 1u;
 #define TGAF_CASE(MTv, XFv)                                                                          \
     if (mt == MTv && xf32 == XFv)                                                                    \
-        return bf ? launch_stream<GB, BITS, MTv, XFv, 1>(p, tmap, ctas, pdl, stream)                 \
-                  : launch_stream<GB, BITS, MTv, XFv, 0>(p, tmap, ctas, pdl, stream);
+        return bf ? launch_stream<GB, BITS, MTv, XFv, 1>(p, tmap, next, ctas, pdl, stream)                 \
+                  : launch_stream<GB, BITS, MTv, XFv, 0>(p, tmap, next, ctas, pdl, stream);
     TGAF_CASE(1, false)
     TGAF_CASE(2, false)
     TGAF_CASE(1, true)
@@ -1553,23 +1605,38 @@ cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bo
     p.units = pl.units;
     p.max_slots = pl.max_slots;
     p.probe = static_cast<uint32_t>(tune.probe);
+    // optional hint: the weight the following launch will stream (same unit geometry on either GEMV kernel)
+    const WeightView *next = nullptr;
+    p.next_units = p.next_chunks = p.next_ctas = p.next_gps = p.next_prefetch = 0u;
+    if (tune.next && tune.prefetch_units > 0 && tune.next->has_tmap) {
+        const uint32_t ngb = tune.next->group * tune.next->bits / 8u;
+        if (ngb != 0u && kChunkBytes % ngb == 0u) {
+            const GemvPlan np = plan_gemv(*tune.next, tune, sm_count);
+            next = tune.next;
+            p.next_units = np.units;
+            p.next_chunks = np.chunks;
+            p.next_ctas = np.ctas;
+            p.next_gps = kChunkBytes / ngb;
+            p.next_prefetch = static_cast<uint32_t>(tune.prefetch_units);
+        }
+    }
     const bool pdl = tune.pdl != 0;
     if (w.bits == 4 && M <= 2u && !x_f32 && !tune.no_dp4a) {
         // one or two bf16 activation rows: the integer dot-product formulation (its 13-bit activations
         // are ample next to bf16 inputs; f32 callers keep the hi + lo tensor-core path and its 1e-3 accuracy)
         const bool small = tune.dp4a_small != 0 && gb >= 32u;
-        if (gb == 16u) return dispatch_dp4a<16>(p, w, pl.ctas, M, false, pdl, stream);
-        if (gb == 32u) return dispatch_dp4a<32>(p, w, pl.ctas, M, small, pdl, stream);
-        if (gb == 64u) return dispatch_dp4a<64>(p, w, pl.ctas, M, small, pdl, stream);
+        if (gb == 16u) return dispatch_dp4a<16>(p, w, next, pl.ctas, M, false, pdl, stream);
+        if (gb == 32u) return dispatch_dp4a<32>(p, w, next, pl.ctas, M, small, pdl, stream);
+        if (gb == 64u) return dispatch_dp4a<64>(p, w, next, pl.ctas, M, small, pdl, stream);
     }
     if (w.bits == 4) {
-        if (gb == 16u) return dispatch_stream<16, 4>(p, w, pl.ctas, mt, x_f32, pdl, stream);
-        if (gb == 32u) return dispatch_stream<32, 4>(p, w, pl.ctas, mt, x_f32, pdl, stream);
-        if (gb == 64u) return dispatch_stream<64, 4>(p, w, pl.ctas, mt, x_f32, pdl, stream);
+        if (gb == 16u) return dispatch_stream<16, 4>(p, w, next, pl.ctas, mt, x_f32, pdl, stream);
+        if (gb == 32u) return dispatch_stream<32, 4>(p, w, next, pl.ctas, mt, x_f32, pdl, stream);
+        if (gb == 64u) return dispatch_stream<64, 4>(p, w, next, pl.ctas, mt, x_f32, pdl, stream);
     } else {
-        if (gb == 32u) return dispatch_stream<32, 8>(p, w, pl.ctas, mt, x_f32, pdl, stream);
-        if (gb == 64u) return dispatch_stream<64, 8>(p, w, pl.ctas, mt, x_f32, pdl, stream);
-        if (gb == 128u) return dispatch_stream<128, 8>(p, w, pl.ctas, mt, x_f32, pdl, stream);
+        if (gb == 32u) return dispatch_stream<32, 8>(p, w, next, pl.ctas, mt, x_f32, pdl, stream);
+        if (gb == 64u) return dispatch_stream<64, 8>(p, w, next, pl.ctas, mt, x_f32, pdl, stream);
+        if (gb == 128u) return dispatch_stream<128, 8>(p, w, next, pl.ctas, mt, x_f32, pdl, stream);
     }
     return cudaErrorNotSupported;
 }
@@ -1630,6 +1697,7 @@ cudaError_t gemv_mma_static(const WeightView &w, const void *x, void *y, uint32_
     if (e != cudaSuccess) return e;
     GemvTuning t = tune;
     t.pdl = 0;  // the memset before the launch is a full dependency anyway
+    t.next = nullptr;
     return gemv_mma(w, x, y, M, x_f32, sc, t, stream, sm_count, d_error_word);
 }
 

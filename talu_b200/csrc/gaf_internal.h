@@ -43,6 +43,8 @@ struct GemvTuning {
     int dp4a_small;     // M <= 2 path: 8 consumer warps + 2 stages per CTA (two CTAs fit on an SM)
     int no_dp4a;        // keep M <= 2 on the tensor-core formulation (for A/B comparisons)
     int probe;          // measurement aid for the streaming GEMV (0 = off); results are wrong when set
+    int prefetch_units; // units at the head of each CTA range of the hinted next weight to pull into L2
+    const WeightView *next;  // the weight the following launch will stream (one-shot hint; may be null)
 };
 
 // y[M,N] = x[M,K] * W^T for M <= 16 on the tensor-core GEMV path.

@@ -181,6 +181,12 @@ def linear(ctx: Context, w: Weight, x, out=None):
     return out
 
 
+def hint_next_weight(ctx: Context, w) -> None:
+    """Names the weight the linear call AFTER the coming one will use (tgaf_hint_next_weight): the coming
+    call's kernel then pulls the head of `w` into L2 while it drains.  One-shot; None clears it."""
+    ctx._check(ctx._lib.tgaf_hint_next_weight(ctx._h, w._h if w is not None else None))
+
+
 def linear_fixed_scratch(ctx: Context, w: Weight, x, out=None):
     """`linear` for bf16 activations through tgaf_linear_bf16_fixed_scratch: the library call
     allocates nothing (its split-K scratch is a fixed array inside the library image).  The

@@ -70,7 +70,8 @@ def measure(args, existing_ctx=None, existing_stream=None):
     ys = [torch.empty((M, w.N), dtype=torch.bfloat16, device="cuda") for _, _, w in ws]
 
     def step():
-        for (name, kind, w), y in zip(ws, ys):
+        for i, ((name, kind, w), y) in enumerate(zip(ws, ys)):
+            gaf.hint_next_weight(ctx, ws[(i + 1) % len(ws)][2])
             gaf.linear(ctx, w, xs[w.K], out=y)
             if kind == SHARD_ROW and world > 1:
                 ctx.allreduce(y)          # partial sums of the row-parallel output -> full [M, 8192]

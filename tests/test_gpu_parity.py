@@ -200,6 +200,45 @@ def test_split_k_is_deterministic_and_tunable(gaf, ctx, oracle):
     w.free()
 
 
+def test_next_weight_hint_changes_no_result(gaf, ctx, oracle):
+    """The next-weight hint only warms L2: with it, without it, at any depth, with a next weight of
+    another scheme, or with a hinted weight that is freed before the call, outputs keep their bits."""
+    import torch
+    pa, sa, ba = make_weights(oracle, 1000, 2048, 64, 4, seed=21)
+    pb, sb, bb = make_weights(oracle, 300, 1024, 32, 8, seed=22)
+    wa = gaf.Weight.from_host(ctx, pa, sa, ba, 64, 4)
+    wb = gaf.Weight.from_host(ctx, pb, sb, bb, 32, 8)
+    try:
+        for M in (1, 2, 5, 16):
+            xab, xaf = make_x_bf16(oracle, M, 2048, 30 + M)
+            xbb, xbf = make_x_bf16(oracle, M, 1024, 40 + M)
+            xa, xb = torch_bf16_from_bits(xab, "cuda:0"), torch_bf16_from_bits(xbb, "cuda:0")
+            ya0, yb0 = gaf.linear(ctx, wa, xa).clone(), gaf.linear(ctx, wb, xb).clone()
+            assert rel_err(oracle.bf16_to_f32(bits_from_torch_bf16(ya0)), oracle.matmul_f32(xaf, pa, sa, ba, 64, 4)) <= TOL_BF16
+            assert rel_err(oracle.bf16_to_f32(bits_from_torch_bf16(yb0)), oracle.matmul_f32(xbf, pb, sb, bb, 32, 8)) <= TOL_BF16
+            for depth in (0, 1, 3, 4096):
+                ctx.set_option("prefetch_units", depth)
+                gaf.hint_next_weight(ctx, wb)
+                ya = gaf.linear(ctx, wa, xa)
+                gaf.hint_next_weight(ctx, wa)
+                yb = gaf.linear(ctx, wb, xb)
+                ctx.synchronize()
+                assert torch.equal(ya, ya0) and torch.equal(yb, yb0), (M, depth)
+        # a hint whose weight goes away before the call is dropped with it
+        pc, sc, bc = make_weights(oracle, 128, 512, 64, 4, seed=23)
+        wc = gaf.Weight.from_host(ctx, pc, sc, bc, 64, 4)
+        gaf.hint_next_weight(ctx, wc)
+        wc.free()
+        ya = gaf.linear(ctx, wa, xa)
+        ctx.synchronize()
+        assert torch.equal(ya, ya0)
+    finally:
+        ctx.set_option("prefetch_units", 2)
+        gaf.hint_next_weight(ctx, None)
+    wa.free()
+    wb.free()
+
+
 def test_linearity_at_full_size(gaf, ctx, oracle):
     """Size-independent property at the benchmark's full shape: y(2x) = 2 y(x) exactly
     (scaling by two is exact in bf16 and in every partial sum)."""
