@@ -26,7 +26,7 @@ struct NcclUniqueId {
     char internal[TGAF_COMM_ID_BYTES];
 };
 typedef void *NcclComm;
-enum { kNcclSuccess = 0, kNcclSum = 0, kNcclFloat32 = 7, kNcclBfloat16 = 9 };
+enum { kNcclSuccess = 0, kNcclSum = 0, kNcclMin = 3, kNcclUint8 = 1, kNcclInt32 = 2, kNcclFloat32 = 7, kNcclBfloat16 = 9 };
 
 struct NcclApi {
     void *handle = nullptr;
@@ -35,6 +35,7 @@ struct NcclApi {
     int (*CommDestroy)(NcclComm) = nullptr;
     int (*CommAbort)(NcclComm) = nullptr;
     int (*AllReduce)(const void *, void *, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
+    int (*AllGather)(const void *, void *, size_t, int, NcclComm, cudaStream_t) = nullptr;
     const char *(*GetErrorString)(int) = nullptr;
     bool ok = false;
     std::string why;
@@ -59,6 +60,7 @@ NcclApi &nccl_api() {
     api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(api.handle, "ncclCommDestroy"));
     api.CommAbort = reinterpret_cast<decltype(api.CommAbort)>(dlsym(api.handle, "ncclCommAbort"));
     api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(api.handle, "ncclAllReduce"));
+    api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(api.handle, "ncclAllGather"));
     api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(api.handle, "ncclGetErrorString"));
     api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce && api.GetErrorString;
     if (!api.ok) api.why = "libnccl is missing a required symbol";
@@ -76,7 +78,7 @@ struct tgaf_ctx {
     bool owns_stream = false;
     int sm_count = 148;
     Scratch scratch = {nullptr, 0, nullptr, 0};
-    GemvTuning tune = {0, 1, 0, 0, 0, 0, 2, nullptr};
+    GemvTuning tune = {0, 1, 0, 0, 0, 0, 2, nullptr, nullptr};
     // staging for the *_host entry points
     void *stage_x = nullptr;
     size_t stage_x_bytes = 0;
@@ -85,8 +87,16 @@ struct tgaf_ctx {
     unsigned int *d_error_word = nullptr;
     NcclComm comm = nullptr;
     uint32_t comm_rank = 0, comm_size = 1;
+    PeerComm peer = {{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr}, 0, 1, false};
+    int peer_allreduce = 1;  // small tiles go through the peer-memory kernel when the mapping exists
+    int fused_allreduce = 1; // tgaf_linear_bf16_allreduce sums inside the GEMV when it can
+    int peer_pdl = 0;        // programmatic stream serialization for the all-reduce kernel (measured slower)
     char err[512] = {0};
 };
+
+namespace {
+void peer_teardown(tgaf_ctx *ctx);
+}
 
 struct tgaf_weight {
     WeightView v;
@@ -170,7 +180,10 @@ int32_t ensure_stage(tgaf_ctx *ctx, void **buf, size_t *have, size_t need) {
 }
 
 // The operator: picks the kernel for (shape, M) and enqueues it.
-int32_t linear_device(tgaf_ctx *ctx, const WeightView &w, const void *x, uint32_t M, void *y, bool f32) {
+// `reduce`: also sum y over the communicator's ranks (inside the GEMV when it can, else a separate all-reduce).
+int32_t allreduce_device(tgaf_ctx *ctx, void *d_buf, uint64_t count, uint32_t dtype);
+
+int32_t linear_device(tgaf_ctx *ctx, const WeightView &w, const void *x, uint32_t M, void *y, bool f32, bool reduce = false) {
     // the next-weight hint belongs to exactly one call, whichever kernel that call ends up on
     const WeightView *hint = ctx->tune.next;
     ctx->tune.next = nullptr;
@@ -180,7 +193,8 @@ int32_t linear_device(tgaf_ctx *ctx, const WeightView &w, const void *x, uint32_
 
     if (!f32 && gemm_tc_eligible(w, M)) {
         cudaError_t e = gemm_tc(w, x, y, M, ctx->stream, ctx->sm_count, ctx->d_error_word);
-        if (e == cudaSuccess) return TGAF_OK;
+        if (e == cudaSuccess)
+            return reduce ? allreduce_device(ctx, y, static_cast<uint64_t>(M) * w.N, TGAF_DTYPE_BF16) : TGAF_OK;
         if (e != cudaErrorNotSupported) return cuda_fail(ctx, e, "gemm_tc");
     }
 
@@ -195,15 +209,25 @@ int32_t linear_device(tgaf_ctx *ctx, const WeightView &w, const void *x, uint32_
             void *yp = static_cast<uint8_t *>(y) + static_cast<size_t>(m0) * w.N * elt;
             GemvTuning t = ctx->tune;
             t.next = m0 + 16u >= M ? hint : nullptr;  // the last chunk is the one the next launch follows
+            t.fuse = nullptr;
+            if (reduce && M <= 16u && ctx->peer.ok && ctx->fused_allreduce) {
+                t.fuse = &ctx->peer;
+                if (gemv_fused_eligible(w, mc, f32, t)) {
+                    cudaError_t e = gemv_mma(w, xp, yp, mc, f32, ctx->scratch, t, ctx->stream, ctx->sm_count, ctx->d_error_word);
+                    if (e == cudaSuccess) return TGAF_OK;  // y is already the sum over the ranks
+                    if (e != cudaErrorNotSupported) return cuda_fail(ctx, e, "fused gemv launch");
+                }
+                t.fuse = nullptr;
+            }
             cudaError_t e = gemv_mma(w, xp, yp, mc, f32, ctx->scratch, t, ctx->stream, ctx->sm_count,
                                      ctx->d_error_word);
             if (e != cudaSuccess) return cuda_fail(ctx, e, "gemv_mma launch");
         }
-        return TGAF_OK;
+        return reduce ? allreduce_device(ctx, y, static_cast<uint64_t>(M) * w.N, f32 ? TGAF_DTYPE_F32 : TGAF_DTYPE_BF16) : TGAF_OK;
     }
     cudaError_t e = gemv_generic(w, x, y, M, f32, ctx->stream);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "gemv_generic launch");
-    return TGAF_OK;
+    return reduce ? allreduce_device(ctx, y, static_cast<uint64_t>(M) * w.N, f32 ? TGAF_DTYPE_F32 : TGAF_DTYPE_BF16) : TGAF_OK;
 }
 
 int32_t linear_host(tgaf_ctx *ctx, const tgaf_weight *w, const void *xh, uint32_t M, void *yh, bool f32) {
@@ -258,6 +282,103 @@ int32_t raw_matvec(tgaf_ctx *ctx, uint32_t bits, const float *input, const uint3
 // ---------------------------------------------------------------------------
 // exported functions
 // ---------------------------------------------------------------------------
+namespace {
+
+// Unmaps the peers' regions and frees the local one.  Safe at any time after the stream is idle: a rank's
+// last all-reduce returns only after every peer's last push into this rank's region has arrived.
+void peer_teardown(tgaf_ctx *ctx) {
+    PeerComm &pc = ctx->peer;
+    for (uint32_t r = 0; r < static_cast<uint32_t>(kPeerMaxRanks); ++r) {
+        if (!pc.region[r]) continue;
+        if (r == pc.rank)
+            cudaFree(pc.region[r]);
+        else
+            cudaIpcCloseMemHandle(pc.region[r]);
+        pc.region[r] = nullptr;
+    }
+    pc.ok = false;
+}
+
+// Maps every rank's all-reduce region into this process (CUDA IPC; the handles travel by ncclAllGather).
+// Any failure, on any rank, leaves ALL ranks on the NCCL path: the outcome is agreed by an all-reduce(min).
+void peer_setup(tgaf_ctx *ctx, NcclApi &api) {
+    PeerComm &pc = ctx->peer;
+    pc.rank = ctx->comm_rank;
+    pc.size = ctx->comm_size;
+    pc.ok = false;
+    if (!api.AllGather || pc.size < 1 || pc.size > static_cast<uint32_t>(kPeerMaxRanks)) return;
+    const char *env = getenv("TGAF_PEER_ALLREDUCE");
+    const bool wanted = !(env && env[0] == '0');
+    int good = wanted ? 1 : 0;
+    cudaIpcMemHandle_t mine;
+    memset(&mine, 0, sizeof mine);
+    void *local = nullptr;
+    if (good && cudaMalloc(&local, peer_region_bytes()) != cudaSuccess) good = 0, local = nullptr;
+    if (good && cudaMemset(local, 0, peer_region_bytes()) != cudaSuccess) good = 0;
+    if (good && cudaIpcGetMemHandle(&mine, local) != cudaSuccess) good = 0;
+    cudaGetLastError();
+    // exchange {handle, good} of every rank
+    constexpr size_t kRec = sizeof(cudaIpcMemHandle_t) + 8;
+    uint8_t host[kPeerMaxRanks * kRec];
+    memset(host, 0, sizeof host);
+    uint8_t *d_all = nullptr;
+    if (cudaMalloc(reinterpret_cast<void **>(&d_all), pc.size * kRec) != cudaSuccess) {
+        // cannot even exchange: every rank must still enter the collectives below, so use no device scratch
+        d_all = nullptr;
+    }
+    bool exchanged = false;
+    if (d_all) {
+        memcpy(host + pc.rank * kRec, &mine, sizeof mine);
+        host[pc.rank * kRec + sizeof mine] = static_cast<uint8_t>(good);
+        cudaMemcpy(d_all + pc.rank * kRec, host + pc.rank * kRec, kRec, cudaMemcpyHostToDevice);
+        cudaDeviceSynchronize();  // the memset of the region is complete before anybody learns its handle
+        if (api.AllGather(d_all + pc.rank * kRec, d_all, kRec, kNcclUint8, ctx->comm, ctx->stream) == kNcclSuccess &&
+            cudaStreamSynchronize(ctx->stream) == cudaSuccess &&
+            cudaMemcpy(host, d_all, pc.size * kRec, cudaMemcpyDeviceToHost) == cudaSuccess)
+            exchanged = true;
+    }
+    if (!exchanged) good = 0;
+    for (uint32_t r = 0; good && r < pc.size; ++r)
+        if (!host[r * kRec + sizeof mine]) good = 0;
+    if (good) {
+        for (uint32_t r = 0; r < pc.size; ++r) {
+            if (r == pc.rank) {
+                pc.region[r] = local;
+                continue;
+            }
+            cudaIpcMemHandle_t h;
+            memcpy(&h, host + r * kRec, sizeof h);
+            void *ptr = nullptr;
+            if (cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+                cudaGetLastError();
+                good = 0;
+                break;
+            }
+            pc.region[r] = ptr;
+        }
+    }
+    // second agreement: did every rank map every region?
+    if (d_all && exchanged) {
+        int32_t flag = good;
+        cudaMemcpy(d_all, &flag, sizeof flag, cudaMemcpyHostToDevice);
+        if (api.AllReduce(d_all, d_all, 1, kNcclInt32, kNcclMin, ctx->comm, ctx->stream) == kNcclSuccess &&
+            cudaStreamSynchronize(ctx->stream) == cudaSuccess &&
+            cudaMemcpy(&flag, d_all, sizeof flag, cudaMemcpyDeviceToHost) == cudaSuccess)
+            good = flag;
+        else
+            good = 0;
+    }
+    if (d_all) cudaFree(d_all);
+    if (good) {
+        pc.ok = true;
+    } else {
+        if (!pc.region[pc.rank] && local) cudaFree(local);
+        peer_teardown(ctx);
+    }
+}
+
+}  // namespace
+
 extern "C" {
 
 int32_t tgaf_abi_version(void) { return TGAF_ABI_VERSION; }
@@ -333,6 +454,7 @@ int32_t tgaf_ctx_destroy(tgaf_ctx *ctx) {
         if (api.ok && api.CommAbort) api.CommAbort(ctx->comm);
         ctx->comm = nullptr;
     }
+    peer_teardown(ctx);
     if (ctx->scratch.partials) cudaFree(ctx->scratch.partials);
     if (ctx->scratch.counters) cudaFree(ctx->scratch.counters);
     if (ctx->stage_x) cudaFree(ctx->stage_x);
@@ -382,6 +504,12 @@ int32_t tgaf_ctx_set_option(tgaf_ctx *ctx, const char *name, int64_t value) {
         ctx->tune.dp4a_small = value != 0;
     } else if (!strcmp(name, "no_dp4a")) {
         ctx->tune.no_dp4a = value != 0;
+    } else if (!strcmp(name, "peer_allreduce")) {
+        ctx->peer_allreduce = value != 0;
+    } else if (!strcmp(name, "fused_allreduce")) {
+        ctx->fused_allreduce = value != 0;
+    } else if (!strcmp(name, "peer_pdl")) {
+        ctx->peer_pdl = value != 0;
     } else if (!strcmp(name, "prefetch_units")) {
         if (value < 0 || value > 4096) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "prefetch_units out of range");
         ctx->tune.prefetch_units = static_cast<int>(value);
@@ -686,6 +814,7 @@ int32_t tgaf_comm_init(tgaf_ctx *ctx, const uint8_t id[TGAF_COMM_ID_BYTES], uint
     }
     ctx->comm_rank = rank;
     ctx->comm_size = nranks;
+    peer_setup(ctx, api);
     return TGAF_OK;
 }
 
@@ -694,6 +823,7 @@ int32_t tgaf_comm_destroy(tgaf_ctx *ctx) {
     if (!ctx->comm) return TGAF_OK;
     NcclApi &api = nccl_api();
     cudaStreamSynchronize(ctx->stream);
+    peer_teardown(ctx);
     if (api.ok) api.CommDestroy(ctx->comm);
     ctx->comm = nullptr;
     ctx->comm_size = 1;
@@ -701,16 +831,39 @@ int32_t tgaf_comm_destroy(tgaf_ctx *ctx) {
     return TGAF_OK;
 }
 
+int32_t tgaf_comm_uses_peer_memory(const tgaf_ctx *ctx) { return ctx && ctx->peer.ok ? 1 : 0; }
+
 int32_t tgaf_allreduce(tgaf_ctx *ctx, void *d_buf, uint64_t count, uint32_t dtype) {
+    return allreduce_device(ctx, d_buf, count, dtype);
+}
+
+int32_t tgaf_linear_bf16_allreduce(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16, uint32_t m, void *y_bf16) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!w) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null weight");
+    if (!ctx->comm) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "no communicator: call tgaf_comm_init first");
+    cudaSetDevice(ctx->device);
+    return linear_device(ctx, w->v, x_bf16, m, y_bf16, false, true);
+}
+
+}  // extern "C"
+
+namespace {
+int32_t allreduce_device(tgaf_ctx *ctx, void *d_buf, uint64_t count, uint32_t dtype) {
     if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
     if (!d_buf || count == 0) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null buffer or zero count");
     if (dtype != TGAF_DTYPE_F32 && dtype != TGAF_DTYPE_BF16) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "bad dtype %u", dtype);
     if (!ctx->comm) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "no communicator: call tgaf_comm_init first");
+    if (ctx->peer.ok && ctx->peer_allreduce) {
+        // decode-sized tiles: one kernel over NVLink peer memory; anything else falls through to NCCL
+        cudaError_t e = peer_allreduce(ctx->peer, d_buf, count, dtype == TGAF_DTYPE_F32, ctx->tune.pdl != 0 && ctx->peer_pdl != 0, ctx->stream,
+                                       ctx->d_error_word);
+        if (e == cudaSuccess) return TGAF_OK;
+        if (e != cudaErrorNotSupported) return cuda_fail(ctx, e, "peer all-reduce launch");
+    }
     NcclApi &api = nccl_api();
     int rc = api.AllReduce(d_buf, d_buf, count, dtype == TGAF_DTYPE_F32 ? kNcclFloat32 : kNcclBfloat16, kNcclSum,
                            ctx->comm, ctx->stream);
     if (rc != kNcclSuccess) return fail(ctx, TGAF_ERR_NCCL, "ncclAllReduce: %s", api.GetErrorString(rc));
     return TGAF_OK;
 }
-
-}  // extern "C"
+}  // namespace

@@ -96,6 +96,8 @@ struct GemvParams {
     uint32_t next_ctas;      //   the grid it will run on
     uint32_t next_gps;       //   its groups per unit
     uint32_t next_prefetch;  //   units to prefetch at the head of each of its CTA ranges
+    uint8_t *fuse_region[kPeerMaxRanks];  // fused all-reduce: every rank's exchange region ([fuse_rank] is local)
+    uint32_t fuse_rank, fuse_size;        //   fuse_size == 0: plain GEMV
     uint32_t probe;       // measurement aid, bit mask: 1 = skip the arithmetic, 2 = skip the streaming, 4 = skip the write-out,
                           // 8 = skip the activation block, 32 = return at once (launch cost only)
 };
@@ -147,6 +149,17 @@ __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *tmap, uint32_
                  "r"(c0), "r"(c1)
                  : "memory");
 }
+
+// flag words other GPUs write / read (fused all-reduce)
+__device__ __forceinline__ void st_release_sys_u32(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+constexpr uint32_t kPeerPollLimit = 1u << 23;  // polls with back-off (several seconds) before a rank gives up on a peer
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                                uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -954,6 +967,107 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
         asm volatile("griddepcontrol.wait;" ::: "memory");
         const uint32_t rg_last_touched = (u_end - 1u) / p.chunks;
         uint32_t ob = 0, ophase = 0;
+
+        // Fused all-reduce (row-parallel weight under tensor parallelism): the final sums of a row group are
+        // not written to y but pushed, as fp32, into slot `my rank` of every rank's exchange region, followed
+        // by a flag per peer; once all of this CTA's row groups are pushed, it waits for the peers' tiles of
+        // the same row groups, adds the ranks in rank order and writes y.  Early row groups therefore cross
+        // NVLink while later ones are still being computed.
+        const bool fused = p.fuse_size != 0u;
+        uint8_t *my_region = fused ? p.fuse_region[p.fuse_rank] : nullptr;
+        uint32_t *fctl = reinterpret_cast<uint32_t *>(my_region + kFusedCtlOff);  // {epoch, done}
+        uint32_t fepoch = 0u, fphase = 0u;
+        if (fused) {
+            fepoch = __ldcg(fctl) + 1u;  // every CTA of this launch reads the same value: it moves only when all have finished
+            fphase = fepoch & 1u;
+        }
+        constexpr uint32_t kPend = 8;
+        uint32_t pend[kPend];
+        uint32_t npend = 0u;
+        bool peers_ok = true;
+
+        auto store = [&](uint32_t m, uint32_t n, float val) {
+            if (m < p.M && n < p.N) {
+                if constexpr (XF32)
+                    static_cast<float *>(p.y)[static_cast<size_t>(m) * p.N + n] = val;
+                else
+                    static_cast<__nv_bfloat16 *>(p.y)[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(val);
+            }
+        };
+        // wait for every rank's tile of row group rg, add them in rank order, write y
+        auto finish = [&](uint32_t rg) {
+            bool ok = true;
+            if (lane < p.fuse_size) {
+                const uint32_t *flag = reinterpret_cast<const uint32_t *>(my_region + kFusedFlagsOff) +
+                                       (static_cast<size_t>(fphase) * kFusedMaxRowGroups + rg) * kPeerMaxRanks + lane;
+                ok = false;
+                for (uint32_t it = 0; it < kPeerPollLimit; ++it) {
+                    if (static_cast<int32_t>(ld_acquire_sys_u32(flag) - fepoch) >= 0) {
+                        ok = true;
+                        break;
+                    }
+                    if (it > 64) __nanosleep(it > 4096 ? 1000 : 32);
+                }
+                if (!ok) atomicOr(p.error_word, 0x200u);
+            }
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) {
+                peers_ok = false;
+                return;
+            }
+            const float *data = reinterpret_cast<const float *>(my_region + kFusedDataOff +
+                                                                static_cast<size_t>(fphase) * kPeerMaxRanks * kPeerSlotBytes);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t n = rg * kRows + lane + 32u * i;
+#pragma unroll
+                for (int m = 0; m < MD; ++m) {
+                    if (static_cast<uint32_t>(m) < p.M && n < p.N) {
+                        float acc = 0.f;
+                        for (uint32_t r = 0; r < p.fuse_size; ++r)
+                            acc += __ldcg(data + r * (kPeerSlotBytes / 4u) + static_cast<size_t>(m) * p.N + n);
+                        store(m, n, acc);
+                    }
+                }
+            }
+        };
+        // final sums of row group rg (this rank's share of K): to y, or to the peers
+        auto emit = [&](uint32_t rg, const float (&v)[4][MD]) {
+            if (!fused) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int m = 0; m < MD; ++m) store(m, rg * kRows + lane + 32u * i, v[i][m]);
+                return;
+            }
+            const size_t slot = kFusedDataOff + (static_cast<size_t>(fphase) * kPeerMaxRanks + p.fuse_rank) * kPeerSlotBytes;
+            for (uint32_t j = 0; j < p.fuse_size; ++j) {
+                uint32_t r = p.fuse_rank + j;
+                if (r >= p.fuse_size) r -= p.fuse_size;
+                float *dst = reinterpret_cast<float *>(p.fuse_region[r] + slot);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t n = rg * kRows + lane + 32u * i;
+#pragma unroll
+                    for (int m = 0; m < MD; ++m)
+                        if (static_cast<uint32_t>(m) < p.M && n < p.N) dst[static_cast<size_t>(m) * p.N + n] = v[i][m];
+                }
+            }
+            __syncwarp();
+            if (lane < p.fuse_size) {
+                uint32_t *flag = reinterpret_cast<uint32_t *>(p.fuse_region[lane] + kFusedFlagsOff) +
+                                 (static_cast<size_t>(fphase) * kFusedMaxRowGroups + rg) * kPeerMaxRanks + p.fuse_rank;
+                st_release_sys_u32(flag, fepoch);
+            }
+            if (npend == kPend) {  // rare: many short row groups per CTA; settle the oldest first
+                if (peers_ok) finish(pend[0]);
+#pragma unroll
+                for (uint32_t i = 0; i + 1u < kPend; ++i) pend[i] = pend[i + 1u];
+                --npend;
+            }
+            pend[npend++] = rg;
+        };
+
         for (uint32_t rg = rg_begin; rg <= rg_last_touched; ++rg) {
             if (!mbar_wait(smem_u32(&s_out_full[ob]), ophase, p.error_word, 0x8u)) return;
             const uint32_t rg_first = rg * p.chunks, rg_last = rg_first + p.chunks - 1u;
@@ -967,14 +1081,6 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
             // scratch slot layout [128 rows][8]: the same footprint as the tensor-core kernel's single tile
             float *mine = p.partials + (static_cast<size_t>(rg) * p.max_slots + slot) * (kRows * 8);
             const uint32_t obuf = ring + Plan::OFF_OUT + ob * Plan::OUT_BUF;
-            auto store = [&](uint32_t m, uint32_t n, float val) {
-                if (m < p.M && n < p.N) {
-                    if constexpr (XF32)
-                        static_cast<float *>(p.y)[static_cast<size_t>(m) * p.N + n] = val;
-                    else
-                        static_cast<__nv_bfloat16 *>(p.y)[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(val);
-                }
-            };
             float sum[4][MD];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -995,10 +1101,7 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
             if (lane == 0) mbar_arrive(smem_u32(&s_out_empty[ob]));
             if (!(p.probe & 4u)) {
                 if (whole) {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-#pragma unroll
-                        for (int m = 0; m < MD; ++m) store(m, rg * kRows + lane + 32u * i, sum[i][m]);
+                    emit(rg, sum);
                 } else {
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
@@ -1023,16 +1126,28 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
                                 for (int m = 0; m < MD; ++m)
                                     tot[i][m] += __ldcg(all + static_cast<size_t>(sidx) * (kRows * 8) + (lane + 32u * i) * 8 + m);
                         }
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-#pragma unroll
-                            for (int m = 0; m < MD; ++m) store(m, rg * kRows + lane + 32u * i, tot[i][m]);
+                        emit(rg, tot);
                         if (lane == 0) p.counters[rg] = 0u;
                     }
                 }
             }
             ob ^= 1u;
             if (ob == 0u) ophase ^= 1u;
+        }
+        if (fused) {
+            for (uint32_t i = 0; i < npend; ++i)
+                if (peers_ok) finish(pend[i]);
+            // the launch's epoch moves once, when its last CTA is through
+            __syncwarp();
+            if (lane == 0) {
+                __threadfence();
+                const uint32_t t = atomicAdd(fctl + 1, 1u);
+                if (t == gridDim.x - 1u) {
+                    fctl[1] = 0u;
+                    __threadfence();
+                    fctl[0] = fepoch;
+                }
+            }
         }
         return;
     }
@@ -1564,6 +1679,16 @@ bool gemv_mma_eligible(const WeightView &w, const void *x, const void *y, bool x
     return true;
 }
 
+// The all-reduce can ride in the write-out of the M <= 2 kernel when the peers' regions are mapped and the
+// fp32 tile [M][N] fits an exchange slot.
+bool gemv_fused_eligible(const WeightView &w, uint32_t M, bool x_f32, const GemvTuning &tune) {
+    if (!tune.fuse || !tune.fuse->ok || tune.fuse->size == 0u || tune.fuse->size > static_cast<uint32_t>(kPeerMaxRanks)) return false;
+    if (w.bits != 4u || M == 0u || M > 2u || x_f32 || tune.no_dp4a || tune.probe) return false;
+    if (static_cast<size_t>(M) * w.N * sizeof(float) > kPeerSlotBytes) return false;
+    if ((w.N + kRows - 1u) / kRows > kFusedMaxRowGroups) return false;
+    return true;
+}
+
 size_t gemv_mma_scratch_bytes(const WeightView &w, uint32_t M, const GemvTuning &tune, int sm_count) {
     const GemvPlan pl = plan_gemv(w, tune, sm_count);
     const uint32_t mrows = M <= 8u ? 8u : 16u;
@@ -1621,6 +1746,15 @@ cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bo
         }
     }
     const bool pdl = tune.pdl != 0;
+    for (int r = 0; r < kPeerMaxRanks; ++r) p.fuse_region[r] = nullptr;
+    p.fuse_rank = 0u;
+    p.fuse_size = 0u;
+    if (tune.fuse) {
+        if (!gemv_fused_eligible(w, M, x_f32, tune)) return cudaErrorNotSupported;
+        for (int r = 0; r < kPeerMaxRanks; ++r) p.fuse_region[r] = static_cast<uint8_t *>(tune.fuse->region[r]);
+        p.fuse_rank = tune.fuse->rank;
+        p.fuse_size = tune.fuse->size;
+    }
     if (w.bits == 4 && M <= 2u && !x_f32 && !tune.no_dp4a) {
         // one or two bf16 activation rows: the integer dot-product formulation (its 13-bit activations
         // are ample next to bf16 inputs; f32 callers keep the hi + lo tensor-core path and its 1e-3 accuracy)
@@ -1698,6 +1832,7 @@ cudaError_t gemv_mma_static(const WeightView &w, const void *x, void *y, uint32_
     GemvTuning t = tune;
     t.pdl = 0;  // the memset before the launch is a full dependency anyway
     t.next = nullptr;
+    t.fuse = nullptr;
     return gemv_mma(w, x, y, M, x_f32, sc, t, stream, sm_count, d_error_word);
 }
 

@@ -45,6 +45,7 @@ struct GemvTuning {
     int probe;          // measurement aid for the streaming GEMV (0 = off); results are wrong when set
     int prefetch_units; // units at the head of each CTA range of the hinted next weight to pull into L2
     const WeightView *next;  // the weight the following launch will stream (one-shot hint; may be null)
+    const struct PeerComm *fuse;  // sum the outputs over the ranks inside the GEMV (per call; may be null)
 };
 
 // y[M,N] = x[M,K] * W^T for M <= 16 on the tensor-core GEMV path.
@@ -59,6 +60,7 @@ bool gemv_mma_eligible(const WeightView &w, const void *x, const void *y, bool x
 void attach_packed_tmap(WeightView &w);
 cudaError_t make_packed_tmap(const WeightView &w, CUtensorMap *out);
 // scratch the fast path needs for this problem
+bool gemv_fused_eligible(const WeightView &w, uint32_t M, bool x_f32, const GemvTuning &tune);
 size_t gemv_mma_scratch_bytes(const WeightView &w, uint32_t M, const GemvTuning &tune, int sm_count);
 size_t gemv_mma_counter_count(const WeightView &w);
 
@@ -85,5 +87,36 @@ cudaError_t gather_dequant_f32(const WeightView &w, const uint32_t *d_ids, uint3
 cudaError_t gemm_tc(const WeightView &w, const void *x_bf16, void *y_bf16, uint32_t M,
                     cudaStream_t stream, int sm_count, unsigned int *d_error_word);
 bool gemm_tc_eligible(const WeightView &w, uint32_t M);
+
+// ---- all-reduce over NVLink peer memory (gaf_peer.cu) ----
+constexpr int kPeerMaxRanks = 8;                      // ranks of one node
+constexpr int kPeerCtas = 16;                         // CTAs of the all-reduce kernel (always all launched)
+constexpr int kPeerThreads = 256;
+constexpr size_t kPeerSlotBytes = size_t(512) << 10;  // largest tile one call reduces (16 rows x 8192 fp32)
+
+// Region layout (one cudaMalloc per rank, mapped by every rank of the node):
+//   all-reduce kernel: arrival flags u32 [2 phases][kPeerCtas][ranks], per-CTA epochs, data [2][ranks][slot]
+//   fused GEMV + all-reduce: row-group flags u32 [2 phases][kFusedMaxRowGroups][ranks], {epoch, done} words,
+//   data [2][ranks][slot] holding a rank's fp32 partial tile as [activation row][N]
+constexpr size_t kPeerFlagsOff = 0;
+constexpr size_t kPeerEpochOff = 4096;
+constexpr uint32_t kFusedMaxRowGroups = 1024;
+constexpr size_t kFusedFlagsOff = size_t(64) << 10;   // 2 * 1024 * 8 * 4 = 64 KB
+constexpr size_t kFusedCtlOff = size_t(128) << 10;
+constexpr size_t kPeerDataOff = size_t(256) << 10;
+constexpr size_t kFusedDataOff = kPeerDataOff + 2 * size_t(kPeerMaxRanks) * kPeerSlotBytes;
+constexpr size_t kPeerRegionBytes = kFusedDataOff + 2 * size_t(kPeerMaxRanks) * kPeerSlotBytes;
+
+struct PeerComm {
+    void *region[kPeerMaxRanks];  // every rank's region as mapped into this process; [rank] is cudaMalloc'ed here
+    uint32_t rank, size;
+    bool ok;                      // all ranks mapped all regions
+};
+
+size_t peer_region_bytes();
+// In-place sum of d_buf[count] (bf16 or f32) over the ranks.  cudaErrorNotSupported when the tile does not
+// fit a slot, is not a multiple of 16 bytes, or the peer mapping is unavailable (the caller then uses NCCL).
+cudaError_t peer_allreduce(const PeerComm &pc, void *d_buf, size_t count, bool f32, bool pdl, cudaStream_t stream,
+                           unsigned int *d_error_word);
 
 }  // namespace tgaf

@@ -90,6 +90,10 @@ class Context:
         dt = {torch.float32: DTYPE_F32, torch.bfloat16: DTYPE_BF16}[t.dtype]
         self._check(self._lib.tgaf_allreduce(self._h, C.c_void_p(t.data_ptr()), t.numel(), dt))
 
+    def uses_peer_memory(self) -> bool:
+        """True when small all-reduces run as one kernel over NVLink peer memory (else NCCL)."""
+        return bool(self._lib.tgaf_comm_uses_peer_memory(self._h))
+
     def close(self) -> None:
         if getattr(self, "_h", None):
             self._lib.tgaf_ctx_destroy(self._h)
@@ -178,6 +182,21 @@ def linear(ctx: Context, w: Weight, x, out=None):
     else:
         raise GafError(_STATUS_INVALID_ARGUMENT, f"unsupported activation dtype {x.dtype}")
     ctx._check(st)
+    return out
+
+
+def linear_allreduce(ctx: Context, w: Weight, x, out=None):
+    """`linear` on a row-parallel weight followed by the sum over the communicator's ranks
+    (tgaf_linear_bf16_allreduce; one kernel for M <= 2 when the peer-memory path is up).  bf16 only."""
+    import torch
+    if x.dim() != 2 or x.shape[1] != w.K or x.dtype != torch.bfloat16:
+        raise GafError(_STATUS_INVALID_ARGUMENT, f"x must be bf16 [M, {w.K}], got {x.dtype} {tuple(x.shape)}")
+    if not x.is_contiguous():
+        x = x.contiguous()
+    M = x.shape[0]
+    if out is None:
+        out = torch.empty((M, w.N), dtype=x.dtype, device=x.device)
+    ctx._check(ctx._lib.tgaf_linear_bf16_allreduce(ctx._h, w._h, C.c_void_p(x.data_ptr()), M, C.c_void_p(out.data_ptr())))
     return out
 
 

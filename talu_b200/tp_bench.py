@@ -19,6 +19,60 @@ def _weight_bytes(N, K):
     return N * K * BITS // 8 + 2 * N * (K // GROUP) * 2
 
 
+def _check_allreduce(ctx, torch, rank, world, stream):
+    """Every rank can compute every rank's tile, so each checks the sum it gets.  On the peer-memory path
+    the sum is fp32 in rank order, rounded once: the check is exact.  Sizes vary from call to call so
+    that both exchange phases and different CTA counts are used."""
+    exact = ctx.uses_peer_memory()
+    with torch.cuda.stream(stream):
+        for it, (n, dt) in enumerate([(8192, torch.bfloat16), (8, torch.bfloat16), (4096, torch.float32),
+                                      (8192 * 16, torch.bfloat16), (8192, torch.bfloat16), (24, torch.bfloat16),
+                                      (8192 * 16, torch.float32), (8192 * 3, torch.bfloat16)] * 3):
+            tiles = [((torch.arange(n, device="cuda", dtype=torch.float32) * (0.37 + it) % 251.0) - 125.0 + 1.5 * r).to(dt)
+                     for r in range(world)]
+            mine = tiles[rank].clone()
+            ctx.allreduce(mine)
+            acc = torch.zeros(n, device="cuda", dtype=torch.float32)
+            for r in range(world):
+                acc += tiles[r].float()
+            want = acc.to(dt)
+            stream.synchronize()
+            ctx.synchronize()
+            if exact:
+                ok = torch.equal(mine, want)
+            else:
+                ok = torch.allclose(mine.float(), want.float(), rtol=2e-2, atol=1.0)
+            if not ok:
+                bad = (mine != want).nonzero()[:4].flatten().tolist()
+                raise RuntimeError(f"rank {rank}: all-reduce mismatch at call {it} (n={n}, {dt}), first bad indices {bad}")
+
+
+def _check_fused(ctx, torch, dist, rank, world, stream, ws, xs):
+    """Row-parallel linears: the one-kernel path (fp32 partial tiles summed in rank order) against the two-step
+    path (bf16 outputs, then all-reduce) within the bf16 tolerance, and bit-identical results on all ranks."""
+    with torch.cuda.stream(stream):
+        for name, kind, w in ws[:8]:
+            if kind != SHARD_ROW:
+                continue
+            for rep in range(3):
+                y1 = gaf.linear_allreduce(ctx, w, xs[w.K])
+                ctx.set_option("fused_allreduce", 0)
+                y2 = gaf.linear_allreduce(ctx, w, xs[w.K])
+                ctx.set_option("fused_allreduce", 1)
+                stream.synchronize()
+                ctx.synchronize()
+                a, b = y1.float(), y2.float()
+                scale = max(float(b.abs().max()), 1e-6)
+                err = float((a - b).abs().max()) / scale
+                if not err <= 1e-2:
+                    raise RuntimeError(f"rank {rank}: fused {name} differs from the two-step path: rel {err}")
+                mine = y1.view(torch.int16).to(torch.int32).cpu()
+                ref = mine.clone()
+                dist.broadcast(ref, src=0)
+                if not torch.equal(mine, ref):
+                    raise RuntimeError(f"rank {rank}: fused {name} is not bit-identical to rank 0's")
+
+
 def measure(args, existing_ctx=None, existing_stream=None):
     """Runs the stack on this rank (all ranks call it together) and returns (ms per step over ranks,
     whole-job bytes per step, launches per rank, layers, world)."""
@@ -54,6 +108,9 @@ def measure(args, existing_ctx=None, existing_stream=None):
         ctx.comm_init(ids[0], rank, world)
         note("communicator initialised")
 
+        _check_allreduce(ctx, torch, rank, world, stream)
+        note(f"all-reduce checked (peer memory: {ctx.uses_peer_memory()})")
+
     layers = args.layers if args.layers != 12 else 4          # distinct layers in the ring (1.9 GB over all ranks)
     M = 1
     rng = np.random.default_rng(1234)                          # same seed on every rank: same full weights
@@ -72,12 +129,19 @@ def measure(args, existing_ctx=None, existing_stream=None):
     def step():
         for i, ((name, kind, w), y) in enumerate(zip(ws, ys)):
             gaf.hint_next_weight(ctx, ws[(i + 1) % len(ws)][2])
-            gaf.linear(ctx, w, xs[w.K], out=y)
             if kind == SHARD_ROW and world > 1:
-                ctx.allreduce(y)          # partial sums of the row-parallel output -> full [M, 8192]
+                gaf.linear_allreduce(ctx, w, xs[w.K], out=y)   # partial sums of the row-parallel output -> full [M, 8192]
+            else:
+                gaf.linear(ctx, w, xs[w.K], out=y)
 
+    kind_ar = None
+    if world > 1:
+        kind_ar = "fused into the GEMV write-out over NVLink peer memory" if ctx.uses_peer_memory() else "NCCL"
     steps, warmup = args.steps, max(3, args.warmup)
     note(f"{len(ws)} weights uploaded")
+    if world > 1:
+        _check_fused(ctx, torch, dist, rank, world, stream, ws, xs)
+        note("fused linear + all-reduce checked against the two-step path")
     with torch.cuda.stream(stream):
         step()
         stream.synchronize()
@@ -126,11 +190,11 @@ def measure(args, existing_ctx=None, existing_stream=None):
     if debug:
         import faulthandler
         faulthandler.cancel_dump_traceback_later()
-    return ms, total, len(ws), layers, world, rank, steps, warmup
+    return ms, total, len(ws), layers, world, rank, steps, warmup, kind_ar
 
 
 def run(args):
-    ms, total, per_rank_launches, layers, world, rank, steps, warmup = measure(args)
+    ms, total, per_rank_launches, layers, world, rank, steps, warmup, allreduce_kind = measure(args)
     M = 1
     value = total / ms / 1e6
     if rank == 0:
@@ -141,7 +205,8 @@ def run(args):
             "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 5), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "llama3_70b_stack", "scheme": "gaf4_64", "M": M, "layers": layers,
-                       "parallelism": f"tp{world}", "sharding": "qkv, gate|up column-parallel; o, down row-parallel + NCCL allreduce (bf16)",
+                       "parallelism": f"tp{world}", "sharding": "qkv, gate|up column-parallel; o, down row-parallel + all-reduce (bf16 tiles, fp32 sums)",
+                       "allreduce": allreduce_kind,
                        "l2": "distinct layers per step, ring larger than L2 on every rank",
                        "timing": "CUDA graph replay, CUDA events, max over ranks"},
             "roofline": {"bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s",

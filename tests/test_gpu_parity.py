@@ -239,6 +239,53 @@ def test_next_weight_hint_changes_no_result(gaf, ctx, oracle):
     wb.free()
 
 
+def test_one_rank_communicator_runs_the_peer_memory_kernels(gaf, oracle):
+    """A communicator of one rank still takes the peer-memory paths (its own region is the only slot), so the
+    all-reduce kernel and the GEMV with the all-reduce fused into its write-out are exercised on one GPU:
+    a sum over one rank must return the operand's bits, call after call (both exchange phases)."""
+    import torch
+    ctx1 = gaf.Context(0)
+    try:
+        try:
+            ctx1.comm_init(gaf.make_comm_id(), 0, 1)
+        except gaf.GafError as e:  # no libnccl: nothing to test
+            pytest.skip(f"no NCCL on this machine: {e}")
+        assert ctx1.uses_peer_memory()
+        for it, (n, dt) in enumerate([(8192, torch.bfloat16), (8, torch.bfloat16), (4096, torch.float32),
+                                      (8192 * 16, torch.bfloat16), (24, torch.bfloat16), (8192 * 16, torch.float32)] * 2):
+            t = (torch.randn(n, device="cuda") * (1 + it)).to(dt)
+            want = t.clone()
+            ctx1.allreduce(t)
+            ctx1.synchronize()
+            assert torch.equal(t, want), (it, n, dt)
+        big = torch.randn(1 << 20, device="cuda")          # larger than a slot: the library collective
+        want = big.clone()
+        ctx1.allreduce(big)
+        ctx1.synchronize()
+        assert torch.equal(big, want)
+        for (N, K, G) in [(8192, 1024, 64), (300, 2048, 64), (4096, 3584, 128), (1000, 512, 32)]:
+            p, s, b = make_weights(oracle, N, K, G, 4, seed=N + K)
+            w = gaf.Weight.from_host(ctx1, p, s, b, G, 4)
+            for M in (1, 2, 4):
+                xb, xf = make_x_bf16(oracle, M, K, 5 + M)
+                x = torch_bf16_from_bits(xb, "cuda:0")
+                y0 = gaf.linear(ctx1, w, x).clone()
+                for rep in range(3):
+                    y1 = gaf.linear_allreduce(ctx1, w, x)
+                    ctx1.synchronize()
+                    assert torch.equal(y0, y1), (N, K, G, M, rep)
+                for ctas in (1, 7, 500):
+                    ctx1.set_option("gemv_ctas", ctas)
+                    y2 = gaf.linear_allreduce(ctx1, w, x)
+                    ctx1.synchronize()
+                    ctx1.set_option("gemv_ctas", 0)
+                    assert rel_err(oracle.bf16_to_f32(bits_from_torch_bf16(y2)), oracle.matmul_f32(xf, p, s, b, G, 4)) <= TOL_BF16
+            w.free()
+        ctx1._lib.tgaf_comm_destroy(ctx1._h)
+    finally:
+        ctx1.close()
+
+
 def test_linearity_at_full_size(gaf, ctx, oracle):
     """Size-independent property at the benchmark's full shape: y(2x) = 2 y(x) exactly
     (scaling by two is exact in bf16 and in every partial sum)."""
