@@ -77,7 +77,7 @@ struct tgaf_ctx {
     cudaStream_t stream = nullptr;
     bool owns_stream = false;
     int sm_count = 148;
-    Scratch scratch = {nullptr, 0, nullptr, 0};
+    Scratch scratch = {nullptr, 0, nullptr, 0, nullptr, 0};
     GemvTuning tune = {0, 1, 0, 0, 0, 0, 2, nullptr, nullptr};
     // staging for the *_host entry points
     void *stage_x = nullptr;
@@ -143,7 +143,17 @@ bool shape_ok(uint64_t N, uint64_t K, uint32_t group, uint32_t bits, uint32_t sd
     return true;
 }
 
-int32_t ensure_scratch(tgaf_ctx *ctx, size_t partial_bytes, size_t counters) {
+int32_t ensure_scratch(tgaf_ctx *ctx, size_t partial_bytes, size_t counters, size_t tagged_bytes = 0) {
+    if (tagged_bytes > ctx->scratch.tagged_bytes) {
+        TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if (ctx->scratch.tagged) cudaFree(ctx->scratch.tagged);
+        ctx->scratch.tagged = nullptr;
+        ctx->scratch.tagged_bytes = 0;
+        size_t want = tagged_bytes < (size_t(2) << 20) ? (size_t(2) << 20) : tagged_bytes;
+        TGAF_CUDA(ctx, cudaMalloc(reinterpret_cast<void **>(&ctx->scratch.tagged), want));
+        TGAF_CUDA(ctx, cudaMemsetAsync(ctx->scratch.tagged, 0, want, ctx->stream));  // no tag is set
+        ctx->scratch.tagged_bytes = want;
+    }
     if (partial_bytes > ctx->scratch.partial_bytes) {
         // previous launches may still be using the old buffer
         TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -157,6 +167,7 @@ int32_t ensure_scratch(tgaf_ctx *ctx, size_t partial_bytes, size_t counters) {
     if (counters > ctx->scratch.counter_count) {
         TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
         if (ctx->scratch.counters) cudaFree(ctx->scratch.counters);
+    if (ctx->scratch.tagged) cudaFree(ctx->scratch.tagged);
         ctx->scratch.counters = nullptr;
         ctx->scratch.counter_count = 0;
         size_t want = counters < 65536 ? 65536 : counters;
@@ -203,7 +214,8 @@ int32_t linear_device(tgaf_ctx *ctx, const WeightView &w, const void *x, uint32_
         for (uint32_t m0 = 0; m0 < M; m0 += 16u) {
             const uint32_t mc = (M - m0) < 16u ? (M - m0) : 16u;
             const size_t need = gemv_mma_scratch_bytes(w, mc, ctx->tune, ctx->sm_count);
-            int32_t st = ensure_scratch(ctx, need, gemv_mma_counter_count(w));
+            int32_t st = ensure_scratch(ctx, need, gemv_mma_counter_count(w),
+                                        gemv_tagged_bytes(w, mc, f32, ctx->tune, ctx->sm_count));
             if (st != TGAF_OK) return st;
             const void *xp = static_cast<const uint8_t *>(x) + static_cast<size_t>(m0) * w.K * elt;
             void *yp = static_cast<uint8_t *>(y) + static_cast<size_t>(m0) * w.N * elt;
@@ -484,6 +496,7 @@ int32_t tgaf_synchronize(tgaf_ctx *ctx) {
         cudaMemset(ctx->d_error_word, 0, sizeof flag);
         // an abandoned launch may have left arrival counters half way
         if (ctx->scratch.counters) cudaMemset(ctx->scratch.counters, 0, ctx->scratch.counter_count * sizeof(unsigned int));
+        if (ctx->scratch.tagged) cudaMemset(ctx->scratch.tagged, 0, ctx->scratch.tagged_bytes);  // ... or tags set
         return fail(ctx, TGAF_ERR_DEVICE_FLAG, "a kernel gave up a bounded wait (code 0x%x)", flag);
     }
     return TGAF_OK;

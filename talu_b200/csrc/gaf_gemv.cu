@@ -82,6 +82,7 @@ struct GemvParams {
     void *y;
     float *partials;         // [row group][slot][128][MT*8]
     unsigned int *counters;  // [row group]
+    unsigned long long *tagged;  // M <= 2 kernel: {value, tag} words [row group][slot][128][M]; null = use partials + counters
     unsigned int *error_word;
     uint32_t N, K, M;
     uint32_t groups;      // K / G
@@ -1102,6 +1103,58 @@ gaf_gemv_dp4a_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tma
             if (!(p.probe & 4u)) {
                 if (whole) {
                     emit(rg, sum);
+                } else if (p.tagged != nullptr) {
+                    // Partial sums that carry their own arrival tag: {fp32 value, tag} in one 64-bit word, so
+                    // a reader that sees the tag has the value (no flag, no ticket, no fence).  The CTA that
+                    // owns the head of the row group (it gets there last, at the end of its range) collects:
+                    // own sums + the other slots in slot order, and sets the words back to zero.
+                    constexpr uint32_t kTag = 0x5A5A5A5Au;
+                    unsigned long long *slots_base = p.tagged + static_cast<size_t>(rg) * p.max_slots * (kRows * MD);
+                    if (slot != 0u) {
+                        unsigned long long *dst = slots_base + static_cast<size_t>(slot) * (kRows * MD);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+#pragma unroll
+                            for (int m = 0; m < MD; ++m) {
+                                const unsigned long long word =
+                                    (static_cast<unsigned long long>(kTag) << 32) | __float_as_uint(sum[i][m]);
+                                asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(dst + (lane + 32u * i) * MD + m), "l"(word) : "memory");
+                            }
+                    } else {
+                        bool got = true;
+                        for (uint32_t sidx = 1; sidx < slots && got; ++sidx) {  // fixed order: reproducible sums
+                            unsigned long long *src = slots_base + static_cast<size_t>(sidx) * (kRows * MD);
+                            unsigned long long word[4][MD];
+                            got = false;
+                            for (uint32_t it = 0; it < kWaitLimit; ++it) {
+                                bool all = true;
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                                    for (int m = 0; m < MD; ++m) {
+                                        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(word[i][m]) : "l"(src + (lane + 32u * i) * MD + m) : "memory");
+                                        all = all && static_cast<uint32_t>(word[i][m] >> 32) == kTag;
+                                    }
+                                if (__all_sync(0xFFFFFFFFu, all)) {
+                                    got = true;
+                                    break;
+                                }
+                                if (it > 32) __nanosleep(it > 4096 ? 256 : 32);
+                            }
+                            if (!got) {
+                                if (lane == 0) atomicOr(p.error_word, 0x20u);
+                                break;
+                            }
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                                for (int m = 0; m < MD; ++m) {
+                                    sum[i][m] += __uint_as_float(static_cast<uint32_t>(word[i][m]));
+                                    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(src + (lane + 32u * i) * MD + m), "l"(0ull) : "memory");
+                                }
+                        }
+                        if (got) emit(rg, sum);
+                    }
                 } else {
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
@@ -1695,6 +1748,12 @@ size_t gemv_mma_scratch_bytes(const WeightView &w, uint32_t M, const GemvTuning 
     return static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * mrows * sizeof(float);
 }
 
+size_t gemv_tagged_bytes(const WeightView &w, uint32_t M, bool x_f32, const GemvTuning &tune, int sm_count) {
+    if (w.bits != 4u || M == 0u || M > 2u || x_f32 || tune.no_dp4a) return 0;
+    const GemvPlan pl = plan_gemv(w, tune, sm_count);
+    return static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * M * 8u;
+}
+
 size_t gemv_mma_counter_count(const WeightView &w) {
     return static_cast<size_t>((w.N + kRows - 1u) / kRows);
 }
@@ -1718,6 +1777,7 @@ cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bo
     p.y = y;
     p.partials = scratch.partials;
     p.counters = scratch.counters;
+    p.tagged = nullptr;
     p.error_word = d_error_word;
     p.N = w.N;
     p.K = w.K;
@@ -1756,6 +1816,8 @@ cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bo
         p.fuse_size = tune.fuse->size;
     }
     if (w.bits == 4 && M <= 2u && !x_f32 && !tune.no_dp4a) {
+        if (scratch.tagged && static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * M * 8u <= scratch.tagged_bytes)
+            p.tagged = scratch.tagged;
         // one or two bf16 activation rows: the integer dot-product formulation (its 13-bit activations
         // are ample next to bf16 inputs; f32 callers keep the hi + lo tensor-core path and its 1e-3 accuracy)
         const bool small = tune.dp4a_small != 0 && gb >= 32u;
@@ -1826,6 +1888,8 @@ cudaError_t gemv_mma_static(const WeightView &w, const void *x, void *y, uint32_
     sc.partial_bytes = kStaticPartialBytes;
     sc.counters = reinterpret_cast<unsigned int *>(base + kStaticPartialBytes);
     sc.counter_count = kStaticCounters;
+    sc.tagged = nullptr;
+    sc.tagged_bytes = 0;
     // the counters must start at zero; the previous call (or an abandoned one) may have left anything
     cudaError_t e = cudaMemsetAsync(sc.counters, 0, gemv_mma_counter_count(w) * sizeof(unsigned int), stream);
     if (e != cudaSuccess) return e;
