@@ -184,6 +184,20 @@ int32_t tgaf_dequant_f32_host(tgaf_ctx *ctx, const tgaf_weight *w, float *h_out)
 int32_t tgaf_embedding_lookup_f32(tgaf_ctx *ctx, const tgaf_weight *w, const uint32_t *token_ids,
                                   uint32_t count, float multiplier, float *d_out);
 
+/* ---- the SwiGLU FFN as one operator ---------------------------------------
+ * y[m, d_model] = down( silu(gate(x)) * up(x) ), the body of SwiGLU.forward
+ * (core/src/inference/backend/cpu/kernels/ffn.zig:103-400) with the reference's fused gate|up weight
+ * in its concat layout (rows [gate..., up...], ffn.zig:228-241); on the reference's CUDA backend this is
+ * tryFusedGateUpForward + a silu-mul kernel + the down matvec
+ * (core/src/inference/backend/cuda/engine.zig:4476-4553, kernels/ops/quant_ops.cu:221-286).
+ * w_gate_up: [2 * d_ff, d_model], w_down: [d_model, d_ff].  bf16 in, bf16 out.
+ * For M = 1 on gaf4 weights of one group size BOTH linears run in ONE kernel: the copy warp streams
+ * straight on from the first weight into the second, the intermediate stays fp32, and the activation is
+ * applied while the second linear quantises its operand; otherwise: linear, silu-mul kernel, linear.
+ * Option "ffn_one_launch" = 0 forces the latter. */
+int32_t tgaf_ffn_swiglu_bf16(tgaf_ctx *ctx, const tgaf_weight *w_gate_up, const tgaf_weight *w_down,
+                             const void *x_bf16, uint32_t m, void *y_bf16);
+
 /* ---- tensor parallel exchange (no counterpart in the reference, which is
  * single-device): sum of the row-parallel partial outputs over all ranks. ----
  * The communicator belongs to the context.  Rank 0 makes the id and the host
@@ -212,6 +226,10 @@ int32_t tgaf_allreduce(tgaf_ctx *ctx, void *d_buf, uint64_t count, uint32_t dtyp
  * order and rounds once (bit-identical on all ranks; more accurate than summing rounded bf16 outputs).
  * Everything else runs the two steps one after the other.  Option "fused_allreduce" = 0 forces that. */
 int32_t tgaf_linear_bf16_allreduce(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16, uint32_t m, void *y_bf16);
+/* tgaf_ffn_swiglu_bf16 with a column-parallel gate|up (each rank holds matching gate and up rows) and a
+ * row-parallel down whose partial sums are added over the ranks (inside the kernel when it can). */
+int32_t tgaf_ffn_swiglu_bf16_allreduce(tgaf_ctx *ctx, const tgaf_weight *w_gate_up, const tgaf_weight *w_down,
+                                       const void *x_bf16, uint32_t m, void *y_bf16);
 /* 1 when the peer-memory path of tgaf_allreduce is available on this communicator, else 0 */
 int32_t tgaf_comm_uses_peer_memory(const tgaf_ctx *ctx);
 

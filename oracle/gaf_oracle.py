@@ -172,6 +172,24 @@ def matmul_f32(a, packed, scales, biases, group: int, bits: int, sdtype: int = S
     return out
 
 
+def silu_mul_split(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    """siluMulSplit, core/src/compute/cpu/activation.zig:78-94: (gate * sigmoid(gate)) * up in f32.
+    (The reference's exp is a fast approximation; this uses the exact one - tolerance-level parity.)"""
+    g = np.asarray(gate, np.float32)
+    sig = np.float32(1.0) / (np.float32(1.0) + np.exp(-g, dtype=np.float32))
+    return ((g * sig) * np.asarray(up, np.float32)).astype(np.float32)
+
+
+def ffn_swiglu_f32(x, gate_up, down, group: int, bits: int, sdtype: int = SCALES_BF16) -> np.ndarray:
+    """SwiGLU.forward with a fused gate|up weight in the concat layout [gate rows..., up rows...]
+    (core/src/inference/backend/cpu/kernels/ffn.zig:166-241, :388): y = down(silu(gate(x)) * up(x)).
+    gate_up / down are (packed, scales, biases) triples."""
+    gu = matmul_f32(x, *gate_up, group, bits, sdtype)
+    d_ff = gu.shape[1] // 2
+    h = silu_mul_split(gu[:, :d_ff], gu[:, d_ff:])
+    return matmul_f32(h, *down, group, bits, sdtype)
+
+
 def matmul_f64(a, packed, scales, biases, group: int, bits: int, sdtype: int = SCALES_BF16,
                nthreads: int = 0) -> np.ndarray:
     a = _c(a, np.float32)

@@ -41,6 +41,8 @@ SIGNATURES = {
     "tgaf_comm_destroy": (_i32, [_vp]),
     "tgaf_allreduce": (_i32, [_vp, _vp, _u64, _u32]),
     "tgaf_comm_uses_peer_memory": (_i32, [_vp]),
+    "tgaf_ffn_swiglu_bf16": (_i32, [_vp, _vp, _vp, _vp, _u32, _vp]),
+    "tgaf_ffn_swiglu_bf16_allreduce": (_i32, [_vp, _vp, _vp, _vp, _u32, _vp]),
     "tgaf_linear_bf16_allreduce": (_i32, [_vp, _vp, _vp, _u32, _vp]),
 }
 

@@ -85,11 +85,16 @@ struct tgaf_ctx {
     void *stage_y = nullptr;
     size_t stage_y_bytes = 0;
     unsigned int *d_error_word = nullptr;
+    // FFN operator: intermediate activations and the two-operation kernel's arrival counters
+    void *ffn_mid = nullptr;
+    size_t ffn_mid_bytes = 0;
+    unsigned int *d_grid_bar = nullptr;
     NcclComm comm = nullptr;
     uint32_t comm_rank = 0, comm_size = 1;
     PeerComm peer = {{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr}, 0, 1, false};
     int peer_allreduce = 1;  // small tiles go through the peer-memory kernel when the mapping exists
     int fused_allreduce = 1; // tgaf_linear_bf16_allreduce sums inside the GEMV when it can
+    int ffn_one_launch = 1;  // tgaf_ffn_swiglu_bf16 runs both linears in one kernel when it can
     int peer_pdl = 0;        // programmatic stream serialization for the all-reduce kernel (measured slower)
     char err[512] = {0};
 };
@@ -472,6 +477,8 @@ int32_t tgaf_ctx_destroy(tgaf_ctx *ctx) {
     if (ctx->stage_x) cudaFree(ctx->stage_x);
     if (ctx->stage_y) cudaFree(ctx->stage_y);
     if (ctx->d_error_word) cudaFree(ctx->d_error_word);
+    if (ctx->ffn_mid) cudaFree(ctx->ffn_mid);
+    if (ctx->d_grid_bar) cudaFree(ctx->d_grid_bar);
     if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return TGAF_OK;
@@ -519,6 +526,8 @@ int32_t tgaf_ctx_set_option(tgaf_ctx *ctx, const char *name, int64_t value) {
         ctx->tune.no_dp4a = value != 0;
     } else if (!strcmp(name, "peer_allreduce")) {
         ctx->peer_allreduce = value != 0;
+    } else if (!strcmp(name, "ffn_one_launch")) {
+        ctx->ffn_one_launch = value != 0;
     } else if (!strcmp(name, "fused_allreduce")) {
         ctx->fused_allreduce = value != 0;
     } else if (!strcmp(name, "peer_pdl")) {
@@ -842,6 +851,60 @@ int32_t tgaf_comm_destroy(tgaf_ctx *ctx) {
     ctx->comm_size = 1;
     ctx->comm_rank = 0;
     return TGAF_OK;
+}
+
+// FFN operator.  reduce: sum the result over the communicator's ranks (row-parallel down projection).
+static int32_t ffn_swiglu(tgaf_ctx *ctx, const tgaf_weight *wgu, const tgaf_weight *wd, const void *x, uint32_t M, void *y,
+                          bool reduce) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!wgu || !wd || !x || !y || M == 0) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null pointer or M == 0");
+    const WeightView &w1 = wgu->v, &w2 = wd->v;
+    if (w1.N != 2u * w2.K)
+        return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "gate|up has %u rows, down has %u columns (need rows = 2 x columns)", w1.N, w2.K);
+    if (reduce && !ctx->comm) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "no communicator: call tgaf_comm_init first");
+    cudaSetDevice(ctx->device);
+    const WeightView *hint = ctx->tune.next;
+    ctx->tune.next = nullptr;
+    const uint32_t d_ff = w2.K;
+    // intermediate: fp32 [M][2 d_ff] for the one-launch path; bf16 [M][2 d_ff] + bf16 [M][d_ff] otherwise
+    const size_t mid_need = static_cast<size_t>(M) * 2u * d_ff * 4u;
+    int32_t st = ensure_stage(ctx, &ctx->ffn_mid, &ctx->ffn_mid_bytes, mid_need);
+    if (st != TGAF_OK) return st;
+    if (!ctx->d_grid_bar) {
+        TGAF_CUDA(ctx, cudaMalloc(reinterpret_cast<void **>(&ctx->d_grid_bar), 4 * sizeof(unsigned int)));
+        TGAF_CUDA(ctx, cudaMemsetAsync(ctx->d_grid_bar, 0, 4 * sizeof(unsigned int), ctx->stream));
+    }
+    GemvTuning t = ctx->tune;
+    t.fuse = (reduce && ctx->peer.ok && ctx->fused_allreduce) ? &ctx->peer : nullptr;
+    const bool peer_ready = !reduce || (t.fuse && gemv_fused_eligible(w2, M, false, t));
+    if (ctx->ffn_one_launch && !ctx->tune.force_generic && peer_ready && gemv_ffn_eligible(w1, w2, x, y, M, t)) {
+        st = ensure_scratch(ctx, 0, 0, gemv_ffn_tagged_bytes(w1, w2, M, t, ctx->sm_count));
+        if (st != TGAF_OK) return st;
+        cudaError_t e = gemv_ffn_swiglu(w1, w2, x, static_cast<float *>(ctx->ffn_mid), y, M, ctx->scratch, ctx->d_grid_bar, t,
+                                        ctx->stream, ctx->sm_count, ctx->d_error_word);
+        if (e == cudaSuccess) return TGAF_OK;
+        if (e != cudaErrorNotSupported) return cuda_fail(ctx, e, "ffn launch");
+    }
+    // two linears with the activation in between
+    uint8_t *gu = static_cast<uint8_t *>(ctx->ffn_mid);
+    uint8_t *h = gu + static_cast<size_t>(M) * 2u * d_ff * 2u;
+    ctx->tune.next = &w2;
+    st = linear_device(ctx, w1, x, M, gu, false);
+    if (st != TGAF_OK) return st;
+    cudaError_t e = swiglu_bf16(gu, h, M, d_ff, ctx->stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "swiglu launch");
+    ctx->tune.next = hint;
+    return linear_device(ctx, w2, h, M, y, false, reduce);
+}
+
+int32_t tgaf_ffn_swiglu_bf16(tgaf_ctx *ctx, const tgaf_weight *w_gate_up, const tgaf_weight *w_down, const void *x_bf16,
+                             uint32_t m, void *y_bf16) {
+    return ffn_swiglu(ctx, w_gate_up, w_down, x_bf16, m, y_bf16, false);
+}
+
+int32_t tgaf_ffn_swiglu_bf16_allreduce(tgaf_ctx *ctx, const tgaf_weight *w_gate_up, const tgaf_weight *w_down,
+                                       const void *x_bf16, uint32_t m, void *y_bf16) {
+    return ffn_swiglu(ctx, w_gate_up, w_down, x_bf16, m, y_bf16, true);
 }
 
 int32_t tgaf_comm_uses_peer_memory(const tgaf_ctx *ctx) { return ctx && ctx->peer.ok ? 1 : 0; }

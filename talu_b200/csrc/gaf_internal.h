@@ -64,6 +64,16 @@ bool gemv_mma_eligible(const WeightView &w, const void *x, const void *y, bool x
 void attach_packed_tmap(WeightView &w);
 cudaError_t make_packed_tmap(const WeightView &w, CUtensorMap *out);
 // scratch the fast path needs for this problem
+// SwiGLU FFN (stacked gate|up weight, then down) for M = 1 in one launch; `mid` is fp32 [M][2 d_ff] scratch and
+// `grid_bar` two zeroed counters.  cudaErrorNotSupported when the pair is not eligible.
+bool gemv_ffn_eligible(const WeightView &w1, const WeightView &w2, const void *x, const void *y, uint32_t M,
+                       const GemvTuning &tune);
+size_t gemv_ffn_tagged_bytes(const WeightView &w1, const WeightView &w2, uint32_t M, const GemvTuning &tune, int sm_count);
+cudaError_t gemv_ffn_swiglu(const WeightView &w1, const WeightView &w2, const void *x, float *mid, void *y, uint32_t M,
+                            const Scratch &scratch, unsigned int *grid_bar, const GemvTuning &tune,
+                            cudaStream_t stream, int sm_count, unsigned int *d_error_word);
+// h[m][j] = silu(gu[m][j]) * gu[m][d_ff + j], bf16 in / out (the step between the two linears when they run apart)
+cudaError_t swiglu_bf16(const void *gate_up, void *h, uint32_t M, uint32_t d_ff, cudaStream_t stream);
 bool gemv_fused_eligible(const WeightView &w, uint32_t M, bool x_f32, const GemvTuning &tune);
 size_t gemv_mma_scratch_bytes(const WeightView &w, uint32_t M, const GemvTuning &tune, int sm_count);
 size_t gemv_mma_counter_count(const WeightView &w);

@@ -200,6 +200,21 @@ def linear_allreduce(ctx: Context, w: Weight, x, out=None):
     return out
 
 
+def ffn_swiglu(ctx: Context, w_gate_up: Weight, w_down: Weight, x, out=None, allreduce: bool = False):
+    """y = down(silu(gate(x)) * up(x)) with the stacked gate|up weight (tgaf_ffn_swiglu_bf16[_allreduce])."""
+    import torch
+    if x.dim() != 2 or x.shape[1] != w_gate_up.K or x.dtype != torch.bfloat16:
+        raise GafError(_STATUS_INVALID_ARGUMENT, f"x must be bf16 [M, {w_gate_up.K}], got {x.dtype} {tuple(x.shape)}")
+    if not x.is_contiguous():
+        x = x.contiguous()
+    M = x.shape[0]
+    if out is None:
+        out = torch.empty((M, w_down.N), dtype=x.dtype, device=x.device)
+    fn = ctx._lib.tgaf_ffn_swiglu_bf16_allreduce if allreduce else ctx._lib.tgaf_ffn_swiglu_bf16
+    ctx._check(fn(ctx._h, w_gate_up._h, w_down._h, C.c_void_p(x.data_ptr()), M, C.c_void_p(out.data_ptr())))
+    return out
+
+
 def hint_next_weight(ctx: Context, w) -> None:
     """Names the weight the linear call AFTER the coming one will use (tgaf_hint_next_weight): the coming
     call's kernel then pulls the head of `w` into L2 while it drains.  One-shot; None clears it."""

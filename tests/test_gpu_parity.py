@@ -281,9 +281,56 @@ def test_one_rank_communicator_runs_the_peer_memory_kernels(gaf, oracle):
                     ctx1.set_option("gemv_ctas", 0)
                     assert rel_err(oracle.bf16_to_f32(bits_from_torch_bf16(y2)), oracle.matmul_f32(xf, p, s, b, G, 4)) <= TOL_BF16
             w.free()
+        # the FFN operator with the sum over ranks riding in its down projection (one launch at M = 1)
+        pg, sg, bg = make_weights(oracle, 2 * 1024, 512, 64, 4, seed=77)
+        pd, sd, bd = make_weights(oracle, 512, 1024, 64, 4, seed=78)
+        wgu, wd = gaf.Weight.from_host(ctx1, pg, sg, bg, 64, 4), gaf.Weight.from_host(ctx1, pd, sd, bd, 64, 4)
+        for M in (1, 2):
+            xb, _ = make_x_bf16(oracle, M, 512, 90 + M)
+            x = torch_bf16_from_bits(xb, "cuda:0")
+            y0 = gaf.ffn_swiglu(ctx1, wgu, wd, x).clone()
+            for rep in range(3):
+                y1 = gaf.ffn_swiglu(ctx1, wgu, wd, x, allreduce=True)
+                ctx1.synchronize()
+                assert torch.equal(y0, y1), (M, rep)
+        wgu.free()
+        wd.free()
         ctx1._lib.tgaf_comm_destroy(ctx1._h)
     finally:
         ctx1.close()
+
+
+@pytest.mark.parametrize("d_model,d_ff,G", [(512, 1024, 64), (1024, 2816, 64), (256, 384, 32), (4096, 14336, 64), (512, 1536, 128)])
+def test_ffn_swiglu_operator(gaf, ctx, oracle, d_model, d_ff, G):
+    """The FFN operator (gate|up, silu-mul, down) against the oracle's restatement of SwiGLU.forward: the
+    one-launch path (M <= 2), the three-kernel path (M = 5, and M = 1 with the option off) and repeat calls."""
+    import torch
+    pg, sg, bg = make_weights(oracle, 2 * d_ff, d_model, G, 4, seed=d_ff)
+    pd, sd, bd = make_weights(oracle, d_model, d_ff, G, 4, seed=d_ff + 1)
+    wgu = gaf.Weight.from_host(ctx, pg, sg, bg, G, 4)
+    wd = gaf.Weight.from_host(ctx, pd, sd, bd, G, 4)
+    try:
+        for M in (1, 2, 5):
+            xb, xf = make_x_bf16(oracle, M, d_model, 50 + M)
+            xf = xf * 8.0   # weights of N(0, 0.02^2): larger activations put the gate values where silu bends
+            xb = oracle.f32_to_bf16_rne(xf)
+            xf = oracle.bf16_to_f32(xb)
+            ref = oracle.ffn_swiglu_f32(xf, (pg, sg, bg), (pd, sd, bd), G, 4)
+            x = torch_bf16_from_bits(xb, "cuda:0")
+            y1 = gaf.ffn_swiglu(ctx, wgu, wd, x).clone()
+            y2 = gaf.ffn_swiglu(ctx, wgu, wd, x).clone()
+            ctx.set_option("ffn_one_launch", 0)
+            y3 = gaf.ffn_swiglu(ctx, wgu, wd, x).clone()
+            ctx.set_option("ffn_one_launch", 1)
+            ctx.synchronize()
+            assert torch.equal(y1, y2), M
+            # two chained linears + activation: twice the per-linear bf16 budget
+            for y in (y1, y3):
+                assert rel_err(oracle.bf16_to_f32(bits_from_torch_bf16(y)), ref) <= 2 * TOL_BF16, (M, d_model, d_ff)
+    finally:
+        ctx.set_option("ffn_one_launch", 1)
+    wgu.free()
+    wd.free()
 
 
 def test_linearity_at_full_size(gaf, ctx, oracle):
