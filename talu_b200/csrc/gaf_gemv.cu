@@ -997,10 +997,10 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         const uint32_t rg_last_touched = (u_end - 1u) / p.chunks;
 
         // Fused all-reduce (row-parallel weight under tensor parallelism): the final sums of a row group are
-        // not written to y but pushed, as fp32, into slot `my rank` of every rank's exchange region, followed
-        // by a flag per peer; once all of this CTA's row groups are pushed, it waits for the peers' tiles of
-        // the same row groups, adds the ranks in rank order and writes y.  Early row groups therefore cross
-        // NVLink while later ones are still being computed.
+        // not written to y but pushed, as fp32, into slot `my rank` of every rank's exchange region; once all
+        // of this CTA's row groups are pushed, it waits for the peers' words of the same row groups, adds the
+        // ranks in rank order and writes y.  Early row groups therefore cross NVLink while later ones are
+        // still being computed.
         const bool fused = p.fuse_size != 0u;
         uint8_t *my_region = fused ? p.fuse_region[p.fuse_rank] : nullptr;
         uint32_t *fctl = reinterpret_cast<uint32_t *>(my_region + kFusedCtlOff);  // {epoch, done}
@@ -1022,42 +1022,60 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                     static_cast<__nv_bfloat16 *>(p.y)[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(val);
             }
         };
-        // wait for every rank's tile of row group rg, add them in rank order, write y
+        // Exchange words are {fp32 value, launch epoch} in 64 bits, written with one store: a reader that sees
+        // the epoch has the value, so there is no flag, no fence and no second NVLink hop (the same idea as
+        // the split-K words above, and as the "LL" protocols of collective libraries).
+        // wait for every rank's words of row group rg, add them in rank order, write y
         auto finish = [&](uint32_t rg) {
-            bool ok = true;
-            if (lane < p.fuse_size) {
-                const uint32_t *flag = reinterpret_cast<const uint32_t *>(my_region + kFusedFlagsOff) +
-                                       (static_cast<size_t>(fphase) * kFusedMaxRowGroups + rg) * kPeerMaxRanks + lane;
-                ok = false;
+            const unsigned long long *data = reinterpret_cast<const unsigned long long *>(
+                my_region + kFusedDataOff + static_cast<size_t>(fphase) * kPeerMaxRanks * kPeerSlotBytes);
+            float acc[4][MD];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int m = 0; m < MD; ++m) acc[i][m] = 0.f;
+            for (uint32_t r = 0; r < p.fuse_size; ++r) {
+                const unsigned long long *src = data + r * (kPeerSlotBytes / 8u);
+                unsigned long long word[4][MD];
+                bool got = false;
                 for (uint32_t it = 0; it < kPeerPollLimit; ++it) {
-                    if (static_cast<int32_t>(ld_acquire_sys_u32(flag) - fepoch) >= 0) {
-                        ok = true;
+                    bool all = true;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t n = rg * kRows + lane + 32u * i;
+#pragma unroll
+                        for (int m = 0; m < MD; ++m) {
+                            if (static_cast<uint32_t>(m) < p.M && n < p.N) {
+                                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];"
+                                             : "=l"(word[i][m])
+                                             : "l"(src + static_cast<size_t>(m) * p.N + n)
+                                             : "memory");
+                                all = all && static_cast<uint32_t>(word[i][m] >> 32) == fepoch;
+                            } else {
+                                word[i][m] = 0ull;
+                            }
+                        }
+                    }
+                    if (__all_sync(0xFFFFFFFFu, all)) {
+                        got = true;
                         break;
                     }
                     if (it > 64) __nanosleep(it > 4096 ? 1000 : 32);
                 }
-                if (!ok) atomicOr(p.error_word, 0x200u);
-            }
-            ok = __all_sync(0xFFFFFFFFu, ok);
-            if (!ok) {
-                peers_ok = false;
-                return;
-            }
-            const float *data = reinterpret_cast<const float *>(my_region + kFusedDataOff +
-                                                                static_cast<size_t>(fphase) * kPeerMaxRanks * kPeerSlotBytes);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t n = rg * kRows + lane + 32u * i;
-#pragma unroll
-                for (int m = 0; m < MD; ++m) {
-                    if (static_cast<uint32_t>(m) < p.M && n < p.N) {
-                        float acc = 0.f;
-                        for (uint32_t r = 0; r < p.fuse_size; ++r)
-                            acc += __ldcg(data + r * (kPeerSlotBytes / 4u) + static_cast<size_t>(m) * p.N + n);
-                        store(m, n, acc);
-                    }
+                if (!got) {
+                    if (lane == 0) atomicOr(p.error_word, 0x200u);
+                    peers_ok = false;
+                    return;
                 }
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int m = 0; m < MD; ++m) acc[i][m] += __uint_as_float(static_cast<uint32_t>(word[i][m]));
             }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int m = 0; m < MD; ++m) store(m, rg * kRows + lane + 32u * i, acc[i][m]);
         };
         // final sums of row group rg (this rank's share of K): to y, or to the peers
         auto emit = [&](uint32_t rg, const float (&v)[4][MD]) {
@@ -1072,20 +1090,19 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
             for (uint32_t j = 0; j < p.fuse_size; ++j) {
                 uint32_t r = p.fuse_rank + j;
                 if (r >= p.fuse_size) r -= p.fuse_size;
-                float *dst = reinterpret_cast<float *>(p.fuse_region[r] + slot);
+                unsigned long long *dst = reinterpret_cast<unsigned long long *>(p.fuse_region[r] + slot);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const uint32_t n = rg * kRows + lane + 32u * i;
 #pragma unroll
                     for (int m = 0; m < MD; ++m)
-                        if (static_cast<uint32_t>(m) < p.M && n < p.N) dst[static_cast<size_t>(m) * p.N + n] = v[i][m];
+                        if (static_cast<uint32_t>(m) < p.M && n < p.N) {
+                            const unsigned long long word =
+                                (static_cast<unsigned long long>(fepoch) << 32) | __float_as_uint(v[i][m]);
+                            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst + static_cast<size_t>(m) * p.N + n), "l"(word)
+                                         : "memory");
+                        }
                 }
-            }
-            __syncwarp();
-            if (lane < p.fuse_size) {
-                uint32_t *flag = reinterpret_cast<uint32_t *>(p.fuse_region[lane] + kFusedFlagsOff) +
-                                 (static_cast<size_t>(fphase) * kFusedMaxRowGroups + rg) * kPeerMaxRanks + p.fuse_rank;
-                st_release_sys_u32(flag, fepoch);
             }
             if (npend == kPend) {  // rare: many short row groups per CTA; settle the oldest first
                 if (peers_ok) finish(pend[0]);
@@ -1849,8 +1866,7 @@ bool gemv_mma_eligible(const WeightView &w, const void *x, const void *y, bool x
 bool gemv_fused_eligible(const WeightView &w, uint32_t M, bool x_f32, const GemvTuning &tune) {
     if (!tune.fuse || !tune.fuse->ok || tune.fuse->size == 0u || tune.fuse->size > static_cast<uint32_t>(kPeerMaxRanks)) return false;
     if (w.bits != 4u || M == 0u || M > 2u || x_f32 || tune.no_dp4a || tune.probe) return false;
-    if (static_cast<size_t>(M) * w.N * sizeof(float) > kPeerSlotBytes) return false;
-    if ((w.N + kRows - 1u) / kRows > kFusedMaxRowGroups) return false;
+    if (static_cast<size_t>(M) * w.N * 8u > kPeerSlotBytes) return false;  // {value, epoch} words
     return true;
 }
 

@@ -112,12 +112,10 @@ constexpr size_t kPeerSlotBytes = size_t(512) << 10;  // largest tile one call r
 
 // Region layout (one cudaMalloc per rank, mapped by every rank of the node):
 //   all-reduce kernel: arrival flags u32 [2 phases][kPeerCtas][ranks], per-CTA epochs, data [2][ranks][slot]
-//   fused GEMV + all-reduce: row-group flags u32 [2 phases][kFusedMaxRowGroups][ranks], {epoch, done} words,
-//   data [2][ranks][slot] holding a rank's fp32 partial tile as [activation row][N]
+//   fused GEMV + all-reduce: {epoch, done} words, data [2 phases][ranks][slot] holding a rank's partial tile as
+//   64-bit words {fp32 value, launch epoch} [activation row][N]
 constexpr size_t kPeerFlagsOff = 0;
 constexpr size_t kPeerEpochOff = 4096;
-constexpr uint32_t kFusedMaxRowGroups = 1024;
-constexpr size_t kFusedFlagsOff = size_t(64) << 10;   // 2 * 1024 * 8 * 4 = 64 KB
 constexpr size_t kFusedCtlOff = size_t(128) << 10;
 constexpr size_t kPeerDataOff = size_t(256) << 10;
 constexpr size_t kFusedDataOff = kPeerDataOff + 2 * size_t(kPeerMaxRanks) * kPeerSlotBytes;
