@@ -37,9 +37,11 @@ METRIC = "gaf4_64 decode GEMV HBM GB/s"
 GROUP, BITS = 64, 4
 NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, averaged over the step's two launch shapes
-# (gate|up 66,773,760 + 477,440 B; down 33,795,840 + 512 B), from the ncu capture summarised in
-# profiles/gemv_dp4a_llama8b_ffn_m1.md
-NCU_TRAFFIC_PER_LAUNCH = (66_773_760 + 477_440 + 33_795_840 + 512) // 2
+# (gate|up 78,993,664 + 2,137,856 B; down 47,757,056 + 12,544 B), from the ncu capture summarised in
+# profiles/gemv_dp4a_llama8b_ffn_m1.md.  Each launch's reads include ~10.9 MB of next-weight L2 prefetch
+# (2 units x 148 CTAs); ncu flushes the caches between kernels, so under ncu those bytes are read again by
+# the next launch, while in a back-to-back run they replace the same bytes of that launch.
+NCU_TRAFFIC_PER_LAUNCH = (78_993_664 + 2_137_856 + 47_757_056 + 12_544) // 2
 
 
 def measured_peak_hbm():
@@ -335,7 +337,7 @@ def run_single(args):
         "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}",
                      "traffic": NCU_TRAFFIC_PER_LAUNCH,
-                     "traffic_note": "ncu dram bytes per launch, mean of the step's two shapes (algorithmic mean 49.6 MB)"},
+                     "traffic_note": "ncu dram bytes per launch, mean of the step's two shapes (algorithmic mean 49.6 MB; 10.9 MB of it is the next launch's head, prefetched to L2 and counted twice under ncu's cache flush)"},
         "cpu_baseline": {"value": round(cpu_gbs, 3), "unit": "GB/s", "cores": cores, "kind": "port",
                          "sample": f"{cpu_n} calls of one gate-shaped matrix [14336 x 4096], M=1, f32 activations ({cpu_per_call * 1e3:.2f} ms each)"},
         "e2e": {"value": round(e2e_gbs, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
