@@ -85,7 +85,7 @@ struct GemvParams {
     void *y;
     float *partials;         // [row group][slot][128][MT*8]
     unsigned int *counters;  // [row group]
-    unsigned long long *tagged;  // M <= 2 kernel: {value, tag} words [row group][slot][128][M]; null = use partials + counters
+    unsigned long long *tagged;  // M <= 4 kernel: {value, tag} words [row group][slot][128][M]; null = use partials + counters
     unsigned int *error_word;
     uint32_t N, K, M;
     uint32_t groups;      // K / G
@@ -102,9 +102,9 @@ struct GemvParams {
     uint32_t next_prefetch;  //   units to prefetch at the head of each of its CTA ranges
     uint8_t *fuse_region[kPeerMaxRanks];  // fused all-reduce: every rank's exchange region ([fuse_rank] is local)
     uint32_t fuse_rank, fuse_size;        //   fuse_size == 0: plain GEMV
-    uint32_t y_f32;          // M <= 2 kernel: write y as fp32 although x is bf16 (first half of the fused FFN)
-    uint32_t act;            // M <= 2 kernel: 1 = x is fp32 [M][2K] and the operand is silu(x[:, :K]) * x[:, K:]
-    unsigned int *grid_bar;  // M <= 2 kernel, two operations per launch: arrival counters, zero between launches
+    uint32_t y_f32;          // M <= 4 kernel: write y as fp32 although x is bf16 (first half of the fused FFN)
+    uint32_t act;            // M <= 4 kernel: 1 = x is fp32 [M][2K] and the operand is silu(x[:, :K]) * x[:, K:]
+    unsigned int *grid_bar;  // M <= 4 kernel, two operations per launch: arrival counters, zero between launches
     uint32_t probe;       // measurement aid, bit mask: 1 = skip the arithmetic, 2 = skip the streaming, 4 = skip the write-out,
                           // 8 = skip the activation block, 32 = return at once (launch cost only)
 };
@@ -839,7 +839,7 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
 }
 
 // ---------------------------------------------------------------------------
-// Streaming GEMV for M <= 2 on the integer dot-product unit.
+// Streaming GEMV for M <= 4 on the integer dot-product unit (M <= 2) or the int8 tensor-core MMA (M = 3, 4).
 //
 // With one or two activation rows the tensor-core formulation above wastes seven
 // of its eight columns and is bound by instruction issue (unpack + fragment
@@ -855,7 +855,30 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
 // element (bf16 inputs carry 2^-9 relative), far inside the 1e-2 budget.
 // Same producer / ring / split-K protocol as the tensor-core kernel; warp =
 // (group of the unit, block of rows), lane = row.
+//
+// M = 3, 4 (template MD = 4) keep the skeleton and the quantised activations but do the dot products on the
+// int8 tensor-core MMA (m16n8k32, u8 x s8): a packed word's even / odd nibbles, as bytes, ARE the A registers
+// (the k order inside an MMA is free, the activation bytes are laid out to match), and the eight columns are
+// the (activation row, limb) pairs, so four rows cost what one costs.  A warp keeps its group's B registers
+// for all its 16-row blocks; thread (g, t) of a block ends up with the sums of rows g, g + 8 for activation
+// row t.
 // ---------------------------------------------------------------------------
+// float(64 * hi + lo) for |hi|, |lo| < 2^22 without conversion instructions (which issue at a quarter of
+// the rate): adding 1.5 * 2^23 to the bit pattern is exact, and the sum stays below 2^24
+__device__ __forceinline__ float limbs_to_float(int hi, int lo) {
+    const float fh = __int_as_float(hi + 0x4B400000) - 12582912.f;
+    const float fl = __int_as_float(lo + 0x4B400000) - 12582912.f;
+    return fmaf(fh, 64.f, fl);
+}
+// int8 tensor-core MMA: D[16x8] += A[16x32] (u8, row) * B[32x8] (s8, col), s32 accumulate
+__device__ __forceinline__ void mma_u8s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 __device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
     int d;
     asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
@@ -897,6 +920,9 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
     constexpr int RW = kRows * GPS / NCW;  // rows per warp: 128 (G=32), 64 (G=64), 32 (G=128)
     constexpr int R = RW / 32;                        // rows per lane
     constexpr int CH = GB / 16;                       // 16-byte chunks per group and row
+    constexpr bool IM = MD == 4;                      // three or four activation rows: int8 MMA instead of dp4a
+    constexpr int WPT = GB / 16;                      // IM: packed words per quad lane, group and row = MMAs per group
+    constexpr int NRB = RW / 16;                      // IM: 16-row blocks per warp
     static_assert(R >= 1 && GPS <= NCW && GPS * (kRows / RW) == NCW, "unsupported group size");
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -1287,6 +1313,24 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
 #pragma unroll
         for (int m = 0; m < MD; ++m) yacc[i][m] = 0.f;
 
+    // int8-MMA variant: quad layout of the MMA fragments.  Accumulator rows g, g + 8 of a 16-row block are
+    // weight rows wr, wr + 8 (wr = rho(g): the permutation that keeps the swizzled loads conflict free).
+    const uint32_t qg = lane >> 2, qt = lane & 3;
+    const uint32_t wr = rho<GB / 4>(qg);
+    uint32_t aoff[IM ? NRB : 1], sbim[IM ? NRB : 1];
+    float yim[IM ? NRB : 1][2];
+    if constexpr (IM) {
+#pragma unroll
+        for (int rb = 0; rb < NRB; ++rb) {
+            const uint32_t row = rbase + rb * 16u + wr;
+            const uint32_t obyte = gq * GB + qt * (GB / 4);   // this lane's bytes of the group inside the unit row
+            const uint32_t pnl = obyte / kPanelBytes, inp = obyte % kPanelBytes;
+            aoff[rb] = ring + pnl * kPanelSize + row * kPanelBytes + ((((inp >> 4) ^ row) & 7u) << 4) + (inp & 15u);
+            sbim[rb] = ring + kWeightBytes + row * Geo::SBOX + gq * 2u;
+            yim[rb][0] = yim[rb][1] = 0.f;
+        }
+    }
+
     uint32_t stage = 0, phase = 0;   // ring position and out-buffer position run on across operations
     uint32_t ob = 0, ophase = 0;
     bool alive = true;
@@ -1382,7 +1426,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
             int isum = 0;
 #pragma unroll
             for (int e = 0; e < PER; ++e) {
-                int xi = __float2int_rn(xv[tk][e] * up);
+                int xi = __float_as_int(fmaf(xv[tk][e], up, 12582912.f)) - 0x4B400000;  // rint without a conversion instruction
                 xi = max(-4095, min(4095, xi));
                 isum += xi;
                 const int hi = xi >> 6, lo = xi & 63;
@@ -1390,9 +1434,17 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                 const uint32_t k = lane * PER + e;
                 const uint32_t wj = k >> 3, odd = k & 1u, bytepos = (k & 7u) >> 1;
                 // 16 bytes per (word, activation row): {even hi, odd hi, even lo, odd lo} x 4 bytes
-                const uint32_t a = qb + (wj * MD + m) * 16u + odd * 4u + bytepos;
-                asm volatile("st.shared.u8 [%0], %1;" ::"r"(a), "r"(hi & 0xFF) : "memory");
-                asm volatile("st.shared.u8 [%0], %1;" ::"r"(a + 8u), "r"(lo & 0xFF) : "memory");
+                if constexpr (IM) {
+                    // B registers of MMA (wj % WPT) for the quad lane (wj / WPT): 8 bytes {even, odd} per
+                    // (column, quad lane), column 2m = hi limb, 2m + 1 = lo limb
+                    const uint32_t a = qb + (wj % WPT) * 256u + ((2u * m) * 4u + wj / WPT) * 8u + odd * 4u + bytepos;
+                    asm volatile("st.shared.u8 [%0], %1;" ::"r"(a), "r"(hi & 0xFF) : "memory");
+                    asm volatile("st.shared.u8 [%0], %1;" ::"r"(a + 32u), "r"(lo & 0xFF) : "memory");
+                } else {
+                    const uint32_t a = qb + (wj * MD + m) * 16u + odd * 4u + bytepos;
+                    asm volatile("st.shared.u8 [%0], %1;" ::"r"(a), "r"(hi & 0xFF) : "memory");
+                    asm volatile("st.shared.u8 [%0], %1;" ::"r"(a + 8u), "r"(lo & 0xFF) : "memory");
+                }
             }
             // sum of the quantised activations (exact in integers): the bias term then matches the
             // dot products, y = sum_k (s q_k + b) * xq_k
@@ -1427,6 +1479,42 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
             if (!landed) alive = false, s_abort = 1u;
         }
         const bool exists = kc * GPS + gq < p.groups;  // the last K chunk of a row may hold fewer groups
+        if constexpr (IM) {
+            if (landed && exists && !(p.probe & 1u)) {
+                const uint32_t stage_off = stage * Geo::STAGE_BYTES;
+                const uint32_t xq = xq_warp + (buf * BU + ub) * Plan::XQ_UNIT + lane * 8u;
+                uint32_t bfr[WPT][2];  // this group's B registers, kept for all row blocks
+#pragma unroll
+                for (int j = 0; j < WPT; ++j)
+                    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(bfr[j][0]), "=r"(bfr[j][1]) : "r"(xq + j * 256u));
+                float ex, xs;  // activation row qt
+                asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];"
+                             : "=f"(ex), "=f"(xs)
+                             : "r"(xi_warp + (buf * BU + ub) * Plan::XI_UNIT + qt * 8u));
+                const uint32_t sbo = (kc * GPS * 2u) & 15u;
+#pragma unroll
+                for (int rb = 0; rb < NRB; ++rb) {
+                    uint32_t wa[WPT], wb[WPT];
+                    lds_row<WPT>(stage_off + aoff[rb], wr, wa);
+                    lds_row<WPT>(stage_off + aoff[rb] + 8u * kPanelBytes, wr, wb);
+                    int c[4] = {0, 0, 0, 0};
+#pragma unroll
+                    for (int j = 0; j < WPT; ++j)
+                        mma_u8s8_16832(c, wa[j] & 0x0F0F0F0Fu, wb[j] & 0x0F0F0F0Fu, (wa[j] >> 4) & 0x0F0F0F0Fu,
+                                       (wb[j] >> 4) & 0x0F0F0F0Fu, bfr[j][0], bfr[j][1]);
+                    uint16_t s0r, b0r, s1r, b1r;
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s0r) : "r"(stage_off + sbim[rb] + sbo));
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(b0r) : "r"(stage_off + sbim[rb] + sbo + Geo::SB_BYTES));
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s1r) : "r"(stage_off + sbim[rb] + sbo + 8u * Geo::SBOX));
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(b1r) : "r"(stage_off + sbim[rb] + sbo + 8u * Geo::SBOX + Geo::SB_BYTES));
+                    const float s0 = sb_half<SD>(s0r, 0), b0 = sb_half<SD>(b0r, 0);
+                    const float s1 = sb_half<SD>(s1r, 0), b1 = sb_half<SD>(b1r, 0);
+                    // columns 2 qt (hi) and 2 qt + 1 (lo): y += s 2^(E-12) (64 hi + lo) + b 2^(E-12) sum(xi)
+                    yim[rb][0] = fmaf(limbs_to_float(c[0], c[1]), s0 * ex, fmaf(b0, xs, yim[rb][0]));
+                    yim[rb][1] = fmaf(limbs_to_float(c[2], c[3]), s1 * ex, fmaf(b1, xs, yim[rb][1]));
+                }
+            }
+        } else
         if (landed && exists && !(p.probe & 1u)) {
             const uint32_t stage_off = stage * Geo::STAGE_BYTES;
             // packed codes of this lane's rows
@@ -1480,7 +1568,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                 const float s = sb_half<SD>(sraw, 0), b = sb_half<SD>(braw, 0);
 #pragma unroll
                 for (int m = 0; m < MD; ++m) {
-                    const float v = __int2float_rn(ahi[i][m] * 64 + alo[i][m]);
+                    const float v = limbs_to_float(ahi[i][m], alo[i][m]);
                     yacc[i][m] = fmaf(v, s * ex[m], yacc[i][m]);
                     yacc[i][m] = fmaf(b, xs[m], yacc[i][m]);
                 }
@@ -1494,6 +1582,15 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         if ((kc + 1u == p.chunks) || !more) {
             if (alive && !mbar_wait(smem_u32(&s_out_empty[ob]), ophase ^ 1u, p.error_word, 0x10u)) alive = false, s_abort = 1u;
             if (alive) {
+                if constexpr (IM) {
+#pragma unroll
+                    for (int rb = 0; rb < NRB; ++rb) {
+                        const uint32_t row = rbase + rb * 16u + wr;
+                        asm volatile("st.shared.f32 [%0], %1;" ::"r"(out_warp + ob * Plan::OUT_BUF + (row * MD + qt) * 4u), "f"(yim[rb][0]) : "memory");
+                        asm volatile("st.shared.f32 [%0], %1;" ::"r"(out_warp + ob * Plan::OUT_BUF + ((row + 8u) * MD + qt) * 4u), "f"(yim[rb][1]) : "memory");
+                        yim[rb][0] = yim[rb][1] = 0.f;
+                    }
+                } else {
 #pragma unroll
                 for (int i = 0; i < R; ++i)
 #pragma unroll
@@ -1502,6 +1599,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                                                                         ((rbase + lane + 32u * i) * MD + m) * 4u),
                                      "f"(yacc[i][m])
                                      : "memory");
+                }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&s_out_full[ob]));
             }
@@ -1765,6 +1863,9 @@ cudaError_t dispatch_dp4a(const GemvParams &p, const WeightView &w, const Weight
     if (M == 2)
         return bf ? launch_dp4a<GB, 2, false, 1, kConsumerWarps, 3, 8>(p, w, next, ctas, pdl, stream)
                   : launch_dp4a<GB, 2, false, 0, kConsumerWarps, 3, 8>(p, w, next, ctas, pdl, stream);
+    if (M == 3 || M == 4)  // int8-MMA variant, activation blocks of four units
+        return bf ? launch_dp4a<GB, 4, false, 1, kConsumerWarps, NST1, 4>(p, w, next, ctas, pdl, stream)
+                  : launch_dp4a<GB, 4, false, 0, kConsumerWarps, NST1, 4>(p, w, next, ctas, pdl, stream);
     return cudaErrorNotSupported;
 }
 
@@ -1861,11 +1962,11 @@ bool gemv_mma_eligible(const WeightView &w, const void *x, const void *y, bool x
     return true;
 }
 
-// The all-reduce can ride in the write-out of the M <= 2 kernel when the peers' regions are mapped and the
+// The all-reduce can ride in the write-out of the M <= 4 kernel when the peers' regions are mapped and the
 // fp32 tile [M][N] fits an exchange slot.
 bool gemv_fused_eligible(const WeightView &w, uint32_t M, bool x_f32, const GemvTuning &tune) {
     if (!tune.fuse || !tune.fuse->ok || tune.fuse->size == 0u || tune.fuse->size > static_cast<uint32_t>(kPeerMaxRanks)) return false;
-    if (w.bits != 4u || M == 0u || M > 2u || x_f32 || tune.no_dp4a || tune.probe) return false;
+    if (w.bits != 4u || M == 0u || M > 4u || x_f32 || tune.no_dp4a || tune.probe) return false;
     if (static_cast<size_t>(M) * w.N * 8u > kPeerSlotBytes) return false;  // {value, epoch} words
     return true;
 }
@@ -1877,9 +1978,9 @@ size_t gemv_mma_scratch_bytes(const WeightView &w, uint32_t M, const GemvTuning 
 }
 
 size_t gemv_tagged_bytes(const WeightView &w, uint32_t M, bool x_f32, const GemvTuning &tune, int sm_count) {
-    if (w.bits != 4u || M == 0u || M > 2u || x_f32 || tune.no_dp4a) return 0;
+    if (w.bits != 4u || M == 0u || M > 4u || x_f32 || tune.no_dp4a) return 0;
     const GemvPlan pl = plan_gemv(w, tune, sm_count);
-    return static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * M * 8u;
+    return static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * (M <= 2u ? M : 4u) * 8u;
 }
 
 size_t gemv_mma_counter_count(const WeightView &w) {
@@ -1950,12 +2051,13 @@ cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bo
         p.fuse_rank = tune.fuse->rank;
         p.fuse_size = tune.fuse->size;
     }
-    if (w.bits == 4 && M <= 2u && !x_f32 && !tune.no_dp4a) {
-        if (scratch.tagged && static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * M * 8u <= scratch.tagged_bytes)
+    if (w.bits == 4 && M <= 4u && !x_f32 && !tune.no_dp4a) {
+        const uint32_t md = M <= 2u ? M : 4u;  // activation rows the kernel instance is built for
+        if (scratch.tagged && static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * md * 8u <= scratch.tagged_bytes)
             p.tagged = scratch.tagged;
         // one or two bf16 activation rows: the integer dot-product formulation (its 13-bit activations
         // are ample next to bf16 inputs; f32 callers keep the hi + lo tensor-core path and its 1e-3 accuracy)
-        const bool small = tune.dp4a_small != 0 && gb >= 32u;
+        const bool small = tune.dp4a_small != 0 && gb >= 32u && M <= 2u;
         if (gb == 16u) return dispatch_dp4a<16>(p, w, next, pl.ctas, M, false, pdl, stream);
         if (gb == 32u) return dispatch_dp4a<32>(p, w, next, pl.ctas, M, small, pdl, stream);
         if (gb == 64u) return dispatch_dp4a<64>(p, w, next, pl.ctas, M, small, pdl, stream);

@@ -34,7 +34,7 @@ struct Scratch {
     size_t partial_bytes;
     unsigned int *counters;   // [row group][8], self-resetting
     size_t counter_count;
-    // M <= 2 kernel: partial sums that carry their own arrival tag, u64 {value, tag} [row group][slot][128][M];
+    // M <= 4 kernel: partial sums that carry their own arrival tag, u64 {value, tag} [row group][slot][128][M];
     // all tags are zero between launches (null: the kernel uses partials + counters instead)
     unsigned long long *tagged;
     size_t tagged_bytes;
@@ -77,7 +77,7 @@ cudaError_t swiglu_bf16(const void *gate_up, void *h, uint32_t M, uint32_t d_ff,
 bool gemv_fused_eligible(const WeightView &w, uint32_t M, bool x_f32, const GemvTuning &tune);
 size_t gemv_mma_scratch_bytes(const WeightView &w, uint32_t M, const GemvTuning &tune, int sm_count);
 size_t gemv_mma_counter_count(const WeightView &w);
-// bytes of Scratch::tagged the M <= 2 kernel needs for this weight (0 when that kernel does not apply)
+// bytes of Scratch::tagged the M <= 4 kernel needs for this weight (0 when that kernel does not apply)
 size_t gemv_tagged_bytes(const WeightView &w, uint32_t M, bool x_f32, const GemvTuning &tune, int sm_count);
 
 // Same kernel on the library's fixed device-resident scratch: allocates nothing.

@@ -118,7 +118,7 @@ def test_cfg1_gemv_gaf4_64(gaf, ctx, oracle):
 
 
 @pytest.mark.parametrize("bits,G", SCHEMES)
-@pytest.mark.parametrize("M", [1, 8])
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 8])
 def test_cfg3_scheme_sweep(gaf, ctx, oracle, bits, G, M):
     """K = N = 4096, M in {1, 8}, every scheme.  rel <= 1e-2."""
     y, ref = _run_bf16(gaf, ctx, oracle, 4096, 4096, G, bits, M, seed=20 + bits + G)
