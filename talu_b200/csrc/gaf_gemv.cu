@@ -1374,6 +1374,70 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
     auto prep_block = [&](auto act_c, uint32_t kc_first, uint32_t count, uint32_t buf) {
         constexpr bool ACT = decltype(act_c)::value;  // compile-time: the plain path keeps its loads branch-free
         if (p.probe & 8u) return;
+        if constexpr (IM && !ACT && !XF32) {
+            // Four activation rows: a lane takes one packed word's worth (8 consecutive elements, one 16-byte
+            // load) of one (unit, group, activation row); the G/8 lanes of a row reduce among themselves.  The
+            // word's {even, odd} byte pairs are exactly one lane's B registers of one MMA.
+            constexpr int G = GB * 2, WG = G / 8;              // words per group: 4, 8, 16
+            constexpr int TASKS = BU * GPS * MD * WG;          // per block, at most
+            constexpr int IT = (TASKS + NCW * 32 - 1) / (NCW * 32);
+            const uint32_t ntask = count * GPS * MD * WG;
+            const uint32_t gmask = ((WG == 32 ? 0u : (1u << WG)) - 1u) << (lane & ~(WG - 1));
+            uint4 v[IT];
+#pragma unroll
+            for (int it = 0; it < IT; ++it) {
+                const uint32_t id = (it * NCW + warp) * 32u + lane;
+                const uint32_t wd = id % WG, m = (id / WG) % MD, gl = (id / (WG * MD)) % GPS, ubk = id / (WG * MD * GPS);
+                const uint32_t gi = ((kc_first + ubk) % p.chunks) * GPS + gl;
+                v[it] = make_uint4(0u, 0u, 0u, 0u);
+                if (id < ntask && m < p.M && gi < p.groups)
+                    v[it] = *reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(xbase) +
+                                                             static_cast<size_t>(m) * p.K + static_cast<size_t>(gi) * G + wd * 8u);
+            }
+#pragma unroll
+            for (int it = 0; it < IT; ++it) {
+                const uint32_t id = (it * NCW + warp) * 32u + lane;
+                const uint32_t wd = id % WG, m = (id / WG) % MD, gl = (id / (WG * MD)) % GPS, ubk = id / (WG * MD * GPS);
+                const uint32_t w4[4] = {v[it].x, v[it].y, v[it].z, v[it].w};
+                uint32_t amax = 0u;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const uint32_t a = w4[e] & 0x7FFF7FFFu;  // two bf16 magnitudes: they order like integers
+                    amax = max(amax, max(a & 0xFFFFu, a >> 16));
+                }
+                amax = __reduce_max_sync(gmask, amax);
+                const uint32_t eb = amax >> 7;                     // biased exponent of the group's largest |x|
+                const bool nz = eb >= 27u && eb < 255u;
+                const float up = nz ? __uint_as_float((265u - eb) << 23) : 0.f;    // 2^(12 - E), E = eb - 126
+                const float down = nz ? __uint_as_float((eb - 11u) << 23) : 0.f;   // 2^(E - 12)
+                int isum = 0;
+                uint32_t ehi = 0u, ohi = 0u, elo = 0u, olo = 0u;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    int xe = __float_as_int(fmaf(__uint_as_float(w4[e] << 16), up, 12582912.f)) - 0x4B400000;          // element 2e
+                    int xo = __float_as_int(fmaf(__uint_as_float(w4[e] & 0xFFFF0000u), up, 12582912.f)) - 0x4B400000;  // 2e + 1
+                    xe = max(-4095, min(4095, xe));
+                    xo = max(-4095, min(4095, xo));
+                    isum += xe + xo;
+                    ehi |= (static_cast<uint32_t>(xe >> 6) & 0xFFu) << (8 * e);
+                    elo |= (static_cast<uint32_t>(xe) & 63u) << (8 * e);
+                    ohi |= (static_cast<uint32_t>(xo >> 6) & 0xFFu) << (8 * e);
+                    olo |= (static_cast<uint32_t>(xo) & 63u) << (8 * e);
+                }
+                isum = __reduce_add_sync(gmask, isum);
+                if (id < ntask) {
+                    const uint32_t qb = ring + Plan::OFF_XQ + (buf * BU + ubk) * Plan::XQ_UNIT + gl * Plan::XQ_GROUP;
+                    const uint32_t a = qb + (wd % WPT) * 256u + ((2u * m) * 4u + wd / WPT) * 8u;
+                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a), "r"(ehi), "r"(ohi) : "memory");
+                    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a + 32u), "r"(elo), "r"(olo) : "memory");
+                    if (wd == 0u) {
+                        const uint32_t xa = ring + Plan::OFF_XI + (buf * BU + ubk) * Plan::XI_UNIT + (gl * MD + m) * 8u;
+                        asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(xa), "f"(down), "f"(static_cast<float>(isum) * down) : "memory");
+                    }
+                }
+            }
+            return;
+        }
         constexpr int G = GB * 2;                          // elements per group (4-bit codes)
         constexpr int PER = G / 32;                        // elements per lane: 1 (G=32), 2, 4
         constexpr int TPW = (BU * GPS * MD + NCW - 1) / NCW;  // triples per warp, at most
@@ -1457,12 +1521,16 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         }
     };
 
+    // When a row of K fits one activation block (K / 512 <= BU), the block built here holds every K chunk,
+    // in the order this CTA meets them; later row groups reuse it and nothing is rebuilt.
+    const bool whole_k = p.chunks <= block_units;
+    const uint32_t block_len = whole_k ? p.chunks : block_units;
     {
         const uint32_t total = u_end - u_begin;
         if (NOPS > 1 && p.act == 1u)
-            prep_block(std::true_type{}, kc_begin, total < block_units ? total : block_units, 0u);
+            prep_block(std::true_type{}, kc_begin, total < block_len ? total : block_len, 0u);
         else
-            prep_block(std::false_type{}, kc_begin, total < block_units ? total : block_units, 0u);
+            prep_block(std::false_type{}, kc_begin, total < block_len ? total : block_len, 0u);
     }
     asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
 
@@ -1611,9 +1679,9 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                 for (int m = 0; m < MD; ++m) yacc[i][m] = 0.f;
         }
 
-        if (++ub == block_units) {
+        if (++ub == block_len) {
             ub = 0u;
-            if (more) {
+            if (more && !whole_k) {
                 const uint32_t left = u_end - (u + 1u);
                 if (NOPS > 1 && p.act == 1u)
                     prep_block(std::true_type{}, kc_n, left < block_units ? left : block_units, buf ^ 1u);
@@ -1864,8 +1932,8 @@ cudaError_t dispatch_dp4a(const GemvParams &p, const WeightView &w, const Weight
         return bf ? launch_dp4a<GB, 2, false, 1, kConsumerWarps, 3, 8>(p, w, next, ctas, pdl, stream)
                   : launch_dp4a<GB, 2, false, 0, kConsumerWarps, 3, 8>(p, w, next, ctas, pdl, stream);
     if (M == 3 || M == 4)  // int8-MMA variant, activation blocks of four units
-        return bf ? launch_dp4a<GB, 4, false, 1, kConsumerWarps, NST1, 4>(p, w, next, ctas, pdl, stream)
-                  : launch_dp4a<GB, 4, false, 0, kConsumerWarps, NST1, 4>(p, w, next, ctas, pdl, stream);
+        return bf ? launch_dp4a<GB, 4, false, 1, kConsumerWarps, 3, (GB == 16 ? 4 : 8)>(p, w, next, ctas, pdl, stream)
+                  : launch_dp4a<GB, 4, false, 0, kConsumerWarps, 3, (GB == 16 ? 4 : 8)>(p, w, next, ctas, pdl, stream);
     return cudaErrorNotSupported;
 }
 
