@@ -315,6 +315,10 @@ def run_single(args):
     st_ms, st_bytes, st_launches, st_layers, *_ = tp_bench.measure(args, existing_ctx=ctx, existing_stream=stream)
     stack70b = {"workload": "llama3_70b_stack", "layers": st_layers, "ms_per_step": round(st_ms, 5),
                 "gbs": round(st_bytes / st_ms / 1e6, 2), "launches_per_step": st_launches}
+    # the skinny case of the same stack (64 activation rows: the tcgen05 GEMM with one 128-row half), HBM-bound
+    # by its roofline, limited here by the rate at which the dequant warps produce the bf16 operand
+    sk_ms, sk_bytes, *_ = tp_bench.measure(args, existing_ctx=ctx, existing_stream=stream, M=64)
+    stack70b["m64"] = {"ms_per_step": round(sk_ms, 5), "gbs": round(sk_bytes / sk_ms / 1e6, 2)}
 
     peak, peak_kind = measured_peak_hbm()
     launches_per_step = len(weights)

@@ -209,18 +209,18 @@ int32_t tgaf_comm_init(tgaf_ctx *ctx, const uint8_t id[TGAF_COMM_ID_BYTES], uint
  * that captured tgaf_allreduce first: NCCL waits for them.  tgaf_ctx_destroy aborts a
  * communicator that is still there instead of waiting. */
 int32_t tgaf_comm_destroy(tgaf_ctx *ctx);
-/* In place, on the context's stream.  Tiles of up to 512 KiB whose size is a multiple of 16 bytes
- * (decode: [M <= 16, hidden]) are summed by one kernel over NVLink peer memory when every rank of
- * the communicator could map every other rank's exchange region (same node, CUDA IPC): each rank
- * pushes its tile to all peers, then adds the tiles in rank order in fp32 - the result is
- * bit-identical on every rank and from run to run.  Anything else goes to ncclAllReduce.  All
+/* In place, on the context's stream.  Tiles of up to 131072 values (decode: [M <= 16, 8192]) are
+ * summed by one kernel over NVLink peer memory when every rank of the communicator could map every
+ * other rank's exchange region (same node, CUDA IPC): each rank pushes its tile, widened to fp32, to
+ * all peers, then adds the ranks' tiles in rank order - the result is bit-identical on every rank
+ * and from run to run, with one rounding for bf16.  Anything else goes to ncclAllReduce.  All
  * ranks must issue the same sequence of calls.  A peer that does not show up within several
  * seconds makes the kernel give up: tgaf_synchronize then returns TGAF_ERR_DEVICE_FLAG.
  * Option "peer_allreduce" = 0 (tgaf_ctx_set_option, same value on every rank) or the environment
  * variable TGAF_PEER_ALLREDUCE=0 keeps everything on NCCL. */
 int32_t tgaf_allreduce(tgaf_ctx *ctx, void *d_buf, uint64_t count, uint32_t dtype);
 /* y = sum over ranks of x_local * W_local^T for a row-parallel weight (TGAF_SHARD_ROW): tgaf_linear_bf16
- * followed by tgaf_allreduce on y, as one call.  For M <= 2 on gaf4 weights with the peer-memory path
+ * followed by tgaf_allreduce on y, as one call.  For M <= 4 on gaf4 weights with the peer-memory path
  * available it is ONE kernel: the GEMV's write-out pushes each finished block of 128 outputs, as fp32, to
  * every rank over NVLink while later blocks are still being computed, then adds the ranks' blocks in rank
  * order and rounds once (bit-identical on all ranks; more accurate than summing rounded bf16 outputs).

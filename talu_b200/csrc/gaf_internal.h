@@ -108,13 +108,12 @@ bool gemm_tc_eligible(const WeightView &w, uint32_t M);
 constexpr int kPeerMaxRanks = 8;                      // ranks of one node
 constexpr int kPeerCtas = 16;                         // CTAs of the all-reduce kernel (always all launched)
 constexpr int kPeerThreads = 256;
-constexpr size_t kPeerSlotBytes = size_t(512) << 10;  // largest tile one call reduces (16 rows x 8192 fp32)
+constexpr size_t kPeerSlotBytes = size_t(1) << 20;    // one rank's tile as 64-bit words: 131072 values (16 rows x 8192)
 
 // Region layout (one cudaMalloc per rank, mapped by every rank of the node):
-//   all-reduce kernel: arrival flags u32 [2 phases][kPeerCtas][ranks], per-CTA epochs, data [2][ranks][slot]
+//   all-reduce kernel: per-CTA call counters, data [2 phases][ranks][slot] of 64-bit words {fp32 value, epoch}
 //   fused GEMV + all-reduce: {epoch, done} words, data [2 phases][ranks][slot] holding a rank's partial tile as
 //   64-bit words {fp32 value, launch epoch} [activation row][N]
-constexpr size_t kPeerFlagsOff = 0;
 constexpr size_t kPeerEpochOff = 4096;
 constexpr size_t kFusedCtlOff = size_t(128) << 10;
 constexpr size_t kPeerDataOff = size_t(256) << 10;
@@ -129,7 +128,7 @@ struct PeerComm {
 
 size_t peer_region_bytes();
 // In-place sum of d_buf[count] (bf16 or f32) over the ranks.  cudaErrorNotSupported when the tile does not
-// fit a slot, is not a multiple of 16 bytes, or the peer mapping is unavailable (the caller then uses NCCL).
+// fit a slot or the peer mapping is unavailable (the caller then uses NCCL).
 cudaError_t peer_allreduce(const PeerComm &pc, void *d_buf, size_t count, bool f32, bool pdl, cudaStream_t stream,
                            unsigned int *d_error_word);
 

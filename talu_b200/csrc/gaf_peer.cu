@@ -6,18 +6,19 @@
 // file has a one-shot kernel instead:
 //
 //   * every rank owns one region (cudaMalloc) that all other ranks of the node map
-//     through CUDA IPC: data[2 phases][rank][slot] plus arrival flags;
-//   * push: a CTA copies its slice of the local tile into slot `my rank` of EVERY
-//     rank's region (plain 16-byte stores, remote ones travel over NVLink), then
-//     one thread per peer publishes the call's epoch with st.release.sys;
-//   * wait: the CTA polls ITS OWN region's flags (ld.acquire.sys) until every rank's
-//     epoch arrived - bounded; on expiry it raises an error word and leaves;
-//   * reduce: sums the slots in rank order in fp32 and writes the tile back.
-//     Every rank adds the same numbers in the same order: results are bit-identical
-//     on all ranks and from run to run.
+//     through CUDA IPC: data[2 phases][rank][slot] plus per-CTA call counters;
+//   * push: a CTA widens its slice of the local tile to fp32 and stores it into slot
+//     `my rank` of EVERY rank's region as 64-bit words {fp32 value, call epoch}
+//     (plain stores; the remote ones travel over NVLink).  One store carries value
+//     and arrival: a reader that sees the epoch has the value - no flag, no fence,
+//     one NVLink hop (the "LL" idea of collective libraries);
+//   * wait + reduce: the CTA polls ITS OWN region for every rank's words of its slice
+//     (bounded; on expiry it raises an error word and leaves), adds them in rank
+//     order in fp32 and writes the tile back.  Every rank adds the same numbers in
+//     the same order: results are bit-identical on all ranks and from run to run.
 //
 // Two phases (epoch parity) are enough: a rank can be at most one call ahead of the
-// slowest rank, because finishing call k needs every peer's data of call k, and a
+// slowest rank, because finishing call k needs every peer's words of call k, and a
 // rank's calls run one after another on its stream.
 //
 // Plain peer stores and local loads only (no bulk-copy engine, no switch reductions).
@@ -37,39 +38,13 @@ struct PeerArgs {
     unsigned int *error_word;
 };
 
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
+constexpr size_t kEpochOff = kPeerEpochOff, kDataOff = kPeerDataOff;
 
-constexpr size_t kFlagsOff = kPeerFlagsOff, kEpochOff = kPeerEpochOff, kDataOff = kPeerDataOff;
-static_assert(2 * kPeerCtas * kPeerMaxRanks * 4 <= 4096, "flag block");
-
-template <bool F32>
-__device__ __forceinline__ void accumulate(float (&acc)[F32 ? 4 : 8], const uint4 &v) {
-    if constexpr (F32) {
-        acc[0] += __uint_as_float(v.x), acc[1] += __uint_as_float(v.y);
-        acc[2] += __uint_as_float(v.z), acc[3] += __uint_as_float(v.w);
-    } else {
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            acc[2 * i] += __uint_as_float(w[i] << 16);
-            acc[2 * i + 1] += __uint_as_float(w[i] & 0xFFFF0000u);
-        }
-    }
-}
-
-// buf: the tile as nvec 16-byte vectors (the host side only takes tiles that are a whole number of them).
+// buf: count elements (bf16 or f32); a slot holds count 64-bit words
 template <bool F32>
 __global__ void __launch_bounds__(kPeerThreads)
-peer_allreduce_kernel(const PeerArgs a, uint4 *buf, uint32_t nvec) {
+peer_allreduce_kernel(const PeerArgs a, void *buf, uint32_t count) {
     __shared__ uint32_t s_epoch;
-    __shared__ uint32_t s_abort;
     uint8_t *mine = a.region[a.rank];
     const uint32_t cta = blockIdx.x, tid = threadIdx.x;
     // Only meaningful when launched with programmatic stream serialization (off by default: measured slower
@@ -80,78 +55,56 @@ peer_allreduce_kernel(const PeerArgs a, uint4 *buf, uint32_t nvec) {
         uint32_t *ep = reinterpret_cast<uint32_t *>(mine + kEpochOff) + cta;
         s_epoch = *ep + 1u;
         *ep = s_epoch;
-        s_abort = 0u;
     }
     __syncthreads();
     const uint32_t epoch = s_epoch, phase = epoch & 1u;
-    const uint32_t per = (nvec + gridDim.x - 1u) / gridDim.x;
+    const uint32_t per = (count + gridDim.x - 1u) / gridDim.x;
     const uint32_t lo = cta * per;
-    const uint32_t hi = lo + per < nvec ? lo + per : nvec;
+    const uint32_t hi = lo + per < count ? lo + per : count;
     if (lo >= hi) return;  // nothing in this CTA's slice (its epoch still advanced, like everybody's)
 
+    auto load_in = [&](uint32_t i) -> float {
+        if constexpr (F32) return static_cast<const float *>(buf)[i];
+        return __bfloat162float(static_cast<const __nv_bfloat16 *>(buf)[i]);
+    };
     // ---- push my slice into slot `rank` of every region ----
     const size_t slot_off = kDataOff + (static_cast<size_t>(phase) * kPeerMaxRanks + a.rank) * kPeerSlotBytes;
-    for (uint32_t v = lo + tid; v < hi; v += blockDim.x) {
-        const uint4 val = buf[v];
-#pragma unroll
-        for (uint32_t i = 0; i < kPeerMaxRanks; ++i) {
-            if (i < a.size) {
-                const uint32_t r = (a.rank + i) % a.size;  // start with myself, spread the peers
-                reinterpret_cast<uint4 *>(a.region[r] + slot_off)[v] = val;
-            }
+    for (uint32_t i = lo + tid; i < hi; i += blockDim.x) {
+        const unsigned long long word = (static_cast<unsigned long long>(epoch) << 32) | __float_as_uint(load_in(i));
+        for (uint32_t j = 0; j < a.size; ++j) {
+            uint32_t r = a.rank + j;  // start with myself, spread the peers
+            if (r >= a.size) r -= a.size;
+            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(reinterpret_cast<unsigned long long *>(a.region[r] + slot_off) + i), "l"(word)
+                         : "memory");
         }
     }
-    __syncthreads();
-    if (tid < a.size) {
-        uint32_t *flag = reinterpret_cast<uint32_t *>(a.region[tid] + kFlagsOff) + (phase * kPeerCtas + cta) * kPeerMaxRanks + a.rank;
-        st_release_sys(flag, epoch);
-    }
-
-    // ---- wait for every rank's slice ----
-    if (tid < a.size) {
-        const uint32_t *flag = reinterpret_cast<const uint32_t *>(mine + kFlagsOff) + (phase * kPeerCtas + cta) * kPeerMaxRanks + tid;
-        bool ok = false;
-        for (uint32_t it = 0; it < kPeerWaitLimit; ++it) {
-            if (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0) {
-                ok = true;
-                break;
+    // ---- every rank's words of my slice, added in rank order ----
+    const unsigned long long *data =
+        reinterpret_cast<const unsigned long long *>(mine + kDataOff + static_cast<size_t>(phase) * kPeerMaxRanks * kPeerSlotBytes);
+    for (uint32_t i = lo + tid; i < hi; i += blockDim.x) {
+        float acc = 0.f;
+        for (uint32_t r = 0; r < a.size; ++r) {
+            const unsigned long long *src = data + r * (kPeerSlotBytes / 8u) + i;
+            unsigned long long word = 0ull;
+            bool got = false;
+            for (uint32_t it = 0; it < kPeerWaitLimit; ++it) {
+                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(word) : "l"(src) : "memory");
+                if (static_cast<uint32_t>(word >> 32) == epoch) {
+                    got = true;
+                    break;
+                }
+                if (it > 64) __nanosleep(it > 4096 ? 1000 : 32);
             }
-            if (it > 64) __nanosleep(it > 4096 ? 1000 : 32);
-        }
-        if (!ok) {
-            atomicOr(a.error_word, 0x100u);
-            s_abort = 1u;
-        }
-    }
-    __syncthreads();
-    if (s_abort) return;
-
-    // ---- add the slots in rank order ----
-    const uint8_t *data = mine + kDataOff + static_cast<size_t>(phase) * kPeerMaxRanks * kPeerSlotBytes;
-    for (uint32_t v = lo + tid; v < hi; v += blockDim.x) {
-        float acc[F32 ? 4 : 8];
-#pragma unroll
-        for (int i = 0; i < (F32 ? 4 : 8); ++i) acc[i] = 0.f;
-        uint4 in[kPeerMaxRanks];
-#pragma unroll
-        for (uint32_t r = 0; r < kPeerMaxRanks; ++r)
-            if (r < a.size) in[r] = __ldcg(reinterpret_cast<const uint4 *>(data + r * kPeerSlotBytes) + v);
-#pragma unroll
-        for (uint32_t r = 0; r < kPeerMaxRanks; ++r)
-            if (r < a.size) accumulate<F32>(acc, in[r]);
-        uint4 out;
-        if constexpr (F32) {
-            out = make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]), __float_as_uint(acc[2]), __float_as_uint(acc[3]));
-        } else {
-            uint32_t w[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const __nv_bfloat162 p = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-                w[i] = *reinterpret_cast<const uint32_t *>(&p);
+            if (!got) {
+                atomicOr(a.error_word, 0x100u);
+                return;  // no barrier follows: a thread may leave alone
             }
-            out = make_uint4(w[0], w[1], w[2], w[3]);
+            acc += __uint_as_float(static_cast<uint32_t>(word));
         }
-        buf[v] = out;
+        if constexpr (F32)
+            static_cast<float *>(buf)[i] = acc;
+        else
+            static_cast<__nv_bfloat16 *>(buf)[i] = __float2bfloat16_rn(acc);
     }
 }
 
@@ -161,16 +114,15 @@ size_t peer_region_bytes() { return kPeerRegionBytes; }
 
 cudaError_t peer_allreduce(const PeerComm &pc, void *d_buf, size_t count, bool f32, bool pdl, cudaStream_t stream,
                            unsigned int *d_error_word) {
-    const size_t bytes = count * (f32 ? 4u : 2u);
-    if (!pc.ok || bytes == 0 || bytes > kPeerSlotBytes || bytes % 16u != 0 ||
-        reinterpret_cast<uintptr_t>(d_buf) % 16u != 0)
+    // one 64-bit word per element in a slot
+    if (!pc.ok || count == 0 || count * 8u > kPeerSlotBytes || reinterpret_cast<uintptr_t>(d_buf) % (f32 ? 4u : 2u) != 0)
         return cudaErrorNotSupported;
     PeerArgs a;
     for (int r = 0; r < kPeerMaxRanks; ++r) a.region[r] = static_cast<uint8_t *>(pc.region[r]);
     a.rank = pc.rank;
     a.size = pc.size;
     a.error_word = d_error_word;
-    const uint32_t nvec = static_cast<uint32_t>(bytes / 16u);
+    const uint32_t n = static_cast<uint32_t>(count);
     // always the full grid: every CTA's epoch advances on every call, on every rank
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(kPeerCtas);
@@ -182,9 +134,8 @@ cudaError_t peer_allreduce(const PeerComm &pc, void *d_buf, size_t count, bool f
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    uint4 *vbuf = static_cast<uint4 *>(d_buf);
-    if (f32) return cudaLaunchKernelEx(&cfg, peer_allreduce_kernel<true>, a, vbuf, nvec);
-    return cudaLaunchKernelEx(&cfg, peer_allreduce_kernel<false>, a, vbuf, nvec);
+    if (f32) return cudaLaunchKernelEx(&cfg, peer_allreduce_kernel<true>, a, d_buf, n);
+    return cudaLaunchKernelEx(&cfg, peer_allreduce_kernel<false>, a, d_buf, n);
 }
 
 }  // namespace tgaf

@@ -73,7 +73,7 @@ def _check_fused(ctx, torch, dist, rank, world, stream, ws, xs):
                     raise RuntimeError(f"rank {rank}: fused {name} is not bit-identical to rank 0's")
 
 
-def measure(args, existing_ctx=None, existing_stream=None):
+def measure(args, existing_ctx=None, existing_stream=None, M=1):
     """Runs the stack on this rank (all ranks call it together) and returns (ms per step over ranks,
     whole-job bytes per step, launches per rank, layers, world)."""
     import torch
@@ -112,7 +112,6 @@ def measure(args, existing_ctx=None, existing_stream=None):
         note(f"all-reduce checked (peer memory: {ctx.uses_peer_memory()})")
 
     layers = args.layers if args.layers != 12 else 4          # distinct layers in the ring (1.9 GB over all ranks)
-    M = 1
     rng = np.random.default_rng(1234)                          # same seed on every rank: same full weights
     ws = []
     for _ in range(layers):
