@@ -66,5 +66,34 @@ def build(force: bool = False, verbose_ptxas: bool = False) -> Path:
     return LIB
 
 
+SIDELOAD_SRC = CSRC / "sideload" / "talu_kernels_sm100.cu"
+SIDELOAD_DIR = PKG / "sideload"
+SIDELOAD_ARCH = "sm_100"   # talu's arch tag for B200: "sm_{major}{minor}" (core/src/compute/cuda/sideload.zig:46-49)
+# op name -> symbol, as talu's wrappers name them (core/src/compute/cuda/gaffine_u4_matvec.zig:12-13)
+SIDELOAD_KERNELS = [("gaffine_u4_matvec_f32", "talu_gaffine_u4_matvec_f32")]
+
+
+def build_sideload(force: bool = False) -> tuple[Path, Path]:
+    """kernels_sm_100.cubin + manifest_sm_100.json, the pair talu's registry picks up from
+    $TALU_CUDA_CACHE_DIR (core/src/compute/cuda/sideload.zig:24-44, manifest.zig:5-29): the manifest carries the
+    SHA-256 talu verifies before cuModuleLoadData (sideload.zig:78-122)."""
+    import hashlib
+    import json
+    SIDELOAD_DIR.mkdir(parents=True, exist_ok=True)
+    cubin = SIDELOAD_DIR / f"kernels_{SIDELOAD_ARCH}.cubin"
+    manifest = SIDELOAD_DIR / f"manifest_{SIDELOAD_ARCH}.json"
+    if force or not cubin.exists() or cubin.stat().st_mtime < SIDELOAD_SRC.stat().st_mtime:
+        cmd = [NVCC, *ARCH, "-O3", "-std=c++17", "-lineinfo", "-cubin", str(SIDELOAD_SRC), "-o", str(cubin)]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {SIDELOAD_SRC.name}:\n{r.stdout}\n{r.stderr}")
+    digest = hashlib.sha256(cubin.read_bytes()).hexdigest()
+    doc = {"schema_version": 1, "kernel_abi_version": 1, "arch": SIDELOAD_ARCH, "driver_min": "570.00", "sha256": digest,
+           "kernels": [{"op": op, "symbol": sym} for op, sym in SIDELOAD_KERNELS]}
+    manifest.write_text(json.dumps(doc, indent=2) + "\n")
+    return cubin, manifest
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose_ptxas="-v" in sys.argv))
+    print(*build_sideload(force="--force" in sys.argv))
