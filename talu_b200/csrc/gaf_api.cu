@@ -247,7 +247,7 @@ int32_t linear_device(tgaf_ctx *ctx, const WeightView &w, const void *x, uint32_
     return reduce ? allreduce_device(ctx, y, static_cast<uint64_t>(M) * w.N, f32 ? TGAF_DTYPE_F32 : TGAF_DTYPE_BF16) : TGAF_OK;
 }
 
-int32_t linear_host(tgaf_ctx *ctx, const tgaf_weight *w, const void *xh, uint32_t M, void *yh, bool f32) {
+int32_t linear_host(tgaf_ctx *ctx, const tgaf_weight *w, const void *xh, uint32_t M, void *yh, bool f32, bool wait = true) {
     if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
     if (!w || !xh || !yh || M == 0) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null pointer or M == 0");
     const size_t elt = f32 ? 4 : 2;
@@ -260,7 +260,7 @@ int32_t linear_host(tgaf_ctx *ctx, const tgaf_weight *w, const void *xh, uint32_
     st = linear_device(ctx, w->v, ctx->stage_x, M, ctx->stage_y, f32);
     if (st != TGAF_OK) return st;
     TGAF_CUDA(ctx, cudaMemcpyAsync(yh, ctx->stage_y, yb, cudaMemcpyDeviceToHost, ctx->stream));
-    TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (wait) TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return TGAF_OK;
 }
 
@@ -746,6 +746,11 @@ int32_t tgaf_linear_bf16_fixed_scratch(tgaf_ctx *ctx, const tgaf_weight *w, cons
 int32_t tgaf_linear_bf16_host(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16_host, uint32_t M,
                               void *y_bf16_host) {
     return linear_host(ctx, w, x_bf16_host, M, y_bf16_host, false);
+}
+
+int32_t tgaf_linear_bf16_host_async(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16_host, uint32_t M,
+                                    void *y_bf16_host) {
+    return linear_host(ctx, w, x_bf16_host, M, y_bf16_host, false, false);
 }
 
 int32_t tgaf_linear_f32_host(tgaf_ctx *ctx, const tgaf_weight *w, const float *x_host, uint32_t M, float *y_host) {

@@ -238,15 +238,18 @@ def linear_fixed_scratch(ctx: Context, w: Weight, x, out=None):
     return out
 
 
-def linear_host(ctx: Context, w: Weight, x: np.ndarray, out: np.ndarray | None = None) -> np.ndarray:
-    """Same through host buffers: x uint16 (bf16 bit patterns) or float32 [M, K]."""
+def linear_host(ctx: Context, w: Weight, x: np.ndarray, out: np.ndarray | None = None, wait: bool = True) -> np.ndarray:
+    """Same through host buffers: x uint16 (bf16 bit patterns) or float32 [M, K].  wait=False (bf16 only,
+    page-locked buffers) only enqueues: `out` is valid after ctx.synchronize()."""
     x = np.ascontiguousarray(x)
     if x.ndim != 2 or x.shape[1] != w.K:
         raise GafError(_STATUS_INVALID_ARGUMENT, f"x must be [M, {w.K}], got {x.shape}")
     M = x.shape[0]
     if out is None:
         out = np.empty((M, w.N), x.dtype)
-    if x.dtype == np.uint16:
+    if x.dtype == np.uint16 and not wait:
+        st = ctx._lib.tgaf_linear_bf16_host_async(ctx._h, w._h, x.ctypes.data, M, out.ctypes.data)
+    elif x.dtype == np.uint16:
         st = ctx._lib.tgaf_linear_bf16_host(ctx._h, w._h, x.ctypes.data, M, out.ctypes.data)
     elif x.dtype == np.float32:
         st = ctx._lib.tgaf_linear_f32_host(ctx._h, w._h, x.ctypes.data, M, out.ctypes.data)

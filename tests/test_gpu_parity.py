@@ -177,6 +177,32 @@ def test_host_entry_point_equals_device_entry_point(gaf, ctx, oracle):
     assert rel_err(yh, ref) <= TOL_BF16
 
 
+def test_queued_host_calls_equal_waited_ones(gaf, ctx, oracle):
+    """tgaf_linear_bf16_host_async: several calls queued on page-locked buffers, one wait, same bits as the
+    call that waits (the staging buffers are shared between the queued calls in stream order)."""
+    import torch
+    ws, xs, want = [], [], []
+    for i, (N, K, M) in enumerate([(1000, 2048, 1), (384, 1024, 3), (2048, 512, 16)]):
+        p, s, b = make_weights(oracle, N, K, 64, 4, seed=60 + i)
+        w = gaf.Weight.from_host(ctx, p, s, b, 64, 4)
+        xb, _ = make_x_bf16(oracle, M, K, 70 + i)
+        want.append(gaf.linear_host(ctx, w, xb).copy())
+        ws.append(w)
+        xs.append(xb)
+    pinned_x = [torch.from_numpy(x.view(np.int16)).pin_memory() for x in xs]
+    pinned_y = [torch.empty((x.shape[0], w.N), dtype=torch.int16).pin_memory() for x, w in zip(xs, ws)]
+    for rep in range(2):
+        for y in pinned_y:
+            y.zero_()
+        for w, x, y in zip(ws, pinned_x, pinned_y):
+            gaf.linear_host(ctx, w, x.numpy().view(np.uint16), out=y.numpy().view(np.uint16), wait=False)
+        ctx.synchronize()
+        for y, ref in zip(pinned_y, want):
+            assert np.array_equal(y.numpy().view(np.uint16), ref), rep
+    for w in ws:
+        w.free()
+
+
 def test_split_k_is_deterministic_and_tunable(gaf, ctx, oracle):
     """Any number of persistent CTAs (hence any cut of row groups across CTAs) agrees
     within tolerance, and a given cut gives the same bits on every run (partials are
