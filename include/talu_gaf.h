@@ -151,10 +151,11 @@ int32_t tgaf_linear_bf16_host(tgaf_ctx *ctx, const tgaf_weight *w, const void *x
                               uint32_t M, void *y_bf16_host);
 int32_t tgaf_linear_f32_host(tgaf_ctx *ctx, const tgaf_weight *w, const float *x_host,
                              uint32_t M, float *y_host);
-/* The same without the wait: the copies and the kernel are enqueued on the context's stream and the call
- * returns.  Several calls may be queued back to back (they share the context's staging buffers, which is safe
- * in stream order); y_host is valid, and x_host may be changed, after tgaf_synchronize.  Use page-locked host
- * memory, or the copies are not asynchronous. */
+/* The same without the wait: the call returns once everything is enqueued.  Several calls may be queued back
+ * to back; the copies run on the context's own copy streams around the kernels (a ring of four staging
+ * buffers, ordered by events), so x of the next call and y of the previous one travel while a kernel runs.
+ * y_host is valid, and x_host may be changed, after tgaf_synchronize.  Use page-locked host memory, or the
+ * copies are not asynchronous.  Do not capture these calls into a CUDA graph. */
 int32_t tgaf_linear_bf16_host_async(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16_host,
                                     uint32_t M, void *y_bf16_host);
 

@@ -85,6 +85,17 @@ struct tgaf_ctx {
     void *stage_y = nullptr;
     size_t stage_y_bytes = 0;
     unsigned int *d_error_word = nullptr;
+    // queued host-buffer calls: copies run on their own streams around the kernels, over a small ring of
+    // staging buffers (tgaf_linear_bf16_host_async)
+    static constexpr int kPipe = 4;
+    cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
+    void *pipe_x[kPipe] = {nullptr, nullptr, nullptr, nullptr};
+    void *pipe_y[kPipe] = {nullptr, nullptr, nullptr, nullptr};
+    size_t pipe_x_bytes[kPipe] = {0, 0, 0, 0}, pipe_y_bytes[kPipe] = {0, 0, 0, 0};
+    cudaEvent_t ev_x_ready[kPipe] = {nullptr, nullptr, nullptr, nullptr};
+    cudaEvent_t ev_k_done[kPipe] = {nullptr, nullptr, nullptr, nullptr};
+    cudaEvent_t ev_y_done[kPipe] = {nullptr, nullptr, nullptr, nullptr};
+    uint64_t pipe_calls = 0;
     // FFN operator: intermediate activations and the two-operation kernel's arrival counters
     void *ffn_mid = nullptr;
     size_t ffn_mid_bytes = 0;
@@ -477,6 +488,15 @@ int32_t tgaf_ctx_destroy(tgaf_ctx *ctx) {
     if (ctx->stage_x) cudaFree(ctx->stage_x);
     if (ctx->stage_y) cudaFree(ctx->stage_y);
     if (ctx->d_error_word) cudaFree(ctx->d_error_word);
+    for (int i = 0; i < tgaf_ctx::kPipe; ++i) {
+        if (ctx->pipe_x[i]) cudaFree(ctx->pipe_x[i]);
+        if (ctx->pipe_y[i]) cudaFree(ctx->pipe_y[i]);
+        if (ctx->ev_x_ready[i]) cudaEventDestroy(ctx->ev_x_ready[i]);
+        if (ctx->ev_k_done[i]) cudaEventDestroy(ctx->ev_k_done[i]);
+        if (ctx->ev_y_done[i]) cudaEventDestroy(ctx->ev_y_done[i]);
+    }
+    if (ctx->h2d_stream) cudaStreamDestroy(ctx->h2d_stream);
+    if (ctx->d2h_stream) cudaStreamDestroy(ctx->d2h_stream);
     if (ctx->ffn_mid) cudaFree(ctx->ffn_mid);
     if (ctx->d_grid_bar) cudaFree(ctx->d_grid_bar);
     if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
@@ -497,6 +517,10 @@ int32_t tgaf_ctx_set_stream(tgaf_ctx *ctx, void *stream) {
 int32_t tgaf_synchronize(tgaf_ctx *ctx) {
     if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
     TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->d2h_stream) {  // queued host-buffer calls: their last copies run on the copy streams
+        TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->h2d_stream));
+        TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->d2h_stream));
+    }
     unsigned int flag = 0;
     TGAF_CUDA(ctx, cudaMemcpy(&flag, ctx->d_error_word, sizeof flag, cudaMemcpyDeviceToHost));
     if (flag != 0) {
@@ -750,7 +774,57 @@ int32_t tgaf_linear_bf16_host(tgaf_ctx *ctx, const tgaf_weight *w, const void *x
 
 int32_t tgaf_linear_bf16_host_async(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16_host, uint32_t M,
                                     void *y_bf16_host) {
-    return linear_host(ctx, w, x_bf16_host, M, y_bf16_host, false, false);
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!w || !x_bf16_host || !y_bf16_host || M == 0) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null pointer or M == 0");
+    cudaSetDevice(ctx->device);
+    if (!ctx->h2d_stream) {
+        TGAF_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->h2d_stream, cudaStreamNonBlocking));
+        TGAF_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->d2h_stream, cudaStreamNonBlocking));
+        for (int i = 0; i < tgaf_ctx::kPipe; ++i) {
+            TGAF_CUDA(ctx, cudaEventCreateWithFlags(&ctx->ev_x_ready[i], cudaEventDisableTiming));
+            TGAF_CUDA(ctx, cudaEventCreateWithFlags(&ctx->ev_k_done[i], cudaEventDisableTiming));
+            TGAF_CUDA(ctx, cudaEventCreateWithFlags(&ctx->ev_y_done[i], cudaEventDisableTiming));
+        }
+    }
+    const int slot = static_cast<int>(ctx->pipe_calls % tgaf_ctx::kPipe);
+    const bool reused = ctx->pipe_calls >= static_cast<uint64_t>(tgaf_ctx::kPipe);
+    const size_t xb = static_cast<size_t>(M) * w->v.K * 2u, yb = static_cast<size_t>(M) * w->v.N * 2u;
+    if (xb > ctx->pipe_x_bytes[slot] || yb > ctx->pipe_y_bytes[slot]) {
+        // growing a staging buffer: nothing may still be using the old one
+        TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->h2d_stream));
+        TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->d2h_stream));
+        if (xb > ctx->pipe_x_bytes[slot]) {
+            if (ctx->pipe_x[slot]) cudaFree(ctx->pipe_x[slot]);
+            ctx->pipe_x[slot] = nullptr, ctx->pipe_x_bytes[slot] = 0;
+            const size_t want = xb < (size_t(256) << 10) ? (size_t(256) << 10) : xb;
+            TGAF_CUDA(ctx, cudaMalloc(&ctx->pipe_x[slot], want));
+            ctx->pipe_x_bytes[slot] = want;
+        }
+        if (yb > ctx->pipe_y_bytes[slot]) {
+            if (ctx->pipe_y[slot]) cudaFree(ctx->pipe_y[slot]);
+            ctx->pipe_y[slot] = nullptr, ctx->pipe_y_bytes[slot] = 0;
+            const size_t want = yb < (size_t(256) << 10) ? (size_t(256) << 10) : yb;
+            TGAF_CUDA(ctx, cudaMalloc(&ctx->pipe_y[slot], want));
+            ctx->pipe_y_bytes[slot] = want;
+        }
+    }
+    // x: host -> slot, once the kernel that last read this slot is done
+    if (reused) TGAF_CUDA(ctx, cudaStreamWaitEvent(ctx->h2d_stream, ctx->ev_k_done[slot], 0));
+    TGAF_CUDA(ctx, cudaMemcpyAsync(ctx->pipe_x[slot], x_bf16_host, xb, cudaMemcpyHostToDevice, ctx->h2d_stream));
+    TGAF_CUDA(ctx, cudaEventRecord(ctx->ev_x_ready[slot], ctx->h2d_stream));
+    // kernel: after x has landed and the slot's previous y has left
+    TGAF_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_x_ready[slot], 0));
+    if (reused) TGAF_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->ev_y_done[slot], 0));
+    int32_t st = linear_device(ctx, w->v, ctx->pipe_x[slot], M, ctx->pipe_y[slot], false);
+    if (st != TGAF_OK) return st;
+    TGAF_CUDA(ctx, cudaEventRecord(ctx->ev_k_done[slot], ctx->stream));
+    // y: slot -> host
+    TGAF_CUDA(ctx, cudaStreamWaitEvent(ctx->d2h_stream, ctx->ev_k_done[slot], 0));
+    TGAF_CUDA(ctx, cudaMemcpyAsync(y_bf16_host, ctx->pipe_y[slot], yb, cudaMemcpyDeviceToHost, ctx->d2h_stream));
+    TGAF_CUDA(ctx, cudaEventRecord(ctx->ev_y_done[slot], ctx->d2h_stream));
+    ++ctx->pipe_calls;
+    return TGAF_OK;
 }
 
 int32_t tgaf_linear_f32_host(tgaf_ctx *ctx, const tgaf_weight *w, const float *x_host, uint32_t M, float *y_host) {
