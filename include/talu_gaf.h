@@ -158,6 +158,11 @@ int32_t tgaf_linear_f32_host(tgaf_ctx *ctx, const tgaf_weight *w, const float *x
  * copies are not asynchronous.  Do not capture these calls into a CUDA graph. */
 int32_t tgaf_linear_bf16_host_async(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16_host,
                                     uint32_t M, void *y_bf16_host);
+/* `count` such calls in list order with one crossing of the ABI (the list is the layer order, so each launch
+ * is also given the following weight as its next-weight hint).  Stops at the first error. */
+int32_t tgaf_linear_bf16_host_async_batch(tgaf_ctx *ctx, uint32_t count, const tgaf_weight *const *weights,
+                                          const void *const *xs_bf16_host, const uint32_t *ms,
+                                          void *const *ys_bf16_host);
 
 /* Raw-pointer launch with the argument list of the reference's kernel wrapper
  * compute.cuda.gaffine_u4_matvec.runWithFunction

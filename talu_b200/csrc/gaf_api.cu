@@ -827,6 +827,20 @@ int32_t tgaf_linear_bf16_host_async(tgaf_ctx *ctx, const tgaf_weight *w, const v
     return TGAF_OK;
 }
 
+int32_t tgaf_linear_bf16_host_async_batch(tgaf_ctx *ctx, uint32_t count, const tgaf_weight *const *weights,
+                                          const void *const *xs_bf16_host, const uint32_t *ms, void *const *ys_bf16_host) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (count == 0) return TGAF_OK;
+    if (!weights || !xs_bf16_host || !ms || !ys_bf16_host) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null array");
+    for (uint32_t i = 0; i < count; ++i) {
+        // the list is the layer order: each launch also warms L2 with the head of the following weight
+        if (i + 1u < count && weights[i + 1u]) ctx->tune.next = &weights[i + 1u]->v;
+        const int32_t st = tgaf_linear_bf16_host_async(ctx, weights[i], xs_bf16_host[i], ms[i], ys_bf16_host[i]);
+        if (st != TGAF_OK) return st;
+    }
+    return TGAF_OK;
+}
+
 int32_t tgaf_linear_f32_host(tgaf_ctx *ctx, const tgaf_weight *w, const float *x_host, uint32_t M, float *y_host) {
     return linear_host(ctx, w, x_host, M, y_host, true);
 }

@@ -259,6 +259,31 @@ def linear_host(ctx: Context, w: Weight, x: np.ndarray, out: np.ndarray | None =
     return out
 
 
+class HostBatch:
+    """A fixed list of (weight, x, out) host-buffer calls, submitted with one crossing of the C ABI
+    (tgaf_linear_bf16_host_async_batch).  x / out: uint16 arrays (bf16 bit patterns) in page-locked memory; they
+    are read / written when `submit` runs on the GPU, so refill x and read out between ctx.synchronize() calls."""
+
+    def __init__(self, ctx: Context, weights, xs, outs):
+        n = len(weights)
+        if not (len(xs) == len(outs) == n):
+            raise GafError(_STATUS_INVALID_ARGUMENT, "weights, xs and outs must have one entry per call")
+        for w, x, o in zip(weights, xs, outs):
+            if x.dtype != np.uint16 or o.dtype != np.uint16 or x.ndim != 2 or x.shape[1] != w.K or o.shape != (x.shape[0], w.N):
+                raise GafError(_STATUS_INVALID_ARGUMENT, "x must be uint16 [M, K] and out uint16 [M, N]")
+            if not (x.flags.c_contiguous and o.flags.c_contiguous):
+                raise GafError(_STATUS_INVALID_ARGUMENT, "buffers must be contiguous")
+        self.ctx, self.n = ctx, n
+        self._keep = (list(weights), list(xs), list(outs))
+        self._w = (C.c_void_p * n)(*[w._h.value if isinstance(w._h, C.c_void_p) else w._h for w in weights])
+        self._x = (C.c_void_p * n)(*[x.ctypes.data for x in xs])
+        self._y = (C.c_void_p * n)(*[o.ctypes.data for o in outs])
+        self._m = (C.c_uint32 * n)(*[x.shape[0] for x in xs])
+
+    def submit(self) -> None:
+        self.ctx._check(self.ctx._lib.tgaf_linear_bf16_host_async_batch(self.ctx._h, self.n, self._w, self._x, self._m, self._y))
+
+
 def dequant_f32(ctx: Context, w: Weight):
     import torch
     out = torch.empty((w.N, w.K), dtype=torch.float32, device=f"cuda:{ctx.device}")

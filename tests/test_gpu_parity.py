@@ -199,6 +199,15 @@ def test_queued_host_calls_equal_waited_ones(gaf, ctx, oracle):
         ctx.synchronize()
         for y, ref in zip(pinned_y, want):
             assert np.array_equal(y.numpy().view(np.uint16), ref), rep
+    # the same list through one crossing of the ABI
+    batch = gaf.HostBatch(ctx, ws, [x.numpy().view(np.uint16) for x in pinned_x], [y.numpy().view(np.uint16) for y in pinned_y])
+    for rep in range(3):
+        for y in pinned_y:
+            y.zero_()
+        batch.submit()
+        ctx.synchronize()
+        for y, ref in zip(pinned_y, want):
+            assert np.array_equal(y.numpy().view(np.uint16), ref), rep
     for w in ws:
         w.free()
 
