@@ -163,6 +163,17 @@ int32_t tgaf_linear_bf16_host_async(tgaf_ctx *ctx, const tgaf_weight *w, const v
 int32_t tgaf_linear_bf16_host_async_batch(tgaf_ctx *ctx, uint32_t count, const tgaf_weight *const *weights,
                                           const void *const *xs_bf16_host, const uint32_t *ms,
                                           void *const *ys_bf16_host);
+/* The same list recorded once (it is run once, then captured into a CUDA graph of its copies and kernels) and
+ * replayed with one call per step - the form a decoder with fixed page-locked I/O buffers wants: refill the x
+ * buffers, tgaf_host_batch_submit, tgaf_synchronize, read the y buffers.  The buffers, the weights and the
+ * context must outlive the batch; nothing else may be queued with tgaf_linear_bf16_host_async while a batch is
+ * in flight (they share the staging ring). */
+typedef struct tgaf_host_batch tgaf_host_batch;
+int32_t tgaf_host_batch_create(tgaf_ctx *ctx, uint32_t count, const tgaf_weight *const *weights,
+                               const void *const *xs_bf16_host, const uint32_t *ms, void *const *ys_bf16_host,
+                               tgaf_host_batch **out_batch);
+int32_t tgaf_host_batch_submit(tgaf_ctx *ctx, tgaf_host_batch *batch);
+int32_t tgaf_host_batch_destroy(tgaf_ctx *ctx, tgaf_host_batch *batch);
 
 /* Raw-pointer launch with the argument list of the reference's kernel wrapper
  * compute.cuda.gaffine_u4_matvec.runWithFunction

@@ -33,6 +33,9 @@ SIGNATURES = {
     "tgaf_linear_f32_host": (_i32, [_vp, _vp, _vp, _u32, _vp]),
     "tgaf_linear_bf16_host_async": (_i32, [_vp, _vp, _vp, _u32, _vp]),
     "tgaf_linear_bf16_host_async_batch": (_i32, [_vp, _u32, _vp, _vp, _vp, _vp]),
+    "tgaf_host_batch_create": (_i32, [_vp, _u32, _vp, _vp, _vp, _vp, C.POINTER(_vp)]),
+    "tgaf_host_batch_submit": (_i32, [_vp, _vp]),
+    "tgaf_host_batch_destroy": (_i32, [_vp, _vp]),
     "tgaf_gaffine_u4_matvec_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32]),
     "tgaf_gaffine_u8_matvec_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32]),
     "tgaf_dequant_f32": (_i32, [_vp, _vp, _vp]),

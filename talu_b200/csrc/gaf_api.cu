@@ -114,6 +114,13 @@ namespace {
 void peer_teardown(tgaf_ctx *ctx);
 }
 
+// A recorded list of queued host-buffer calls (tgaf_host_batch_*): the CUDA graph of their copies and kernels.
+struct tgaf_host_batch {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    uint32_t count = 0;
+};
+
 struct tgaf_weight {
     WeightView v;
     bool owns = false;
@@ -838,6 +845,82 @@ int32_t tgaf_linear_bf16_host_async_batch(tgaf_ctx *ctx, uint32_t count, const t
         const int32_t st = tgaf_linear_bf16_host_async(ctx, weights[i], xs_bf16_host[i], ms[i], ys_bf16_host[i]);
         if (st != TGAF_OK) return st;
     }
+    return TGAF_OK;
+}
+
+int32_t tgaf_host_batch_create(tgaf_ctx *ctx, uint32_t count, const tgaf_weight *const *weights,
+                               const void *const *xs_bf16_host, const uint32_t *ms, void *const *ys_bf16_host,
+                               tgaf_host_batch **out_batch) {
+    if (out_batch) *out_batch = nullptr;
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!out_batch || count == 0 || !weights || !xs_bf16_host || !ms || !ys_bf16_host)
+        return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null array or empty list");
+    cudaSetDevice(ctx->device);
+    // 1. once for real: every staging buffer, scratch area and kernel attribute the list needs exists afterwards
+    ctx->pipe_calls = 0;
+    int32_t st = tgaf_linear_bf16_host_async_batch(ctx, count, weights, xs_bf16_host, ms, ys_bf16_host);
+    if (st != TGAF_OK) return st;
+    st = tgaf_synchronize(ctx);
+    if (st != TGAF_OK) return st;
+    // 2. the same list into a graph; the copy streams join the capture through the events and are joined back
+    tgaf_host_batch *b = new (std::nothrow) tgaf_host_batch();
+    if (!b) return fail(ctx, TGAF_ERR_OUT_OF_MEMORY, "host batch");
+    b->count = count;
+    ctx->pipe_calls = 0;  // every replay starts on staging slot 0; replays run one after another on the stream
+    cudaError_t e = cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) {
+        delete b;
+        return cuda_fail(ctx, e, "cudaStreamBeginCapture");
+    }
+    // fork: the upload stream enters the capture by depending on the captured stream's start
+    e = cudaEventRecord(ctx->ev_y_done[tgaf_ctx::kPipe - 1], ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->h2d_stream, ctx->ev_y_done[tgaf_ctx::kPipe - 1], 0);
+    st = e == cudaSuccess ? tgaf_linear_bf16_host_async_batch(ctx, count, weights, xs_bf16_host, ms, ys_bf16_host) : TGAF_OK;
+    if (st == TGAF_OK && e == cudaSuccess) {
+        // join: the last copies of every staging slot
+        const uint32_t used = count < static_cast<uint32_t>(tgaf_ctx::kPipe) ? count : static_cast<uint32_t>(tgaf_ctx::kPipe);
+        for (uint32_t i = 0; i < used && e == cudaSuccess; ++i) e = cudaStreamWaitEvent(ctx->stream, ctx->ev_y_done[i], 0);
+        if (e == cudaSuccess) e = cudaEventRecord(ctx->ev_x_ready[0], ctx->h2d_stream);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->stream, ctx->ev_x_ready[0], 0);
+    }
+    cudaGraph_t graph = nullptr;
+    const cudaError_t e_end = cudaStreamEndCapture(ctx->stream, &graph);
+    ctx->pipe_calls = 0;
+    if (st != TGAF_OK || e != cudaSuccess || e_end != cudaSuccess || !graph) {
+        if (graph) cudaGraphDestroy(graph);
+        delete b;
+        cudaGetLastError();
+        if (st != TGAF_OK) return st;
+        return cuda_fail(ctx, e != cudaSuccess ? e : e_end, "capturing the host batch");
+    }
+    b->graph = graph;
+    e = cudaGraphInstantiate(&b->exec, graph, 0);
+    if (e != cudaSuccess) {
+        cudaGraphDestroy(graph);
+        delete b;
+        return cuda_fail(ctx, e, "cudaGraphInstantiate");
+    }
+    *out_batch = b;
+    return TGAF_OK;
+}
+
+int32_t tgaf_host_batch_submit(tgaf_ctx *ctx, tgaf_host_batch *batch) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!batch || !batch->exec) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null batch");
+    cudaSetDevice(ctx->device);
+    TGAF_CUDA(ctx, cudaGraphLaunch(batch->exec, ctx->stream));
+    return TGAF_OK;
+}
+
+int32_t tgaf_host_batch_destroy(tgaf_ctx *ctx, tgaf_host_batch *batch) {
+    if (!batch) return TGAF_OK;
+    if (ctx) {
+        cudaSetDevice(ctx->device);
+        cudaStreamSynchronize(ctx->stream);
+    }
+    if (batch->exec) cudaGraphExecDestroy(batch->exec);
+    if (batch->graph) cudaGraphDestroy(batch->graph);
+    delete batch;
     return TGAF_OK;
 }
 

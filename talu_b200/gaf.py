@@ -280,8 +280,31 @@ class HostBatch:
         self._y = (C.c_void_p * n)(*[o.ctypes.data for o in outs])
         self._m = (C.c_uint32 * n)(*[x.shape[0] for x in xs])
 
+        self._g = None
+
+    def record(self) -> "HostBatch":
+        """Runs the list once and records it as a CUDA graph (tgaf_host_batch_create); `submit` then replays it."""
+        h = C.c_void_p()
+        self.ctx._check(self.ctx._lib.tgaf_host_batch_create(self.ctx._h, self.n, self._w, self._x, self._m, self._y, C.byref(h)))
+        self._g = h
+        return self
+
     def submit(self) -> None:
-        self.ctx._check(self.ctx._lib.tgaf_linear_bf16_host_async_batch(self.ctx._h, self.n, self._w, self._x, self._m, self._y))
+        if self._g is not None:
+            self.ctx._check(self.ctx._lib.tgaf_host_batch_submit(self.ctx._h, self._g))
+        else:
+            self.ctx._check(self.ctx._lib.tgaf_linear_bf16_host_async_batch(self.ctx._h, self.n, self._w, self._x, self._m, self._y))
+
+    def close(self) -> None:
+        if self._g is not None and getattr(self.ctx, "_h", None):
+            self.ctx._lib.tgaf_host_batch_destroy(self.ctx._h, self._g)
+        self._g = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 def dequant_f32(ctx: Context, w: Weight):

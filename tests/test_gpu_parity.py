@@ -208,6 +208,16 @@ def test_queued_host_calls_equal_waited_ones(gaf, ctx, oracle):
         ctx.synchronize()
         for y, ref in zip(pinned_y, want):
             assert np.array_equal(y.numpy().view(np.uint16), ref), rep
+    # ... and recorded once, replayed per step
+    batch.record()
+    for rep in range(3):
+        for y in pinned_y:
+            y.zero_()
+        batch.submit()
+        ctx.synchronize()
+        for y, ref in zip(pinned_y, want):
+            assert np.array_equal(y.numpy().view(np.uint16), ref), rep
+    batch.close()
     for w in ws:
         w.free()
 
