@@ -856,6 +856,8 @@ int32_t tgaf_host_batch_create(tgaf_ctx *ctx, uint32_t count, const tgaf_weight 
     if (!out_batch || count == 0 || !weights || !xs_bf16_host || !ms || !ys_bf16_host)
         return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null array or empty list");
     cudaSetDevice(ctx->device);
+    if (ctx->stream == cudaStreamLegacy || ctx->stream == cudaStreamPerThread || ctx->stream == nullptr)
+        return fail(ctx, TGAF_ERR_UNSUPPORTED, "recording needs a context on a stream of its own (the default streams cannot be captured)");
     // 1. once for real: every staging buffer, scratch area and kernel attribute the list needs exists afterwards
     ctx->pipe_calls = 0;
     int32_t st = tgaf_linear_bf16_host_async_batch(ctx, count, weights, xs_bf16_host, ms, ys_bf16_host);

@@ -208,16 +208,24 @@ def test_queued_host_calls_equal_waited_ones(gaf, ctx, oracle):
         ctx.synchronize()
         for y, ref in zip(pinned_y, want):
             assert np.array_equal(y.numpy().view(np.uint16), ref), rep
-    # ... and recorded once, replayed per step
-    batch.record()
-    for rep in range(3):
-        for y in pinned_y:
-            y.zero_()
-        batch.submit()
-        ctx.synchronize()
-        for y, ref in zip(pinned_y, want):
-            assert np.array_equal(y.numpy().view(np.uint16), ref), rep
-    batch.close()
+    # ... and recorded once, replayed per step: needs a context on a stream of its own
+    with pytest.raises(gaf.GafError):
+        batch.record()                      # this context runs on torch's default stream
+    stream = torch.cuda.Stream()
+    ctx2 = gaf.Context(0, stream=stream.cuda_stream)
+    try:
+        batch2 = gaf.HostBatch(ctx2, ws, [x.numpy().view(np.uint16) for x in pinned_x],
+                               [y.numpy().view(np.uint16) for y in pinned_y]).record()
+        for rep in range(3):
+            for y in pinned_y:
+                y.zero_()
+            batch2.submit()
+            ctx2.synchronize()
+            for y, ref in zip(pinned_y, want):
+                assert np.array_equal(y.numpy().view(np.uint16), ref), rep
+        batch2.close()
+    finally:
+        ctx2.close()
     for w in ws:
         w.free()
 
