@@ -267,7 +267,7 @@ def run_single(args):
     results = {}
     clocks = ClockSampler(dev)
     with clocks:
-        for M in ((1,) if args.quick else (1, 4, 16)):
+        for M in ((1,) if args.quick else (1, 2, 4, 8, 16)):
             xs, ys = make_io(M)
 
             def step():

@@ -234,8 +234,9 @@ int32_t linear_device(tgaf_ctx *ctx, const WeightView &w, const void *x, uint32_
 
     if (!ctx->tune.force_generic && gemv_mma_eligible(w, x, y, f32)) {
         // rows in chunks of 16; each chunk streams the weights once
-        for (uint32_t m0 = 0; m0 < M; m0 += 16u) {
-            const uint32_t mc = (M - m0) < 16u ? (M - m0) : 16u;
+        const uint32_t step = gemv_mma_max_rows(w, f32);
+        for (uint32_t m0 = 0; m0 < M; m0 += step) {
+            const uint32_t mc = (M - m0) < step ? (M - m0) : step;
             const size_t need = gemv_mma_scratch_bytes(w, mc, ctx->tune, ctx->sm_count);
             int32_t st = ensure_scratch(ctx, need, gemv_mma_counter_count(w),
                                         gemv_tagged_bytes(w, mc, f32, ctx->tune, ctx->sm_count));
@@ -243,7 +244,7 @@ int32_t linear_device(tgaf_ctx *ctx, const WeightView &w, const void *x, uint32_
             const void *xp = static_cast<const uint8_t *>(x) + static_cast<size_t>(m0) * w.K * elt;
             void *yp = static_cast<uint8_t *>(y) + static_cast<size_t>(m0) * w.N * elt;
             GemvTuning t = ctx->tune;
-            t.next = m0 + 16u >= M ? hint : nullptr;  // the last chunk is the one the next launch follows
+            t.next = m0 + step >= M ? hint : nullptr;  // the last chunk is the one the next launch follows
             t.fuse = nullptr;
             if (reduce && M <= 16u && ctx->peer.ok && ctx->fused_allreduce) {
                 t.fuse = &ctx->peer;

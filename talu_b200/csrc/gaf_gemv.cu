@@ -323,7 +323,9 @@ template <int GB, int MT, bool XF32>
 struct SmemPlan {
     static constexpr int NF = XF32 ? 2 : 1;
     static constexpr int UNIT_FRAG_MAX = kFragItems * MT * NF * 512;            // one unit's fragments, 8 rows per tile
-    static constexpr int FRAG_BUF = UNIT_FRAG_MAX > 16384 ? UNIT_FRAG_MAX : 16384;  // one block of units
+    // one block of units: at least two (32-element groups with two tiles have room for one)
+    static constexpr int FRAG_MIN = (GB == 16 && MT == 2) ? 16384 : 32768;
+    static constexpr int FRAG_BUF = UNIT_FRAG_MAX > FRAG_MIN ? UNIT_FRAG_MAX : FRAG_MIN;
     static constexpr int XS_UNIT = (kChunkBytes / GB) * MT * 8 * 4;             // group sums of one unit
     static constexpr int XS_BUF = kMaxBlockUnits * XS_UNIT;
     static constexpr int OUT_BUF = 2 * kRowBlocks * 32 * MT * 4 * 4;           // both K halves of one row group
@@ -1847,6 +1849,7 @@ cudaError_t launch_stream(const GemvParams &p, const WeightView &w, const Weight
                           cudaStream_t stream) {
     auto kern = gaf_gemv_stream_kernel<GB, BITS, MT, XF32, SD>;
     using Plan = SmemPlan<GB, MT, XF32>;
+    if constexpr (Plan::TOTAL > 227 * 1024) return cudaErrorNotSupported;  // see gemv_mma_max_rows
     static bool configured = false;  // per instantiation; the attribute belongs to the function, not the stream
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::TOTAL);
@@ -2051,6 +2054,12 @@ size_t gemv_tagged_bytes(const WeightView &w, uint32_t M, bool x_f32, const Gemv
     return static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * (M <= 2u ? M : 4u) * 8u;
 }
 
+// Activation rows one launch of the fast path takes: 16, except where two tiles do not fit in shared memory
+// (4-bit codes in groups of 32 with fp32 activations: hi + lo fragments double the block).
+uint32_t gemv_mma_max_rows(const WeightView &w, bool x_f32) {
+    return (w.bits == 4u && w.group == 32u && x_f32) ? 8u : 16u;
+}
+
 size_t gemv_mma_counter_count(const WeightView &w) {
     return static_cast<size_t>((w.N + kRows - 1u) / kRows);
 }
@@ -2083,7 +2092,7 @@ static GemvParams base_params(const WeightView &w, const void *x, void *y, uint3
 cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bool x_f32,
                      const Scratch &scratch, const GemvTuning &tune, cudaStream_t stream, int sm_count,
                      unsigned int *d_error_word) {
-    if (M == 0 || M > 16u) return cudaErrorNotSupported;
+    if (M == 0 || M > gemv_mma_max_rows(w, x_f32)) return cudaErrorNotSupported;
     if (!gemv_mma_eligible(w, x, y, x_f32)) return cudaErrorNotSupported;
     const GemvPlan pl = plan_gemv(w, tune, sm_count);
     const int mt = M <= 8u ? 1 : 2;

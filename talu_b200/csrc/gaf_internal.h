@@ -77,6 +77,7 @@ cudaError_t swiglu_bf16(const void *gate_up, void *h, uint32_t M, uint32_t d_ff,
 bool gemv_fused_eligible(const WeightView &w, uint32_t M, bool x_f32, const GemvTuning &tune);
 size_t gemv_mma_scratch_bytes(const WeightView &w, uint32_t M, const GemvTuning &tune, int sm_count);
 size_t gemv_mma_counter_count(const WeightView &w);
+uint32_t gemv_mma_max_rows(const WeightView &w, bool x_f32);
 // bytes of Scratch::tagged the M <= 4 kernel needs for this weight (0 when that kernel does not apply)
 size_t gemv_tagged_bytes(const WeightView &w, uint32_t M, bool x_f32, const GemvTuning &tune, int sm_count);
 

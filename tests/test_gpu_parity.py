@@ -144,7 +144,8 @@ def test_ragged_shapes(gaf, ctx, oracle, M):
 def test_f32_contract(gaf, ctx, oracle):
     """The reference's f32-in / f32-out contract, tolerance 1e-3 (its policy for f32 matmul)."""
     import torch
-    for bits, G, N, K, M in [(4, 64, 1024, 2048, 1), (4, 32, 515, 1024, 7), (8, 64, 512, 1024, 16), (4, 128, 256, 4096, 12)]:
+    for bits, G, N, K, M in [(4, 64, 1024, 2048, 1), (4, 32, 515, 1024, 7), (8, 64, 512, 1024, 16), (4, 128, 256, 4096, 12),
+                             (4, 32, 300, 1024, 12), (4, 32, 300, 1024, 16)]:
         p, s, b = make_weights(oracle, N, K, G, bits, seed=G + M)
         x = np.random.default_rng(M).standard_normal((M, K), dtype=np.float32)
         w = gaf.Weight.from_host(ctx, p, s, b, G, bits)
