@@ -618,6 +618,10 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
     const uint32_t unit_frag_bytes = kFragItems * MT * NF * item_bytes;   // one unit
     uint32_t block_units = Plan::FRAG_BUF / unit_frag_bytes;              // units prepared together
     if (block_units > static_cast<uint32_t>(kMaxBlockUnits)) block_units = kMaxBlockUnits;
+    // When the fragments of a whole row of K fit the two buffers taken together, they are built once, in the
+    // order this CTA meets the K chunks, and every later row group reuses them: no rebuild, no CTA barrier.
+    const bool whole_k = p.chunks <= static_cast<uint32_t>(kMaxBlockUnits) && p.chunks * unit_frag_bytes <= 2u * Plan::FRAG_BUF;
+    const uint32_t block_len = whole_k ? p.chunks : block_units;
     const bool has_x = g < mg;
 
     // shared-memory offsets of this lane's pieces of a panel row, one per group of the panel
@@ -696,7 +700,7 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
     asm volatile("griddepcontrol.wait;" ::: "memory");
     {
         const uint32_t total = u_end - u_begin;
-        prep_block(kc_begin, total < block_units ? total : block_units, 0u);
+        prep_block(kc_begin, total < block_len ? total : block_len, 0u);
     }
     consumer_barrier();
 
@@ -826,9 +830,9 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
         }
 
         // ---- end of a fragment block: build the next one in the other buffer, then everybody meets ----
-        if (++ub == block_units) {
+        if (++ub == block_len) {
             ub = 0u;
-            if (more) {
+            if (more && !whole_k) {
                 const uint32_t left = u_end - (u + 1u);
                 prep_block(kc_n, left < block_units ? left : block_units, buf ^ 1u);
                 consumer_barrier();
