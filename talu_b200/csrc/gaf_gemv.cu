@@ -487,6 +487,7 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
         asm volatile("griddepcontrol.wait;" ::: "memory");
         const uint32_t rg_last_touched = (u_end - 1u) / p.chunks;
         uint32_t ob = 0, ophase = 0;
+        bool tagged_ok = true;  // false once a wait for another CTA's partial sums ran out
         for (uint32_t rg = rg_begin; rg <= rg_last_touched; ++rg) {
             if (!mbar_wait(smem_u32(&s_out_full[ob]), ophase, p.error_word, 0x8u)) return;
             const uint32_t rg_first = rg * p.chunks, rg_last = rg_first + p.chunks - 1u;
@@ -507,7 +508,88 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                         static_cast<__nv_bfloat16 *>(p.y)[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(val);
                 }
             };
-            if (!(p.probe & 4u)) {
+            // split row group with tagged partial sums: the CTA that owns the head (slot 0) collects
+            const bool finisher = !whole && p.tagged != nullptr && slot == 0u;
+            if (finisher && tagged_ok && !(p.probe & 4u)) {
+                constexpr uint32_t kTag = 0x5A5A5A5Au;
+                constexpr uint32_t RBC = MT == 1 ? 4u : 2u;  // row blocks per batch: every load in flight before the first check
+                unsigned long long *base = p.tagged + static_cast<size_t>(rg) * p.max_slots * (kRows * MT * 8);
+#pragma unroll 1
+                for (uint32_t rb0 = 0; rb0 < kRowBlocks && tagged_ok; rb0 += RBC) {
+                    float acc[RBC][MT][4];
+#pragma unroll
+                    for (uint32_t i = 0; i < RBC; ++i)
+#pragma unroll
+                        for (int mt = 0; mt < MT; ++mt) {
+                            float b0, b1, b2, b3;
+                            asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                                         : "=f"(acc[i][mt][0]), "=f"(acc[i][mt][1]), "=f"(acc[i][mt][2]), "=f"(acc[i][mt][3])
+                                         : "r"(obuf + (rb0 + i) * (32u * MT * 16u) + mt * 16u));
+                            asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                                         : "=f"(b0), "=f"(b1), "=f"(b2), "=f"(b3)
+                                         : "r"(obuf + (kRowBlocks + rb0 + i) * (32u * MT * 16u) + mt * 16u));
+                            acc[i][mt][0] += b0, acc[i][mt][1] += b1, acc[i][mt][2] += b2, acc[i][mt][3] += b3;
+                        }
+                    for (uint32_t sidx = 1; sidx < slots && tagged_ok; ++sidx) {  // fixed order: reproducible sums
+                        unsigned long long *src = base + static_cast<size_t>(sidx) * (kRows * MT * 8);
+                        unsigned long long wd[RBC][MT][4];
+                        bool got = false;
+                        for (uint32_t it = 0; it < kWaitLimit; ++it) {
+                            bool all = true;
+#pragma unroll
+                            for (uint32_t i = 0; i < RBC; ++i)
+#pragma unroll
+                                for (int mt = 0; mt < MT; ++mt) {
+                                    const uint32_t r0 = (rb0 + i) * 16u + wr;
+                                    const uint32_t o0 = r0 * (MT * 8) + mt * 8 + 2 * t, o1 = o0 + 8u * (MT * 8);
+                                    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(wd[i][mt][0]), "=l"(wd[i][mt][1]) : "l"(src + o0) : "memory");
+                                    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(wd[i][mt][2]), "=l"(wd[i][mt][3]) : "l"(src + o1) : "memory");
+                                }
+#pragma unroll
+                            for (uint32_t i = 0; i < RBC; ++i)
+#pragma unroll
+                                for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                                    for (int q = 0; q < 4; ++q) all = all && static_cast<uint32_t>(wd[i][mt][q] >> 32) == kTag;
+                            if (__all_sync(0xFFFFFFFFu, all)) {
+                                got = true;
+                                break;
+                            }
+                            if (it > 32) __nanosleep(it > 4096 ? 256 : 32);
+                        }
+                        if (!got) {
+                            if (lane == 0) atomicOr(p.error_word, 0x20u);
+                            tagged_ok = false;
+                            break;
+                        }
+#pragma unroll
+                        for (uint32_t i = 0; i < RBC; ++i)
+#pragma unroll
+                            for (int mt = 0; mt < MT; ++mt) {
+                                const uint32_t r0 = (rb0 + i) * 16u + wr;
+                                const uint32_t o0 = r0 * (MT * 8) + mt * 8 + 2 * t, o1 = o0 + 8u * (MT * 8);
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) acc[i][mt][q] += __uint_as_float(static_cast<uint32_t>(wd[i][mt][q]));
+                                asm volatile("st.relaxed.gpu.global.v2.u64 [%0], {%1,%2};" ::"l"(src + o0), "l"(0ull), "l"(0ull) : "memory");
+                                asm volatile("st.relaxed.gpu.global.v2.u64 [%0], {%1,%2};" ::"l"(src + o1), "l"(0ull), "l"(0ull) : "memory");
+                            }
+                    }
+                    if (tagged_ok) {
+#pragma unroll
+                        for (uint32_t i = 0; i < RBC; ++i) {
+                            const uint32_t n0 = rg * kRows + (rb0 + i) * 16u + wr, n1 = n0 + 8u;
+#pragma unroll
+                            for (int mt = 0; mt < MT; ++mt) {
+                                store(mt * 8 + 2 * t, n0, acc[i][mt][0]);
+                                store(mt * 8 + 2 * t + 1, n0, acc[i][mt][1]);
+                                store(mt * 8 + 2 * t, n1, acc[i][mt][2]);
+                                store(mt * 8 + 2 * t + 1, n1, acc[i][mt][3]);
+                            }
+                        }
+                    }
+                }
+            }
+            if (!(p.probe & 4u) && !finisher) {
 #pragma unroll 2
                 for (uint32_t rb = 0; rb < kRowBlocks; ++rb) {
                     const uint32_t r0 = rb * 16u + wr, r1 = r0 + 8u;
@@ -527,6 +609,24 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                             store(mt * 8 + 2 * t + 1, n0, a1);
                             store(mt * 8 + 2 * t, n1, a2);
                             store(mt * 8 + 2 * t + 1, n1, a3);
+                        } else if (p.tagged != nullptr) {
+                            // Partial sums that carry their own arrival tag ({fp32 value, tag} in one 64-bit
+                            // word): the CTA that owns the head of the row group (slot 0; it gets there last)
+                            // adds the other slots to its own sums in slot order and clears the words; nobody
+                            // takes a ticket or fences.
+                            constexpr uint32_t kTag = 0x5A5A5A5Au;
+                            constexpr unsigned long long kTagHi = static_cast<unsigned long long>(kTag) << 32;
+                            unsigned long long *base = p.tagged + static_cast<size_t>(rg) * p.max_slots * (kRows * MT * 8);
+                            const uint32_t o0 = r0 * (MT * 8) + mt * 8 + 2 * t, o1 = r1 * (MT * 8) + mt * 8 + 2 * t;
+                            if (slot != 0u) {
+                                unsigned long long *dst = base + static_cast<size_t>(slot) * (kRows * MT * 8);
+                                asm volatile("st.relaxed.gpu.global.v2.u64 [%0], {%1,%2};" ::"l"(dst + o0), "l"(kTagHi | __float_as_uint(a0)),
+                                             "l"(kTagHi | __float_as_uint(a1))
+                                             : "memory");
+                                asm volatile("st.relaxed.gpu.global.v2.u64 [%0], {%1,%2};" ::"l"(dst + o1), "l"(kTagHi | __float_as_uint(a2)),
+                                             "l"(kTagHi | __float_as_uint(a3))
+                                             : "memory");
+                            }
                         } else {
                             // slot layout [128 rows][MT*8]: this lane's values are 8-byte pairs
                             *reinterpret_cast<float2 *>(mine + r0 * (MT * 8) + mt * 8 + 2 * t) = make_float2(a0, a1);
@@ -537,7 +637,7 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&s_out_empty[ob]));  // the consumers may refill this buffer
-            if (!whole && !(p.probe & 4u)) {
+            if (!whole && !(p.probe & 4u) && p.tagged == nullptr) {
                 // release the partial (all lanes' stores are ordered before lane 0's atomic by the warp
                 // barrier) and learn whether the other owners of this row group are done
                 unsigned int ticket = 0;
@@ -2053,9 +2153,12 @@ size_t gemv_mma_scratch_bytes(const WeightView &w, uint32_t M, const GemvTuning 
 }
 
 size_t gemv_tagged_bytes(const WeightView &w, uint32_t M, bool x_f32, const GemvTuning &tune, int sm_count) {
-    if (w.bits != 4u || M == 0u || M > 4u || x_f32 || tune.no_dp4a) return 0;
+    if (M == 0u || M > 16u) return 0;
     const GemvPlan pl = plan_gemv(w, tune, sm_count);
-    return static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * (M <= 2u ? M : 4u) * 8u;
+    const uint32_t gb = w.group * w.bits / 8u;
+    const bool integer_path = w.bits == 4u && (M <= 4u) && !x_f32 && !tune.no_dp4a && gb != 0u;
+    const uint32_t cols = integer_path ? (M <= 2u ? M : 4u) : (M <= 8u ? 8u : 16u);
+    return static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * cols * 8u;
 }
 
 // Activation rows one launch of the fast path takes: 16, except where two tiles do not fit in shared memory
@@ -2143,6 +2246,9 @@ cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bo
         if (gb == 32u) return dispatch_dp4a<32>(p, w, next, pl.ctas, M, small, pdl, stream);
         if (gb == 64u) return dispatch_dp4a<64>(p, w, next, pl.ctas, M, small, pdl, stream);
     }
+    // tensor-core formulation: tagged partial sums [row group][slot][128][8 or 16] when the scratch has room
+    if (scratch.tagged && static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * (mt * 8) * 8u <= scratch.tagged_bytes)
+        p.tagged = scratch.tagged;
     if (w.bits == 4) {
         if (gb == 16u) return dispatch_stream<16, 4>(p, w, next, pl.ctas, mt, x_f32, pdl, stream);
         if (gb == 32u) return dispatch_stream<32, 4>(p, w, next, pl.ctas, mt, x_f32, pdl, stream);
