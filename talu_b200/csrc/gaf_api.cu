@@ -552,8 +552,6 @@ int32_t tgaf_ctx_set_option(tgaf_ctx *ctx, const char *name, int64_t value) {
         ctx->tune.pdl = value != 0;
     } else if (!strcmp(name, "force_generic")) {
         ctx->tune.force_generic = value != 0;
-    } else if (!strcmp(name, "dp4a_small")) {
-        ctx->tune.dp4a_small = value != 0;
     } else if (!strcmp(name, "no_dp4a")) {
         ctx->tune.no_dp4a = value != 0;
     } else if (!strcmp(name, "peer_allreduce")) {

@@ -1005,9 +1005,8 @@ struct DpPlan {
     static constexpr int TOTAL = OFF_OUT + 2 * OUT_BUF + 1024;
 };
 
-// NCW consumer warps, NST ring stages, BU units per activation block.  The small configuration
-// (8 warps, 2 stages) fits two CTAs on an SM, so one CTA's prologue and write-out tail overlap the
-// other's streaming, and the next launch's CTAs become resident while this one drains.
+// NCW consumer warps, NST ring stages, BU units per activation block.  (A configuration with 8 warps and 2
+// stages, two CTAs per SM, measured no better and was dropped.)
 //
 // NOPS = 2 runs two dependent linears in ONE launch (the FFN: gate|up, then down on silu(gate) * up): the
 // copy warp walks straight on into the second weight while the first one's sums are still being collected,
@@ -1015,7 +1014,7 @@ struct DpPlan {
 // counter (every CTA's writer arrives when its share of the first output is stored) before they read that
 // output.  In that mode the "next" tensor maps are the second weight's.
 template <int GB, int MD, bool XF32, int SD, int NCW, int NST, int BU, int NOPS>
-__global__ void __launch_bounds__((NCW + 2) * 32, NCW == 8 ? 2 : 1)
+__global__ void __launch_bounds__((NCW + 2) * 32, 1)
 gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_constant__ CUtensorMap tmap_w,
                      const __grid_constant__ CUtensorMap tmap_s, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap next_w, const __grid_constant__ CUtensorMap next_s,
@@ -1734,11 +1733,9 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
             const uint32_t sbo = (kc * GPS * 2u) & 15u;
 #pragma unroll
             for (int i = 0; i < R; ++i) {
-                uint16_t sraw = 0x3BAE, braw = 0xBD24;
-                if (!(p.probe & 16u)) {
-                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sraw) : "r"(stage_off + sboff[i] + sbo));
-                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(braw) : "r"(stage_off + sboff[i] + sbo + Geo::SB_BYTES));
-                }
+                uint16_t sraw, braw;
+                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sraw) : "r"(stage_off + sboff[i] + sbo));
+                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(braw) : "r"(stage_off + sboff[i] + sbo + Geo::SB_BYTES));
                 const float s = sb_half<SD>(sraw, 0), b = sb_half<SD>(braw, 0);
 #pragma unroll
                 for (int m = 0; m < MD; ++m) {
@@ -2012,23 +2009,10 @@ cudaError_t dispatch_ffn(const GemvParams &p1, const GemvParams &p2, const Weigh
     return cudaErrorNotSupported;
 }
 
-// small = true: 8 consumer warps, 2 stages, two CTAs per SM (group sizes 64 and 128 only)
 template <int GB>
 cudaError_t dispatch_dp4a(const GemvParams &p, const WeightView &w, const WeightView *next, uint32_t ctas, uint32_t M,
-                          bool small, bool pdl,
-                          cudaStream_t stream) {
+                          bool pdl, cudaStream_t stream) {
     const bool bf = p.sdtype == 1u;
-    if constexpr (GB >= 32) {
-        if (small) {
-#define TGAF_CASE(MDv)                                                                                   \
-    if (M == MDv)                                                                                        \
-        return bf ? launch_dp4a<GB, MDv, false, 1, 8, 2, 8>(p, w, next, ctas, pdl, stream)                     \
-                  : launch_dp4a<GB, MDv, false, 0, 8, 2, 8>(p, w, next, ctas, pdl, stream);
-            TGAF_CASE(1)
-            TGAF_CASE(2)
-#undef TGAF_CASE
-        }
-    }
     // Ring depth: four stages for one activation row where shared memory allows (group sizes 64 / 128),
     // three otherwise.  (Five stages measured no better: the kernel is issue-bound before it is latency-bound.)
     constexpr int NST1 = GB == 16 ? 3 : 4;
@@ -2038,7 +2022,7 @@ cudaError_t dispatch_dp4a(const GemvParams &p, const WeightView &w, const Weight
     if (M == 2)
         return bf ? launch_dp4a<GB, 2, false, 1, kConsumerWarps, 3, 8>(p, w, next, ctas, pdl, stream)
                   : launch_dp4a<GB, 2, false, 0, kConsumerWarps, 3, 8>(p, w, next, ctas, pdl, stream);
-    if (M == 3 || M == 4)  // int8-MMA variant, activation blocks of four units
+    if (M == 3 || M == 4)  // int8-MMA variant, three stages, activation blocks of eight units (four for 32-element groups)
         return bf ? launch_dp4a<GB, 4, false, 1, kConsumerWarps, 3, (GB == 16 ? 4 : 8)>(p, w, next, ctas, pdl, stream)
                   : launch_dp4a<GB, 4, false, 0, kConsumerWarps, 3, (GB == 16 ? 4 : 8)>(p, w, next, ctas, pdl, stream);
     return cudaErrorNotSupported;
@@ -2241,10 +2225,9 @@ cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bo
             p.tagged = scratch.tagged;
         // one or two bf16 activation rows: the integer dot-product formulation (its 13-bit activations
         // are ample next to bf16 inputs; f32 callers keep the hi + lo tensor-core path and its 1e-3 accuracy)
-        const bool small = tune.dp4a_small != 0 && gb >= 32u && M <= 2u;
-        if (gb == 16u) return dispatch_dp4a<16>(p, w, next, pl.ctas, M, false, pdl, stream);
-        if (gb == 32u) return dispatch_dp4a<32>(p, w, next, pl.ctas, M, small, pdl, stream);
-        if (gb == 64u) return dispatch_dp4a<64>(p, w, next, pl.ctas, M, small, pdl, stream);
+        if (gb == 16u) return dispatch_dp4a<16>(p, w, next, pl.ctas, M, pdl, stream);
+        if (gb == 32u) return dispatch_dp4a<32>(p, w, next, pl.ctas, M, pdl, stream);
+        if (gb == 64u) return dispatch_dp4a<64>(p, w, next, pl.ctas, M, pdl, stream);
     }
     // tensor-core formulation: tagged partial sums [row group][slot][128][8 or 16] when the scratch has room
     if (scratch.tagged && static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * (mt * 8) * 8u <= scratch.tagged_bytes)
@@ -2268,7 +2251,7 @@ cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bo
 bool gemv_ffn_eligible(const WeightView &w1, const WeightView &w2, const void *x, const void *y, uint32_t M,
                        const GemvTuning &tune) {
     // one activation row only: with two, the two-launch path measured faster (0.41 vs 0.47 ms on the 8B stack)
-    if (M != 1u || tune.no_dp4a || tune.probe || tune.dp4a_small) return false;
+    if (M != 1u || tune.no_dp4a || tune.probe) return false;
     if (w1.bits != 4u || w2.bits != 4u || w1.group != w2.group || w1.sdtype != w2.sdtype) return false;
     if (w1.N != 2u * w2.K) return false;
     if (!gemv_mma_eligible(w1, x, y, false)) return false;

@@ -44,7 +44,7 @@ struct GemvTuning {
     int ctas;           // persistent CTAs of the streaming GEMV (0 = one per SM)
     int pdl;            // launch with programmatic stream serialization
     int force_generic;  // use the shape-agnostic kernel even when the fast path applies
-    int dp4a_small;     // M <= 2 path: 8 consumer warps + 2 stages per CTA (two CTAs fit on an SM)
+    int reserved0;      // (was a tuning switch; kept so that the initialiser lists stay put)
     int no_dp4a;        // keep M <= 2 on the tensor-core formulation (for A/B comparisons)
     int probe;          // measurement aid for the streaming GEMV (0 = off); results are wrong when set
     int prefetch_units; // units at the head of each CTA range of the hinted next weight to pull into L2
