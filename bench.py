@@ -267,7 +267,7 @@ def run_single(args):
     results = {}
     clocks = ClockSampler(dev)
     with clocks:
-        for M in ((1,) if args.quick else (1, 2, 4, 8, 16)):
+        for M in ((args.m,) if args.quick else (1, 2, 4, 8, 16)):
             xs, ys = make_io(M)
 
             def step():
@@ -281,7 +281,8 @@ def run_single(args):
             results[M] = {"ms_per_step": ms, "gbs": nbytes / ms / 1e6, "bytes": nbytes}
 
         if args.quick:
-            print(json.dumps({"quick": True, "M1_gbs": round(results[1]["gbs"], 2), "ms_per_step": results[1]["ms_per_step"]}))
+            print(json.dumps({"quick": True, "M": args.m, f"M{args.m}_gbs": round(results[args.m]["gbs"], 2),
+                              "ms_per_step": results[args.m]["ms_per_step"]}))
             return
         # ---- end to end through the C ABI with host buffers (pinned), M = 1 ----
         M = 1
@@ -372,6 +373,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="length of the CPU-baseline sample")
     ap.add_argument("--case", default="decode", choices=["decode", "prefill"],
                     help="with --quick: which kernel the small case runs")
+    ap.add_argument("--m", type=int, default=1, help="activation rows of the --quick decode case (1..16)")
     ap.add_argument("--quick", action="store_true",
                     help="M = 1 only, no end-to-end and no CPU leg (small case for profilers; not a bench value)")
     args = ap.parse_args()
