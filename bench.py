@@ -124,13 +124,12 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- CPU arm
-def cpu_path(sample_seconds: float, threads: int):
+def cpu_path(sample_seconds: float, threads: int, N: int = 14336, K: int = 4096):
     """Times the CPU restatement of the reference's gaf4_64 matmul (oracle port) on one
-    gate-shaped matrix [14336, 4096], M = 1, f32 activations, for about sample_seconds."""
+    matrix [N, K] (default: an 8B gate matrix), M = 1, f32 activations, for about sample_seconds."""
     from oracle import gaf_oracle as oracle
     oracle.build()
     rng = np.random.default_rng(0)
-    N, K = 14336, 4096
     packed, scales, biases = synth_weight(rng, N, K)
     x = rng.standard_normal((1, K), dtype=np.float32)
     oracle.matmul_f32(x, packed, scales, biases, GROUP, BITS, nthreads=threads)  # warm the pool and the caches
@@ -153,22 +152,26 @@ def run_reference(args):
     from oracle import gaf_oracle as oracle
     oracle.build()
     cores = oracle.logical_cpu_count()
-    # each step is a bounded sample of the workload (one gate matrix at M = 1)
+    # each step is a bounded sample of the workload of the matching arm: one 8B gate matrix at N = 1, one
+    # 70B o-projection matrix when the arm runs the 70B stack (N > 1); M = 1
+    multi = args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1
+    N, K = (8192, 8192) if multi else (14336, 4096)
+    workload = "llama3_70b_stack" if multi else "llama3_8b_ffn"
     per_step = max(0.2, min(2.0, 60.0 / max(1, args.steps + args.warmup)))
     for _ in range(args.warmup):
-        cpu_path(per_step, cores)
+        cpu_path(per_step, cores, N, K)
     vals, t_per = [], []
     for _ in range(args.steps):
-        g, per_call, _ = cpu_path(per_step, cores)
+        g, per_call, _ = cpu_path(per_step, cores, N, K)
         vals.append(g)
         t_per.append(per_call)
     value = float(np.mean(vals))
-    sample = "one gate-shaped matrix [14336 x 4096] gaf4_64, M=1, f32 activations, repeated; C port of the reference CPU kernels (oracle/), the Zig reference cannot be built here"
+    sample = f"one matrix [{N} x {K}] gaf4_64 of the workload, M=1, f32 activations, repeated; C port of the reference CPU kernels (oracle/), the Zig reference cannot be built here"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(float(np.mean(t_per)) * 1e3, 4),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "llama3_8b_ffn", "scheme": "gaf4_64", "M": 1},
+        "higher_is_better": True, "scaling": "strong" if multi else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload, "scheme": "gaf4_64", "M": 1},
         "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
