@@ -74,8 +74,14 @@ int32_t tgaf_ctx_destroy(tgaf_ctx *ctx);
 int32_t tgaf_ctx_set_stream(tgaf_ctx *ctx, void *stream);
 int32_t tgaf_synchronize(tgaf_ctx *ctx);
 const char *tgaf_last_error(const tgaf_ctx *ctx);
-/* Tuning knobs by name ("gemv_ctas", "pdl", "force_generic", "prefetch_units"); unknown names
- * are TGAF_ERR_INVALID_ARGUMENT. */
+/* Tuning knobs by name; unknown names are TGAF_ERR_INVALID_ARGUMENT.
+ *   "gemv_ctas"        persistent CTAs of the streaming GEMVs (0 = one per SM)
+ *   "pdl"              programmatic dependent launch between consecutive GEMVs (default 1)
+ *   "prefetch_units"   depth of the next-weight L2 prefetch per CTA (default 2, 0 = off)
+ *   "force_generic"    shape-agnostic kernel only; "no_dp4a": M <= 4 on the bf16 tensor-core GEMV (A/B aids)
+ *   "peer_allreduce", "fused_allreduce", "peer_pdl", "ffn_one_launch": see tgaf_allreduce,
+ *                      tgaf_linear_bf16_allreduce, tgaf_ffn_swiglu_bf16
+ *   "probe"            measurement aid (skips parts of a GEMV; results are wrong while it is set) */
 int32_t tgaf_ctx_set_option(tgaf_ctx *ctx, const char *name, int64_t value);
 
 /* ---- weights ------------------------------------------------------------
