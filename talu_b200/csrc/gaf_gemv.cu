@@ -1626,16 +1626,21 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         }
     };
 
-    // When a row of K fits one activation block (K / 512 <= BU), the block built here holds every K chunk,
-    // in the order this CTA meets them; later row groups reuse it and nothing is rebuilt.
-    const bool whole_k = p.chunks <= block_units;
+    // When a row of K fits the two activation buffers taken together (K / 512 <= 2 BU), they are filled here
+    // with every K chunk, in the order this CTA meets them; later row groups reuse them and nothing is rebuilt.
+    const bool whole_k = p.chunks <= 2u * block_units;
     const uint32_t block_len = whole_k ? p.chunks : block_units;
     {
         const uint32_t total = u_end - u_begin;
-        if (NOPS > 1 && p.act == 1u)
-            prep_block(std::true_type{}, kc_begin, total < block_len ? total : block_len, 0u);
-        else
-            prep_block(std::false_type{}, kc_begin, total < block_len ? total : block_len, 0u);
+        const uint32_t first = total < block_len ? total : block_len;
+        const uint32_t head = first < block_units ? first : block_units;
+        if (NOPS > 1 && p.act == 1u) {
+            prep_block(std::true_type{}, kc_begin, head, 0u);
+            if (first > head) prep_block(std::true_type{}, (kc_begin + head) % p.chunks, first - head, 1u);
+        } else {
+            prep_block(std::false_type{}, kc_begin, head, 0u);
+            if (first > head) prep_block(std::false_type{}, (kc_begin + head) % p.chunks, first - head, 1u);
+        }
     }
     asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
 
