@@ -171,6 +171,43 @@ def measure(args, existing_ctx=None, existing_stream=None, M=1):
     ms = float(ms.item())
     note(f"timed: {ms} ms/step")
 
+    # end to end on every rank: each launch's x comes from page-locked host memory and its y goes back there,
+    # copies on the launching stream inside the timed region, one wait per step
+    e2e = None
+    if world > 1 and M == 1:
+        hx = {k: torch.randn((M, k)).to(torch.bfloat16).pin_memory() for k in xs}
+        hy = [torch.empty((M, w.N), dtype=torch.bfloat16).pin_memory() for _, _, w in ws]
+
+        def e2e_step():
+            for i, ((name, kind, w), y, yh) in enumerate(zip(ws, ys, hy)):
+                xs[w.K].copy_(hx[w.K], non_blocking=True)
+                gaf.hint_next_weight(ctx, ws[(i + 1) % len(ws)][2])
+                if kind == SHARD_ROW:
+                    gaf.linear_allreduce(ctx, w, xs[w.K], out=y)
+                else:
+                    gaf.linear(ctx, w, xs[w.K], out=y)
+                yh.copy_(y, non_blocking=True)
+            stream.synchronize()
+
+        e2e_steps = max(3, min(steps, 20))
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                e2e_step()
+            dist.barrier()
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            f0.record(stream)
+            for _ in range(e2e_steps):
+                e2e_step()
+            f1.record(stream)
+            stream.synchronize()
+            dist.barrier()
+        t = torch.tensor([f0.elapsed_time(f1) / e2e_steps])
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e = {"ms_per_step": float(t.item()),
+               "h2d_bytes_per_step": world * sum(M * w.K * 2 for _, _, w in ws),
+               "d2h_bytes_per_step": world * sum(M * w.N * 2 for _, _, w in ws)}
+        note(f"end to end: {e2e['ms_per_step']} ms/step")
+
     # whole-job algorithmic bytes: the full (unsharded) stack once per step
     total = 0
     for _ in range(layers):
@@ -189,11 +226,11 @@ def measure(args, existing_ctx=None, existing_stream=None, M=1):
     if debug:
         import faulthandler
         faulthandler.cancel_dump_traceback_later()
-    return ms, total, len(ws), layers, world, rank, steps, warmup, kind_ar
+    return ms, total, len(ws), layers, world, rank, steps, warmup, kind_ar, e2e
 
 
 def run(args):
-    ms, total, per_rank_launches, layers, world, rank, steps, warmup, allreduce_kind = measure(args)
+    ms, total, per_rank_launches, layers, world, rank, steps, warmup, allreduce_kind, e2e = measure(args)
     M = 1
     value = total / ms / 1e6
     if rank == 0:
@@ -212,6 +249,9 @@ def run(args):
                          "frac": round(value / world / peak, 4), "peak_kind": f"of {kind}", "traffic": None,
                          "note": "per-GPU share of the aggregate; allreduce time included"},
             "cpu_baseline": None,
-            "e2e": None,
+            "e2e": None if e2e is None else {
+                "value": round(total / e2e["ms_per_step"] / 1e6, 2), "unit": "GB/s", "ms_per_step": round(e2e["ms_per_step"], 5),
+                "h2d_bytes_per_step": e2e["h2d_bytes_per_step"], "d2h_bytes_per_step": e2e["d2h_bytes_per_step"],
+                "note": "per launch and rank: pinned host x -> device, linear (row-parallel ones with the sum over ranks), y -> pinned host; one wait per step"},
             "gpu_launches": per_rank_launches * steps * world,
         }))
