@@ -75,13 +75,20 @@ int32_t tgaf_ctx_set_stream(tgaf_ctx *ctx, void *stream);
 int32_t tgaf_synchronize(tgaf_ctx *ctx);
 const char *tgaf_last_error(const tgaf_ctx *ctx);
 /* Tuning knobs by name; unknown names are TGAF_ERR_INVALID_ARGUMENT.
- *   "gemv_ctas"        persistent CTAs of the streaming GEMVs (0 = one per SM)
+ *   "gemv_ctas"        persistent CTAs of the streaming GEMVs (0 = one per SM; at most one per SM, because the
+ *                      CTAs of a launch wait on one another)
  *   "pdl"              programmatic dependent launch between consecutive GEMVs (default 1)
  *   "prefetch_units"   depth of the next-weight L2 prefetch per CTA (default 2, 0 = off)
  *   "force_generic"    shape-agnostic kernel only; "no_dp4a": M <= 4 on the bf16 tensor-core GEMV (A/B aids)
  *   "peer_allreduce", "fused_allreduce", "peer_pdl", "ffn_one_launch": see tgaf_allreduce,
  *                      tgaf_linear_bf16_allreduce, tgaf_ffn_swiglu_bf16
- *   "probe"            measurement aid (skips parts of a GEMV; results are wrong while it is set) */
+ *   "comm_timeout_ms"  wall-clock limit of tgaf_synchronize while a communicator exists (default 30000,
+ *                      0 = wait for ever)
+ *   "wait_limit"       polls a kernel of tgaf_allreduce makes for a peer's word before it gives up
+ *                      (0 = default, several seconds)
+ *   "peer_expect_absent_rank"  diagnostic for the give-up path: tgaf_allreduce's kernel also waits for a
+ *                      rank that does not exist, so its bounded wait runs out (tgaf_synchronize then
+ *                      returns TGAF_ERR_DEVICE_FLAG and the context stays usable) */
 int32_t tgaf_ctx_set_option(tgaf_ctx *ctx, const char *name, int64_t value);
 
 /* ---- weights ------------------------------------------------------------
@@ -136,6 +143,13 @@ int32_t tgaf_linear_bf16(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16
                          uint32_t M, void *y_bf16);
 int32_t tgaf_linear_f32(tgaf_ctx *ctx, const tgaf_weight *w, const float *x,
                         uint32_t M, float *y);
+/* Linear.forward with its optional bias (core/src/inference/backend/cpu/executor/model.zig:98-139): the matmul,
+ * then y[m, n] += bias[n] (addBiasRows).  d_bias: f32 [N_local] on the device, or NULL for none.  The bias is
+ * added to this rank's output as it is: for a row-parallel weight add it on one rank only, or after the sum. */
+int32_t tgaf_linear_bf16_bias(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16, uint32_t M,
+                              const float *d_bias, void *y_bf16);
+int32_t tgaf_linear_f32_bias(tgaf_ctx *ctx, const tgaf_weight *w, const float *x, uint32_t M,
+                             const float *d_bias, float *y);
 /* No counterpart in the reference.  tgaf_linear_bf16 for hosts that must not allocate
  * while they serve: a backend that gives the rest of the device's memory to its KV cache
  * at start-up cannot afford a cudaMalloc in the token loop (it synchronises the device
@@ -146,7 +160,7 @@ int32_t tgaf_linear_f32(tgaf_ctx *ctx, const tgaf_weight *w, const float *x,
  *   - A problem that needs more scratch than that (very many output rows at M > 8) is
  *     rejected with TGAF_ERR_UNSUPPORTED and a message; nothing is launched.
  *   - The first call on a device looks the array's device address up; make that call
- *     before any stream capture.
+ *     before any stream capture, and not from two host threads at once.
  *   - All calls on a device share the array: calls that overlap on the GPU (two streams)
  *     race.  The counters are cleared on the stream before each launch. */
 int32_t tgaf_linear_bf16_fixed_scratch(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16,
@@ -226,6 +240,14 @@ int32_t tgaf_embedding_lookup_f32(tgaf_ctx *ctx, const tgaf_weight *w, const uin
  * Option "ffn_one_launch" = 0 forces the latter. */
 int32_t tgaf_ffn_swiglu_bf16(tgaf_ctx *ctx, const tgaf_weight *w_gate_up, const tgaf_weight *w_down,
                              const void *x_bf16, uint32_t m, void *y_bf16);
+/* The same with the gate's activation chosen by the caller, as SwiGLU.forward does with use_gelu
+ * (ffn.zig:213-266): TGAF_ACT_SILU = silu(g) * u (talu_silu_mul_f32,
+ * core/src/compute/cuda/kernels/ops/reduction_ops.cu:46-57), TGAF_ACT_GELU = tanh-form gelu(g) * u
+ * (talu_gelu_mul_f32, reduction_ops.cu:59-72). */
+#define TGAF_ACT_SILU 1u
+#define TGAF_ACT_GELU 2u
+int32_t tgaf_ffn_gated_bf16(tgaf_ctx *ctx, const tgaf_weight *w_gate_up, const tgaf_weight *w_down,
+                            const void *x_bf16, uint32_t m, uint32_t activation, void *y_bf16);
 
 /* ---- tensor parallel exchange (no counterpart in the reference, which is
  * single-device): sum of the row-parallel partial outputs over all ranks. ----
@@ -261,6 +283,27 @@ int32_t tgaf_ffn_swiglu_bf16_allreduce(tgaf_ctx *ctx, const tgaf_weight *w_gate_
                                        const void *x_bf16, uint32_t m, void *y_bf16);
 /* 1 when the peer-memory path of tgaf_allreduce is available on this communicator, else 0 */
 int32_t tgaf_comm_uses_peer_memory(const tgaf_ctx *ctx);
+
+/* ---- failure handling on the host ------------------------------------------
+ * The reference's model is typed driver errors returned to the caller
+ * (core/src/compute/cuda/device.zig:226-237); it has no collectives.  Here a stream can hold a collective
+ * that never completes because a rank is missing or has failed.  While a context has a communicator,
+ * tgaf_synchronize therefore does not block: it polls the stream and the collective library's asynchronous
+ * error state (ncclCommGetAsyncError) under a wall-clock limit (option "comm_timeout_ms"); on an error
+ * (TGAF_ERR_NCCL) or at the limit (TGAF_ERR_TIMEOUT) it aborts the communicator (ncclCommAbort), drops the
+ * peer mappings and returns; single-GPU calls on the context keep working, tgaf_comm_init makes a new
+ * communicator.  tgaf_watchdog_wait is that loop with its three hooks in the caller's hands, for hosts that
+ * run their own collectives next to this library (and for tests without a GPU):
+ *   work_done(user)   > 0 finished, 0 still running, < 0 failed (-> TGAF_ERR_CUDA)
+ *   async_error(user) 0 = none, anything else -> abort_comm(user), TGAF_ERR_NCCL        (may be NULL)
+ *   abort_comm(user)  called once before TGAF_ERR_NCCL / TGAF_ERR_TIMEOUT is returned   (may be NULL)
+ * timeout_ms = 0 waits for ever. */
+typedef struct tgaf_watch_fns {
+    int32_t (*work_done)(void *user);
+    int32_t (*async_error)(void *user);
+    void (*abort_comm)(void *user);
+} tgaf_watch_fns;
+int32_t tgaf_watchdog_wait(const tgaf_watch_fns *fns, void *user, uint32_t timeout_ms);
 
 #ifdef __cplusplus
 }

@@ -34,6 +34,19 @@ def build(force: bool = False) -> Path:
     return _LIB_PATH
 
 
+REF_CUBIN = _HERE / "_ref" / "talu_ref_quant_sm_100.cubin"
+
+
+def build_ref(reference_root: str | os.PathLike = "/root/reference") -> Path | None:
+    """Compile the reference's own CUDA kernels for this path, unchanged, into oracle/_ref/ (`make ref`).
+    Needs a talu checkout at `reference_root`; where there is none (the GPU box) the cubin built earlier is
+    used as it is.  Returns the cubin's path, or None when it neither exists nor can be built."""
+    src = Path(reference_root) / "core/src/compute/cuda/kernels/ops/quant_ops.cu"
+    if src.exists():
+        subprocess.run(["make", "-C", str(_HERE), "ref", f"REF={reference_root}"], check=True, capture_output=True)
+    return REF_CUBIN if REF_CUBIN.exists() else None
+
+
 _lib = None
 
 
@@ -180,13 +193,21 @@ def silu_mul_split(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
     return ((g * sig) * np.asarray(up, np.float32)).astype(np.float32)
 
 
-def ffn_swiglu_f32(x, gate_up, down, group: int, bits: int, sdtype: int = SCALES_BF16) -> np.ndarray:
+def gelu_mul_split(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    """geluMulSplit (core/src/compute/cpu/activation.zig:22-27, :70-75): tanh-form gelu(gate) * up in f32."""
+    g = np.asarray(gate, np.float32)
+    inner = np.float32(0.7978845608) * (g + np.float32(0.044715) * (g * g * g))
+    return ((g * np.float32(0.5) * (np.float32(1.0) + np.tanh(inner, dtype=np.float32))) * np.asarray(up, np.float32)).astype(np.float32)
+
+
+def ffn_swiglu_f32(x, gate_up, down, group: int, bits: int, sdtype: int = SCALES_BF16, gelu: bool = False) -> np.ndarray:
     """SwiGLU.forward with a fused gate|up weight in the concat layout [gate rows..., up rows...]
-    (core/src/inference/backend/cpu/kernels/ffn.zig:166-241, :388): y = down(silu(gate(x)) * up(x)).
-    gate_up / down are (packed, scales, biases) triples."""
+    (core/src/inference/backend/cpu/kernels/ffn.zig:166-241, :388): y = down(act(gate(x)) * up(x)), act =
+    silu, or the tanh-form gelu when `gelu` (the reference's use_gelu).  gate_up / down are (packed, scales,
+    biases) triples."""
     gu = matmul_f32(x, *gate_up, group, bits, sdtype)
     d_ff = gu.shape[1] // 2
-    h = silu_mul_split(gu[:, :d_ff], gu[:, d_ff:])
+    h = (gelu_mul_split if gelu else silu_mul_split)(gu[:, :d_ff], gu[:, d_ff:])
     return matmul_f32(h, *down, group, bits, sdtype)
 
 

@@ -49,7 +49,20 @@ SIGNATURES = {
     "tgaf_ffn_swiglu_bf16": (_i32, [_vp, _vp, _vp, _vp, _u32, _vp]),
     "tgaf_ffn_swiglu_bf16_allreduce": (_i32, [_vp, _vp, _vp, _vp, _u32, _vp]),
     "tgaf_linear_bf16_allreduce": (_i32, [_vp, _vp, _vp, _u32, _vp]),
+    "tgaf_linear_bf16_bias": (_i32, [_vp, _vp, _vp, _u32, _vp, _vp]),
+    "tgaf_linear_f32_bias": (_i32, [_vp, _vp, _vp, _u32, _vp, _vp]),
+    "tgaf_ffn_gated_bf16": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _vp]),
+    "tgaf_watchdog_wait": (_i32, [_vp, _vp, _u32]),
 }
+
+# tgaf_watch_fns: the three hooks of tgaf_watchdog_wait
+WORK_DONE_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p)
+ASYNC_ERROR_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p)
+ABORT_FN = C.CFUNCTYPE(None, C.c_void_p)
+
+
+class WatchFns(C.Structure):
+    _fields_ = [("work_done", WORK_DONE_FN), ("async_error", ASYNC_ERROR_FN), ("abort_comm", ABORT_FN)]
 
 _lib = None
 

@@ -70,7 +70,10 @@ SIDELOAD_SRC = CSRC / "sideload" / "talu_kernels_sm100.cu"
 SIDELOAD_DIR = PKG / "sideload"
 SIDELOAD_ARCH = "sm_100"   # talu's arch tag for B200: "sm_{major}{minor}" (core/src/compute/cuda/sideload.zig:46-49)
 # op name -> symbol, as talu's wrappers name them (core/src/compute/cuda/gaffine_u4_matvec.zig:12-13)
-SIDELOAD_KERNELS = [("gaffine_u4_matvec_f32", "talu_gaffine_u4_matvec_f32")]
+SIDELOAD_KERNELS = [("gaffine_u4_matvec_f32", "talu_gaffine_u4_matvec_f32"),
+                    # the fused decode launches (gaffine_u4_matvec_qkv.zig:13-14, gaffine_u4_matvec_gate_up.zig:12-13)
+                    ("gaffine_u4_matvec_qkv_f32", "talu_gaffine_u4_matvec_qkv_f32"),
+                    ("gaffine_u4_matvec_gate_up_f32", "talu_gaffine_u4_matvec_gate_up_f32")]
 
 
 def build_sideload(force: bool = False) -> tuple[Path, Path]:

@@ -8,12 +8,14 @@
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 
+#include <chrono>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
+#include <thread>
 
 using namespace tgaf;
 
@@ -26,7 +28,7 @@ struct NcclUniqueId {
     char internal[TGAF_COMM_ID_BYTES];
 };
 typedef void *NcclComm;
-enum { kNcclSuccess = 0, kNcclSum = 0, kNcclMin = 3, kNcclUint8 = 1, kNcclInt32 = 2, kNcclFloat32 = 7, kNcclBfloat16 = 9 };
+enum { kNcclSuccess = 0, kNcclInProgress = 7, kNcclSum = 0, kNcclMin = 3, kNcclUint8 = 1, kNcclInt32 = 2, kNcclFloat32 = 7, kNcclBfloat16 = 9 };
 
 struct NcclApi {
     void *handle = nullptr;
@@ -34,6 +36,7 @@ struct NcclApi {
     int (*CommInitRank)(NcclComm *, int, NcclUniqueId, int) = nullptr;
     int (*CommDestroy)(NcclComm) = nullptr;
     int (*CommAbort)(NcclComm) = nullptr;
+    int (*CommGetAsyncError)(NcclComm, int *) = nullptr;
     int (*AllReduce)(const void *, void *, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
     int (*AllGather)(const void *, void *, size_t, int, NcclComm, cudaStream_t) = nullptr;
     const char *(*GetErrorString)(int) = nullptr;
@@ -46,8 +49,10 @@ NcclApi &nccl_api() {
     static bool tried = false;
     if (tried) return api;
     tried = true;
-    const char *names[] = {"libnccl.so.2", "libnccl.so"};
+    // TGAF_NCCL_LIBRARY names another build of the collective library (same C API)
+    const char *names[] = {getenv("TGAF_NCCL_LIBRARY"), "libnccl.so.2", "libnccl.so"};
     for (const char *n : names) {
+        if (!n || !n[0]) continue;
         api.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
         if (api.handle) break;
     }
@@ -59,6 +64,7 @@ NcclApi &nccl_api() {
     api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(api.handle, "ncclCommInitRank"));
     api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(api.handle, "ncclCommDestroy"));
     api.CommAbort = reinterpret_cast<decltype(api.CommAbort)>(dlsym(api.handle, "ncclCommAbort"));
+    api.CommGetAsyncError = reinterpret_cast<decltype(api.CommGetAsyncError)>(dlsym(api.handle, "ncclCommGetAsyncError"));
     api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(api.handle, "ncclAllReduce"));
     api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(api.handle, "ncclAllGather"));
     api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(api.handle, "ncclGetErrorString"));
@@ -107,6 +113,12 @@ struct tgaf_ctx {
     int fused_allreduce = 1; // tgaf_linear_bf16_allreduce sums inside the GEMV when it can
     int ffn_one_launch = 1;  // tgaf_ffn_swiglu_bf16 runs both linears in one kernel when it can
     int peer_pdl = 0;        // programmatic stream serialization for the all-reduce kernel (measured slower)
+    int peer_expect_absent_rank = 0;  // diagnostic: the all-reduce kernel also waits for a rank that does not exist
+    uint32_t comm_timeout_ms = 30000; // wall-clock limit of tgaf_synchronize while a communicator exists (0 = wait for ever)
+    // tensor maps of raw-pointer weights (tgaf_gaffine_u*_matvec_f32), keyed on pointers and dimensions
+    static constexpr int kRawCache = 32;
+    WeightView raw_cache[kRawCache];
+    int raw_cache_used = 0, raw_cache_next = 0;
     char err[512] = {0};
 };
 
@@ -190,7 +202,6 @@ int32_t ensure_scratch(tgaf_ctx *ctx, size_t partial_bytes, size_t counters, siz
     if (counters > ctx->scratch.counter_count) {
         TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
         if (ctx->scratch.counters) cudaFree(ctx->scratch.counters);
-    if (ctx->scratch.tagged) cudaFree(ctx->scratch.tagged);
         ctx->scratch.counters = nullptr;
         ctx->scratch.counter_count = 0;
         size_t want = counters < 65536 ? 65536 : counters;
@@ -224,6 +235,7 @@ int32_t linear_device(tgaf_ctx *ctx, const WeightView &w, const void *x, uint32_
     if (!x || !y) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null activation or output pointer");
     if (M == 0) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "M must be > 0");
     const size_t elt = f32 ? 4 : 2;
+    TGAF_CUDA(ctx, cudaSetDevice(ctx->device));  // scratch growth and launches below belong to the context's device
 
     if (!f32 && gemm_tc_eligible(w, M)) {
         cudaError_t e = gemm_tc(w, x, y, M, ctx->stream, ctx->sm_count, ctx->d_error_word);
@@ -271,6 +283,7 @@ int32_t linear_host(tgaf_ctx *ctx, const tgaf_weight *w, const void *xh, uint32_
     if (!w || !xh || !yh || M == 0) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null pointer or M == 0");
     const size_t elt = f32 ? 4 : 2;
     const size_t xb = static_cast<size_t>(M) * w->v.K * elt, yb = static_cast<size_t>(M) * w->v.N * elt;
+    TGAF_CUDA(ctx, cudaSetDevice(ctx->device));
     int32_t st = ensure_stage(ctx, &ctx->stage_x, &ctx->stage_x_bytes, xb);
     if (st != TGAF_OK) return st;
     st = ensure_stage(ctx, &ctx->stage_y, &ctx->stage_y_bytes, yb);
@@ -309,8 +322,17 @@ int32_t raw_matvec(tgaf_ctx *ctx, uint32_t bits, const float *input, const uint3
     v.sdtype = sdtype;
     v.row_bytes = in_dim / vpw * 4u;
     v.groups = in_dim / group_size;
+    // a decoder calls this once per token and weight with the same pointers: encode the tensor maps once
+    for (int i = 0; i < ctx->raw_cache_used; ++i) {
+        const WeightView &c = ctx->raw_cache[i];
+        if (c.packed == v.packed && c.scales == v.scales && c.biases == v.biases && c.N == v.N && c.K == v.K &&
+            c.group == v.group && c.bits == v.bits && c.sdtype == v.sdtype)
+            return linear_device(ctx, c, input, batch_rows, out, true);
+    }
     attach_packed_tmap(v);
-    return linear_device(ctx, v, input, batch_rows, out, true);
+    const int slot = ctx->raw_cache_used < tgaf_ctx::kRawCache ? ctx->raw_cache_used++ : (ctx->raw_cache_next++ % tgaf_ctx::kRawCache);
+    ctx->raw_cache[slot] = v;
+    return linear_device(ctx, ctx->raw_cache[slot], input, batch_rows, out, true);
 }
 
 }  // namespace
@@ -493,6 +515,7 @@ int32_t tgaf_ctx_destroy(tgaf_ctx *ctx) {
     peer_teardown(ctx);
     if (ctx->scratch.partials) cudaFree(ctx->scratch.partials);
     if (ctx->scratch.counters) cudaFree(ctx->scratch.counters);
+    if (ctx->scratch.tagged) cudaFree(ctx->scratch.tagged);
     if (ctx->stage_x) cudaFree(ctx->stage_x);
     if (ctx->stage_y) cudaFree(ctx->stage_y);
     if (ctx->d_error_word) cudaFree(ctx->d_error_word);
@@ -522,8 +545,88 @@ int32_t tgaf_ctx_set_stream(tgaf_ctx *ctx, void *stream) {
     return TGAF_OK;
 }
 
+int32_t tgaf_watchdog_wait(const tgaf_watch_fns *fns, void *user, uint32_t timeout_ms) {
+    if (!fns || !fns->work_done) return TGAF_ERR_INVALID_ARGUMENT;
+    const auto t0 = std::chrono::steady_clock::now();
+    for (uint64_t it = 0;; ++it) {
+        const int32_t done = fns->work_done(user);
+        if (done > 0) return TGAF_OK;
+        if (done < 0) return TGAF_ERR_CUDA;
+        if (fns->async_error && fns->async_error(user) != 0) {
+            if (fns->abort_comm) fns->abort_comm(user);
+            return TGAF_ERR_NCCL;
+        }
+        const auto waited = std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count();
+        if (timeout_ms != 0 && waited >= static_cast<int64_t>(timeout_ms) * 1000) {
+            if (fns->abort_comm) fns->abort_comm(user);
+            return TGAF_ERR_TIMEOUT;
+        }
+        // a decode step is tens of microseconds: poll flat out for the first 2 ms, then yield between polls
+        if (waited > 2000) std::this_thread::sleep_for(std::chrono::microseconds(it & 63 ? 50 : 500));
+    }
+}
+
+namespace {
+// tgaf_synchronize with a communicator: the stream may hold a collective that never completes when a rank is
+// missing or has failed, so the wait polls instead of blocking and gives the communicator up at the limit.
+struct CommWatch {
+    tgaf_ctx *ctx;
+    cudaError_t stream_error;
+    int nccl_error;
+};
+int32_t watch_work_done(void *user) {
+    CommWatch *cw = static_cast<CommWatch *>(user);
+    cudaStream_t streams[3] = {cw->ctx->stream, cw->ctx->h2d_stream, cw->ctx->d2h_stream};
+    for (cudaStream_t st : streams) {
+        if (st == nullptr) continue;  // the copy streams exist only after a queued host-buffer call
+        const cudaError_t e = cudaStreamQuery(st);
+        if (e == cudaErrorNotReady) return 0;
+        if (e != cudaSuccess) {
+            cw->stream_error = e;
+            return -1;
+        }
+    }
+    return 1;
+}
+int32_t watch_async_error(void *user) {
+    CommWatch *cw = static_cast<CommWatch *>(user);
+    NcclApi &api = nccl_api();
+    if (!cw->ctx->comm || !api.CommGetAsyncError) return 0;
+    int async_err = 0;
+    if (api.CommGetAsyncError(cw->ctx->comm, &async_err) != kNcclSuccess) async_err = -1;
+    if (async_err == kNcclInProgress) async_err = 0;  // a non-blocking communicator still setting up
+    cw->nccl_error = async_err;
+    return async_err;
+}
+void watch_abort(void *user) {
+    CommWatch *cw = static_cast<CommWatch *>(user);
+    NcclApi &api = nccl_api();
+    if (cw->ctx->comm && api.CommAbort) api.CommAbort(cw->ctx->comm);  // the library's kernels leave the stream
+    cw->ctx->comm = nullptr;
+    cw->ctx->comm_size = 1;
+    cw->ctx->comm_rank = 0;
+}
+}  // namespace
+
 int32_t tgaf_synchronize(tgaf_ctx *ctx) {
     if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    TGAF_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (ctx->comm && ctx->comm_timeout_ms != 0) {
+        CommWatch cw = {ctx, cudaSuccess, 0};
+        const tgaf_watch_fns fns = {watch_work_done, watch_async_error, watch_abort};
+        const int32_t st = tgaf_watchdog_wait(&fns, &cw, ctx->comm_timeout_ms);
+        if (st == TGAF_ERR_CUDA) return cuda_fail(ctx, cw.stream_error, "cudaStreamQuery");
+        if (st != TGAF_OK) {
+            // the communicator is gone; this library's own kernels give their waits up by themselves (bounded polls)
+            cudaStreamSynchronize(ctx->stream);
+            peer_teardown(ctx);
+            if (st == TGAF_ERR_TIMEOUT)
+                return fail(ctx, TGAF_ERR_TIMEOUT, "the stream did not finish within %u ms (a rank missing?): communicator aborted", ctx->comm_timeout_ms);
+            NcclApi &api = nccl_api();
+            return fail(ctx, TGAF_ERR_NCCL, "asynchronous communicator error (%s): communicator aborted",
+                        cw.nccl_error > 0 && api.GetErrorString ? api.GetErrorString(cw.nccl_error) : "query failed");
+        }
+    }
     TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (ctx->d2h_stream) {  // queued host-buffer calls: their last copies run on the copy streams
         TGAF_CUDA(ctx, cudaStreamSynchronize(ctx->h2d_stream));
@@ -536,6 +639,7 @@ int32_t tgaf_synchronize(tgaf_ctx *ctx) {
         // an abandoned launch may have left arrival counters half way
         if (ctx->scratch.counters) cudaMemset(ctx->scratch.counters, 0, ctx->scratch.counter_count * sizeof(unsigned int));
         if (ctx->scratch.tagged) cudaMemset(ctx->scratch.tagged, 0, ctx->scratch.tagged_bytes);  // ... or tags set
+        if (ctx->d_grid_bar) cudaMemset(ctx->d_grid_bar, 0, 4 * sizeof(unsigned int));
         return fail(ctx, TGAF_ERR_DEVICE_FLAG, "a kernel gave up a bounded wait (code 0x%x)", flag);
     }
     return TGAF_OK;
@@ -546,7 +650,10 @@ const char *tgaf_last_error(const tgaf_ctx *ctx) { return ctx ? ctx->err : "null
 int32_t tgaf_ctx_set_option(tgaf_ctx *ctx, const char *name, int64_t value) {
     if (!ctx || !name) return TGAF_ERR_INVALID_ARGUMENT;
     if (!strcmp(name, "gemv_ctas")) {
-        if (value < 0 || value > 65535) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "gemv_ctas out of range");
+        // the split-K collection and the two-operation launch wait on other CTAs of the same grid, so every
+        // CTA must be resident at once: one per SM at most
+        if (value < 0 || value > ctx->sm_count)
+            return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "gemv_ctas must be 0 (one per SM) or 1..%d", ctx->sm_count);
         ctx->tune.ctas = static_cast<int>(value);
     } else if (!strcmp(name, "pdl")) {
         ctx->tune.pdl = value != 0;
@@ -565,8 +672,14 @@ int32_t tgaf_ctx_set_option(tgaf_ctx *ctx, const char *name, int64_t value) {
     } else if (!strcmp(name, "prefetch_units")) {
         if (value < 0 || value > 4096) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "prefetch_units out of range");
         ctx->tune.prefetch_units = static_cast<int>(value);
-    } else if (!strcmp(name, "probe")) {
-        ctx->tune.probe = static_cast<int>(value);
+    } else if (!strcmp(name, "wait_limit")) {
+        if (value < 0 || value > (int64_t(1) << 30)) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "wait_limit out of range");
+        ctx->tune.wait_limit = static_cast<int>(value);
+    } else if (!strcmp(name, "peer_expect_absent_rank")) {
+        ctx->peer_expect_absent_rank = value != 0;
+    } else if (!strcmp(name, "comm_timeout_ms")) {
+        if (value < 0 || value > 3600000) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "comm_timeout_ms out of range");
+        ctx->comm_timeout_ms = static_cast<uint32_t>(value);
     } else {
         return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "unknown option '%s'", name);
     }
@@ -739,6 +852,25 @@ int32_t tgaf_linear_f32(tgaf_ctx *ctx, const tgaf_weight *w, const float *x, uin
     if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
     if (!w) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null weight");
     return linear_device(ctx, w->v, x, M, y, true);
+}
+
+// the reference's Linear.forward with its optional bias: matmul, then addBiasRows
+static int32_t linear_bias(tgaf_ctx *ctx, const tgaf_weight *w, const void *x, uint32_t M, const float *bias, void *y, bool f32) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!w) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null weight");
+    const int32_t st = linear_device(ctx, w->v, x, M, y, f32);
+    if (st != TGAF_OK || !bias) return st;
+    cudaError_t e = add_bias_rows(y, bias, M, w->v.N, f32, ctx->stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "bias rows launch");
+    return TGAF_OK;
+}
+
+int32_t tgaf_linear_bf16_bias(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16, uint32_t M, const float *d_bias, void *y_bf16) {
+    return linear_bias(ctx, w, x_bf16, M, d_bias, y_bf16, false);
+}
+
+int32_t tgaf_linear_f32_bias(tgaf_ctx *ctx, const tgaf_weight *w, const float *x, uint32_t M, const float *d_bias, float *y) {
+    return linear_bias(ctx, w, x, M, d_bias, y, true);
 }
 
 int32_t tgaf_linear_bf16_fixed_scratch(tgaf_ctx *ctx, const tgaf_weight *w, const void *x_bf16, uint32_t M,
@@ -948,6 +1080,7 @@ int32_t tgaf_gaffine_u8_matvec_f32(tgaf_ctx *ctx, const float *input, const uint
 int32_t tgaf_dequant_f32(tgaf_ctx *ctx, const tgaf_weight *w, float *d_out) {
     if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
     if (!w || !d_out) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null pointer");
+    TGAF_CUDA(ctx, cudaSetDevice(ctx->device));
     cudaError_t e = dequant_f32(w->v, d_out, ctx->stream);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "dequant launch");
     return TGAF_OK;
@@ -956,6 +1089,7 @@ int32_t tgaf_dequant_f32(tgaf_ctx *ctx, const tgaf_weight *w, float *d_out) {
 int32_t tgaf_dequant_f32_host(tgaf_ctx *ctx, const tgaf_weight *w, float *h_out) {
     if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
     if (!w || !h_out) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null pointer");
+    TGAF_CUDA(ctx, cudaSetDevice(ctx->device));
     const size_t bytes = static_cast<size_t>(w->v.N) * w->v.K * sizeof(float);
     float *d = nullptr;
     TGAF_CUDA(ctx, cudaMalloc(&d, bytes));
@@ -972,6 +1106,7 @@ int32_t tgaf_embedding_lookup_f32(tgaf_ctx *ctx, const tgaf_weight *w, const uin
     if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
     if (!w || !token_ids || !d_out) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null pointer");
     if (count == 0) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "count must be > 0");
+    TGAF_CUDA(ctx, cudaSetDevice(ctx->device));
     for (uint32_t i = 0; i < count; ++i)
         if (token_ids[i] >= w->v.N)
             return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "token id %u at position %u is outside the table of %u rows",
@@ -1032,8 +1167,9 @@ int32_t tgaf_comm_destroy(tgaf_ctx *ctx) {
 
 // FFN operator.  reduce: sum the result over the communicator's ranks (row-parallel down projection).
 static int32_t ffn_swiglu(tgaf_ctx *ctx, const tgaf_weight *wgu, const tgaf_weight *wd, const void *x, uint32_t M, void *y,
-                          bool reduce) {
+                          bool reduce, uint32_t act = TGAF_ACT_SILU) {
     if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (act != TGAF_ACT_SILU && act != TGAF_ACT_GELU) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "bad activation %u", act);
     if (!wgu || !wd || !x || !y || M == 0) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null pointer or M == 0");
     const WeightView &w1 = wgu->v, &w2 = wd->v;
     if (w1.N != 2u * w2.K)
@@ -1057,7 +1193,7 @@ static int32_t ffn_swiglu(tgaf_ctx *ctx, const tgaf_weight *wgu, const tgaf_weig
     if (ctx->ffn_one_launch && !ctx->tune.force_generic && peer_ready && gemv_ffn_eligible(w1, w2, x, y, M, t)) {
         st = ensure_scratch(ctx, 0, 0, gemv_ffn_tagged_bytes(w1, w2, M, t, ctx->sm_count));
         if (st != TGAF_OK) return st;
-        cudaError_t e = gemv_ffn_swiglu(w1, w2, x, static_cast<float *>(ctx->ffn_mid), y, M, ctx->scratch, ctx->d_grid_bar, t,
+        cudaError_t e = gemv_ffn_swiglu(w1, w2, x, static_cast<float *>(ctx->ffn_mid), y, M, act, ctx->scratch, ctx->d_grid_bar, t,
                                         ctx->stream, ctx->sm_count, ctx->d_error_word);
         if (e == cudaSuccess) return TGAF_OK;
         if (e != cudaErrorNotSupported) return cuda_fail(ctx, e, "ffn launch");
@@ -1068,7 +1204,7 @@ static int32_t ffn_swiglu(tgaf_ctx *ctx, const tgaf_weight *wgu, const tgaf_weig
     ctx->tune.next = &w2;
     st = linear_device(ctx, w1, x, M, gu, false);
     if (st != TGAF_OK) return st;
-    cudaError_t e = swiglu_bf16(gu, h, M, d_ff, ctx->stream);
+    cudaError_t e = swiglu_bf16(gu, h, M, d_ff, act, ctx->stream);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "swiglu launch");
     ctx->tune.next = hint;
     return linear_device(ctx, w2, h, M, y, false, reduce);
@@ -1077,6 +1213,11 @@ static int32_t ffn_swiglu(tgaf_ctx *ctx, const tgaf_weight *wgu, const tgaf_weig
 int32_t tgaf_ffn_swiglu_bf16(tgaf_ctx *ctx, const tgaf_weight *w_gate_up, const tgaf_weight *w_down, const void *x_bf16,
                              uint32_t m, void *y_bf16) {
     return ffn_swiglu(ctx, w_gate_up, w_down, x_bf16, m, y_bf16, false);
+}
+
+int32_t tgaf_ffn_gated_bf16(tgaf_ctx *ctx, const tgaf_weight *w_gate_up, const tgaf_weight *w_down, const void *x_bf16,
+                            uint32_t m, uint32_t activation, void *y_bf16) {
+    return ffn_swiglu(ctx, w_gate_up, w_down, x_bf16, m, y_bf16, false, activation);
 }
 
 int32_t tgaf_ffn_swiglu_bf16_allreduce(tgaf_ctx *ctx, const tgaf_weight *w_gate_up, const tgaf_weight *w_down,
@@ -1109,7 +1250,7 @@ int32_t allreduce_device(tgaf_ctx *ctx, void *d_buf, uint64_t count, uint32_t dt
     if (ctx->peer.ok && ctx->peer_allreduce) {
         // decode-sized tiles: one kernel over NVLink peer memory; anything else falls through to NCCL
         cudaError_t e = peer_allreduce(ctx->peer, d_buf, count, dtype == TGAF_DTYPE_F32, ctx->tune.pdl != 0 && ctx->peer_pdl != 0, ctx->stream,
-                                       ctx->d_error_word);
+                                       ctx->d_error_word, static_cast<uint32_t>(ctx->tune.wait_limit), ctx->peer_expect_absent_rank != 0);
         if (e == cudaSuccess) return TGAF_OK;
         if (e != cudaErrorNotSupported) return cuda_fail(ctx, e, "peer all-reduce launch");
     }

@@ -451,11 +451,13 @@ cudaError_t gemm_tc(const WeightView &w, const void *x_bf16, void *y_bf16, uint3
     p.m_tiles = (M + kBM - 1u) / kBM;
     p.n_tiles = (w.N + kBN - 1u) / kBN;
     p.k_blocks = w.K / kBK;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {};  // per device: the opt-in belongs to the function on one device
+    int dev = 0;
+    if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(gaf_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
         if (e != cudaSuccess) return e;
-        configured = true;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const uint32_t tiles = p.m_tiles * p.n_tiles;
     const uint32_t ctas = tiles < static_cast<uint32_t>(sm_count) ? tiles : static_cast<uint32_t>(sm_count);

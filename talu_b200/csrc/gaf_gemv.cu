@@ -103,10 +103,8 @@ struct GemvParams {
     uint8_t *fuse_region[kPeerMaxRanks];  // fused all-reduce: every rank's exchange region ([fuse_rank] is local)
     uint32_t fuse_rank, fuse_size;        //   fuse_size == 0: plain GEMV
     uint32_t y_f32;          // M <= 4 kernel: write y as fp32 although x is bf16 (first half of the fused FFN)
-    uint32_t act;            // M <= 4 kernel: 1 = x is fp32 [M][2K] and the operand is silu(x[:, :K]) * x[:, K:]
+    uint32_t act;            // M <= 4 kernel: 1 / 2 = x is fp32 [M][2K] and the operand is silu / gelu(x[:, :K]) * x[:, K:]
     unsigned int *grid_bar;  // M <= 4 kernel, two operations per launch: arrival counters, zero between launches
-    uint32_t probe;       // measurement aid, bit mask: 1 = skip the arithmetic, 2 = skip the streaming, 4 = skip the write-out,
-                          // 8 = skip the activation block, 32 = return at once (launch cost only)
 };
 
 // ---- small PTX wrappers ----------------------------------------------------
@@ -445,9 +443,7 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
             if (round > 0) ok = mbar_wait(smem_u32(&s_empty[stage]), (round - 1u) & 1u, p.error_word, 0x1u);
             if (!ok) break;
             const uint32_t full = smem_u32(&s_full[stage]);
-            if (p.probe & 2u) {
-                mbar_arrive(full);
-            } else {
+            {
                 // rows past N and bytes past a row end are zero-filled by the copy engine,
                 // so every unit delivers the same byte count
                 const uint32_t base = ring + stage * Geo::STAGE_BYTES;
@@ -510,7 +506,7 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
             };
             // split row group with tagged partial sums: the CTA that owns the head (slot 0) collects
             const bool finisher = !whole && p.tagged != nullptr && slot == 0u;
-            if (finisher && tagged_ok && !(p.probe & 4u)) {
+            if (finisher && tagged_ok) {
                 constexpr uint32_t kTag = 0x5A5A5A5Au;
                 constexpr uint32_t RBC = MT == 1 ? 4u : 2u;  // row blocks per batch: every load in flight before the first check
                 unsigned long long *base = p.tagged + static_cast<size_t>(rg) * p.max_slots * (kRows * MT * 8);
@@ -589,7 +585,7 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
                     }
                 }
             }
-            if (!(p.probe & 4u) && !finisher) {
+            if (!finisher) {
 #pragma unroll 2
                 for (uint32_t rb = 0; rb < kRowBlocks; ++rb) {
                     const uint32_t r0 = rb * 16u + wr, r1 = r0 + 8u;
@@ -637,7 +633,7 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&s_out_empty[ob]));  // the consumers may refill this buffer
-            if (!whole && !(p.probe & 4u) && p.tagged == nullptr) {
+            if (!whole && p.tagged == nullptr) {
                 // release the partial (all lanes' stores are ordered before lane 0's atomic by the warp
                 // barrier) and learn whether the other owners of this row group are done
                 unsigned int ticket = 0;
@@ -824,7 +820,7 @@ gaf_gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap t
 
         const uint32_t off = kc * kChunkBytes + kh * kPanelBytes;
         const uint32_t bytes = off < p.row_bytes ? min(static_cast<uint32_t>(kPanelBytes), p.row_bytes - off) : 0u;
-        const uint32_t ngroups = (landed && !(p.probe & 1u)) ? bytes / GB : 0u;  // groups of this warp's panel that exist
+        const uint32_t ngroups = landed ? bytes / GB : 0u;  // groups of this warp's panel that exist
         const uint32_t stage_off = stage * Geo::STAGE_BYTES;
         const uint32_t fragb = frag_lane + buf * Plan::FRAG_BUF + ub * unit_frag_bytes + (kh * GPP * WPT * MT * NF) * item_bytes;
         const uint32_t xsb = xs_lane + buf * Plan::XS_BUF + ub * Plan::XS_UNIT + (kh * GPP * MT * 8) * 4u;
@@ -985,6 +981,16 @@ __device__ __forceinline__ void mma_u8s8_16832(int (&d)[4], uint32_t a0, uint32_
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// the gate's activation: 1 = silu (core/src/compute/cuda/kernels/ops/reduction_ops.cu:46-57),
+// 2 = tanh-form gelu (reduction_ops.cu:59-72)
+__device__ __forceinline__ float gate_activation(float g, uint32_t act) {
+    if (act == 2u) {
+        const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+        return 0.5f * g * (1.f + tanhf(inner));
+    }
+    return g / (1.f + __expf(-g));
+}
+
 __device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
     int d;
     asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
@@ -1058,7 +1064,6 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
     __syncthreads();
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    if (pa.probe & 32u) return;
     // every CTA has at least one unit of every operation (the host caps the grid at the smallest unit count)
     if (range_begin(blockIdx.x, pa.units, gridDim.x) >= range_begin(blockIdx.x + 1u, pa.units, gridDim.x)) return;
 
@@ -1086,9 +1091,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                 if (round > 0) ok = mbar_wait(smem_u32(&s_empty[stage]), (round - 1u) & 1u, p.error_word, 0x1u);
                 if (!ok) break;
                 const uint32_t full = smem_u32(&s_full[stage]);
-                if (p.probe & 2u) {
-                    mbar_arrive(full);
-                } else {
+                {
                     const uint32_t base = ring + stage * Geo::STAGE_BYTES;
                     mbar_arrive_expect_tx(full, Geo::STAGE_BYTES);
 #pragma unroll
@@ -1275,7 +1278,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&s_out_empty[ob]));
-            if (!(p.probe & 4u)) {
+            {
                 if (whole) {
                     emit(rg, sum);
                 } else if (p.tagged != nullptr) {
@@ -1478,7 +1481,6 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
     // Two passes so that all of a warp's global loads are in flight together.
     auto prep_block = [&](auto act_c, uint32_t kc_first, uint32_t count, uint32_t buf) {
         constexpr bool ACT = decltype(act_c)::value;  // compile-time: the plain path keeps its loads branch-free
-        if (p.probe & 8u) return;
         if constexpr (IM && !ACT && !XF32) {
             // Four activation rows: a lane takes one packed word's worth (8 consecutive elements, one 16-byte
             // load) of one (unit, group, activation row); the G/8 lanes of a row reduce among themselves.  The
@@ -1565,7 +1567,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                         const size_t gidx = static_cast<size_t>(m) * 2u * p.K + static_cast<size_t>(gi) * G + lane * PER + e;
                         const float gt = __ldcg(reinterpret_cast<const float *>(xbase) + gidx);
                         const float up = __ldcg(reinterpret_cast<const float *>(xbase) + gidx + p.K);
-                        v = gt / (1.f + __expf(-gt)) * up;
+                        v = gate_activation(gt, p.act) * up;
                     } else if constexpr (XF32) {
                         v = reinterpret_cast<const float *>(xbase)[idx];
                     } else {
@@ -1634,7 +1636,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         const uint32_t total = u_end - u_begin;
         const uint32_t first = total < block_len ? total : block_len;
         const uint32_t head = first < block_units ? first : block_units;
-        if (NOPS > 1 && p.act == 1u) {
+        if (NOPS > 1 && p.act != 0u) {
             prep_block(std::true_type{}, kc_begin, head, 0u);
             if (first > head) prep_block(std::true_type{}, (kc_begin + head) % p.chunks, first - head, 1u);
         } else {
@@ -1658,7 +1660,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         }
         const bool exists = kc * GPS + gq < p.groups;  // the last K chunk of a row may hold fewer groups
         if constexpr (IM) {
-            if (landed && exists && !(p.probe & 1u)) {
+            if (landed && exists) {
                 const uint32_t stage_off = stage * Geo::STAGE_BYTES;
                 const uint32_t xq = xq_warp + (buf * BU + ub) * Plan::XQ_UNIT + lane * 8u;
                 uint32_t bfr[WPT][2];  // this group's B registers, kept for all row blocks
@@ -1693,7 +1695,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                 }
             }
         } else
-        if (landed && exists && !(p.probe & 1u)) {
+        if (landed && exists) {
             const uint32_t stage_off = stage * Geo::STAGE_BYTES;
             // packed codes of this lane's rows
             uint32_t w[R][WPG];
@@ -1791,7 +1793,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
             ub = 0u;
             if (more && !whole_k) {
                 const uint32_t left = u_end - (u + 1u);
-                if (NOPS > 1 && p.act == 1u)
+                if (NOPS > 1 && p.act != 0u)
                     prep_block(std::true_type{}, kc_n, left < block_units ? left : block_units, buf ^ 1u);
                 else
                     prep_block(std::false_type{}, kc_n, left < block_units ? left : block_units, buf ^ 1u);
@@ -1919,13 +1921,13 @@ gaf_gather_dequant_f32_kernel(const uint8_t *packed, const uint16_t *scales, con
 // SwiGLU between two separately launched linears: h = silu(gate) * up on bf16 rows [gate | up]
 // (core/src/inference/backend/cpu/kernels/ffn.zig:213-266; CUDA: reduction_ops.cu:46-72).
 __global__ void __launch_bounds__(256)
-gaf_swiglu_bf16_kernel(const __nv_bfloat16 *gu, __nv_bfloat16 *h, uint32_t M, uint32_t d_ff) {
+gaf_swiglu_bf16_kernel(const __nv_bfloat16 *gu, __nv_bfloat16 *h, uint32_t M, uint32_t d_ff, uint32_t act) {
     const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= static_cast<size_t>(M) * d_ff) return;
     const size_t m = i / d_ff, j = i - m * d_ff;
     const float g = __bfloat162float(gu[m * 2u * d_ff + j]);
     const float u = __bfloat162float(gu[m * 2u * d_ff + d_ff + j]);
-    h[i] = __float2bfloat16_rn(g / (1.f + __expf(-g)) * u);
+    h[i] = __float2bfloat16_rn(gate_activation(g, act) * u);
 }
 
 // ---------------------------------------------------------------------------
@@ -1935,12 +1937,29 @@ struct GemvPlan {
     uint32_t rgs, chunks, units, ctas, max_slots;
 };
 
+constexpr int kMaxDevices = 64;
+
+// The opt-in to more than 48 KB of dynamic shared memory is a property of (function, device): set it the first
+// time a kernel instance is launched on each device of the process.
+template <typename Kern>
+cudaError_t opt_in_shared_memory(Kern kern, int bytes, bool (&configured)[kMaxDevices]) {
+    int dev = 0;
+    if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (configured[dev]) return cudaSuccess;
+    if (cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); e != cudaSuccess) return e;
+    configured[dev] = true;
+    return cudaSuccess;
+}
+
 GemvPlan plan_gemv(const WeightView &w, const GemvTuning &tune, int sm_count) {
     GemvPlan pl;
     pl.rgs = (w.N + kRows - 1u) / kRows;
     pl.chunks = (w.row_bytes + kChunkBytes - 1u) / kChunkBytes;
     pl.units = pl.rgs * pl.chunks;
     uint32_t ctas = tune.ctas > 0 ? static_cast<uint32_t>(tune.ctas) : static_cast<uint32_t>(sm_count);
+    // CTAs of one launch wait on one another (split-K collection, the two-operation launch): all must be resident
+    if (ctas > static_cast<uint32_t>(sm_count)) ctas = static_cast<uint32_t>(sm_count);
     if (ctas > pl.units) ctas = pl.units;
     if (ctas < 1u) ctas = 1u;
     pl.ctas = ctas;
@@ -1956,12 +1975,8 @@ cudaError_t launch_stream(const GemvParams &p, const WeightView &w, const Weight
     auto kern = gaf_gemv_stream_kernel<GB, BITS, MT, XF32, SD>;
     using Plan = SmemPlan<GB, MT, XF32>;
     if constexpr (Plan::TOTAL > 227 * 1024) return cudaErrorNotSupported;  // see gemv_mma_max_rows
-    static bool configured = false;  // per instantiation; the attribute belongs to the function, not the stream
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::TOTAL);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static bool configured[kMaxDevices] = {};  // per instantiation and device: the attribute belongs to the function on one device
+    if (cudaError_t e = opt_in_shared_memory(kern, Plan::TOTAL, configured); e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas);
     cfg.blockDim = dim3(kThreads);
@@ -1981,12 +1996,8 @@ cudaError_t launch_dp4a(const GemvParams &p, const WeightView &w, const WeightVi
                         cudaStream_t stream, const GemvParams *second = nullptr) {
     auto kern = gaf_gemv_dp4a_kernel<GB, MD, XF32, SD, NCW, NST, BU, NOPS>;
     using Plan = DpPlan<GB, MD, XF32, NST, BU>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan::TOTAL);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static bool configured[kMaxDevices] = {};
+    if (cudaError_t e = opt_in_shared_memory(kern, Plan::TOTAL, configured); e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas);
     cfg.blockDim = dim3((NCW + 2) * 32);
@@ -2130,7 +2141,7 @@ bool gemv_mma_eligible(const WeightView &w, const void *x, const void *y, bool x
 // fp32 tile [M][N] fits an exchange slot.
 bool gemv_fused_eligible(const WeightView &w, uint32_t M, bool x_f32, const GemvTuning &tune) {
     if (!tune.fuse || !tune.fuse->ok || tune.fuse->size == 0u || tune.fuse->size > static_cast<uint32_t>(kPeerMaxRanks)) return false;
-    if (w.bits != 4u || M == 0u || M > 4u || x_f32 || tune.no_dp4a || tune.probe) return false;
+    if (w.bits != 4u || M == 0u || M > 4u || x_f32 || tune.no_dp4a) return false;
     if (static_cast<size_t>(M) * w.N * 8u > kPeerSlotBytes) return false;  // {value, epoch} words
     return true;
 }
@@ -2162,7 +2173,7 @@ size_t gemv_mma_counter_count(const WeightView &w) {
 
 // the fields every GEMV launch fills the same way
 static GemvParams base_params(const WeightView &w, const void *x, void *y, uint32_t M, const GemvPlan &pl,
-                              unsigned int *d_error_word, uint32_t probe) {
+                              unsigned int *d_error_word) {
     GemvParams p;
     memset(&p, 0, sizeof p);
     p.packed = w.packed;
@@ -2181,7 +2192,6 @@ static GemvParams base_params(const WeightView &w, const void *x, void *y, uint3
     p.chunks = pl.chunks;
     p.units = pl.units;
     p.max_slots = pl.max_slots;
-    p.probe = probe;
     return p;
 }
 
@@ -2196,7 +2206,7 @@ cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bo
     if (need > scratch.partial_bytes || gemv_mma_counter_count(w) > scratch.counter_count)
         return cudaErrorMemoryAllocation;
     const uint32_t gb = w.group * w.bits / 8u;
-    GemvParams p = base_params(w, x, y, M, pl, d_error_word, static_cast<uint32_t>(tune.probe));
+    GemvParams p = base_params(w, x, y, M, pl, d_error_word);
     p.partials = scratch.partials;
     p.counters = scratch.counters;
     // optional hint: the weight the following launch will stream (same unit geometry on either GEMV kernel)
@@ -2256,7 +2266,7 @@ cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bo
 bool gemv_ffn_eligible(const WeightView &w1, const WeightView &w2, const void *x, const void *y, uint32_t M,
                        const GemvTuning &tune) {
     // one activation row only: with two, the two-launch path measured faster (0.41 vs 0.47 ms on the 8B stack)
-    if (M != 1u || tune.no_dp4a || tune.probe) return false;
+    if (M != 1u || tune.no_dp4a) return false;
     if (w1.bits != 4u || w2.bits != 4u || w1.group != w2.group || w1.sdtype != w2.sdtype) return false;
     if (w1.N != 2u * w2.K) return false;
     if (!gemv_mma_eligible(w1, x, y, false)) return false;
@@ -2274,7 +2284,7 @@ size_t gemv_ffn_tagged_bytes(const WeightView &w1, const WeightView &w2, uint32_
 }
 
 cudaError_t gemv_ffn_swiglu(const WeightView &w1, const WeightView &w2, const void *x, float *mid, void *y, uint32_t M,
-                            const Scratch &scratch, unsigned int *grid_bar, const GemvTuning &tune,
+                            uint32_t act, const Scratch &scratch, unsigned int *grid_bar, const GemvTuning &tune,
                             cudaStream_t stream, int sm_count, unsigned int *d_error_word) {
     if (!gemv_ffn_eligible(w1, w2, x, y, M, tune)) return cudaErrorNotSupported;
     GemvTuning t = tune;
@@ -2284,13 +2294,13 @@ cudaError_t gemv_ffn_swiglu(const WeightView &w1, const WeightView &w2, const vo
     const size_t need1 = static_cast<size_t>(pl1.rgs) * pl1.max_slots * kRows * M;  // 64-bit words
     const size_t need2 = static_cast<size_t>(pl2.rgs) * pl2.max_slots * kRows * M;
     if (!scratch.tagged || (need1 + need2) * 8u > scratch.tagged_bytes || !grid_bar) return cudaErrorMemoryAllocation;
-    GemvParams p1 = base_params(w1, x, mid, M, pl1, d_error_word, 0u);
+    GemvParams p1 = base_params(w1, x, mid, M, pl1, d_error_word);
     p1.tagged = scratch.tagged;
     p1.y_f32 = 1u;
     p1.grid_bar = grid_bar;
-    GemvParams p2 = base_params(w2, mid, y, M, pl2, d_error_word, 0u);
+    GemvParams p2 = base_params(w2, mid, y, M, pl2, d_error_word);
     p2.tagged = scratch.tagged + need1;
-    p2.act = 1u;
+    p2.act = act;
     p2.grid_bar = grid_bar;
     if (tune.fuse && gemv_fused_eligible(w2, M, false, tune)) {  // tensor parallel: the sum over ranks rides in the down projection
         for (int r = 0; r < kPeerMaxRanks; ++r) p2.fuse_region[r] = static_cast<uint8_t *>(tune.fuse->region[r]);
@@ -2330,7 +2340,6 @@ constexpr size_t kStaticCounters = 8192;                 // one per 128-row grou
 constexpr size_t kStaticScratchBytes = kStaticPartialBytes + kStaticCounters * sizeof(unsigned int);
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-constexpr int kMaxDevices = 64;
 static void *g_static_ptr[kMaxDevices];  // device address of g_static_scratch, per device (0 = not looked up yet)
 
 size_t gemv_static_scratch_capacity() { return kStaticPartialBytes; }
@@ -2413,11 +2422,36 @@ cudaError_t dequant_f32(const WeightView &w, float *out, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
-cudaError_t swiglu_bf16(const void *gate_up, void *h, uint32_t M, uint32_t d_ff, cudaStream_t stream) {
+// y[m, n] += bias[n] (core/src/inference/backend/cpu/executor/model.zig:134-136, addBiasRows); bf16 y is
+// widened, added in fp32 and rounded once
+template <bool F32>
+__global__ void __launch_bounds__(256)
+gaf_add_bias_rows_kernel(void *y, const float *bias, uint32_t M, uint32_t N) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= static_cast<size_t>(M) * N) return;
+    const float b = bias[i % N];
+    if constexpr (F32)
+        static_cast<float *>(y)[i] += b;
+    else
+        static_cast<__nv_bfloat16 *>(y)[i] = __float2bfloat16_rn(__bfloat162float(static_cast<__nv_bfloat16 *>(y)[i]) + b);
+}
+
+cudaError_t add_bias_rows(void *y, const float *bias, uint32_t M, uint32_t N, bool f32, cudaStream_t stream) {
+    const size_t n = static_cast<size_t>(M) * N;
+    if (n == 0) return cudaSuccess;
+    const unsigned blocks = static_cast<unsigned>((n + 255) / 256);
+    if (f32)
+        gaf_add_bias_rows_kernel<true><<<blocks, 256, 0, stream>>>(y, bias, M, N);
+    else
+        gaf_add_bias_rows_kernel<false><<<blocks, 256, 0, stream>>>(y, bias, M, N);
+    return cudaGetLastError();
+}
+
+cudaError_t swiglu_bf16(const void *gate_up, void *h, uint32_t M, uint32_t d_ff, uint32_t act, cudaStream_t stream) {
     const size_t n = static_cast<size_t>(M) * d_ff;
     if (n == 0) return cudaSuccess;
     gaf_swiglu_bf16_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16 *>(gate_up), static_cast<__nv_bfloat16 *>(h), M, d_ff);
+        static_cast<const __nv_bfloat16 *>(gate_up), static_cast<__nv_bfloat16 *>(h), M, d_ff, act);
     return cudaGetLastError();
 }
 

@@ -46,7 +46,7 @@ struct GemvTuning {
     int force_generic;  // use the shape-agnostic kernel even when the fast path applies
     int reserved0;      // (was a tuning switch; kept so that the initialiser lists stay put)
     int no_dp4a;        // keep M <= 2 on the tensor-core formulation (for A/B comparisons)
-    int probe;          // measurement aid for the streaming GEMV (0 = off); results are wrong when set
+    int wait_limit;     // polls (with back-off) a device-side wait on another CTA or rank makes before it gives up (0 = default)
     int prefetch_units; // units at the head of each CTA range of the hinted next weight to pull into L2
     const WeightView *next;  // the weight the following launch will stream (one-shot hint; may be null)
     const struct PeerComm *fuse;  // sum the outputs over the ranks inside the GEMV (per call; may be null)
@@ -70,10 +70,13 @@ bool gemv_ffn_eligible(const WeightView &w1, const WeightView &w2, const void *x
                        const GemvTuning &tune);
 size_t gemv_ffn_tagged_bytes(const WeightView &w1, const WeightView &w2, uint32_t M, const GemvTuning &tune, int sm_count);
 cudaError_t gemv_ffn_swiglu(const WeightView &w1, const WeightView &w2, const void *x, float *mid, void *y, uint32_t M,
-                            const Scratch &scratch, unsigned int *grid_bar, const GemvTuning &tune,
+                            uint32_t act, const Scratch &scratch, unsigned int *grid_bar, const GemvTuning &tune,
                             cudaStream_t stream, int sm_count, unsigned int *d_error_word);
-// h[m][j] = silu(gu[m][j]) * gu[m][d_ff + j], bf16 in / out (the step between the two linears when they run apart)
-cudaError_t swiglu_bf16(const void *gate_up, void *h, uint32_t M, uint32_t d_ff, cudaStream_t stream);
+// h[m][j] = act(gu[m][j]) * gu[m][d_ff + j], bf16 in / out (the step between the two linears when they run apart);
+// act: 1 = silu, 2 = tanh-form gelu
+cudaError_t swiglu_bf16(const void *gate_up, void *h, uint32_t M, uint32_t d_ff, uint32_t act, cudaStream_t stream);
+// y[m][n] += bias[n] in place (y f32 or bf16, bias f32 on the device)
+cudaError_t add_bias_rows(void *y, const float *bias, uint32_t M, uint32_t N, bool f32, cudaStream_t stream);
 bool gemv_fused_eligible(const WeightView &w, uint32_t M, bool x_f32, const GemvTuning &tune);
 size_t gemv_mma_scratch_bytes(const WeightView &w, uint32_t M, const GemvTuning &tune, int sm_count);
 size_t gemv_mma_counter_count(const WeightView &w);
@@ -130,7 +133,10 @@ struct PeerComm {
 size_t peer_region_bytes();
 // In-place sum of d_buf[count] (bf16 or f32) over the ranks.  cudaErrorNotSupported when the tile does not
 // fit a slot or the peer mapping is unavailable (the caller then uses NCCL).
+// wait_limit: polls per awaited word before a rank gives up (0 = the default of several seconds).
+// expect_absent_rank: diagnostic - also wait for the words of rank `size`, which nobody writes, so that the
+// bounded wait runs out by design (size < kPeerMaxRanks only).
 cudaError_t peer_allreduce(const PeerComm &pc, void *d_buf, size_t count, bool f32, bool pdl, cudaStream_t stream,
-                           unsigned int *d_error_word);
+                           unsigned int *d_error_word, uint32_t wait_limit = 0, bool expect_absent_rank = false);
 
 }  // namespace tgaf

@@ -35,6 +35,8 @@ constexpr uint32_t kPeerWaitLimit = 1u << 23;  // polls with back-off (several s
 struct PeerArgs {
     uint8_t *region[kPeerMaxRanks];  // every rank's region as mapped here; [rank] is the local one
     uint32_t rank, size;
+    uint32_t wait_size;   // ranks whose words are awaited (= size, or size + 1 for the diagnostic that makes a wait run out)
+    uint32_t wait_limit;  // polls per awaited word
     unsigned int *error_word;
 };
 
@@ -83,11 +85,11 @@ peer_allreduce_kernel(const PeerArgs a, void *buf, uint32_t count) {
         reinterpret_cast<const unsigned long long *>(mine + kDataOff + static_cast<size_t>(phase) * kPeerMaxRanks * kPeerSlotBytes);
     for (uint32_t i = lo + tid; i < hi; i += blockDim.x) {
         float acc = 0.f;
-        for (uint32_t r = 0; r < a.size; ++r) {
+        for (uint32_t r = 0; r < a.wait_size; ++r) {
             const unsigned long long *src = data + r * (kPeerSlotBytes / 8u) + i;
             unsigned long long word = 0ull;
             bool got = false;
-            for (uint32_t it = 0; it < kPeerWaitLimit; ++it) {
+            for (uint32_t it = 0; it < a.wait_limit; ++it) {
                 asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(word) : "l"(src) : "memory");
                 if (static_cast<uint32_t>(word >> 32) == epoch) {
                     got = true;
@@ -113,7 +115,7 @@ peer_allreduce_kernel(const PeerArgs a, void *buf, uint32_t count) {
 size_t peer_region_bytes() { return kPeerRegionBytes; }
 
 cudaError_t peer_allreduce(const PeerComm &pc, void *d_buf, size_t count, bool f32, bool pdl, cudaStream_t stream,
-                           unsigned int *d_error_word) {
+                           unsigned int *d_error_word, uint32_t wait_limit, bool expect_absent_rank) {
     // one 64-bit word per element in a slot
     if (!pc.ok || count == 0 || count * 8u > kPeerSlotBytes || reinterpret_cast<uintptr_t>(d_buf) % (f32 ? 4u : 2u) != 0)
         return cudaErrorNotSupported;
@@ -121,6 +123,8 @@ cudaError_t peer_allreduce(const PeerComm &pc, void *d_buf, size_t count, bool f
     for (int r = 0; r < kPeerMaxRanks; ++r) a.region[r] = static_cast<uint8_t *>(pc.region[r]);
     a.rank = pc.rank;
     a.size = pc.size;
+    a.wait_size = pc.size + ((expect_absent_rank && pc.size < static_cast<uint32_t>(kPeerMaxRanks)) ? 1u : 0u);
+    a.wait_limit = wait_limit ? wait_limit : kPeerWaitLimit;
     a.error_word = d_error_word;
     const uint32_t n = static_cast<uint32_t>(count);
     // always the full grid: every CTA's epoch advances on every call, on every rank

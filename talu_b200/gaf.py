@@ -185,6 +185,26 @@ def linear(ctx: Context, w: Weight, x, out=None):
     return out
 
 
+def linear_bias(ctx: Context, w: Weight, x, bias, out=None):
+    """`linear` followed by y[m, n] += bias[n] (the reference's Linear.forward with its optional bias,
+    core/src/inference/backend/cpu/executor/model.zig:98-139).  bias: torch f32 [N] on the device, or None."""
+    import torch
+    if x.dim() != 2 or x.shape[1] != w.K:
+        raise GafError(_STATUS_INVALID_ARGUMENT, f"x must be [M, {w.K}], got {tuple(x.shape)}")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != w.N):
+        raise GafError(_STATUS_INVALID_ARGUMENT, f"bias must be f32 [{w.N}]")
+    x = x.contiguous()
+    M = x.shape[0]
+    if out is None:
+        out = torch.empty((M, w.N), dtype=x.dtype, device=x.device)
+    fn = {torch.bfloat16: ctx._lib.tgaf_linear_bf16_bias, torch.float32: ctx._lib.tgaf_linear_f32_bias}.get(x.dtype)
+    if fn is None:
+        raise GafError(_STATUS_INVALID_ARGUMENT, f"unsupported activation dtype {x.dtype}")
+    ctx._check(fn(ctx._h, w._h, C.c_void_p(x.data_ptr()), M, C.c_void_p(bias.data_ptr() if bias is not None else 0),
+                  C.c_void_p(out.data_ptr())))
+    return out
+
+
 def linear_allreduce(ctx: Context, w: Weight, x, out=None):
     """`linear` on a row-parallel weight followed by the sum over the communicator's ranks
     (tgaf_linear_bf16_allreduce; one kernel for M <= 2 when the peer-memory path is up).  bf16 only."""
@@ -200,8 +220,13 @@ def linear_allreduce(ctx: Context, w: Weight, x, out=None):
     return out
 
 
-def ffn_swiglu(ctx: Context, w_gate_up: Weight, w_down: Weight, x, out=None, allreduce: bool = False):
-    """y = down(silu(gate(x)) * up(x)) with the stacked gate|up weight (tgaf_ffn_swiglu_bf16[_allreduce])."""
+ACT_SILU, ACT_GELU = 1, 2
+
+
+def ffn_swiglu(ctx: Context, w_gate_up: Weight, w_down: Weight, x, out=None, allreduce: bool = False,
+               activation: int = ACT_SILU):
+    """y = down(act(gate(x)) * up(x)) with the stacked gate|up weight (tgaf_ffn_swiglu_bf16[_allreduce];
+    tgaf_ffn_gated_bf16 for ACT_GELU, the reference's use_gelu variant)."""
     import torch
     if x.dim() != 2 or x.shape[1] != w_gate_up.K or x.dtype != torch.bfloat16:
         raise GafError(_STATUS_INVALID_ARGUMENT, f"x must be bf16 [M, {w_gate_up.K}], got {x.dtype} {tuple(x.shape)}")
@@ -210,6 +235,12 @@ def ffn_swiglu(ctx: Context, w_gate_up: Weight, w_down: Weight, x, out=None, all
     M = x.shape[0]
     if out is None:
         out = torch.empty((M, w_down.N), dtype=x.dtype, device=x.device)
+    if activation != ACT_SILU:
+        if allreduce:
+            raise GafError(_STATUS_INVALID_ARGUMENT, "the all-reduce form takes the silu activation only")
+        ctx._check(ctx._lib.tgaf_ffn_gated_bf16(ctx._h, w_gate_up._h, w_down._h, C.c_void_p(x.data_ptr()), M, activation,
+                                                C.c_void_p(out.data_ptr())))
+        return out
     fn = ctx._lib.tgaf_ffn_swiglu_bf16_allreduce if allreduce else ctx._lib.tgaf_ffn_swiglu_bf16
     ctx._check(fn(ctx._h, w_gate_up._h, w_down._h, C.c_void_p(x.data_ptr()), M, C.c_void_p(out.data_ptr())))
     return out

@@ -42,3 +42,78 @@ def torch_bf16_from_bits(bits_u16, device):
 def bits_from_torch_bf16(t):
     import torch
     return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+class CubinModule:
+    """A cubin loaded the way talu's registry loads one (cuModuleLoadData + cuModuleGetFunction) and launched
+    the way its wrappers launch (cuLaunchKernel, block 256, no dynamic shared memory;
+    core/src/compute/cuda/gaffine_u4_matvec.zig:87-96).  Arguments: torch tensors (passed as device
+    pointers) and Python ints (passed as u32)."""
+
+    def __init__(self, path):
+        import torch
+        from cuda.bindings import driver as cu
+        self._cu = cu
+        torch.cuda.init()
+        torch.zeros(1, device="cuda")                      # the primary context talu's backend would also use
+        self.mod = self._ok(cu.cuModuleLoadData(open(path, "rb").read()))
+        self._fns = {}
+
+    @staticmethod
+    def _ok(res):
+        assert int(res[0]) == 0, res[0]
+        return res[1] if len(res) == 2 else res[1:]
+
+    def launch(self, symbol, grid, args, block=256):
+        import ctypes
+        import torch
+        cu = self._cu
+        if symbol not in self._fns:
+            self._fns[symbol] = self._ok(cu.cuModuleGetFunction(self.mod, symbol.encode()))
+        vals = tuple(a.data_ptr() if hasattr(a, "data_ptr") else int(a) for a in args)
+        types = tuple(ctypes.c_void_p if hasattr(a, "data_ptr") else ctypes.c_uint32 for a in args)
+        stream = torch.cuda.current_stream().cuda_stream
+        (err,) = cu.cuLaunchKernel(self._fns[symbol], grid[0], grid[1], 1, block, 1, 1, 0, stream, (vals, types), 0)
+        assert int(err) == 0, err
+
+
+def to_dev(a):
+    """numpy u32 / u16 / f32 array -> torch device tensor of the same bits."""
+    import torch
+    a = np.ascontiguousarray(a)
+    view = {np.dtype(np.uint32): np.int32, np.dtype(np.uint16): np.int16}.get(a.dtype)
+    return torch.from_numpy(a.view(view) if view else a).cuda()
+
+
+def matvec_u4(mod, x, packed, scales, biases, group, tag=1, symbol="talu_gaffine_u4_matvec_f32"):
+    """One launch of the ten-argument matvec kernel under the reference's geometry: grid (ceil(N / 8), M)."""
+    import torch
+    M, K = x.shape
+    N = packed.shape[0]
+    dx, dp, ds, db = to_dev(x), to_dev(packed), to_dev(scales), to_dev(biases)
+    dy = torch.full((M, N), float("nan"), device="cuda")
+    mod.launch(symbol, ((N + 7) // 8, M), (dx, dp, ds, db, dy, K, N, group, tag, M))
+    torch.cuda.synchronize()
+    return dy.cpu().numpy()
+
+
+def matvec_u4_fused(mod, symbol, x, parts, in_dim, tag=1):
+    """The fused q|k|v (three parts) or gate|up (two parts) launch: per part (packed, scales, biases, group);
+    grid.x = ceil(sum of the output dims / 8) (gaffine_u4_matvec_qkv.zig:193-198, _gate_up.zig:79-85)."""
+    import torch
+    M = x.shape[0]
+    dx = to_dev(x)
+    args, outs, total = [dx], [], 0
+    keep = []
+    for packed, scales, biases, group in parts:
+        n = packed.shape[0]
+        dp, ds, db = to_dev(packed), to_dev(scales), to_dev(biases)
+        dy = torch.full((M, n), float("nan"), device="cuda")
+        keep += [dp, ds, db]
+        args += [dp, ds, db, dy, n, group, tag]
+        outs.append(dy)
+        total += n
+    args += [in_dim, M]
+    mod.launch(symbol, ((total + 7) // 8, M), tuple(args))
+    torch.cuda.synchronize()
+    return [o.cpu().numpy() for o in outs]

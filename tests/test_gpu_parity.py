@@ -242,7 +242,10 @@ def test_split_k_is_deterministic_and_tunable(gaf, ctx, oracle):
     x = torch_bf16_from_bits(xb, "cuda:0")
     ref = oracle.matmul_f32(xf, p, s, b, 64, 4)
     try:
-        for ctas in [0, 1, 2, 3, 7, 33, 79, 80, 500]:
+        with pytest.raises(gaf.GafError) as ei:      # more CTAs than SMs could not all be resident: refused
+            ctx.set_option("gemv_ctas", 500)
+        assert ei.value.invalid_argument
+        for ctas in [0, 1, 2, 3, 7, 33, 79, 80, 148]:
             ctx.set_option("gemv_ctas", ctas)
             y1 = gaf.linear(ctx, w, x).clone()
             y2 = gaf.linear(ctx, w, x).clone()
@@ -328,7 +331,7 @@ def test_one_rank_communicator_runs_the_peer_memory_kernels(gaf, oracle):
                     y1 = gaf.linear_allreduce(ctx1, w, x)
                     ctx1.synchronize()
                     assert torch.equal(y0, y1), (N, K, G, M, rep)
-                for ctas in (1, 7, 500):
+                for ctas in (1, 7, 148):
                     ctx1.set_option("gemv_ctas", ctas)
                     y2 = gaf.linear_allreduce(ctx1, w, x)
                     ctx1.synchronize()

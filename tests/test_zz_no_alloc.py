@@ -77,3 +77,44 @@ def test_fixed_scratch_refuses_what_does_not_fit(gaf, oracle):
         w.free()
     finally:
         ctx.close()
+
+
+def test_fixed_scratch_allocates_nothing(gaf, oracle):
+    """The property the entry point exists for: free device memory (cudaMemGetInfo) is the same before and
+    after its calls.  The first call on a device is made beforehand (it looks the fixed array's address up,
+    which is also when the driver materialises the library's image on that device).  The measured calls use a
+    shape whose split-K scratch on the regular path (4 MiB of tagged words) is larger than anything this
+    fresh context holds, so a call that grew the context's scratch would show as lost memory."""
+    import torch
+    ctx = gaf.Context(0)
+    try:
+        rng = np.random.default_rng(1)
+        small = gaf.Weight.from_host(ctx, *make_weights(oracle, 256, 1024, 64, 4, seed=1), 64, 4)
+        N, K, G, M = 65536, 512, 64, 4
+        p = rng.integers(0, 2 ** 32, size=(N, K // 8), dtype=np.uint32)
+        s = np.full((N, K // G), 0x3C00, np.uint16)        # bf16 2^-7
+        b = np.full((N, K // G), 0xBD80, np.uint16)        # bf16 -2^-4
+        big = gaf.Weight.from_host(ctx, p, s, b, G, 4)
+        xs = torch_bf16_from_bits(make_x_bf16(oracle, 1, 1024, seed=2)[0], "cuda:0")
+        ys = torch.empty((1, 256), dtype=torch.bfloat16, device="cuda:0")
+        xb, xf = make_x_bf16(oracle, M, K, seed=3)
+        x = torch_bf16_from_bits(xb, "cuda:0")
+        y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda:0")
+        call = lambda w, xi, yi, m: ctx._lib.tgaf_linear_bf16_fixed_scratch(ctx._h, w._h, C.c_void_p(xi.data_ptr()), m,
+                                                                            C.c_void_p(yi.data_ptr()))
+        assert call(small, xs, ys, 1) == 0                 # first call on the device: set-up
+        ctx.synchronize()
+        torch.cuda.synchronize()
+        free0, _ = torch.cuda.mem_get_info()
+        for _ in range(2):
+            assert call(big, x, y, M) == 0, ctx._lib.tgaf_last_error(ctx._h)
+        ctx.synchronize()
+        torch.cuda.synchronize()
+        free1, _ = torch.cuda.mem_get_info()
+        assert free1 == free0, f"{free0 - free1} bytes of device memory went during allocation-free calls"
+        got = oracle.bf16_to_f32(bits_from_torch_bf16(y))
+        assert rel_err(got, oracle.matmul_f32(xf, p, s, b, G, 4)) <= TOL_BF16
+        small.free()
+        big.free()
+    finally:
+        ctx.close()
