@@ -95,14 +95,15 @@ def test_fixed_scratch_allocates_nothing(gaf, oracle):
         s = np.full((N, K // G), 0x3C00, np.uint16)        # bf16 2^-7
         b = np.full((N, K // G), 0xBD80, np.uint16)        # bf16 -2^-4
         big = gaf.Weight.from_host(ctx, p, s, b, G, 4)
-        xs = torch_bf16_from_bits(make_x_bf16(oracle, 1, 1024, seed=2)[0], "cuda:0")
-        ys = torch.empty((1, 256), dtype=torch.bfloat16, device="cuda:0")
+        xs = torch_bf16_from_bits(make_x_bf16(oracle, 4, 1024, seed=2)[0], "cuda:0")
+        ys = torch.empty((4, 256), dtype=torch.bfloat16, device="cuda:0")
         xb, xf = make_x_bf16(oracle, M, K, seed=3)
         x = torch_bf16_from_bits(xb, "cuda:0")
         y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda:0")
         call = lambda w, xi, yi, m: ctx._lib.tgaf_linear_bf16_fixed_scratch(ctx._h, w._h, C.c_void_p(xi.data_ptr()), m,
                                                                             C.c_void_p(yi.data_ptr()))
         assert call(small, xs, ys, 1) == 0                 # first call on the device: set-up
+        assert call(small, xs, ys, 4) == 0                 # and the first launch of the kernel the measured calls use
         ctx.synchronize()
         torch.cuda.synchronize()
         free0, _ = torch.cuda.mem_get_info()
