@@ -267,6 +267,12 @@ def run_single(args):
     if args.quick and args.case == "prefill":
         print(json.dumps({"quick": True, "prefill": time_prefill(gaf, ctx, torch, stream, rng, iters=2)}))
         return
+    if args.quick and args.case == "stack70b":
+        from talu_b200 import tp_bench
+        ms, nbytes, *_ = tp_bench.measure(args, existing_ctx=ctx, existing_stream=stream, M=args.m)
+        print(json.dumps({"quick": True, "workload": "llama3_70b_stack", "M": args.m, "layers": args.layers,
+                          "ms_per_step": ms, "gbs": round(nbytes / ms / 1e6, 2)}))
+        return
     results = {}
     clocks = ClockSampler(dev)
     with clocks:
@@ -374,9 +380,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=12, help="distinct FFN layers in the weight ring")
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="length of the CPU-baseline sample")
-    ap.add_argument("--case", default="decode", choices=["decode", "prefill"],
+    ap.add_argument("--case", default="decode", choices=["decode", "prefill", "stack70b"],
                     help="with --quick: which kernel the small case runs")
-    ap.add_argument("--m", type=int, default=1, help="activation rows of the --quick decode case (1..16)")
+    ap.add_argument("--m", type=int, default=1, help="activation rows of the --quick decode / stack70b case")
     ap.add_argument("--quick", action="store_true",
                     help="M = 1 only, no end-to-end and no CPU leg (small case for profilers; not a bench value)")
     args = ap.parse_args()

@@ -106,6 +106,11 @@ struct tgaf_ctx {
     void *ffn_mid = nullptr;
     size_t ffn_mid_bytes = 0;
     unsigned int *d_grid_bar = nullptr;
+    // tensor-core GEMM: one fp32 partial tile per CTA and the flags that announce them
+    float *gemm_ws = nullptr;
+    size_t gemm_ws_bytes = 0;
+    unsigned int *gemm_flags = nullptr;
+    size_t gemm_flag_count = 0;
     NcclComm comm = nullptr;
     uint32_t comm_rank = 0, comm_size = 1;
     PeerComm peer = {{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr}, 0, 1, false};
@@ -238,7 +243,17 @@ int32_t linear_device(tgaf_ctx *ctx, const WeightView &w, const void *x, uint32_
     TGAF_CUDA(ctx, cudaSetDevice(ctx->device));  // scratch growth and launches below belong to the context's device
 
     if (!f32 && gemm_tc_eligible(w, M)) {
-        cudaError_t e = gemm_tc(w, x, y, M, ctx->stream, ctx->sm_count, ctx->d_error_word);
+        if (!ctx->gemm_ws) {
+            // first GEMM on this context: the split-tile workspace (38 MB on 148 SMs) and its flags
+            const size_t wb = gemm_tc_workspace_bytes(ctx->sm_count), fc = gemm_tc_flag_count(ctx->sm_count);
+            TGAF_CUDA(ctx, cudaMalloc(reinterpret_cast<void **>(&ctx->gemm_flags), fc * sizeof(unsigned int)));
+            ctx->gemm_flag_count = fc;
+            TGAF_CUDA(ctx, cudaMemsetAsync(ctx->gemm_flags, 0, fc * sizeof(unsigned int), ctx->stream));
+            TGAF_CUDA(ctx, cudaMalloc(reinterpret_cast<void **>(&ctx->gemm_ws), wb));
+            ctx->gemm_ws_bytes = wb;
+        }
+        cudaError_t e = gemm_tc(w, x, y, M, ctx->stream, ctx->sm_count, ctx->d_error_word, ctx->gemm_ws, ctx->gemm_ws_bytes,
+                                ctx->gemm_flags, ctx->gemm_flag_count);
         if (e == cudaSuccess)
             return reduce ? allreduce_device(ctx, y, static_cast<uint64_t>(M) * w.N, TGAF_DTYPE_BF16) : TGAF_OK;
         if (e != cudaErrorNotSupported) return cuda_fail(ctx, e, "gemm_tc");
@@ -530,6 +545,8 @@ int32_t tgaf_ctx_destroy(tgaf_ctx *ctx) {
     if (ctx->d2h_stream) cudaStreamDestroy(ctx->d2h_stream);
     if (ctx->ffn_mid) cudaFree(ctx->ffn_mid);
     if (ctx->d_grid_bar) cudaFree(ctx->d_grid_bar);
+    if (ctx->gemm_ws) cudaFree(ctx->gemm_ws);
+    if (ctx->gemm_flags) cudaFree(ctx->gemm_flags);
     if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return TGAF_OK;
@@ -640,6 +657,7 @@ int32_t tgaf_synchronize(tgaf_ctx *ctx) {
         if (ctx->scratch.counters) cudaMemset(ctx->scratch.counters, 0, ctx->scratch.counter_count * sizeof(unsigned int));
         if (ctx->scratch.tagged) cudaMemset(ctx->scratch.tagged, 0, ctx->scratch.tagged_bytes);  // ... or tags set
         if (ctx->d_grid_bar) cudaMemset(ctx->d_grid_bar, 0, 4 * sizeof(unsigned int));
+        if (ctx->gemm_flags) cudaMemset(ctx->gemm_flags, 0, ctx->gemm_flag_count * sizeof(unsigned int));
         return fail(ctx, TGAF_ERR_DEVICE_FLAG, "a kernel gave up a bounded wait (code 0x%x)", flag);
     }
     return TGAF_OK;

@@ -1,60 +1,95 @@
-// Prefill dequant-GEMM for gaf4 weights on the 5th-generation tensor cores.
+// Dequant-GEMM for grouped-affine weights on the 5th-generation tensor cores (M > 16).
 //
-//   y[M, N] (bf16) = x[M, K] (bf16) * W^T,  W[n, k] = q * scale + bias (gaf4, group 32 / 64 / 128)
+//   y[M, N] (bf16) = x[M, K] (bf16) * W^T,  W[n, k] = q * scale + bias (gaf4 / gaf8, group 32 / 64 / 128)
 //
-// Replaces, for large M, the CPU 4x2 micro-kernel path (core/src/compute/cpu/matmul_prefill.zig:121-358)
-// and the reference CUDA backend's loop of the matvec kernel over rows
+// Replaces, for M > 16, the CPU 4x2 micro-kernel paths (core/src/compute/cpu/matmul_prefill.zig:121-358 for
+// 4-bit codes, :572-759 for 8-bit codes) and the reference CUDA backend's loop of the matvec kernel over rows
 // (core/src/inference/backend/cuda/engine.zig:4433-4473).
 //
-// One persistent CTA per SM computes 256 x 256 output tiles:
-//   * warp 0 (one lane): TMA producer.  Per 64-deep K block it loads two 128-row x 64 activation
-//     tiles (128-byte swizzle, the layout the MMA descriptor names) and the packed codes of 256
-//     weight rows (256 x 32 bytes) into a 3-stage shared-memory ring.
-//   * warps 2..9 (256 threads, one weight row each): unpack the 64 codes of their row, apply
-//     scale and bias in bf16 (one fused multiply-add per pair, a single rounding of q*s+b), and
-//     write the row of the K-major bf16 B tile with the same 128-byte swizzle.
-//   * warp 1 (one lane): issues tcgen05.mma (128 x 256 x 16, bf16 -> fp32) for the two 128-row
-//     halves of the tile, accumulators in tensor memory (2 x 256 columns), and commits to the
-//     ring's mbarriers.
-//   * after the last K block warps 2..9 read the accumulators back (tcgen05.ld), round to bf16
-//     and store y.
-// Tiles are walked N-tile major so that the CTAs running at the same time share weight rows in L2.
+// One persistent CTA per SM.  A = activations (two 128-row halves of a 256-row tile when M > 128 and the codes
+// are 4-bit; one half otherwise), B = 256 weight rows: D[128 x 256] in tensor memory per half.  Roles:
+//   * warp 0 (one lane): TMA producer.  Per 64-deep K block it loads the activation tile (128-byte swizzle,
+//     the layout the MMA descriptor names) into a stage of the ring; per 128 (or 64) packed bytes of K it loads
+//     the packed codes of 256 weight rows into a ring of their own, which the dequant warps hand back.
+//   * warps 2..17 (512 threads, half a weight row each): unpack the 32 codes of their half row, apply scale
+//     and bias and write their 64 bytes of the K-major bf16 weight tile (same 128-byte swizzle) into the
+//     stage.  4-bit codes with bf16 scales: the affine runs in bf16 (one fused multiply-add per pair, a
+//     single rounding of q*s+b); 8-bit codes and f16 scales: fmaf(q, s, b) in fp32 (exact product), then one
+//     rounding to bf16.  Scales and biases are fetched eight groups at a time, one fetch ahead of their use.
+//     A waiting warp polls with one lane and backs off: polling by all 512 threads floods the pipeline that
+//     the copy and MMA issuing threads go through too.
+//   * warp 1 (one lane): issues tcgen05.mma (bf16 -> fp32, 128 x 256 x 16), accumulators in tensor memory, and
+//     commits to the ring's mbarriers.  This thread is the pace-maker (a timeline of one CTA showed ~250 cycles
+//     per mbarrier wait even when satisfied, ~100 per tcgen05 instruction, against 135 cycles of tensor work per
+//     MMA), so per K block it waits ONCE (the dequant warps signal only after the activation tile has landed
+//     too) and commits ONCE (activation tile and weight tile live in the same stage).  An earlier form with
+//     the weights as the A operand for M <= 128 (tensor work proportional to M) needed twice as many MMA
+//     instructions per K block and was slower for that reason alone.
+//   * warps 2..17 again: read the accumulators back (tcgen05.ld), round to bf16 and store y.
 //
-// All waits on mbarriers are bounded; a wait that runs out sets the host-visible error word and
-// a CTA-wide abort flag, every role then falls through to the common exit where tensor memory is
+// Work is dealt stream-K fashion: the (tile, K block) pairs of the whole problem, tile-major, are cut into
+// equal contiguous ranges, one per CTA, so every SM gets the same number of K blocks whatever the tile count
+// (a 70B-shaped o / down projection at M = 64 has 32 tiles; the prefill benchmark shape has 448 = 3.03 waves).
+// A CTA whose range covers only part of a tile's K blocks either owns the tile (it holds K block 0: it gets
+// there at the END of its range) or parks its fp32 partial tile in its workspace slot and raises a flag.  The
+// owner adds the partials in CTA order (reproducible sums) and clears the flags.  A CTA writes at most one
+// partial per launch, so the workspace is one tile per CTA.
+//
+// All waits (mbarriers, flags of other CTAs) are bounded; a wait that runs out sets the host-visible error
+// word and a CTA-wide abort flag, every role then falls through to the common exit where tensor memory is
 // released.
 #include "gaf_internal.h"
 
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 namespace tgaf {
 namespace {
 
-constexpr int kBM = 256;           // tile rows of x (two UMMA M = 128 halves)
-constexpr int kBN = 256;           // tile rows of W (UMMA N)
+constexpr int kBN = 256;           // weight rows per tile
 constexpr int kBK = 64;            // K block: 64 bf16 = 128 bytes, the swizzle span
-constexpr int kStagesTc = 3;
-constexpr int kATile = 128 * 128;  // 128 rows x 128 bytes
-constexpr int kBTile = kBN * 128;  // 256 rows x 128 bytes
-constexpr int kPTile = kBN * 32;   // packed codes: 256 rows x 32 bytes
-constexpr int kStageTc = 2 * kATile + kBTile + kPTile;  // 73728
-constexpr int kSmemTc = kStagesTc * kStageTc + 1024;
+constexpr int kMaxStages = 4;      // stage ring: activation tile + dequantized weight tile of one K block
+constexpr int kHalfTile = 128 * 128;  // 128 rows x 128 bytes
+constexpr int kWTile = kBN * 128;     // 256 weight rows x 128 bytes of bf16
 constexpr int kDequantWarps = 8;
 constexpr int kThreadsTc = (2 + kDequantWarps) * 32;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kWaitLimitTc = 1u << 22;
+constexpr uint32_t kTileFloats = 256 * 256;   // workspace slot of one CTA (fp32 partial tile)
+
+// Optional timeline of one CTA (debug builds with -DTGAF_GEMM_TRACE only): SM clock at the hand-over points of
+// the first kTraceLen K blocks, read back by tgaf_debug_gemm_trace.
+#ifdef TGAF_GEMM_TRACE
+constexpr int kTraceLen = 256, kTraceRows = 12;
+__device__ unsigned long long g_gemm_trace[kTraceRows][kTraceLen];
+#define TGAF_TRACE(row, idx)                                                                    \
+    do {                                                                                        \
+        if (blockIdx.x == 1u && (idx) < static_cast<uint32_t>(kTraceLen)) g_gemm_trace[row][idx] = clock64(); \
+    } while (0)
+#else
+#define TGAF_TRACE(row, idx) \
+    do {                     \
+    } while (0)
+#endif
 
 struct GemmParams {
     const uint16_t *scales;
     const uint16_t *biases;
     void *y;
+    float *ws;              // [ctas][kTileFloats] partial tiles
+    unsigned int *flags;    // [ctas][kDequantWarps], zero between launches
     unsigned int *error_word;
     uint32_t M, N, K;
     uint32_t groups;   // K / G
     uint32_t group;    // G
     uint32_t sdtype;   // 1 bf16, 0 f16
     uint32_t m_tiles, n_tiles, k_blocks;
+    uint32_t bm;            // activation rows per tile: 256 or 128
+    uint32_t x_bytes;       // activation bytes per stage
+    uint32_t stages;        // depth of the stage ring
+    uint32_t total_units;   // tiles * k_blocks
+    uint32_t wait_limit;    // polls for another CTA's flag
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -80,19 +115,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait that also gives up as soon as another role has raised the abort flag.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
-                                          unsigned int *error_word, uint32_t code) {
+// Bounded wait that also gives up once another role has raised the abort flag.  Every lane waits in the
+// try_wait itself (which suspends the thread in hardware until the phase completes or a time-out): a version
+// that polled with one lane and slept between polls lost more in wake-up latency at each hand-over of the
+// pipeline (three or four per K block) than it saved in polling traffic.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                               unsigned int *error_word, uint32_t code) {
     for (uint32_t it = 0; it < kWaitLimitTc; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (it > 64) {
-            if (*abort_flag) return false;
-            __nanosleep(it > 4096 ? 128 : 20);
-        }
+        if ((it & 255u) == 255u && *abort_flag) return false;
     }
     atomicOr(error_word, code);
     *abort_flag = 1u;
     return false;
+}
+// One lane of a converged warp.  The copy and MMA issuing warps run their loops with all lanes, so that ring
+// positions, addresses and descriptors are warp-uniform values (the compiler keeps them in uniform registers, which
+// is where tcgen05 and TMA instructions take their operands from), and only the issuing instruction is elected.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xFFFFFFFF;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0u;
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tmap, uint32_t c0, uint32_t c1, uint32_t bar) {
     asm volatile(
@@ -116,8 +163,10 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     d |= static_cast<uint64_t>(2) << 61;                      // layout: 128-byte swizzle
     return d;
 }
-// bf16 x bf16 -> f32, both operands K-major, M = 128, N = 256
-constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((128u >> 4) << 24);
+// bf16 x bf16 -> f32, both operands K-major, M = 128, N = n (a multiple of 16, 16..256)
+__device__ __forceinline__ uint32_t instr_desc(uint32_t n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+}
 
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -125,6 +174,15 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// the same with the accumulate flag fixed to "add to the accumulator"
+__device__ __forceinline__ void umma_f16_acc(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.eq.b32 p, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -142,45 +200,85 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "memory");
 }
 
-// one of the eight 16-bit values held in a uint4, as a bf16x2 register {v, v} (f16 sources are converted)
-__device__ __forceinline__ uint32_t pick_pair(const uint4 &v, uint32_t idx, uint32_t sdtype) {
-    const uint32_t w = (idx & 4u) ? ((idx & 2u) ? v.w : v.z) : ((idx & 2u) ? v.y : v.x);
-    uint32_t h = (idx & 1u) ? (w >> 16) : (w & 0xFFFFu);
-    if (sdtype == 0u) {
-        const float f = __half2float(__ushort_as_half(static_cast<unsigned short>(h)));
-        h = __bfloat16_as_ushort(__float2bfloat16_rn(f));  // only exact for f16 values with <= 8 significant bits
-    }
-    return h | (h << 16);
+__device__ __forceinline__ float sb_f32(uint32_t raw, uint32_t sdtype) {
+    // core/src/compute/cuda/kernels/ops/common_decode.cuh:1-13
+    if (sdtype == 0u) return __half2float(__ushort_as_half(static_cast<unsigned short>(raw)));
+    return __uint_as_float(raw << 16);
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
 }
 
+// contiguous, near-equal unit ranges: the first `rem` CTAs take one unit more
+__device__ __forceinline__ uint32_t range_begin(uint32_t cta, uint32_t units, uint32_t ctas) {
+    const uint32_t q = units / ctas, rem = units % ctas;
+    return cta * q + (cta < rem ? cta : rem);
+}
+__device__ __forceinline__ uint32_t unit_owner(uint32_t u, uint32_t units, uint32_t ctas) {
+    const uint32_t q = units / ctas, rem = units % ctas;
+    const uint32_t cut = rem * (q + 1u);
+    return u < cut ? u / (q + 1u) : rem + (u - cut) / q;
+}
+
+// Position in a ring of `n` stages with the mbarrier phase parity of the current pass; advanced without a
+// division (the ring depths are run-time values).
+struct RingPos {
+    uint32_t stage, parity;
+    __device__ __forceinline__ void advance(uint32_t n) {
+        if (++stage == n) stage = 0u, parity ^= 1u;
+    }
+};
+
+// A CTA's range as segments: maximal runs of K blocks inside one tile.
+struct Segment {
+    uint32_t tile, kb0, kb1;
+};
+__device__ __forceinline__ Segment segment_at(uint32_t u, uint32_t u_end, uint32_t k_blocks) {
+    Segment s;
+    s.tile = u / k_blocks;
+    s.kb0 = u - s.tile * k_blocks;
+    const uint32_t left = u_end - u;
+    s.kb1 = s.kb0 + left < k_blocks ? s.kb0 + left : k_blocks;
+    return s;
+}
+
+// BITS: code width.  FAST: bf16 scales on 4-bit codes (affine in bf16).
+template <int BITS, bool FAST>
 __global__ void __launch_bounds__(kThreadsTc, 1)
 gaf_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x,
                    const __grid_constant__ CUtensorMap tmap_p) {
+    static_assert(!FAST || BITS == 4, "the bf16 affine is for 4-bit codes");
+    constexpr uint32_t kRowPacked = kBK * BITS / 8;  // packed bytes per weight row and K block: 32 or 64
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t s_full[kStagesTc];    // TMA landed (x tiles + packed codes)
-    __shared__ __align__(8) uint64_t s_bready[kStagesTc];  // B tile dequantized
-    __shared__ __align__(8) uint64_t s_empty[kStagesTc];   // MMAs that read the stage have completed
-    __shared__ __align__(8) uint64_t s_acc_full;           // all MMAs of the tile have completed
-    __shared__ __align__(8) uint64_t s_acc_empty;          // accumulators have been read back
+    __shared__ __align__(8) uint64_t s_full[kMaxStages];    // TMA landed (activation tile and packed codes of the stage)
+    __shared__ __align__(8) uint64_t s_ready[kMaxStages];   // weight tile dequantized (which implies: the TMA data landed)
+    __shared__ __align__(8) uint64_t s_free[kMaxStages];    // the MMAs that read the stage have completed
+    __shared__ __align__(8) uint64_t s_acc_full;            // all MMAs of the segment have completed
+    __shared__ __align__(8) uint64_t s_acc_empty;           // accumulators have been read back
     __shared__ uint32_t s_tmem_base;
     __shared__ volatile uint32_t s_abort;
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t stages = p.stages;
+    constexpr uint32_t kPacked = kBN * kRowPacked;                 // packed codes of a stage: 8 or 16 KB
+    const uint32_t off_p = p.x_bytes + kWTile;                     // a stage: activation tile, weight tile, packed codes
+    const uint32_t stage_bytes = off_p + kPacked;
 
     if (threadIdx.x == 0) {
         s_abort = 0u;
-        for (int s = 0; s < kStagesTc; ++s) {
+        for (uint32_t s = 0; s < stages; ++s) {
             mbar_init(smem_u32(&s_full[s]), 1);
-            mbar_init(smem_u32(&s_bready[s]), kDequantWarps);
-            mbar_init(smem_u32(&s_empty[s]), 1);
+            mbar_init(smem_u32(&s_ready[s]), kDequantWarps);
+            mbar_init(smem_u32(&s_free[s]), 1);
         }
         mbar_init(smem_u32(&s_acc_full), 1);
         mbar_init(smem_u32(&s_acc_empty), kDequantWarps);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        // tensor memory: all 512 columns (two 128 x 256 fp32 accumulators); this warp also frees them
+        // tensor memory: all 512 columns; this warp also frees them
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
                      "r"(kTmemCols)
                      : "memory");
@@ -191,180 +289,332 @@ gaf_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = s_tmem_base;
 
-    const uint32_t total_tiles = p.m_tiles * p.n_tiles;
+    const uint32_t u_begin = range_begin(blockIdx.x, p.total_units, gridDim.x);
+    const uint32_t u_end = range_begin(blockIdx.x + 1u, p.total_units, gridDim.x);
+    // tile -> first weight row and first activation row (tiles are walked weight-tile major so that CTAs
+    // running at the same time share weight rows in L2)
+    auto tile_n0 = [&](uint32_t tile) { return (tile / p.m_tiles) * static_cast<uint32_t>(kBN); };
+    auto tile_m0 = [&](uint32_t tile) { return (tile % p.m_tiles) * p.bm; };
 
     if (warp == 0) {
-        // ------------------------------ TMA producer ------------------------------
-        if (lane == 0) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_x)) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_p)) : "memory");
+        // ------------------------------ TMA producer (whole warp, elected issue) ------------------------------
+        {
+            if (lane == 0) {
+                asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_x)) : "memory");
+                asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_p)) : "memory");
+            }
             uint32_t it = 0;
+            RingPos rp = {0u, 0u};
             bool ok = true;
-            for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const uint32_t n0 = (tile / p.m_tiles) * kBN, m0 = (tile % p.m_tiles) * kBM;
-                for (uint32_t kb = 0; kb < p.k_blocks; ++kb, ++it) {
-                    const uint32_t stage = it % kStagesTc, round = it / kStagesTc;
-                    if (round > 0 && !mbar_wait(smem_u32(&s_empty[stage]), (round - 1u) & 1u, &s_abort, p.error_word, 0x100u)) {
+            for (uint32_t u = u_begin; u < u_end && ok;) {
+                const Segment sg = segment_at(u, u_end, p.k_blocks);
+                const uint32_t n0 = tile_n0(sg.tile), m0 = tile_m0(sg.tile);
+                for (uint32_t kb = sg.kb0; kb < sg.kb1; ++kb, ++it, rp.advance(stages)) {
+                    // from the second pass over the ring on, a stage is refilled once the MMAs of its previous use are done
+                    if (it >= stages && !mbar_wait_warp(smem_u32(&s_free[rp.stage]), rp.parity ^ 1u, &s_abort, p.error_word, 0x100u)) {
                         ok = false;
                         break;
                     }
-                    const uint32_t sb = base + stage * kStageTc;
-                    const uint32_t full = smem_u32(&s_full[stage]);
-                    mbar_arrive_expect_tx(full, 2 * kATile + kPTile);  // out-of-range rows arrive as zeros
-                    tma_load_2d(sb, &tmap_x, kb * kBK, m0, full);
-                    tma_load_2d(sb + kATile, &tmap_x, kb * kBK, m0 + 128u, full);
-                    tma_load_2d(sb + 2 * kATile + kBTile, &tmap_p, kb * 32u, n0, full);
+                    const uint32_t sb = base + rp.stage * stage_bytes;
+                    const uint32_t full = smem_u32(&s_full[rp.stage]);
+                    if (elect_one()) {
+                        TGAF_TRACE(0, it);
+                        mbar_arrive_expect_tx(full, p.x_bytes + kPacked);  // out-of-range rows arrive as zeros
+                        tma_load_2d(sb + off_p, &tmap_p, kb * kRowPacked, n0, full);
+                        tma_load_2d(sb, &tmap_x, kb * kBK, m0, full);
+                        if (p.bm > 128u) tma_load_2d(sb + kHalfTile, &tmap_x, kb * kBK, m0 + 128u, full);
+                    }
+                    __syncwarp();
                 }
+                u += sg.kb1 - sg.kb0;
             }
-            if (!ok) {
-                // copies already issued get a bounded time to land before shared memory is released
-                const uint32_t pending = it < static_cast<uint32_t>(kStagesTc) ? it : static_cast<uint32_t>(kStagesTc);
+            if (!ok && lane == 0) {
+                // copies already issued get a bounded time to land before shared memory is released (error path:
+                // the divisions do not matter here)
+                const uint32_t pending = it < stages ? it : stages;
                 for (uint32_t i = 0; i < pending; ++i) {
                     const uint32_t idx = it - 1u - i;
                     for (uint32_t spin = 0; spin < (1u << 20); ++spin)
-                        if (mbar_try_wait(smem_u32(&s_full[idx % kStagesTc]), (idx / kStagesTc) & 1u)) break;
+                        if (mbar_try_wait(smem_u32(&s_full[idx % stages]), (idx / stages) & 1u)) break;
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
-        if (lane == 0) {
-            uint32_t it = 0, ti = 0;
+        // Measured on this part: every instruction of this one thread is expensive (a satisfied mbarrier wait
+        // ~250 cycles, a tcgen05.mma ~100 to issue, a commit ~100) against 135 cycles of tensor work per
+        // 128 x 256 x 16 MMA, so it does the minimum per K block: ONE wait (the dequant warps arrive only after
+        // the activation tile has landed too), the MMAs, ONE commit (activation and weight tile share a stage).
+        {
+            uint32_t si = 0, mit = 0;
+            RingPos rp = {0u, 0u};
             bool ok = true;
-            for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++ti) {
-                if (ti > 0 && !mbar_wait(smem_u32(&s_acc_empty), (ti - 1u) & 1u, &s_abort, p.error_word, 0x200u)) break;
+            const uint32_t idesc = instr_desc(static_cast<uint32_t>(kBN));
+            const uint64_t xd0 = umma_desc_sw128(base), wd0 = umma_desc_sw128(base + p.x_bytes);
+            const uint32_t stage_step = stage_bytes >> 4;   // descriptors differ from stage to stage in the address field only
+            for (uint32_t u = u_begin; u < u_end && ok; ++si) {
+                const Segment sg = segment_at(u, u_end, p.k_blocks);
+                if (si > 0 && !mbar_wait_warp(smem_u32(&s_acc_empty), (si - 1u) & 1u, &s_abort, p.error_word, 0x200u)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                // rows 128..255 of the tile exist only when M reaches them (skinny M: half the tensor work)
-                const bool two_halves = (tile % p.m_tiles) * kBM + 128u < p.M;
-                for (uint32_t kb = 0; kb < p.k_blocks; ++kb, ++it) {
-                    const uint32_t stage = it % kStagesTc, par = (it / kStagesTc) & 1u;
-                    if (!mbar_wait(smem_u32(&s_full[stage]), par, &s_abort, p.error_word, 0x400u) ||
-                        !mbar_wait(smem_u32(&s_bready[stage]), par, &s_abort, p.error_word, 0x800u)) {
+                // the second accumulator (activation rows 128.. of the tile) exists only when the tile reaches it
+                const bool second = p.bm > 128u && tile_m0(sg.tile) + 128u < p.M;
+                for (uint32_t kb = sg.kb0; kb < sg.kb1; ++kb, rp.advance(stages)) {
+                    if (lane == 0) TGAF_TRACE(1, mit);
+                    if (!mbar_wait_warp(smem_u32(&s_ready[rp.stage]), rp.parity, &s_abort, p.error_word, 0x800u)) {
                         ok = false;
                         break;
                     }
+                    if (lane == 0) TGAF_TRACE(2, mit);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t sb = base + stage * kStageTc;
-                    const uint64_t a0 = umma_desc_sw128(sb), a1 = umma_desc_sw128(sb + kATile);
-                    const uint64_t bd = umma_desc_sw128(sb + 2 * kATile);
+                    const uint64_t xd = xd0 + rp.stage * stage_step, wd = wd0 + rp.stage * stage_step;
+                    const uint32_t free_bar = smem_u32(&s_free[rp.stage]);
+                    if (elect_one()) {
+                        TGAF_TRACE(4, mit);
+                        // advancing 16 elements (32 bytes) along K inside the swizzle span: +2 in the address field;
+                        // the second 128-row half of the activation tile lies 16 KB further: +1024
+                        const uint32_t acc0 = kb > sg.kb0 ? 1u : 0u;
+                        umma_f16(tmem_base, xd, wd, idesc, acc0);
+                        if (second) umma_f16(tmem_base + 256u, xd + 1024, wd, idesc, acc0);
+                        TGAF_TRACE(8, mit);
 #pragma unroll
-                    for (uint32_t k16 = 0; k16 < kBK / 16; ++k16) {
-                        const uint32_t acc = (kb | k16) ? 1u : 0u;
-                        // advancing 16 elements (32 bytes) along K inside the swizzle span: +2 in the address field
-                        umma_f16(tmem_base, a0 + 2 * k16, bd + 2 * k16, kInstrDesc, acc);
-                        if (two_halves) umma_f16(tmem_base + 256u, a1 + 2 * k16, bd + 2 * k16, kInstrDesc, acc);
+                        for (uint32_t k16 = 1; k16 < kBK / 16; ++k16) {
+                            umma_f16_acc(tmem_base, xd + 2 * k16, wd + 2 * k16, idesc);
+                            if (second) umma_f16_acc(tmem_base + 256u, xd + 1024 + 2 * k16, wd + 2 * k16, idesc);
+                        }
+                        TGAF_TRACE(9, mit);
+                        umma_commit(free_bar);  // frees the stage once these MMAs have read it
+                        TGAF_TRACE(3, mit);
                     }
-                    umma_commit(smem_u32(&s_empty[stage]));  // frees the stage once these MMAs have read it
+                    __syncwarp();
+                    ++mit;
                 }
-                if (ok) umma_commit(smem_u32(&s_acc_full));
+                if (ok && elect_one()) umma_commit(smem_u32(&s_acc_full));
+                __syncwarp();
+                u += sg.kb1 - sg.kb0;
             }
         }
     } else {
         // ------------------------------ dequant + epilogue warps ------------------------------
-        const uint32_t r = (warp - 2) * 32 + lane;  // weight row of the tile this thread dequantizes
+        const uint32_t wi = warp - 2;               // 0..7
+        const uint32_t r = wi * 32 + lane;          // weight row of the tile this thread dequantizes
         const uint32_t q = warp & 3;                // tensor-memory lane quadrant this warp may read
-        const uint32_t hsel = (warp - 2) >> 2;      // accumulator (128-row half of the tile) this warp writes out
+        const uint32_t hsel = wi >> 2;              // accumulator this warp writes out
         const uint32_t gshift = p.group == 32u ? 5u : (p.group == 64u ? 6u : 7u);
-        uint32_t it = 0, ti = 0;
+        uint32_t it = 0, si = 0;
+        RingPos rp = {0u, 0u};
         bool ok = true;
-        for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++ti) {
-            const uint32_t n0 = (tile / p.m_tiles) * kBN, m0 = (tile % p.m_tiles) * kBM;
+        // this thread's fixed offsets inside a stage: its packed row, the eight 16-byte chunks of its weight tile row
+        // (swizzled: 16-byte chunk index XOR (row & 7))
+        const uint32_t prow_off = off_p + r * kRowPacked;
+        const uint32_t wrow_off = p.x_bytes + r * 128u;
+        const uint32_t rx = (r & 7u) << 4;
+        for (uint32_t u = u_begin; u < u_end && ok; ++si) {
+            const Segment sg = segment_at(u, u_end, p.k_blocks);
+            const uint32_t n0 = tile_n0(sg.tile), m0 = tile_m0(sg.tile);
             const uint32_t nrow = min(n0 + r, p.N - 1u);  // rows past N: read a valid row, never stored
             const uint16_t *srow = p.scales + static_cast<size_t>(nrow) * p.groups;
             const uint16_t *brow = p.biases + static_cast<size_t>(nrow) * p.groups;
-            uint4 sv = make_uint4(0, 0, 0, 0), bv = make_uint4(0, 0, 0, 0);
-            uint32_t have = 0xFFFFFFFFu;  // first group index held in sv / bv
-            for (uint32_t kb = 0; kb < p.k_blocks; ++kb, ++it) {
-                const uint32_t stage = it % kStagesTc, par = (it / kStagesTc) & 1u;
-                // scales / biases: eight consecutive groups per 16-byte load
+            // scales / biases of eight consecutive groups per 16-byte load; the next eight are fetched as soon as
+            // these come into use, so that no load is waited for
+            uint4 sv = make_uint4(0, 0, 0, 0), bv = make_uint4(0, 0, 0, 0), sv_n = sv, bv_n = bv;
+            uint32_t have = 0xFFFFFFFFu, have_n = 0xFFFFFFFFu;  // first group index held in sv / bv and in sv_n / bv_n
+            for (uint32_t kb = sg.kb0; kb < sg.kb1; ++kb, ++it, rp.advance(stages)) {
                 const uint32_t g_first = (kb * kBK) >> gshift;
                 if ((g_first & ~7u) != have) {
                     have = g_first & ~7u;
-                    sv = __ldg(reinterpret_cast<const uint4 *>(srow + have));
-                    bv = __ldg(reinterpret_cast<const uint4 *>(brow + have));
+                    if (have == have_n) {
+                        sv = sv_n, bv = bv_n;
+                    } else {
+                        sv = __ldg(reinterpret_cast<const uint4 *>(srow + have));
+                        bv = __ldg(reinterpret_cast<const uint4 *>(brow + have));
+                    }
+                    have_n = have + 8u;
+                    if (have_n < p.groups) {
+                        sv_n = __ldg(reinterpret_cast<const uint4 *>(srow + have_n));
+                        bv_n = __ldg(reinterpret_cast<const uint4 *>(brow + have_n));
+                    }
                 }
-                if (!mbar_wait(smem_u32(&s_full[stage]), par, &s_abort, p.error_word, 0x1000u)) {
+                if (warp == 2 && lane == 0) TGAF_TRACE(5, it);
+                // the TMA data of this use of the stage (which also means: the MMAs of its previous use are done,
+                // the producer refilled it only then)
+                if (!mbar_wait_warp(smem_u32(&s_full[rp.stage]), rp.parity, &s_abort, p.error_word, 0x1000u)) {
                     ok = false;
                     break;
                 }
-                const uint32_t sb = base + stage * kStageTc;
-                const uint32_t prow = sb + 2 * kATile + kBTile + r * 32u;
-                uint32_t w[8];
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(prow));
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "r"(prow + 16u));
-                const uint32_t brow_s = sb + 2 * kATile + r * 128u;
-                const __nv_bfloat162 k128 = __floats2bfloat162_rn(128.f, 128.f);
+                if (warp == 2 && lane == 0) TGAF_TRACE(6, it);
+                const uint32_t sb = base + rp.stage * stage_bytes;
+                uint32_t w[kRowPacked / 4];
+#pragma unroll
+                for (int i = 0; i < static_cast<int>(kRowPacked / 16); ++i)
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(w[4 * i]), "=r"(w[4 * i + 1]), "=r"(w[4 * i + 2]), "=r"(w[4 * i + 3])
+                                 : "r"(sb + prow_off + 16u * i));
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     const uint32_t gi = (kb * kBK + half * 32u) >> gshift;
-                    const uint32_t s2u = pick_pair(sv, gi & 7u, p.sdtype), b2u = pick_pair(bv, gi & 7u, p.sdtype);
-                    const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162 *>(&s2u);
-                    const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162 *>(&b2u);
+                    // the 16-bit value number (gi & 7) of sv / bv, already doubled into both halves of a register
+                    const uint32_t sel = 0x1010u + 0x2222u * (gi & 3u);
+                    const uint32_t s2u = prmt((gi & 4u) ? sv.z : sv.x, (gi & 4u) ? sv.w : sv.y, sel);
+                    const uint32_t b2u = prmt((gi & 4u) ? bv.z : bv.x, (gi & 4u) ? bv.w : bv.y, sel);
+                    if constexpr (FAST) {
+                        const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162 *>(&s2u);
+                        const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162 *>(&b2u);
+                        const __nv_bfloat162 k128 = __floats2bfloat162_rn(128.f, 128.f);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint32_t word = w[half * 4 + j];
-                        uint32_t pr[4];
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t word = w[half * 4 + j];
+                            // byte i of `word` holds code 2i in its low nibble; byte i of `word >> 4` holds code 2i + 1
+                            // there: one byte permute and one mask-or per pair of consecutive codes
+                            const uint32_t wsh = word >> 4;
+                            uint32_t o[4];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) pr[i] = ((word >> (4 * i)) & 0x000F000Fu) | 0x43004300u;  // {128+q_i, 128+q_{i+4}}
-                        // natural K order: {q0,q1} {q2,q3} {q4,q5} {q6,q7}
-                        uint32_t nat[4] = {prmt(pr[0], pr[1], 0x5410u), prmt(pr[2], pr[3], 0x5410u),
-                                           prmt(pr[0], pr[1], 0x7632u), prmt(pr[2], pr[3], 0x7632u)};
-                        uint32_t o[4];
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162 *>(&nat[i]);
-                            v = __hsub2(v, k128);        // exact: the code itself
-                            v = __hfma2(v, s2, b2);      // bf16(q * s + b), one rounding
-                            o[i] = *reinterpret_cast<uint32_t *>(&v);
+                            for (int i = 0; i < 4; ++i) {
+                                const uint32_t pr = (prmt(word, wsh, 0x0400u + 0x0101u * i) & 0x000F000Fu) | 0x43004300u;
+                                __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162 *>(&pr);  // {128 + q[2i], 128 + q[2i+1]}
+                                v = __hsub2(v, k128);        // exact: the code itself
+                                v = __hfma2(v, s2, b2);      // bf16(q * s + b), one rounding
+                                o[i] = *reinterpret_cast<uint32_t *>(&v);
+                            }
+                            const uint32_t chunk = half * 4 + j;  // 16-byte chunk = 8 consecutive k
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sb + wrow_off + ((chunk << 4) ^ rx)), "r"(o[0]),
+                                         "r"(o[1]), "r"(o[2]), "r"(o[3])
+                                         : "memory");
                         }
-                        const uint32_t chunk = half * 4 + j;  // 16-byte chunk = 8 consecutive k
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(brow_s + (((chunk ^ r) & 7u) << 4)),
-                                     "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
-                                     : "memory");
+                    } else {
+                        const float s = sb_f32(s2u & 0xFFFFu, p.sdtype), b = sb_f32(b2u & 0xFFFFu, p.sdtype);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            float f[8];
+                            if constexpr (BITS == 4) {
+                                const uint32_t word = w[half * 4 + j];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i)
+                                    f[i] = __uint_as_float(0x4B000000u | ((word >> (4 * i)) & 0xFu)) - 8388608.f;   // exact q
+                            } else {
+                                const uint32_t w0 = w[half * 8 + 2 * j], w1 = w[half * 8 + 2 * j + 1];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    f[i] = __uint_as_float(prmt(w0, 0x4B000000u, 0x7650u + i)) - 8388608.f;
+                                    f[4 + i] = __uint_as_float(prmt(w1, 0x4B000000u, 0x7650u + i)) - 8388608.f;
+                                }
+                            }
+                            uint32_t o[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)  // fmaf(q, s, b) exactly as the reference dequant, then one rounding to bf16
+                                o[i] = pack_bf16x2(fmaf(f[2 * i], s, b), fmaf(f[2 * i + 1], s, b));
+                            const uint32_t chunk = half * 4 + j;
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sb + wrow_off + ((chunk << 4) ^ rx)), "r"(o[0]),
+                                         "r"(o[1]), "r"(o[2]), "r"(o[3])
+                                         : "memory");
+                        }
                     }
                 }
                 // make the generic-proxy writes visible to the tensor core's reads, then signal
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&s_bready[stage]));
+                if (lane == 0) mbar_arrive(smem_u32(&s_ready[rp.stage]));
+                if (warp == 2 && lane == 0) TGAF_TRACE(7, it);
             }
             if (!ok) break;
 
-            // ---- epilogue: accumulators -> bf16 -> y ----
-            if (!mbar_wait(smem_u32(&s_acc_full), ti & 1u, &s_abort, p.error_word, 0x2000u)) break;
+            // ---- the segment's accumulators: to y, to the workspace, or to y together with the others' ----
+            if (!mbar_wait_warp(smem_u32(&s_acc_full), si & 1u, &s_abort, p.error_word, 0x2000u)) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t mrow = m0 + hsel * 128u + q * 32u + lane;
-            __nv_bfloat16 *yrow = static_cast<__nv_bfloat16 *>(p.y) + static_cast<size_t>(mrow) * p.N;
-#pragma unroll 1
-            for (uint32_t c = 0; c < kBN / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + ((q * 32u) << 16) + hsel * 256u + c * 32u, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const uint32_t col0 = n0 + c * 32u;
-                if (mrow < p.M && col0 < p.N) {
-                    if (col0 + 32u <= p.N && (p.N & 7u) == 0u) {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            uint4 o;
-                            __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 0]), __uint_as_float(v[8 * i + 1]));
-                            __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3]));
-                            __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5]));
-                            __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7]));
-                            o.x = *reinterpret_cast<uint32_t *>(&t0);
-                            o.y = *reinterpret_cast<uint32_t *>(&t1);
-                            o.z = *reinterpret_cast<uint32_t *>(&t2);
-                            o.w = *reinterpret_cast<uint32_t *>(&t3);
-                            *reinterpret_cast<uint4 *>(yrow + col0 + 8 * i) = o;
+            const bool whole = sg.kb0 == 0u && sg.kb1 == p.k_blocks;
+            const bool owner = sg.kb0 == 0u;
+            const bool acc_live = hsel == 0u || (p.bm > 128u && m0 + 128u < p.M);
+            // partial tiles of the CTAs after this one that hold the rest of the tile's K blocks
+            uint32_t last_cta = blockIdx.x;
+            bool peers_ok = true;
+            if (owner && !whole) {
+                last_cta = unit_owner(sg.tile * p.k_blocks + p.k_blocks - 1u, p.total_units, gridDim.x);
+                for (uint32_t c = blockIdx.x + 1u; c <= last_cta && peers_ok; ++c) {
+                    const unsigned int *flag = p.flags + c * kDequantWarps + wi;
+                    bool got = false;
+                    if (lane == 0) {
+                        for (uint32_t spin = 0; spin < p.wait_limit; ++spin) {
+                            unsigned int v;
+                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+                            if (v != 0u) {
+                                got = true;
+                                break;
+                            }
+                            if (s_abort) break;
+                            __nanosleep(spin > 4096 ? 256 : 64);
                         }
-                    } else {
-                        for (int i = 0; i < 32; ++i)
-                            if (col0 + i < p.N) yrow[col0 + i] = __float2bfloat16_rn(__uint_as_float(v[i]));
+                    }
+                    got = __shfl_sync(0xFFFFFFFFu, got ? 1u : 0u, 0) != 0u;   // the warp barrier also orders the others' reads
+                    if (!got) {
+                        if (lane == 0) atomicOr(p.error_word, 0x4000u);
+                        s_abort = 1u;
+                        peers_ok = false;
+                    }
+                }
+            }
+            float *my_ws = p.ws + static_cast<size_t>(blockIdx.x) * kTileFloats;
+            if (acc_live && peers_ok) {
+#pragma unroll 1
+                for (uint32_t c = 0; c < kBN / 32u; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + ((q * 32u) << 16) + hsel * 256u + c * 32u, v);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    // workspace layout: [accumulator][chunk][128 lanes][32 columns], one 128-byte line per thread
+                    const size_t slot = ((static_cast<size_t>(hsel) * 8u + c) * 128u + q * 32u + lane) * 32u;
+                    if (!owner) {
+                        float4 *dst = reinterpret_cast<float4 *>(my_ws + slot);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                 __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+                        continue;
+                    }
+                    for (uint32_t pc = blockIdx.x + 1u; pc <= last_cta; ++pc) {  // CTA order: reproducible sums
+                        const float4 *src = reinterpret_cast<const float4 *>(p.ws + static_cast<size_t>(pc) * kTileFloats + slot);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float4 t = __ldcg(src + i);
+                            v[4 * i] = __float_as_uint(__uint_as_float(v[4 * i]) + t.x);
+                            v[4 * i + 1] = __float_as_uint(__uint_as_float(v[4 * i + 1]) + t.y);
+                            v[4 * i + 2] = __float_as_uint(__uint_as_float(v[4 * i + 2]) + t.z);
+                            v[4 * i + 3] = __float_as_uint(__uint_as_float(v[4 * i + 3]) + t.w);
+                        }
+                    }
+                    const uint32_t mrow = m0 + hsel * 128u + q * 32u + lane;
+                    __nv_bfloat16 *yrow = static_cast<__nv_bfloat16 *>(p.y) + static_cast<size_t>(mrow) * p.N;
+                    const uint32_t col0 = n0 + c * 32u;
+                    if (mrow < p.M && col0 < p.N) {
+                        if (col0 + 32u <= p.N && (p.N & 7u) == 0u) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                uint4 o;
+                                o.x = pack_bf16x2(__uint_as_float(v[8 * i + 0]), __uint_as_float(v[8 * i + 1]));
+                                o.y = pack_bf16x2(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3]));
+                                o.z = pack_bf16x2(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5]));
+                                o.w = pack_bf16x2(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7]));
+                                *reinterpret_cast<uint4 *>(yrow + col0 + 8 * i) = o;
+                            }
+                        } else {
+                            for (int i = 0; i < 32; ++i)
+                                if (col0 + i < p.N) yrow[col0 + i] = __float2bfloat16_rn(__uint_as_float(v[i]));
+                        }
                     }
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&s_acc_empty));
+            if (lane == 0) {
+                mbar_arrive(smem_u32(&s_acc_empty));
+                if (!owner) {
+                    // this warp's share of the partial tile is in the workspace: raise its flag
+                    __threadfence();
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.flags + blockIdx.x * kDequantWarps + wi), "r"(1u) : "memory");
+                } else if (!whole && peers_ok) {
+                    for (uint32_t c = blockIdx.x + 1u; c <= last_cta; ++c)  // consumed: ready for the next launch
+                        asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p.flags + c * kDequantWarps + wi), "r"(0u) : "memory");
+                }
+            }
+            if (!peers_ok) break;
+            u += sg.kb1 - sg.kb0;
         }
     }
 
@@ -395,14 +645,39 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
+template <int BITS, bool FAST>
+cudaError_t launch_gemm(const GemmParams &p, const CUtensorMap &tmx, const CUtensorMap &tmp, uint32_t ctas, int smem,
+                        cudaStream_t stream) {
+    auto kern = gaf_gemm_tc_kernel<BITS, FAST>;
+    static int configured[64] = {};  // per device: the largest opt-in made for this instance
+    int dev = 0;
+    if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64 || configured[dev] < smem) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = smem;
+    }
+    kern<<<ctas, kThreadsTc, smem, stream>>>(p, tmx, tmp);
+    return cudaGetLastError();
+}
+
 }  // namespace
+
+#ifdef TGAF_GEMM_TRACE
+extern "C" int tgaf_debug_gemm_trace(unsigned long long *out) {
+    return static_cast<int>(cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(unsigned long long) * kTraceRows * kTraceLen));
+}
+#endif
+
+size_t gemm_tc_workspace_bytes(int sm_count) { return static_cast<size_t>(sm_count) * kTileFloats * sizeof(float); }
+size_t gemm_tc_flag_count(int sm_count) { return static_cast<size_t>(sm_count) * kDequantWarps; }
 
 bool gemm_tc_eligible(const WeightView &w, uint32_t M) {
     if (M <= 16u) return false;                                   // the decode GEMV kernels take M <= 16
-    if (w.bits != 4u) return false;
+    if (w.bits != 4u && w.bits != 8u) return false;
     if (w.group != 32u && w.group != 64u && w.group != 128u) return false;
     if (w.K % kBK != 0u || w.groups % 8u != 0u) return false;      // whole K blocks; 16-byte loads of scales
-    if (w.row_bytes != w.K / 2u || w.row_bytes % 16u != 0u) return false;
+    if (w.row_bytes != w.K * w.bits / 8u || w.row_bytes % 16u != 0u) return false;
     if (reinterpret_cast<uintptr_t>(w.packed) % 16u != 0 || reinterpret_cast<uintptr_t>(w.scales) % 16u != 0 ||
         reinterpret_cast<uintptr_t>(w.biases) % 16u != 0)
         return false;
@@ -410,17 +685,49 @@ bool gemm_tc_eligible(const WeightView &w, uint32_t M) {
 }
 
 cudaError_t gemm_tc(const WeightView &w, const void *x_bf16, void *y_bf16, uint32_t M, cudaStream_t stream,
-                    int sm_count, unsigned int *d_error_word) {
+                    int sm_count, unsigned int *d_error_word, float *ws, size_t ws_bytes, unsigned int *flags,
+                    size_t flag_count) {
     if (!gemm_tc_eligible(w, M)) return cudaErrorNotSupported;
     if (reinterpret_cast<uintptr_t>(x_bf16) % 16u != 0 || reinterpret_cast<uintptr_t>(y_bf16) % 16u != 0 ||
         (static_cast<size_t>(w.K) * 2u) % 16u != 0)
         return cudaErrorNotSupported;
+    if (!ws || !flags || ws_bytes < gemm_tc_workspace_bytes(sm_count) || flag_count < gemm_tc_flag_count(sm_count))
+        return cudaErrorMemoryAllocation;
     EncodeTiledFn enc = encode_fn();
+    GemmParams p;
+    p.scales = w.scales;
+    p.biases = w.biases;
+    p.y = y_bf16;
+    p.ws = ws;
+    p.flags = flags;
+    p.error_word = d_error_word;
+    p.M = M;
+    p.N = w.N;
+    p.K = w.K;
+    p.groups = w.groups;
+    p.group = w.group;
+    p.sdtype = w.sdtype;
+    p.n_tiles = (w.N + kBN - 1u) / kBN;
+    p.k_blocks = w.K / kBK;
+    // two activation halves per tile when there are rows for them and the ring still gets three stages
+    p.bm = (M > 128u && w.bits == 4u) ? 256u : 128u;
+    p.m_tiles = (M + p.bm - 1u) / p.bm;
+    p.x_bytes = p.bm * 128u;
+    // 227 KB per CTA, minus the static part and the slack that aligns the ring = 225 KB: three stages with two
+    // activation halves (72 KB each), four with one (56 KB; 64 KB for 8-bit codes: three)
+    const uint32_t stage_bytes = p.x_bytes + kWTile + kBN * (kBK * w.bits / 8u);
+    p.stages = (225u * 1024u) / stage_bytes;
+    if (p.stages > static_cast<uint32_t>(kMaxStages)) p.stages = kMaxStages;
+    if (p.stages < 2u) return cudaErrorNotSupported;
+    p.total_units = p.m_tiles * p.n_tiles * p.k_blocks;
+    p.wait_limit = kWaitLimitTc;
+    const int smem = static_cast<int>(p.stages * stage_bytes + 1024u);
+
     CUtensorMap tmx, tmp;
     {
         const cuuint64_t dims[2] = {w.K, M};
         const cuuint64_t strides[1] = {static_cast<cuuint64_t>(w.K) * 2u};
-        const cuuint32_t box[2] = {kBK, 128};
+        const cuuint32_t box[2] = {kBK, 128u};
         const cuuint32_t estr[2] = {1, 1};
         if (enc(&tmx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(x_bf16), dims, strides, box, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -430,39 +737,18 @@ cudaError_t gemm_tc(const WeightView &w, const void *x_bf16, void *y_bf16, uint3
     {
         const cuuint64_t dims[2] = {w.row_bytes, w.N};
         const cuuint64_t strides[1] = {w.row_bytes};
-        const cuuint32_t box[2] = {32, kBN};
+        const cuuint32_t box[2] = {kBK * w.bits / 8u, kBN};   // the codes of one K block: 32 or 64 bytes per row
         const cuuint32_t estr[2] = {1, 1};
         if (enc(&tmp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(w.packed), dims, strides, box, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
     }
-    GemmParams p;
-    p.scales = w.scales;
-    p.biases = w.biases;
-    p.y = y_bf16;
-    p.error_word = d_error_word;
-    p.M = M;
-    p.N = w.N;
-    p.K = w.K;
-    p.groups = w.groups;
-    p.group = w.group;
-    p.sdtype = w.sdtype;
-    p.m_tiles = (M + kBM - 1u) / kBM;
-    p.n_tiles = (w.N + kBN - 1u) / kBN;
-    p.k_blocks = w.K / kBK;
-    static bool configured[64] = {};  // per device: the opt-in belongs to the function on one device
-    int dev = 0;
-    if (cudaError_t e = cudaGetDevice(&dev); e != cudaSuccess) return e;
-    if (dev < 0 || dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gaf_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTc);
-        if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) configured[dev] = true;
-    }
-    const uint32_t tiles = p.m_tiles * p.n_tiles;
-    const uint32_t ctas = tiles < static_cast<uint32_t>(sm_count) ? tiles : static_cast<uint32_t>(sm_count);
-    gaf_gemm_tc_kernel<<<ctas, kThreadsTc, kSmemTc, stream>>>(p, tmx, tmp);
-    return cudaGetLastError();
+    const uint32_t ctas = p.total_units < static_cast<uint32_t>(sm_count) ? p.total_units : static_cast<uint32_t>(sm_count);
+    if (w.bits == 4u)
+        return w.sdtype == 1u ? launch_gemm<4, true>(p, tmx, tmp, ctas, smem, stream)
+                              : launch_gemm<4, false>(p, tmx, tmp, ctas, smem, stream);
+    return launch_gemm<8, false>(p, tmx, tmp, ctas, smem, stream);
 }
 
 }  // namespace tgaf

@@ -103,10 +103,16 @@ cudaError_t dequant_f32(const WeightView &w, float *out, cudaStream_t stream);
 cudaError_t gather_dequant_f32(const WeightView &w, const uint32_t *d_ids, uint32_t count, float multiplier,
                                float *out, cudaStream_t stream);
 
-// Prefill dequant-GEMM on tcgen05 (bf16 in/out).  cudaErrorNotSupported when not eligible.
+// Dequant-GEMM on tcgen05 for M > 16 (bf16 in/out; 4- and 8-bit codes).  cudaErrorNotSupported when not eligible.
+// `ws`: fp32 workspace of gemm_tc_workspace_bytes (one partial tile per CTA, for tiles whose K blocks are shared
+// between CTAs); `flags`: gemm_tc_flag_count words, zero between launches.  cudaErrorMemoryAllocation when
+// either is too small.
 cudaError_t gemm_tc(const WeightView &w, const void *x_bf16, void *y_bf16, uint32_t M,
-                    cudaStream_t stream, int sm_count, unsigned int *d_error_word);
+                    cudaStream_t stream, int sm_count, unsigned int *d_error_word, float *ws, size_t ws_bytes,
+                    unsigned int *flags, size_t flag_count);
 bool gemm_tc_eligible(const WeightView &w, uint32_t M);
+size_t gemm_tc_workspace_bytes(int sm_count);
+size_t gemm_tc_flag_count(int sm_count);
 
 // ---- all-reduce over NVLink peer memory (gaf_peer.cu) ----
 constexpr int kPeerMaxRanks = 8;                      // ranks of one node
