@@ -49,11 +49,12 @@ namespace {
 
 constexpr int kBN = 256;           // weight rows per tile
 constexpr int kBK = 64;            // K block: 64 bf16 = 128 bytes, the swizzle span
-constexpr int kMaxStages = 4;      // stage ring: activation tile + dequantized weight tile of one K block
+constexpr int kMaxRing = 8;        // deepest ring
 constexpr int kHalfTile = 128 * 128;  // 128 rows x 128 bytes
 constexpr int kWTile = kBN * 128;     // 256 weight rows x 128 bytes of bf16
-constexpr int kDequantWarps = 8;
-constexpr int kThreadsTc = (2 + kDequantWarps) * 32;
+constexpr int kDequantWarps = 16;
+constexpr int kFirstDequantWarp = 3;   // warps 0, 1, 2: activation copies, MMA issue, packed-code copies
+constexpr int kThreadsTc = (kFirstDequantWarp + kDequantWarps) * 32;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kWaitLimitTc = 1u << 22;
 constexpr uint32_t kTileFloats = 256 * 256;   // workspace slot of one CTA (fp32 partial tile)
@@ -63,11 +64,21 @@ constexpr uint32_t kTileFloats = 256 * 256;   // workspace slot of one CTA (fp32
 #ifdef TGAF_GEMM_TRACE
 constexpr int kTraceLen = 256, kTraceRows = 12;
 __device__ unsigned long long g_gemm_trace[kTraceRows][kTraceLen];
+__device__ unsigned long long g_gemm_cta[160][8];
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define TGAF_CTA(slot) g_gemm_cta[blockIdx.x < 160u ? blockIdx.x : 159u][slot] = gtime()
 #define TGAF_TRACE(row, idx)                                                                    \
     do {                                                                                        \
         if (blockIdx.x == 1u && (idx) < static_cast<uint32_t>(kTraceLen)) g_gemm_trace[row][idx] = clock64(); \
     } while (0)
 #else
+#define TGAF_CTA(slot) \
+    do {               \
+    } while (0)
 #define TGAF_TRACE(row, idx) \
     do {                     \
     } while (0)
@@ -87,7 +98,8 @@ struct GemmParams {
     uint32_t m_tiles, n_tiles, k_blocks;
     uint32_t bm;            // activation rows per tile: 256 or 128
     uint32_t x_bytes;       // activation bytes per stage
-    uint32_t stages;        // depth of the stage ring
+    uint32_t x_stages, p_stages, w_stages;   // depths of the activation, packed-code and weight-tile rings
+    uint32_t p_row;         // packed bytes per row and packed stage: 128 (swizzled; 4 or 2 K blocks) or 64
     uint32_t total_units;   // tiles * k_blocks
     uint32_t wait_limit;    // polls for another CTA's flag
 };
@@ -251,9 +263,11 @@ gaf_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
     static_assert(!FAST || BITS == 4, "the bf16 affine is for 4-bit codes");
     constexpr uint32_t kRowPacked = kBK * BITS / 8;  // packed bytes per weight row and K block: 32 or 64
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t s_full[kMaxStages];    // TMA landed (activation tile and packed codes of the stage)
-    __shared__ __align__(8) uint64_t s_ready[kMaxStages];   // weight tile dequantized (which implies: the TMA data landed)
-    __shared__ __align__(8) uint64_t s_free[kMaxStages];    // the MMAs that read the stage have completed
+    __shared__ __align__(8) uint64_t s_xfull[kMaxRing];     // TMA landed (activation tile)
+    __shared__ __align__(8) uint64_t s_pfull[kMaxRing];     // TMA landed (packed codes)
+    __shared__ __align__(8) uint64_t s_pempty[kMaxRing];    // every dequant warp has read the packed codes
+    __shared__ __align__(8) uint64_t s_wready[kMaxRing];    // weight tile dequantized AND its activation tile landed
+    __shared__ __align__(8) uint64_t s_wempty[kMaxRing];    // the MMAs that read the weight tile AND the activation tile of the same K block have completed
     __shared__ __align__(8) uint64_t s_acc_full;            // all MMAs of the segment have completed
     __shared__ __align__(8) uint64_t s_acc_empty;           // accumulators have been read back
     __shared__ uint32_t s_tmem_base;
@@ -261,17 +275,26 @@ gaf_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t stages = p.stages;
-    constexpr uint32_t kPacked = kBN * kRowPacked;                 // packed codes of a stage: 8 or 16 KB
-    const uint32_t off_p = p.x_bytes + kWTile;                     // a stage: activation tile, weight tile, packed codes
-    const uint32_t stage_bytes = off_p + kPacked;
+    const uint32_t kPacked = kBN * p.p_row;                        // a packed stage: the codes of `kpp` K blocks
+    const uint32_t kpp = p.p_row / kRowPacked;
+    const bool pswz = p.p_row == 128u;                             // 128-byte packed rows are swizzled like the operand tiles
+    const uint32_t NX = p.x_stages, NP = p.p_stages, NW = p.w_stages;
+    const uint32_t xring = base;                                   // activation tiles,
+    const uint32_t wring = xring + NX * p.x_bytes;                 // then weight tiles,
+    const uint32_t pring = wring + NW * kWTile;                    // then packed codes
 
     if (threadIdx.x == 0) {
         s_abort = 0u;
-        for (uint32_t s = 0; s < stages; ++s) {
-            mbar_init(smem_u32(&s_full[s]), 1);
-            mbar_init(smem_u32(&s_ready[s]), kDequantWarps);
-            mbar_init(smem_u32(&s_free[s]), 1);
+        for (uint32_t s = 0; s < NX; ++s) {
+            mbar_init(smem_u32(&s_xfull[s]), 1);
+        }
+        for (uint32_t s = 0; s < NP; ++s) {
+            mbar_init(smem_u32(&s_pfull[s]), 1);
+            mbar_init(smem_u32(&s_pempty[s]), kDequantWarps);
+        }
+        for (uint32_t s = 0; s < NW; ++s) {
+            mbar_init(smem_u32(&s_wready[s]), kDequantWarps / 2);
+            mbar_init(smem_u32(&s_wempty[s]), 1);
         }
         mbar_init(smem_u32(&s_acc_full), 1);
         mbar_init(smem_u32(&s_acc_empty), kDequantWarps);
@@ -288,6 +311,8 @@ gaf_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = s_tmem_base;
+    if (threadIdx.x == 0) TGAF_TRACE(10, 0u);
+    if (threadIdx.x == 0) TGAF_CTA(0);
 
     const uint32_t u_begin = range_begin(blockIdx.x, p.total_units, gridDim.x);
     const uint32_t u_end = range_begin(blockIdx.x + 1u, p.total_units, gridDim.x);
@@ -296,47 +321,57 @@ gaf_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
     auto tile_n0 = [&](uint32_t tile) { return (tile / p.m_tiles) * static_cast<uint32_t>(kBN); };
     auto tile_m0 = [&](uint32_t tile) { return (tile % p.m_tiles) * p.bm; };
 
-    if (warp == 0) {
-        // ------------------------------ TMA producer (whole warp, elected issue) ------------------------------
-        {
-            if (lane == 0) {
-                asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_x)) : "memory");
-                asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_p)) : "memory");
-            }
-            uint32_t it = 0;
-            RingPos rp = {0u, 0u};
-            bool ok = true;
-            for (uint32_t u = u_begin; u < u_end && ok;) {
-                const Segment sg = segment_at(u, u_end, p.k_blocks);
-                const uint32_t n0 = tile_n0(sg.tile), m0 = tile_m0(sg.tile);
-                for (uint32_t kb = sg.kb0; kb < sg.kb1; ++kb, ++it, rp.advance(stages)) {
-                    // from the second pass over the ring on, a stage is refilled once the MMAs of its previous use are done
-                    if (it >= stages && !mbar_wait_warp(smem_u32(&s_free[rp.stage]), rp.parity ^ 1u, &s_abort, p.error_word, 0x100u)) {
-                        ok = false;
-                        break;
-                    }
-                    const uint32_t sb = base + rp.stage * stage_bytes;
-                    const uint32_t full = smem_u32(&s_full[rp.stage]);
-                    if (elect_one()) {
+    if (warp == 0 || warp == 2) {
+        // ---------------- TMA producers (whole warp, elected issue): warp 0 activations, warp 2 packed codes ----------------
+        // Each runs as far ahead as its own ring allows: the codes (the only HBM traffic when M is small) up to
+        // eight K blocks, so that neither copy latency is part of the dequantize -> MMA -> free cycle.
+        const bool codes = warp == 2;
+        const uint32_t n_stages = codes ? NP : NX;
+        // the activation ring is as deep as the weight ring and shares its "free" barriers: one commit per K block
+        uint64_t *fullb = codes ? s_pfull : s_xfull, *emptyb = codes ? s_pempty : s_wempty;
+        if (lane == 0)
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(codes ? &tmap_p : &tmap_x)) : "memory");
+        uint32_t it = 0;
+        RingPos rp = {0u, 0u};
+        bool ok = true;
+        for (uint32_t u = u_begin; u < u_end && ok;) {
+            const Segment sg = segment_at(u, u_end, p.k_blocks);
+            const uint32_t n0 = tile_n0(sg.tile), m0 = tile_m0(sg.tile);
+            for (uint32_t kb = sg.kb0; kb < sg.kb1; ++kb) {
+                // a packed stage holds the codes of `kpp` K blocks: one copy per stage, at its first K block
+                if (codes && kb != sg.kb0 && kb % kpp != 0u) continue;
+                // from the second pass over the ring on, a stage is refilled once its readers are done with it
+                if (it >= n_stages && !mbar_wait_warp(smem_u32(&emptyb[rp.stage]), rp.parity ^ 1u, &s_abort, p.error_word, codes ? 0x80u : 0x100u)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t full = smem_u32(&fullb[rp.stage]);
+                if (elect_one()) {
+                    if (codes) {
+                        mbar_arrive_expect_tx(full, kPacked);  // out-of-range rows arrive as zeros
+                        tma_load_2d(pring + rp.stage * kPacked, &tmap_p, (kb - kb % kpp) * kRowPacked, n0, full);
+                    } else {
                         TGAF_TRACE(0, it);
-                        mbar_arrive_expect_tx(full, p.x_bytes + kPacked);  // out-of-range rows arrive as zeros
-                        tma_load_2d(sb + off_p, &tmap_p, kb * kRowPacked, n0, full);
+                        const uint32_t sb = xring + rp.stage * p.x_bytes;
+                        mbar_arrive_expect_tx(full, p.x_bytes);
                         tma_load_2d(sb, &tmap_x, kb * kBK, m0, full);
                         if (p.bm > 128u) tma_load_2d(sb + kHalfTile, &tmap_x, kb * kBK, m0 + 128u, full);
                     }
-                    __syncwarp();
                 }
-                u += sg.kb1 - sg.kb0;
+                __syncwarp();
+                ++it;
+                rp.advance(n_stages);
             }
-            if (!ok && lane == 0) {
-                // copies already issued get a bounded time to land before shared memory is released (error path:
-                // the divisions do not matter here)
-                const uint32_t pending = it < stages ? it : stages;
-                for (uint32_t i = 0; i < pending; ++i) {
-                    const uint32_t idx = it - 1u - i;
-                    for (uint32_t spin = 0; spin < (1u << 20); ++spin)
-                        if (mbar_try_wait(smem_u32(&s_full[idx % stages]), (idx / stages) & 1u)) break;
-                }
+            u += sg.kb1 - sg.kb0;
+        }
+        if (!ok && lane == 0) {
+            // copies already issued get a bounded time to land before shared memory is released (error path:
+            // the divisions do not matter here)
+            const uint32_t pending = it < n_stages ? it : n_stages;
+            for (uint32_t i = 0; i < pending; ++i) {
+                const uint32_t idx = it - 1u - i;
+                for (uint32_t spin = 0; spin < (1u << 20); ++spin)
+                    if (mbar_try_wait(smem_u32(&fullb[idx % n_stages]), (idx / n_stages) & 1u)) break;
             }
         }
     } else if (warp == 1) {
@@ -347,27 +382,28 @@ gaf_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
         // the activation tile has landed too), the MMAs, ONE commit (activation and weight tile share a stage).
         {
             uint32_t si = 0, mit = 0;
-            RingPos rp = {0u, 0u};
+            RingPos xp = {0u, 0u}, wp = {0u, 0u};
             bool ok = true;
             const uint32_t idesc = instr_desc(static_cast<uint32_t>(kBN));
-            const uint64_t xd0 = umma_desc_sw128(base), wd0 = umma_desc_sw128(base + p.x_bytes);
-            const uint32_t stage_step = stage_bytes >> 4;   // descriptors differ from stage to stage in the address field only
+            // descriptors differ from stage to stage in the address field (16-byte units) only
+            const uint64_t xd0 = umma_desc_sw128(xring), wd0 = umma_desc_sw128(wring);
+            const uint32_t x_step = p.x_bytes >> 4, w_step = kWTile >> 4;
             for (uint32_t u = u_begin; u < u_end && ok; ++si) {
                 const Segment sg = segment_at(u, u_end, p.k_blocks);
                 if (si > 0 && !mbar_wait_warp(smem_u32(&s_acc_empty), (si - 1u) & 1u, &s_abort, p.error_word, 0x200u)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 // the second accumulator (activation rows 128.. of the tile) exists only when the tile reaches it
                 const bool second = p.bm > 128u && tile_m0(sg.tile) + 128u < p.M;
-                for (uint32_t kb = sg.kb0; kb < sg.kb1; ++kb, rp.advance(stages)) {
+                for (uint32_t kb = sg.kb0; kb < sg.kb1; ++kb, xp.advance(NX), wp.advance(NW)) {
                     if (lane == 0) TGAF_TRACE(1, mit);
-                    if (!mbar_wait_warp(smem_u32(&s_ready[rp.stage]), rp.parity, &s_abort, p.error_word, 0x800u)) {
+                    if (!mbar_wait_warp(smem_u32(&s_wready[wp.stage]), wp.parity, &s_abort, p.error_word, 0x800u)) {
                         ok = false;
                         break;
                     }
                     if (lane == 0) TGAF_TRACE(2, mit);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t xd = xd0 + rp.stage * stage_step, wd = wd0 + rp.stage * stage_step;
-                    const uint32_t free_bar = smem_u32(&s_free[rp.stage]);
+                    const uint64_t xd = xd0 + xp.stage * x_step, wd = wd0 + wp.stage * w_step;
+                    const uint32_t wfree = smem_u32(&s_wempty[wp.stage]);
                     if (elect_one()) {
                         TGAF_TRACE(4, mit);
                         // advancing 16 elements (32 bytes) along K inside the swizzle span: +2 in the address field;
@@ -382,7 +418,7 @@ gaf_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
                             if (second) umma_f16_acc(tmem_base + 256u, xd + 1024 + 2 * k16, wd + 2 * k16, idesc);
                         }
                         TGAF_TRACE(9, mit);
-                        umma_commit(free_bar);  // frees the stage once these MMAs have read it
+                        umma_commit(wfree);  // frees the activation tile and the weight tile once these MMAs have read them
                         TGAF_TRACE(3, mit);
                     }
                     __syncwarp();
@@ -395,18 +431,23 @@ gaf_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
         }
     } else {
         // ------------------------------ dequant + epilogue warps ------------------------------
-        const uint32_t wi = warp - 2;               // 0..7
-        const uint32_t r = wi * 32 + lane;          // weight row of the tile this thread dequantizes
+        const uint32_t wi = warp - kFirstDequantWarp;   // 0..15
+        const uint32_t r = (wi & 7u) * 32 + lane;   // weight row of the tile this thread dequantizes
+        // Two groups of eight warps take alternate K blocks.  What a warp spends per K block is mostly latency
+        // (shared-memory round trips, the proxy fence, the barrier hand-overs: ~900 cycles whether it unpacks 32 or
+        // 64 codes per thread), so two K blocks in flight in the dequant stage double its throughput.
+        const uint32_t grp = wi >> 3;
         const uint32_t q = warp & 3;                // tensor-memory lane quadrant this warp may read
-        const uint32_t hsel = wi >> 2;              // accumulator this warp writes out
+        const uint32_t hsel = (wi >> 2) & 1u;       // accumulator this warp writes out ...
+        const uint32_t cfirst = wi >> 3;            // ... and its 32-column chunks: cfirst, cfirst + 2, ...
         const uint32_t gshift = p.group == 32u ? 5u : (p.group == 64u ? 6u : 7u);
         uint32_t it = 0, si = 0;
-        RingPos rp = {0u, 0u};
+        RingPos xp = {0u, 0u}, pp = {0u, 0u}, wp = {0u, 0u};
         bool ok = true;
-        // this thread's fixed offsets inside a stage: its packed row, the eight 16-byte chunks of its weight tile row
-        // (swizzled: 16-byte chunk index XOR (row & 7))
-        const uint32_t prow_off = off_p + r * kRowPacked;
-        const uint32_t wrow_off = p.x_bytes + r * 128u;
+        // this thread's fixed offsets: its packed bytes inside a packed stage, its row of a weight tile (whose 16-byte
+        // chunks are swizzled: chunk index XOR (row & 7))
+        const uint32_t prow_off = r * p.p_row;
+        const uint32_t wrow_off = r * 128u;
         const uint32_t rx = (r & 7u) << 4;
         for (uint32_t u = u_begin; u < u_end && ok; ++si) {
             const Segment sg = segment_at(u, u_end, p.k_blocks);
@@ -418,8 +459,12 @@ gaf_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
             // these come into use, so that no load is waited for
             uint4 sv = make_uint4(0, 0, 0, 0), bv = make_uint4(0, 0, 0, 0), sv_n = sv, bv_n = bv;
             uint32_t have = 0xFFFFFFFFu, have_n = 0xFFFFFFFFu;  // first group index held in sv / bv and in sv_n / bv_n
-            for (uint32_t kb = sg.kb0; kb < sg.kb1; ++kb, ++it, rp.advance(stages)) {
+            uint32_t sub = sg.kb0 % kpp;   // K block inside its packed stage
+            bool p_waited = false;         // this warp has seen the current packed stage land
+            for (uint32_t kb = sg.kb0; kb < sg.kb1; ++kb, ++it, xp.advance(NX), wp.advance(NW)) {
+                const bool mine = (it & 1u) == grp;   // else: the other group's K block
                 const uint32_t g_first = (kb * kBK) >> gshift;
+                if (mine) {
                 if ((g_first & ~7u) != have) {
                     have = g_first & ~7u;
                     if (have == have_n) {
@@ -434,21 +479,24 @@ gaf_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
                         bv_n = __ldg(reinterpret_cast<const uint4 *>(brow + have_n));
                     }
                 }
-                if (warp == 2 && lane == 0) TGAF_TRACE(5, it);
-                // the TMA data of this use of the stage (which also means: the MMAs of its previous use are done,
-                // the producer refilled it only then)
-                if (!mbar_wait_warp(smem_u32(&s_full[rp.stage]), rp.parity, &s_abort, p.error_word, 0x1000u)) {
+                if (wi == 0 && lane == 0) TGAF_TRACE(5, it);
+                // the codes have landed, and the MMAs that read the previous contents of the weight tile are done
+                if ((!p_waited && !mbar_wait_warp(smem_u32(&s_pfull[pp.stage]), pp.parity, &s_abort, p.error_word, 0x1000u)) ||
+                    (it >= NW && !mbar_wait_warp(smem_u32(&s_wempty[wp.stage]), wp.parity ^ 1u, &s_abort, p.error_word, 0x8000u))) {
                     ok = false;
                     break;
                 }
-                if (warp == 2 && lane == 0) TGAF_TRACE(6, it);
-                const uint32_t sb = base + rp.stage * stage_bytes;
+                p_waited = true;
+                if (wi == 0 && lane == 0) TGAF_TRACE(6, it);
+                const uint32_t pb = pring + pp.stage * kPacked, sb = wring + wp.stage * kWTile;
                 uint32_t w[kRowPacked / 4];
 #pragma unroll
-                for (int i = 0; i < static_cast<int>(kRowPacked / 16); ++i)
+                for (int i = 0; i < static_cast<int>(kRowPacked / 16); ++i) {
+                    const uint32_t chunk = sub * (kRowPacked / 16) + i;   // 16-byte chunk of the packed row
                     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                                  : "=r"(w[4 * i]), "=r"(w[4 * i + 1]), "=r"(w[4 * i + 2]), "=r"(w[4 * i + 3])
-                                 : "r"(sb + prow_off + 16u * i));
+                                 : "r"(pb + prow_off + ((pswz ? ((chunk ^ r) & 7u) : chunk) << 4)));
+                }
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     const uint32_t gi = (kb * kBK + half * 32u) >> gshift;
@@ -509,16 +557,35 @@ gaf_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
                         }
                     }
                 }
-                // make the generic-proxy writes visible to the tensor core's reads, then signal
+                // make the generic-proxy writes visible to the tensor core's reads, then signal; the first dequant
+                // warp signals only once the K block's activation tile has landed as well, so that the MMA warp
+                // has a single barrier to wait for
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                if ((wi & 7u) == 0u && !mbar_wait_warp(smem_u32(&s_xfull[xp.stage]), xp.parity, &s_abort, p.error_word, 0x400u)) {
+                    ok = false;
+                    break;
+                }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&s_ready[rp.stage]));
-                if (warp == 2 && lane == 0) TGAF_TRACE(7, it);
+                if (lane == 0) mbar_arrive(smem_u32(&s_wready[wp.stage]));
+                if (wi == 0 && lane == 0) TGAF_TRACE(7, it);
+                }  // mine
+                if (++sub == kpp || kb + 1u == sg.kb1) {
+                    // last K block of the packed stage (or of the segment): every warp hands the stage back, whether or
+                    // not its group had a K block in it
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&s_pempty[pp.stage]));
+                    pp.advance(NP);
+                    sub = 0u;
+                    p_waited = false;
+                }
             }
             if (!ok) break;
 
             // ---- the segment's accumulators: to y, to the workspace, or to y together with the others' ----
+            if (wi == 0 && lane == 0) TGAF_TRACE(10, 1u + 4u * si);
+            if (wi == 0 && lane == 0 && si < 3u) TGAF_CTA(1 + 2 * si);
             if (!mbar_wait_warp(smem_u32(&s_acc_full), si & 1u, &s_abort, p.error_word, 0x2000u)) break;
+            if (wi == 0 && lane == 0) TGAF_TRACE(10, 2u + 4u * si);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const bool whole = sg.kb0 == 0u && sg.kb1 == p.k_blocks;
             const bool owner = sg.kb0 == 0u;
@@ -552,31 +619,40 @@ gaf_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
                 }
             }
             float *my_ws = p.ws + static_cast<size_t>(blockIdx.x) * kTileFloats;
+            if (wi == 0 && lane == 0) TGAF_TRACE(10, 3u + 4u * si);
             if (acc_live && peers_ok) {
 #pragma unroll 1
-                for (uint32_t c = 0; c < kBN / 32u; ++c) {
+                for (uint32_t c = cfirst; c < kBN / 32u; c += 2u) {
                     uint32_t v[32];
                     tmem_ld32(tmem_base + ((q * 32u) << 16) + hsel * 256u + c * 32u, v);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    // workspace layout: [accumulator][chunk][128 lanes][32 columns], one 128-byte line per thread
-                    const size_t slot = ((static_cast<size_t>(hsel) * 8u + c) * 128u + q * 32u + lane) * 32u;
+                    // workspace layout: [accumulator][chunk][column quad 0..7][128 lanes] of float4, so that the 32
+                    // lanes of a warp read and write 512 contiguous bytes per instruction
+                    const size_t slot = (((static_cast<size_t>(hsel) * 8u + c) * 8u) * 128u + q * 32u + lane) * 4u;
                     if (!owner) {
                         float4 *dst = reinterpret_cast<float4 *>(my_ws + slot);
 #pragma unroll
                         for (int i = 0; i < 8; ++i)
-                            dst[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                                 __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+                            dst[i * 128] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                       __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
                         continue;
                     }
-                    for (uint32_t pc = blockIdx.x + 1u; pc <= last_cta; ++pc) {  // CTA order: reproducible sums
-                        const float4 *src = reinterpret_cast<const float4 *>(p.ws + static_cast<size_t>(pc) * kTileFloats + slot);
+                    // CTA order: reproducible sums; two peers' loads in flight at a time
+                    for (uint32_t pc = blockIdx.x + 1u; pc <= last_cta; pc += 2u) {
+                        const float4 *src0 = reinterpret_cast<const float4 *>(p.ws + static_cast<size_t>(pc) * kTileFloats + slot);
+                        const bool two = pc + 1u <= last_cta;
+                        const float4 *src1 = two ? src0 + kTileFloats / 4u : src0;
+                        float4 t0[8], t1[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) t0[i] = __ldcg(src0 + i * 128);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) t1[i] = two ? __ldcg(src1 + i * 128) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
-                            const float4 t = __ldcg(src + i);
-                            v[4 * i] = __float_as_uint(__uint_as_float(v[4 * i]) + t.x);
-                            v[4 * i + 1] = __float_as_uint(__uint_as_float(v[4 * i + 1]) + t.y);
-                            v[4 * i + 2] = __float_as_uint(__uint_as_float(v[4 * i + 2]) + t.z);
-                            v[4 * i + 3] = __float_as_uint(__uint_as_float(v[4 * i + 3]) + t.w);
+                            v[4 * i] = __float_as_uint((__uint_as_float(v[4 * i]) + t0[i].x) + t1[i].x);
+                            v[4 * i + 1] = __float_as_uint((__uint_as_float(v[4 * i + 1]) + t0[i].y) + t1[i].y);
+                            v[4 * i + 2] = __float_as_uint((__uint_as_float(v[4 * i + 2]) + t0[i].z) + t1[i].z);
+                            v[4 * i + 3] = __float_as_uint((__uint_as_float(v[4 * i + 3]) + t0[i].w) + t1[i].w);
                         }
                     }
                     const uint32_t mrow = m0 + hsel * 128u + q * 32u + lane;
@@ -614,9 +690,13 @@ gaf_gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
                 }
             }
             if (!peers_ok) break;
+            if (wi == 0 && lane == 0) TGAF_TRACE(10, 4u + 4u * si);
+            if (wi == 0 && lane == 0 && si < 3u) TGAF_CTA(2 + 2 * si);
             u += sg.kb1 - sg.kb0;
         }
     }
+    if (threadIdx.x == 0) TGAF_TRACE(11, 0u);
+    if (threadIdx.x == 0) TGAF_CTA(7);
 
     // common exit: everybody meets, then the allocating warp returns tensor memory
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -664,6 +744,9 @@ cudaError_t launch_gemm(const GemmParams &p, const CUtensorMap &tmx, const CUten
 }  // namespace
 
 #ifdef TGAF_GEMM_TRACE
+extern "C" int tgaf_debug_gemm_cta(unsigned long long *out) {
+    return static_cast<int>(cudaMemcpyFromSymbol(out, g_gemm_cta, sizeof(unsigned long long) * 160 * 8));
+}
 extern "C" int tgaf_debug_gemm_trace(unsigned long long *out) {
     return static_cast<int>(cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(unsigned long long) * kTraceRows * kTraceLen));
 }
@@ -713,15 +796,18 @@ cudaError_t gemm_tc(const WeightView &w, const void *x_bf16, void *y_bf16, uint3
     p.bm = (M > 128u && w.bits == 4u) ? 256u : 128u;
     p.m_tiles = (M + p.bm - 1u) / p.bm;
     p.x_bytes = p.bm * 128u;
-    // 227 KB per CTA, minus the static part and the slack that aligns the ring = 225 KB: three stages with two
-    // activation halves (72 KB each), four with one (56 KB; 64 KB for 8-bit codes: three)
-    const uint32_t stage_bytes = p.x_bytes + kWTile + kBN * (kBK * w.bits / 8u);
-    p.stages = (225u * 1024u) / stage_bytes;
-    if (p.stages > static_cast<uint32_t>(kMaxStages)) p.stages = kMaxStages;
-    if (p.stages < 2u) return cudaErrorNotSupported;
+    // 227 KB per CTA, minus the static part and the slack that aligns the rings = 225 KB.  Three weight tiles
+    // (96 KB) cover the dequantize -> MMA -> free cycle, with as many activation stages (48 or 96 KB).  With one
+    // activation half: two packed stages of 128-byte rows (64 KB: the codes are fetched as full 128-byte lines,
+    // four K blocks of 4-bit codes per row at once); with two halves: two packed stages of 64-byte rows (32 KB).
+    p.w_stages = 3u;
+    p.x_stages = 3u;   // = w_stages: the two rings share their "free" barriers
+    p.p_stages = 2u;
+    p.p_row = p.bm > 128u ? 64u : 128u;
     p.total_units = p.m_tiles * p.n_tiles * p.k_blocks;
     p.wait_limit = kWaitLimitTc;
-    const int smem = static_cast<int>(p.stages * stage_bytes + 1024u);
+    const int smem = static_cast<int>(p.w_stages * kWTile + p.x_stages * p.x_bytes + p.p_stages * kBN * p.p_row + 1024u);
+    if (smem > 226 * 1024) return cudaErrorNotSupported;
 
     CUtensorMap tmx, tmp;
     {
@@ -737,11 +823,11 @@ cudaError_t gemm_tc(const WeightView &w, const void *x_bf16, void *y_bf16, uint3
     {
         const cuuint64_t dims[2] = {w.row_bytes, w.N};
         const cuuint64_t strides[1] = {w.row_bytes};
-        const cuuint32_t box[2] = {kBK * w.bits / 8u, kBN};   // the codes of one K block: 32 or 64 bytes per row
+        const cuuint32_t box[2] = {p.p_row, kBN};   // p_row bytes of every row: the codes of several K blocks at once
         const cuuint32_t estr[2] = {1, 1};
         if (enc(&tmp, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(w.packed), dims, strides, box, estr,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+                CU_TENSOR_MAP_INTERLEAVE_NONE, p.p_row == 128u ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
     }
     const uint32_t ctas = p.total_units < static_cast<uint32_t>(sm_count) ? p.total_units : static_cast<uint32_t>(sm_count);
