@@ -7,16 +7,24 @@
 
 Workloads (synthetic, seeded; shapes from the reference's model families):
   * N = 1  `llama3_8b_ffn`: a stack of distinct Llama-3-8B FFN layers in gaf4_64
-    (gate|up [2 x 14336, 4096] issued as one fused launch, down [4096, 14336]),
-    bf16 activations, M = 1 (also timed at M = 4 and 16).  A step is one pass over
-    the whole stack; the stack (1.19 GB) is several times the 126 MB L2, so every
-    weight byte comes from HBM.
+    (gate|up [2 x 14336, 4096] stacked, down [4096, 14336]), bf16 activations ~ N(0, 1),
+    each GEMV with its own activations, M = 1 (also M = 2, 4, 8, 16).  A step is one pass
+    over the whole stack (24 GEMVs, 1.19 GB of weights: several times the 126 MB L2, so
+    every weight byte comes from HBM).  The step is submitted as ONE launch list
+    (tgaf_batch_run); the same step as 24 separate launches, and as a list in which every
+    GEMV waits for its predecessor, is timed beside it.
   * N > 1  `llama3_70b_stack`: Llama-3-70B-shaped decoder-layer linears (qkv, o,
-    gate|up, down) in gaf4_64, column- / row-sharded over the ranks, NCCL allreduce
-    on the row-parallel outputs; strong scaling (total work fixed).
+    gate|up, down) in gaf4_64, column- / row-sharded over the ranks, the sum over ranks on
+    the row-parallel outputs; strong scaling (total work fixed).
 
-One JSON line on stdout (rank 0).  `value` is GB/s of algorithmic bytes (packed
-codes + scales + biases + activations in + out, each once per launch).
+Timing: the step is captured into a CUDA graph and replayed for at least a second; an
+event is recorded after every replay, so each case reports min / p50 / p90 / mean of the
+per-step times (the reference's harness reports the same four,
+core/bench/compute/cpu/harness.zig:8-35).  `ms_per_step` / `value` are the mean of the LAST
+K steps of that run (K = --steps), i.e. with the clocks where a long run leaves them.
+
+One JSON line on stdout (rank 0).  `value` is GB/s of algorithmic bytes (packed codes +
+scales + biases + activations in + out, each once per GEMV).
 """
 from __future__ import annotations
 
@@ -24,7 +32,6 @@ import argparse
 import json
 import os
 import sys
-import threading
 import time
 from pathlib import Path
 
@@ -36,113 +43,68 @@ sys.path.insert(0, str(ROOT))
 METRIC = "gaf4_64 decode GEMV HBM GB/s"
 GROUP, BITS = 64, 4
 NOMINAL_HBM_GBS = 8000.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, averaged over the step's two launch shapes
-# (gate|up 78,993,664 + 2,137,856 B; down 47,757,056 + 12,544 B), from the ncu capture summarised in
-# profiles/gemv_dp4a_llama8b_ffn_m1.md.  Each launch's reads include ~10.9 MB of next-weight L2 prefetch
-# (2 units x 148 CTAs); ncu flushes the caches between kernels, so under ncu those bytes are read again by
-# the next launch, while in a back-to-back run they replace the same bytes of that launch.
-NCU_TRAFFIC_PER_LAUNCH = (78_993_664 + 2_137_856 + 47_757_056 + 12_544) // 2
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch list of the --quick case (2 layers = 4 GEMVs,
+# 198,377,472 algorithmic bytes), from the ncu capture summarised in profiles/gemv_list_llama8b_ffn_m1.md,
+# divided by the four GEMVs of the launch (None until that capture exists)
+NCU_TRAFFIC_PER_GEMV = None
 
 
 def measured_peak_hbm():
-    p = ROOT / "MEASURED_PEAKS.json"
-    if p.exists():
-        try:
-            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
-        except Exception:
-            pass
-    return 6650.0, "fallback"
+    from talu_b200.peaks import measured_peak_hbm as f
+    return f()
 
 
 def weight_bytes(N, K, group=GROUP, bits=BITS):
     return N * K * bits // 8 + 2 * N * (K // group) * 2
 
 
-def launch_bytes(N, K, M):
-    return weight_bytes(N, K) + M * K * 2 + M * N * 2
+def launch_bytes(N, K, M, group=GROUP, bits=BITS):
+    return weight_bytes(N, K, group, bits) + M * K * 2 + M * N * 2
 
 
-def synth_weight(rng, N, K):
+def synth_weight(rng, N, K, group=GROUP, bits=BITS):
     """Random codes with realistic scale / bias magnitudes.  Timing does not depend on the
-    values; parity on converter-made weights is the job of tests/."""
-    packed = rng.integers(0, 2 ** 32, size=(N, K * BITS // 32), dtype=np.uint32)
-    scales = (np.full((N, K // GROUP), 0.0053, np.float32).view(np.uint32) >> 16).astype(np.uint16)
-    biases = (np.full((N, K // GROUP), -0.04, np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    values; parity on converter-made weights is the job of tests/ (and of the output check
+    below, which runs the timed configuration against the oracle once)."""
+    packed = rng.integers(0, 2 ** 32, size=(N, K * bits // 32), dtype=np.uint32)
+    scales = (np.full((N, K // group), 0.0053 if bits == 4 else 0.00031, np.float32).view(np.uint32) >> 16).astype(np.uint16)
+    biases = (np.full((N, K // group), -0.04, np.float32).view(np.uint32) >> 16).astype(np.uint16)
     return packed, scales, biases
 
 
-# --------------------------------------------------------------------------- clocks
-class ClockSampler:
-    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
-
-    def __init__(self, index: int):
-        self.samples, self.reasons, self.sm_max = [], set(), None
-        self._stop = threading.Event()
-        self._thr = None
-        try:
-            import pynvml
-            pynvml.nvmlInit()
-            self._nv = pynvml
-            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.sm_max = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
-        except Exception:
-            self._nv = None
-
-    def _run(self):
-        nv = self._nv
-        names = {
-            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
-            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
-            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
-            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
-        }
-        while not self._stop.is_set():
-            try:
-                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
-                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
-                for k, bit in names.items():
-                    if r & bit:
-                        self.reasons.add(k)
-            except Exception:
-                pass
-            time.sleep(0.01)
-
-    def __enter__(self):
-        if self._nv:
-            self._thr = threading.Thread(target=self._run, daemon=True)
-            self._thr.start()
-        return self
-
-    def __exit__(self, *a):
-        self._stop.set()
-        if self._thr:
-            self._thr.join()
-
-    def summary(self):
-        med = float(np.median(self.samples)) if self.samples else None
-        return {"sm_mhz": med, "sm_max_mhz": self.sm_max, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+def stats_ms(samples):
+    a = np.sort(np.asarray(samples, np.float64))
+    return {"min": round(float(a[0]), 5), "p50": round(float(np.percentile(a, 50)), 5),
+            "p90": round(float(np.percentile(a, 90)), 5), "mean": round(float(a.mean()), 5), "n": int(a.size)}
 
 
 # --------------------------------------------------------------------------- CPU arm
-def cpu_path(sample_seconds: float, threads: int, N: int = 14336, K: int = 4096):
-    """Times the CPU restatement of the reference's gaf4_64 matmul (oracle port) on one
-    matrix [N, K] (default: an 8B gate matrix), M = 1, f32 activations, for about sample_seconds."""
-    from oracle import gaf_oracle as oracle
-    oracle.build()
-    rng = np.random.default_rng(0)
-    packed, scales, biases = synth_weight(rng, N, K)
-    x = rng.standard_normal((1, K), dtype=np.float32)
-    oracle.matmul_f32(x, packed, scales, biases, GROUP, BITS, nthreads=threads)  # warm the pool and the caches
-    t0, n = time.perf_counter(), 0
-    while True:
-        oracle.matmul_f32(x, packed, scales, biases, GROUP, BITS, nthreads=threads)
-        n += 1
-        dt = time.perf_counter() - t0
-        if dt >= sample_seconds or n >= 2000:
-            break
-    per_call = dt / n
-    gbs = launch_bytes(N, K, 1) / per_call / 1e9
-    return gbs, per_call, n
+def cpu_stack(shapes, rng_seed=0):
+    """The weights of one step on the host (the same generator and seed as the GPU arm)."""
+    rng = np.random.default_rng(rng_seed)
+    return [(N, K, *synth_weight(rng, N, K)) for (N, K) in shapes]
+
+
+def cpu_time_step(oracle, stack, threads, steps, warmup):
+    """One step = one pass of the reference CPU matmul (C port) over every matrix of the stack, M = 1, f32
+    activations.  Returns per-step seconds."""
+    xs = {K: np.random.default_rng(1).standard_normal((1, K), dtype=np.float32) for K in {k for _, k, *_ in stack}}
+    out = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        for N, K, p, s, b in stack:
+            oracle.matmul_f32(xs[K], p, s, b, GROUP, BITS, nthreads=threads)
+        if i >= warmup:
+            out.append(time.perf_counter() - t0)
+    return out
+
+
+def ffn_shapes(layers):
+    return [s for _ in range(layers) for s in ((2 * 14336, 4096), (4096, 14336))]
+
+
+def stack70b_shapes(layers):
+    return [s for _ in range(layers) for s in ((10240, 8192), (8192, 8192), (2 * 28672, 8192), (8192, 28672))]
 
 
 def run_reference(args):
@@ -151,35 +113,42 @@ def run_reference(args):
         return
     from oracle import gaf_oracle as oracle
     oracle.build()
-    cores = oracle.logical_cpu_count()
-    # each step is a bounded sample of the workload of the matching arm: one 8B gate matrix at N = 1, one
-    # 70B o-projection matrix when the arm runs the 70B stack (N > 1); M = 1
+    logical = oracle.logical_cpu_count()
+    policy = oracle.reference_thread_count()
     multi = args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1
-    N, K = (8192, 8192) if multi else (14336, 4096)
+    # the same matrices as the GPU arm of the same N: the whole 8B FFN stack (N = 1), the 70B-shaped stack (N > 1)
+    layers = 8 if (multi and args.layers == 12) else args.layers
+    shapes = stack70b_shapes(layers) if multi else ffn_shapes(layers)
     workload = "llama3_70b_stack" if multi else "llama3_8b_ffn"
-    per_step = max(0.2, min(2.0, 60.0 / max(1, args.steps + args.warmup)))
-    for _ in range(args.warmup):
-        cpu_path(per_step, cores, N, K)
-    vals, t_per = [], []
-    for _ in range(args.steps):
-        g, per_call, _ = cpu_path(per_step, cores, N, K)
-        vals.append(g)
-        t_per.append(per_call)
-    value = float(np.mean(vals))
-    sample = f"one matrix [{N} x {K}] gaf4_64 of the workload, M=1, f32 activations, repeated; C port of the reference CPU kernels (oracle/), the Zig reference cannot be built here"
+    stack = cpu_stack(shapes)
+    nbytes = sum(launch_bytes(N, K, 1) for N, K, *_ in stack)
+    # keep the whole run within a couple of minutes whatever --steps says
+    probe = cpu_time_step(oracle, stack, logical, 1, 1)[0]
+    steps = max(1, min(args.steps, int(60.0 / max(probe, 1e-3))))
+    warmup = max(1, min(args.warmup, 3))
+    t_all = cpu_time_step(oracle, stack, logical, steps, warmup)
+    t_pol = cpu_time_step(oracle, stack, policy, max(1, steps // 2), 1)
+    value = nbytes / float(np.mean(t_all)) / 1e9
+    sample = (f"every matrix of the arm's own stack ({len(stack)} GEMVs, {nbytes / 1e9:.2f} GB per step), M=1, f32 activations; "
+              "C port of the reference CPU kernels (oracle/), the Zig reference cannot be built here")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": "GB/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(float(np.mean(t_per)) * 1e3, 4),
+        "steps": steps, "warmup": warmup, "ms_per_step": round(float(np.mean(t_all)) * 1e3, 4),
         "higher_is_better": True, "scaling": "strong" if multi else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload, "scheme": "gaf4_64", "M": 1},
-        "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "config": {"workload": workload, "scheme": "gaf4_64", "M": 1, "layers": layers},
+        "stats_ms": stats_ms([t * 1e3 for t in t_all]),
+        "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": logical, "kind": "port", "sample": sample,
+                         "reference_thread_policy": {"threads": policy, "value": round(nbytes / float(np.mean(t_pol)) / 1e9, 3),
+                                                     "rule": "min(physical, 8 + physical / 4), physical = logical / 2 (core/src/system/parallel.zig:41-50)"}},
         "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
 # --------------------------------------------------------------------------- GPU arm
-def time_graph(ctx, torch, stream, launch_step, steps, warmup):
-    """Captures one step into a CUDA graph on `stream`, replays it, returns ms per step."""
+def time_graph(ctx, torch, stream, launch_step, steps, warmup, min_seconds=1.0, clocks=None):
+    """Captures one step into a CUDA graph on `stream` and replays it for at least `min_seconds` (and at least
+    `steps` times), an event after every replay.  Returns (mean ms of the last `steps` replays, stats over all,
+    clocks seen)."""
     with torch.cuda.stream(stream):
         launch_step()  # sizes the library's scratch before capture
         stream.synchronize()
@@ -188,49 +157,46 @@ def time_graph(ctx, torch, stream, launch_step, steps, warmup):
             launch_step()
         for _ in range(max(3, warmup)):
             graph.replay()
-        stream.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        for _ in range(steps):
+        for _ in range(5):
             graph.replay()
         e1.record(stream)
         stream.synchronize()
+        est = max(e0.elapsed_time(e1) / 5, 1e-3)
+        n = int(min(20000, max(steps, min_seconds * 1e3 / est)))
+        mark = clocks.mark() if clocks else 0
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
+        evs[0].record(stream)
+        for i in range(n):
+            graph.replay()
+            evs[i + 1].record(stream)
+        stream.synchronize()
     ctx.synchronize()
-    return e0.elapsed_time(e1) / steps
+    samples = [evs[i].elapsed_time(evs[i + 1]) for i in range(n)]
+    del graph
+    return float(np.mean(samples[-steps:])), stats_ms(samples), (clocks.since(mark) if clocks else None)
 
 
 def measured_peak_tflops():
-    p = ROOT / "MEASURED_PEAKS.json"
-    if p.exists():
-        try:
-            j = json.loads(p.read_text())
-            return float(j["bf16_tflops"]), float(j["bf16_tflops_sustained"]), "measured"
-        except Exception:
-            pass
-    return 1590.0, 1400.0, "fallback"
+    from talu_b200.peaks import measured_peak_tflops as f
+    return f()
 
 
-def time_prefill(gaf, ctx, torch, stream, rng, iters=20):
+def time_prefill(gaf, ctx, torch, stream, rng, iters=20, clocks=None):
     """gaf4_64 prefill dequant-GEMM: x bf16 [2048, 4096], W [14336, 4096] (tcgen05 path).
     TFLOP/s = 2*M*N*K / time; the dequant work is not counted."""
     M, K, N = 2048, 4096, 14336
     ws = [gaf.Weight.from_host(ctx, *synth_weight(rng, N, K), GROUP, BITS) for _ in range(2)]
     x = torch.randn((M, K), device="cuda").to(torch.bfloat16)
     y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
-    with torch.cuda.stream(stream):
-        for _ in range(3):
-            for w in ws:
-                gaf.linear(ctx, w, x, out=y)
-        stream.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(iters):
-            for w in ws:
-                gaf.linear(ctx, w, x, out=y)
-        e1.record(stream)
-        stream.synchronize()
-    ctx.synchronize()
-    ms = e0.elapsed_time(e1) / (iters * len(ws))
+
+    def step():
+        for w in ws:
+            gaf.linear(ctx, w, x, out=y)
+
+    ms, st, clk = time_graph(ctx, torch, stream, step, iters, 3, min_seconds=1.0 if iters > 2 else 0.0, clocks=clocks)
+    ms /= len(ws)
     tf = 2.0 * M * N * K / ms / 1e9
     burst, sustained, kind = measured_peak_tflops()
     for w in ws:
@@ -238,7 +204,164 @@ def time_prefill(gaf, ctx, torch, stream, rng, iters=20):
     return {"workload": "gaf4_64 prefill M=2048 K=4096 N=14336", "tflops": round(tf, 1), "ms": round(ms, 4),
             "frac_of_burst_peak": round(tf / burst, 4), "frac_of_sustained_peak": round(tf / sustained, 4),
             "peak_tflops": {"burst": burst, "sustained": sustained, "kind": f"of {kind}"},
-            "bound": "tensor"}
+            "stats_ms_per_two_gemms": st, "clocks": clk, "bound": "tensor"}
+
+
+def check_outputs(gaf, ctx, torch, stream):
+    """The timed configuration once on converter-made weights against the CPU oracle: one 8B FFN layer (gate|up and
+    down, M = 1) through a launch list and through single calls.  Returns the largest relative error; raises
+    when it exceeds 1e-2."""
+    from oracle import gaf_oracle as oracle
+    sys.path.insert(0, str(ROOT / "tests"))
+    from helpers import bits_from_torch_bf16, make_weights, make_x_bf16, rel_err, torch_bf16_from_bits
+    worst = 0.0
+    ws, xs, ys, refs = [], [], [], []
+    with torch.cuda.stream(stream):
+        for i, (N, K) in enumerate(((2 * 14336, 4096), (4096, 14336))):
+            p, s, b = make_weights(oracle, N, K, GROUP, BITS, seed=i)
+            xb, xf = make_x_bf16(oracle, 1, K, seed=10 + i)
+            ws.append(gaf.Weight.from_host(ctx, p, s, b, GROUP, BITS))
+            xs.append(torch_bf16_from_bits(xb, "cuda:0"))
+            ys.append(torch.zeros((1, N), dtype=torch.bfloat16, device="cuda"))
+            refs.append(oracle.matmul_f32(xf, p, s, b, GROUP, BITS))
+        batch = gaf.Batch(ctx, ws, xs, ys)
+        batch.run()
+        stream.synchronize()
+        ctx.synchronize()
+        for w, x, y, ref in zip(ws, xs, ys, refs):
+            worst = max(worst, rel_err(oracle.bf16_to_f32(bits_from_torch_bf16(y)), ref))
+            single = gaf.linear(ctx, w, x)
+            stream.synchronize()
+            ctx.synchronize()
+            worst = max(worst, rel_err(oracle.bf16_to_f32(bits_from_torch_bf16(single)), ref))
+        batch.close()
+        for w in ws:
+            w.free()
+    if not worst <= 1e-2:
+        raise RuntimeError(f"output check failed: rel {worst}")
+    return worst
+
+
+def time_incumbent_kernel(torch, weights_host, steps=5):
+    """The reference's own CUDA kernel (talu_gaffine_u4_matvec_f32, compiled unchanged into oracle/_ref/) on the
+    same weights under its own launch geometry, f32 activations: the GPU baseline this path replaces."""
+    from oracle import gaf_oracle as oracle
+    cubin = oracle.build_ref()
+    if cubin is None:
+        return None
+    sys.path.insert(0, str(ROOT / "tests"))
+    from helpers import CubinModule, to_dev
+    mod = CubinModule(cubin)
+    dev = [(N, K, to_dev(p), to_dev(s), to_dev(b)) for (N, K, p, s, b) in weights_host]
+    xs = {K: torch.randn((1, K), device="cuda") for K in {k for _, k, *_ in dev}}
+    ys = [torch.empty((1, N), device="cuda") for N, *_ in dev]
+
+    def step():
+        for (N, K, dp, ds, db), y in zip(dev, ys):
+            mod.launch("talu_gaffine_u4_matvec_f32", ((N + 7) // 8, 1), (xs[K], dp, ds, db, y, K, N, GROUP, 1, 1))
+
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    nbytes = sum(weight_bytes(N, K) + K * 4 + N * 4 for N, K, *_ in dev)
+    return {"kernel": "talu_gaffine_u4_matvec_f32 (core/src/compute/cuda/kernels/ops/quant_ops.cu:46-93, compiled unchanged)",
+            "ms_per_step": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 2), "gemvs": len(dev),
+            "note": "the first two layers of the same stack, f32 activations as its contract requires, block 256 / grid ceil(N / 8)"}
+
+
+def tp_parity_check(ctx, torch, dist, rank, world, stream):
+    """Every rank's output of sharded linears against the UNSHARDED CPU oracle, on converter-made weights (the
+    oracle's quantizer): a column-parallel -> row-parallel chain (hidden 1024, ffn 2048; M = 1, 2, 4) and one
+    full-size Llama-3-70B `down` shard (8192 x 28672, M = 1), the sum over ranks taken by every path the library
+    has.  Raises when any rank is beyond 1e-2 (max relative error); returns the worst figure and the paths."""
+    import talu_b200 as gaf
+    from talu_b200.tp import SHARD_COL, SHARD_ROW
+    from oracle import gaf_oracle as oracle
+    if rank == 0:
+        oracle.build()
+    dist.barrier()
+    sys.path.insert(0, str(ROOT / "tests"))
+    from helpers import bits_from_torch_bf16, make_weights, make_x_bf16, rel_err, torch_bf16_from_bits
+    peer = ctx.uses_peer_memory()
+    paths = [("launch list, sums inside the launch", None),
+             ("fused into the GEMV write-out", {"fused_allreduce": 1, "peer_allreduce": 1}),
+             ("GEMV then the one-shot peer-memory kernel", {"fused_allreduce": 0, "peer_allreduce": 1}),
+             ("GEMV then NCCL all-reduce", {"fused_allreduce": 0, "peer_allreduce": 0})]
+    worst, report = 0.0, []
+
+    def to_f32(t):
+        return oracle.bf16_to_f32(bits_from_torch_bf16(t))
+
+    with torch.cuda.stream(stream):
+        # ---- chain ----
+        H, F = 1024, 2048
+        p1, s1, b1 = make_weights(oracle, F, H, GROUP, BITS, seed=101)
+        p2, s2, b2 = make_weights(oracle, H, F, GROUP, BITS, seed=102)
+        w1 = gaf.Weight.from_host(ctx, p1, s1, b1, GROUP, BITS, shard=SHARD_COL, tp_rank=rank, tp_size=world)
+        w2 = gaf.Weight.from_host(ctx, p2, s2, b2, GROUP, BITS, shard=SHARD_ROW, tp_rank=rank, tp_size=world)
+        # ---- one full-size row-parallel shard ----
+        N3, K3 = 8192, 28672
+        p3, s3, b3 = make_weights(oracle, N3, K3, GROUP, BITS, seed=103)
+        w3 = gaf.Weight.from_host(ctx, p3, s3, b3, GROUP, BITS, shard=SHARD_ROW, tp_rank=rank, tp_size=world)
+        xb3, xf3 = make_x_bf16(oracle, 1, K3, seed=113)
+        ref3 = oracle.matmul_f32(xf3, p3, s3, b3, GROUP, BITS)
+        k3 = K3 // world
+        x3 = torch_bf16_from_bits(np.ascontiguousarray(xb3[:, rank * k3:(rank + 1) * k3]), "cuda")
+        for name, opts in paths:
+            for k, v in (opts or {}).items():
+                ctx.set_option(k, v)
+            errs = []
+            for M in (1, 2, 4):
+                xb, xf = make_x_bf16(oracle, M, H, seed=110 + M)
+                href = oracle.matmul_f32(xf, p1, s1, b1, GROUP, BITS)
+                href = oracle.bf16_to_f32(oracle.f32_to_bf16_rne(href))      # the chain hands bf16 activations on
+                yref = oracle.matmul_f32(href, p2, s2, b2, GROUP, BITS)
+                x = torch_bf16_from_bits(xb, "cuda")
+                h = torch.empty((M, F // world), dtype=torch.bfloat16, device="cuda")
+                y = torch.empty((M, H), dtype=torch.bfloat16, device="cuda")
+                if opts is None:
+                    b = gaf.Batch(ctx, [w1, w2], [x, h], [h, y], depends=[0, 1], reduce=[0, 1])
+                    b.run()
+                    stream.synchronize()
+                    ctx.synchronize()
+                    b.close()
+                else:
+                    gaf.linear(ctx, w1, x, out=h)
+                    gaf.linear_allreduce(ctx, w2, h, out=y)
+                    stream.synchronize()
+                    ctx.synchronize()
+                errs.append(rel_err(to_f32(y), yref))
+            y3 = torch.empty((1, N3), dtype=torch.bfloat16, device="cuda")
+            if opts is None:
+                b = gaf.Batch(ctx, [w3], [x3], [y3], reduce=[1])
+                b.run()
+                stream.synchronize()
+                ctx.synchronize()
+                b.close()
+            else:
+                gaf.linear_allreduce(ctx, w3, x3, out=y3)
+                stream.synchronize()
+                ctx.synchronize()
+            errs.append(rel_err(to_f32(y3), ref3))
+            e = torch.tensor([max(errs)], dtype=torch.float64)
+            dist.all_reduce(e, op=dist.ReduceOp.MAX)            # the worst rank
+            report.append({"path": name, "rel": round(float(e.item()), 6)})
+            worst = max(worst, float(e.item()))
+        ctx.set_option("fused_allreduce", 1)
+        ctx.set_option("peer_allreduce", 1)
+        for w in (w1, w2, w3):
+            w.free()
+    if not worst <= 1e-2:
+        raise RuntimeError(f"rank {rank}: sharded linears differ from the unsharded oracle: {report}")
+    return {"rel": round(worst, 6), "tolerance": 1e-2, "peer_memory": bool(peer), "paths": report,
+            "cases": "col->row chain 1024/2048 at M = 1, 2, 4; 8192 x 28672 row-parallel shard at M = 1; every rank compared"}
 
 
 def run_single(args):
@@ -252,16 +375,19 @@ def run_single(args):
     rng = np.random.default_rng(0)
     layers = args.layers
     shapes = [("gate_up", 2 * 14336, 4096), ("down", 4096, 14336)]
-    weights = []
-    for _ in range(layers):
+    weights, weights_host = [], []
+    for li in range(layers):
         for name, N, K in shapes:
             p, s, b = synth_weight(rng, N, K)
             weights.append((name, gaf.Weight.from_host(ctx, p, s, b, GROUP, BITS)))
+            if li < 2:
+                weights_host.append((N, K, p, s, b))
     ring_bytes = sum(weight_bytes(w.N, w.K) for _, w in weights)
+    wl = [w for _, w in weights]
 
-    def make_io(M, pinned=False):
+    def make_io(M):
         xs = {K: torch.randn((M, K), device="cuda").to(torch.bfloat16) for K in (4096, 14336)}
-        ys = [torch.empty((M, w.N), dtype=torch.bfloat16, device="cuda") for _, w in weights]
+        ys = [torch.empty((M, w.N), dtype=torch.bfloat16, device="cuda") for w in wl]
         return xs, ys
 
     if args.quick and args.case == "prefill":
@@ -269,38 +395,137 @@ def run_single(args):
         return
     if args.quick and args.case == "stack70b":
         from talu_b200 import tp_bench
-        ms, nbytes, *_ = tp_bench.measure(args, existing_ctx=ctx, existing_stream=stream, M=args.m)
-        print(json.dumps({"quick": True, "workload": "llama3_70b_stack", "M": args.m, "layers": args.layers,
-                          "ms_per_step": ms, "gbs": round(nbytes / ms / 1e6, 2)}))
+        r = tp_bench.measure(args, existing_ctx=ctx, existing_stream=stream, M=args.m, quick=True)
+        print(json.dumps({"quick": True, "workload": "llama3_70b_stack", "M": args.m, "layers": r["layers"],
+                          "ms_per_step": r["ms"], "gbs": round(r["bytes"] / r["ms"] / 1e6, 2)}))
         return
-    results = {}
-    clocks = ClockSampler(dev)
-    with clocks:
-        for M in ((args.m,) if args.quick else (1, 2, 4, 8, 16)):
-            xs, ys = make_io(M)
+    if args.quick:
+        # small case for profilers: one launch list (or the separate launches with --separate), not a bench value
+        M = args.m
+        xs, ys = make_io(M)
+        with torch.cuda.stream(stream):
+            if args.separate or M > 4:
+                def step():
+                    for i, (w, y) in enumerate(zip(wl, ys)):
+                        gaf.hint_next_weight(ctx, wl[(i + 1) % len(wl)])
+                        gaf.linear(ctx, w, xs[w.K], out=y)
+            else:
+                batch = gaf.Batch(ctx, wl, [xs[w.K] for w in wl], ys)
+                step = batch.run
+            for _ in range(max(1, args.warmup)):
+                step()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(args.steps):
+                step()
+            e1.record(stream)
+            stream.synchronize()
+        ctx.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        nbytes = sum(launch_bytes(w.N, w.K, M) for w in wl)
+        print(json.dumps({"quick": True, "M": M, "mode": "separate" if (args.separate or M > 4) else "launch list",
+                          "gbs": round(nbytes / ms / 1e6, 2), "ms_per_step": ms}))
+        return
 
-            def step():
+    peak, peak_kind = measured_peak_hbm()
+    parity_rel = check_outputs(gaf, ctx, torch, stream)
+    results, lists = {}, {}
+    from talu_b200.clocks import ClockSampler
+    clocks = ClockSampler(dev)
+
+    def frac(gbs):
+        return {"gbs": round(gbs, 2), "frac_of_measured_hbm": round(gbs / peak, 4), "frac_of_nominal_8TBs": round(gbs / NOMINAL_HBM_GBS, 4)}
+
+    with clocks:
+        for M in (1, 2, 4, 8, 16):
+            xs, ys = make_io(M)
+            nbytes = sum(launch_bytes(w.N, w.K, M) for w in wl)
+
+            def separate():
                 # a decoder knows its layer order: each call names the weight the following call streams
-                for i, ((_, w), y) in enumerate(zip(weights, ys)):
-                    gaf.hint_next_weight(ctx, weights[(i + 1) % len(weights)][1])
+                for i, (w, y) in enumerate(zip(wl, ys)):
+                    gaf.hint_next_weight(ctx, wl[(i + 1) % len(wl)])
                     gaf.linear(ctx, w, xs[w.K], out=y)
 
-            ms = time_graph(ctx, torch, stream, step, args.steps, args.warmup)
-            nbytes = sum(launch_bytes(w.N, w.K, M) for _, w in weights)
-            results[M] = {"ms_per_step": ms, "gbs": nbytes / ms / 1e6, "bytes": nbytes}
+            ms, st, clk = time_graph(ctx, torch, stream, separate, args.steps, args.warmup, clocks=clocks)
+            results[M] = {"ms_per_step": ms, "gbs": nbytes / ms / 1e6, "bytes": nbytes, "stats_ms": st, "clocks": clk}
+            if M <= 4:
+                b = gaf.Batch(ctx, wl, [xs[w.K] for w in wl], ys)
+                ms, st, clk = time_graph(ctx, torch, stream, b.run, args.steps, args.warmup, clocks=clocks)
+                lists[M] = {"independent": {"ms_per_step": ms, "gbs": nbytes / ms / 1e6, "stats_ms": st, "clocks": clk,
+                                            "one_launch": b.one_launch}}
+                b.close()
+                b = gaf.Batch(ctx, wl, [xs[w.K] for w in wl], ys, depends=[0] + [1] * (len(wl) - 1))
+                ms, st, clk = time_graph(ctx, torch, stream, b.run, args.steps, args.warmup, min_seconds=0.5, clocks=clocks)
+                lists[M]["chained"] = {"ms_per_step": ms, "gbs": nbytes / ms / 1e6, "stats_ms": st}
+                b.close()
 
-        if args.quick:
-            print(json.dumps({"quick": True, "M": args.m, f"M{args.m}_gbs": round(results[args.m]["gbs"], 2),
-                              "ms_per_step": results[args.m]["ms_per_step"]}))
-            return
+        # ---- cfg2 as written: gate and up as separate weights (three GEMVs per layer) ----
+        un_layers = min(layers, 6)
+        un = []
+        for _ in range(un_layers):
+            for N, K in ((14336, 4096), (14336, 4096), (4096, 14336)):
+                un.append(gaf.Weight.from_host(ctx, *synth_weight(rng, N, K), GROUP, BITS))
+        xs, _ = make_io(1)
+        uys = [torch.empty((1, w.N), dtype=torch.bfloat16, device="cuda") for w in un]
+        unbytes = sum(launch_bytes(w.N, w.K, 1) for w in un)
+
+        def un_separate():
+            for i, (w, y) in enumerate(zip(un, uys)):
+                gaf.hint_next_weight(ctx, un[(i + 1) % len(un)])
+                gaf.linear(ctx, w, xs[w.K], out=y)
+
+        ms_s, st_s, _ = time_graph(ctx, torch, stream, un_separate, args.steps, args.warmup, min_seconds=0.5, clocks=clocks)
+        b = gaf.Batch(ctx, un, [xs[w.K] for w in un], uys)
+        ms_l, st_l, _ = time_graph(ctx, torch, stream, b.run, args.steps, args.warmup, min_seconds=0.5, clocks=clocks)
+        b.close()
+        unstacked = {"layers": un_layers, "gemvs_per_layer": 3,
+                     "separate_launches": {**frac(unbytes / ms_s / 1e6), "ms_per_step": round(ms_s, 5), "stats_ms": st_s},
+                     "launch_list": {**frac(unbytes / ms_l / 1e6), "ms_per_step": round(ms_l, 5), "stats_ms": st_l}}
+        for w in un:
+            w.free()
+
+        # ---- cfg1 (latency-bound: 2.4 MB per GEMV) and the cfg3 scheme sweep (K = N = 4096, ring >= 1 GB) ----
+        def sweep_case(N, K, G, bits, M, ring_target):
+            per = weight_bytes(N, K, G, bits)
+            n = max(8, int(ring_target // per))
+            ws_ = [gaf.Weight.from_host(ctx, *synth_weight(rng, N, K, G, bits), G, bits) for _ in range(n)]
+            x = torch.randn((M, K), device="cuda").to(torch.bfloat16)
+            ys_ = [torch.empty((M, N), dtype=torch.bfloat16, device="cuda") for _ in ws_]
+            nb = n * launch_bytes(N, K, M, G, bits)
+
+            def sep():
+                for i, (w, y) in enumerate(zip(ws_, ys_)):
+                    gaf.hint_next_weight(ctx, ws_[(i + 1) % n])
+                    gaf.linear(ctx, w, x, out=y)
+
+            ms, st, _ = time_graph(ctx, torch, stream, sep, args.steps, args.warmup, min_seconds=0.3, clocks=clocks)
+            out = {"gemvs": n, "ring_gb": round(n * per / 1e9, 3),
+                   "separate_launches": {**frac(nb / ms / 1e6), "us_per_gemv": round(ms * 1e3 / n, 3), "stats_ms": st}}
+            if bits == 4 and M <= 4:
+                b_ = gaf.Batch(ctx, ws_, [x] * n, ys_)
+                ms, st, _ = time_graph(ctx, torch, stream, b_.run, args.steps, args.warmup, min_seconds=0.3, clocks=clocks)
+                out["launch_list"] = {**frac(nb / ms / 1e6), "us_per_gemv": round(ms * 1e3 / n, 3), "stats_ms": st}
+                b_.close()
+            for w in ws_:
+                w.free()
+            return out
+
+        cfg1 = sweep_case(4096, 1024, 64, 4, 1, 0.6e9)
+        cfg1["note"] = "N=4096 K=1024 M=1: 2.4 MB per GEMV, latency-bound; reported for completeness, not against the roofline"
+        cfg3 = {}
+        for bits, G in ((4, 32), (4, 64), (4, 128), (8, 32), (8, 64), (8, 128)):
+            for M in (1, 8):
+                cfg3[f"gaf{bits}_{G}_M{M}"] = sweep_case(4096, 4096, G, bits, M, 1.0e9)
+
         # ---- end to end through the C ABI with host buffers (pinned), M = 1 ----
         M = 1
         hx = {K: torch.randn((M, K)).to(torch.bfloat16).pin_memory() for K in (4096, 14336)}
-        hy = [torch.empty((M, w.N), dtype=torch.bfloat16).pin_memory() for _, w in weights]
+        hy = [torch.empty((M, w.N), dtype=torch.bfloat16).pin_memory() for w in wl]
         hx_np = {K: v.view(torch.int16).numpy().view(np.uint16) for K, v in hx.items()}
         hy_np = [v.view(torch.int16).numpy().view(np.uint16) for v in hy]
 
-        batch = gaf.HostBatch(ctx, [w for _, w in weights], [hx_np[w.K] for _, w in weights], hy_np)
+        batch = gaf.HostBatch(ctx, wl, [hx_np[w.K] for w in wl], hy_np)
         e2e_mode = "tgaf_host_batch_submit (the list recorded once as a CUDA graph)"
         try:
             batch.record()
@@ -308,65 +533,84 @@ def run_single(args):
             e2e_mode = f"tgaf_linear_bf16_host_async_batch (recording failed: {exc})"
 
         def e2e_step():
-            # per launch: H2D copy of x from page-locked memory, kernel, D2H copy of y; one submit and one wait per step
+            # per GEMV: H2D copy of x from page-locked memory, kernel, D2H copy of y; one submit and one wait per step
             batch.submit()
             ctx.synchronize()
 
-        e2e_steps = max(3, min(args.steps, 20))
-        for _ in range(3):
+        e2e_steps = max(args.steps, 200)
+        for _ in range(5):
             e2e_step()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with torch.cuda.stream(stream):
-            e0.record(stream)
-            for _ in range(e2e_steps):
-                e2e_step()
-            e1.record(stream)
-            stream.synchronize()
-        e2e_ms = e0.elapsed_time(e1) / e2e_steps
-    h2d = sum(M * w.K * 2 for _, w in weights)
-    d2h = sum(M * w.N * 2 for _, w in weights)
-    e2e_gbs = results[1]["bytes"] / e2e_ms / 1e6
+        e2e_samples = []
+        for _ in range(e2e_steps):
+            t0 = time.perf_counter()
+            e2e_step()
+            e2e_samples.append((time.perf_counter() - t0) * 1e3)
+        e2e_ms = float(np.mean(e2e_samples[-args.steps:]))
+        batch.close()
+        h2d = sum(M * w.K * 2 for w in wl)
+        d2h = sum(M * w.N * 2 for w in wl)
+        e2e_gbs = results[1]["bytes"] / e2e_ms / 1e6
 
-    prefill = time_prefill(gaf, ctx, torch, stream, rng)
-    # the multi-GPU workload on this one GPU, so that the N > 1 lines have their N = 1 reference
-    from talu_b200 import tp_bench
-    st_ms, st_bytes, st_launches, st_layers, *_ = tp_bench.measure(args, existing_ctx=ctx, existing_stream=stream)
-    stack70b = {"workload": "llama3_70b_stack", "layers": st_layers, "ms_per_step": round(st_ms, 5),
-                "gbs": round(st_bytes / st_ms / 1e6, 2), "launches_per_step": st_launches}
-    # the skinny case of the same stack (64 activation rows: the tcgen05 GEMM with one 128-row half), HBM-bound
-    # by its roofline, limited here by the rate at which the dequant warps produce the bf16 operand
-    sk_ms, sk_bytes, *_ = tp_bench.measure(args, existing_ctx=ctx, existing_stream=stream, M=64)
-    stack70b["m64"] = {"ms_per_step": round(sk_ms, 5), "gbs": round(sk_bytes / sk_ms / 1e6, 2)}
+        prefill = time_prefill(gaf, ctx, torch, stream, rng, clocks=clocks)
+        # the multi-GPU workload on this one GPU, so that the N > 1 lines have their N = 1 reference
+        from talu_b200 import tp_bench
+        st70 = tp_bench.measure(args, existing_ctx=ctx, existing_stream=stream, also_m=(64,))
+        stack70b = {"workload": "llama3_70b_stack", "layers": st70["layers"], "ms_per_step": round(st70["ms"], 5),
+                    **frac(st70["bytes"] / st70["ms"] / 1e6), "stats_ms": st70["stats"], "submission": st70["submission"],
+                    "separate_launches": st70.get("separate")}
+        # the skinny case of the same stack (64 activation rows: the tcgen05 GEMM with one 128-row activation half)
+        sk = st70["also"][64]
+        stack70b["m64"] = {"ms_per_step": round(sk["ms"], 5), **frac(sk["bytes"] / sk["ms"] / 1e6), "stats_ms": sk["stats"]}
+    incumbent = time_incumbent_kernel(torch, weights_host)
 
-    peak, peak_kind = measured_peak_hbm()
-    launches_per_step = len(weights)
-    avg_launch_ms = results[1]["ms_per_step"] / launches_per_step
-    achieved = results[1]["bytes"] / launches_per_step / avg_launch_ms / 1e6
-    cores = os.cpu_count() or 1
-    cpu_gbs, cpu_per_call, cpu_n = cpu_path(args.cpu_seconds, cores)
+    head = lists[1]["independent"]
+    gemvs_per_step = len(wl)
+    achieved = head["gbs"]
+    from oracle import gaf_oracle as oracle
+    logical, policy = oracle.logical_cpu_count(), oracle.reference_thread_count()
+    cstack = cpu_stack(ffn_shapes(min(layers, 4)))
+    cbytes = sum(launch_bytes(N, K, 1) for N, K, *_ in cstack)
+    n_cpu = max(2, int(args.cpu_seconds / 0.02 / max(1, len(cstack) // 2)))
+    t_all = cpu_time_step(oracle, cstack, logical, n_cpu, 1)
+    t_pol = cpu_time_step(oracle, cstack, policy, max(2, n_cpu // 2), 1)
+    cpu_gbs = cbytes / float(np.mean(t_all)) / 1e9
 
     out = {
-        "metric": METRIC, "value": round(results[1]["gbs"], 2), "unit": "GB/s", "n_gpus": 1,
-        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(results[1]["ms_per_step"], 5),
+        "metric": METRIC, "value": round(head["gbs"], 2), "unit": "GB/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(head["ms_per_step"], 5),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "llama3_8b_ffn", "scheme": "gaf4_64", "M": 1, "layers": layers,
-                   "launches_per_step": launches_per_step, "gate_up_fused": True,
-                   "l2": f"distinct weights per launch, ring {ring_bytes / 1e9:.2f} GB > 126 MB L2 (no flush needed)",
-                   "timing": "CUDA graph replay, CUDA events on the launching stream"},
-        "decode": {f"M{m}": {"gbs": round(r["gbs"], 2), "ms_per_step": round(r["ms_per_step"], 5),
-                             "frac_of_measured_hbm": round(r["gbs"] / peak, 4),
-                             "frac_of_nominal_8TBs": round(r["gbs"] / NOMINAL_HBM_GBS, 4)} for m, r in results.items()},
+                   "gemvs_per_step": gemvs_per_step, "gate_up_stacked": True,
+                   "submission": "one launch list per step (tgaf_batch_run): 24 GEMVs, each with its own activations, one kernel launch",
+                   "l2": f"distinct weights per GEMV, ring {ring_bytes / 1e9:.2f} GB > 126 MB L2 (no flush needed)",
+                   "timing": "CUDA graph replay for >= 1 s, an event per step; value = mean of the last --steps steps"},
+        "stats_ms": head["stats_ms"],
+        "output_check": {"rel_err_vs_oracle": round(parity_rel, 6), "tolerance": 1e-2,
+                         "what": "one FFN layer of converter-made weights, M = 1, launch list and single calls"},
+        "decode": {f"M{m}": {"separate_launches": {**frac(r["gbs"]), "ms_per_step": round(r["ms_per_step"], 5), "stats_ms": r["stats_ms"], "clocks": r["clocks"]},
+                             **({"launch_list": {**frac(lists[m]["independent"]["gbs"]), "ms_per_step": round(lists[m]["independent"]["ms_per_step"], 5),
+                                                 "stats_ms": lists[m]["independent"]["stats_ms"], "clocks": lists[m]["independent"]["clocks"]},
+                                 "launch_list_every_gemv_waits_for_its_predecessor": {**frac(lists[m]["chained"]["gbs"]),
+                                                                                       "ms_per_step": round(lists[m]["chained"]["ms_per_step"], 5)}}
+                                if m in lists else {})}
+                   for m, r in results.items()},
+        "cfg2_gate_and_up_as_separate_weights": unstacked,
+        "cfg1": cfg1, "cfg3": cfg3,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
-                     "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}",
-                     "traffic": NCU_TRAFFIC_PER_LAUNCH,
-                     "traffic_note": "ncu dram bytes per launch, mean of the step's two shapes (algorithmic mean 49.6 MB; 10.9 MB of it is the next launch's head, prefetched to L2 and counted twice under ncu's cache flush)"},
-        "cpu_baseline": {"value": round(cpu_gbs, 3), "unit": "GB/s", "cores": cores, "kind": "port",
-                         "sample": f"{cpu_n} calls of one gate-shaped matrix [14336 x 4096], M=1, f32 activations ({cpu_per_call * 1e3:.2f} ms each)"},
+                     "frac": round(achieved / peak, 4), "frac_of_nominal_8TBs": round(achieved / NOMINAL_HBM_GBS, 4),
+                     "peak_kind": f"of {peak_kind}", "traffic": NCU_TRAFFIC_PER_GEMV,
+                     "note": "achieved = algorithmic bytes of a step / its time (= bytes per GEMV / (launch time / 24)); traffic: ncu dram bytes per GEMV of a launch list"},
+        "cpu_baseline": {"value": round(cpu_gbs, 3), "unit": "GB/s", "cores": logical, "kind": "port",
+                         "sample": f"{len(t_all)} passes over the first {len(cstack)} matrices of the same stack ({cbytes / 1e6:.0f} MB per pass), M=1, f32 activations",
+                         "reference_thread_policy": {"threads": policy, "value": round(cbytes / float(np.mean(t_pol)) / 1e9, 3)}},
+        "incumbent_gpu_kernel": incumbent,
         "e2e": {"value": round(e2e_gbs, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": round(e2e_ms, 4), "note": e2e_mode + " + tgaf_synchronize per step: per launch pinned host x -> device, kernel, y -> pinned host, copies on their own streams"},
+                "ms_per_step": round(e2e_ms, 4), "stats_ms": stats_ms(e2e_samples),
+                "note": e2e_mode + " + tgaf_synchronize per step, host wall clock: per GEMV pinned host x -> device, kernel, y -> pinned host, copies on their own streams"},
         "prefill": prefill,
         "llama3_70b_stack_1gpu": stack70b,
-        "gpu_launches": launches_per_step * args.steps,
+        "gpu_launches": args.steps,
+        "gpu_launches_note": "kernel launches inside the timed K steps of the headline: one launch list per step (24 GEMVs each)",
         "clocks": clocks.summary(),
     }
     print(json.dumps(out))
@@ -383,8 +627,9 @@ def main():
     ap.add_argument("--case", default="decode", choices=["decode", "prefill", "stack70b"],
                     help="with --quick: which kernel the small case runs")
     ap.add_argument("--m", type=int, default=1, help="activation rows of the --quick decode / stack70b case")
+    ap.add_argument("--separate", action="store_true", help="with --quick: separate launches instead of one launch list")
     ap.add_argument("--quick", action="store_true",
-                    help="M = 1 only, no end-to-end and no CPU leg (small case for profilers; not a bench value)")
+                    help="one configuration only, no end-to-end and no CPU leg (small case for profilers; not a bench value)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -392,7 +637,7 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1 or args.gpus > 1:
         from talu_b200 import tp_bench
-        tp_bench.run(args)
+        tp_bench.run(args, parity_check=tp_parity_check)
         return
     run_single(args)
 

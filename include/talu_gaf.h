@@ -192,8 +192,42 @@ typedef struct tgaf_host_batch tgaf_host_batch;
 int32_t tgaf_host_batch_create(tgaf_ctx *ctx, uint32_t count, const tgaf_weight *const *weights,
                                const void *const *xs_bf16_host, const uint32_t *ms, void *const *ys_bf16_host,
                                tgaf_host_batch **out_batch);
+/* The same with reduce[i] = 1 marking row-parallel weights whose y_i is summed over the communicator's ranks
+ * before it travels back (every rank records and submits the same list; all ms equal).  reduce == NULL: as above.
+ * Either call records the STAGED form when all ms are equal and the list can run as one launch (see launch
+ * lists below) or has a sum over the ranks: the x buffers go up into one device block, one launch list runs, the
+ * y block comes down; host buffers that lie back to back in memory travel as one copy, so a caller that keeps
+ * its activations (and its outputs) in one page-locked block pays two copies per step. */
+int32_t tgaf_host_batch_create_reduce(tgaf_ctx *ctx, uint32_t count, const tgaf_weight *const *weights,
+                                      const void *const *xs_bf16_host, const uint32_t *ms, void *const *ys_bf16_host,
+                                      const uint8_t *reduce, tgaf_host_batch **out_batch);
+/* 1 when the recorded list is the staged form around ONE kernel launch */
+int32_t tgaf_host_batch_uses_one_launch(const tgaf_host_batch *batch);
 int32_t tgaf_host_batch_submit(tgaf_ctx *ctx, tgaf_host_batch *batch);
 int32_t tgaf_host_batch_destroy(tgaf_ctx *ctx, tgaf_host_batch *batch);
+
+/* ---- launch lists ---------------------------------------------------------
+ * The linears of a decoder step as ONE call: `count` operations y_i = x_i * W_i^T, bf16 device buffers, all with
+ * the same m.  No counterpart in the reference, whose decoder issues each linear on its own
+ * (core/src/inference/backend/cuda/engine.zig:4431-4474); it is the device-buffer sibling of tgaf_host_batch.
+ * When every weight is gaf4 with one group size and scales dtype and m <= 4, the whole list runs as ONE kernel
+ * launch: the copy warps stream from one weight straight into the next, so launch gap, ring ramp-up / drain and
+ * write-out tail are paid once per list instead of once per weight; otherwise the calls run one after the other.
+ *   depends[i] = 1: x_i is written by an earlier operation of the list (as down after gate|up): operation i starts
+ *                   on its activations only when operation i - 1 is complete on the whole GPU.  0 (or depends ==
+ *                   NULL): the caller promises that x_i is written by no operation of this list.
+ *   reduce[i]  = 1: W_i is row-parallel; y_i is summed over the communicator's ranks (inside the launch when the
+ *                   peer-memory path is up, see tgaf_linear_bf16_allreduce).  NULL: none.
+ * The buffers, the weights and the context must outlive the batch.  tgaf_batch_run only enqueues (it may be
+ * captured into a CUDA graph after one eager run). */
+typedef struct tgaf_batch tgaf_batch;
+int32_t tgaf_batch_create(tgaf_ctx *ctx, uint32_t count, const tgaf_weight *const *weights, const void *const *xs_bf16,
+                          uint32_t m, void *const *ys_bf16, const uint8_t *depends, const uint8_t *reduce,
+                          tgaf_batch **out_batch);
+int32_t tgaf_batch_run(tgaf_ctx *ctx, tgaf_batch *batch);
+/* 1 when the list runs as one kernel launch, 0 when its calls run one after the other */
+int32_t tgaf_batch_uses_one_launch(const tgaf_batch *batch);
+int32_t tgaf_batch_destroy(tgaf_ctx *ctx, tgaf_batch *batch);
 
 /* Raw-pointer launch with the argument list of the reference's kernel wrapper
  * compute.cuda.gaffine_u4_matvec.runWithFunction

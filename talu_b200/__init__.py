@@ -30,10 +30,11 @@ from .gaf import (  # noqa: F401
     ffn_swiglu,
     linear_host,
     HostBatch,
+    Batch,
     make_comm_id,
 )
 
 __all__ = [
-    "Context", "Weight", "GafError", "linear", "linear_fixed_scratch", "hint_next_weight", "linear_allreduce", "linear_bias", "ACT_SILU", "ACT_GELU", "ffn_swiglu", "linear_host", "HostBatch", "make_comm_id", "dequant_f32", "dequant_f32_host", "embedding_lookup_f32",
+    "Context", "Weight", "GafError", "linear", "linear_fixed_scratch", "hint_next_weight", "linear_allreduce", "linear_bias", "ACT_SILU", "ACT_GELU", "ffn_swiglu", "linear_host", "HostBatch", "Batch", "make_comm_id", "dequant_f32", "dequant_f32_host", "embedding_lookup_f32",
     "gaffine_matvec_f32", "SCALES_F16", "SCALES_BF16", "SHARD_NONE", "SHARD_COL", "SHARD_ROW",
 ]

@@ -34,6 +34,8 @@ SIGNATURES = {
     "tgaf_linear_bf16_host_async": (_i32, [_vp, _vp, _vp, _u32, _vp]),
     "tgaf_linear_bf16_host_async_batch": (_i32, [_vp, _u32, _vp, _vp, _vp, _vp]),
     "tgaf_host_batch_create": (_i32, [_vp, _u32, _vp, _vp, _vp, _vp, C.POINTER(_vp)]),
+    "tgaf_host_batch_create_reduce": (_i32, [_vp, _u32, _vp, _vp, _vp, _vp, _vp, C.POINTER(_vp)]),
+    "tgaf_host_batch_uses_one_launch": (_i32, [_vp]),
     "tgaf_host_batch_submit": (_i32, [_vp, _vp]),
     "tgaf_host_batch_destroy": (_i32, [_vp, _vp]),
     "tgaf_gaffine_u4_matvec_f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32]),
@@ -53,6 +55,10 @@ SIGNATURES = {
     "tgaf_linear_f32_bias": (_i32, [_vp, _vp, _vp, _u32, _vp, _vp]),
     "tgaf_ffn_gated_bf16": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _vp]),
     "tgaf_watchdog_wait": (_i32, [_vp, _vp, _u32]),
+    "tgaf_batch_create": (_i32, [_vp, _u32, _vp, _vp, _u32, _vp, _vp, _vp, C.POINTER(_vp)]),
+    "tgaf_batch_run": (_i32, [_vp, _vp]),
+    "tgaf_batch_uses_one_launch": (_i32, [_vp]),
+    "tgaf_batch_destroy": (_i32, [_vp, _vp]),
 }
 
 # tgaf_watch_fns: the three hooks of tgaf_watchdog_wait

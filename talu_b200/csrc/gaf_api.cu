@@ -16,6 +16,7 @@
 #include <new>
 #include <string>
 #include <thread>
+#include <vector>
 
 using namespace tgaf;
 
@@ -111,6 +112,7 @@ struct tgaf_ctx {
     size_t gemm_ws_bytes = 0;
     unsigned int *gemm_flags = nullptr;
     size_t gemm_flag_count = 0;
+    std::vector<tgaf_batch *> batches;   // live launch lists (their counters are reset after an abandoned launch)
     NcclComm comm = nullptr;
     uint32_t comm_rank = 0, comm_size = 1;
     PeerComm peer = {{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr}, 0, 1, false};
@@ -131,11 +133,27 @@ namespace {
 void peer_teardown(tgaf_ctx *ctx);
 }
 
+// A launch list of device-buffer linears (tgaf_batch_*): one kernel launch when the list qualifies, the calls one
+// after the other otherwise.
+struct tgaf_batch {
+    GemvList *list = nullptr;
+    unsigned long long *tagged = nullptr;   // the list's own split-K words (its operations overlap in time)
+    size_t tagged_bytes = 0;
+    uint32_t m = 0;
+    std::vector<const tgaf_weight *> weights;
+    std::vector<const void *> xs;
+    std::vector<void *> ys;
+    std::vector<uint8_t> deps, reduce;
+};
+
 // A recorded list of queued host-buffer calls (tgaf_host_batch_*): the CUDA graph of their copies and kernels.
 struct tgaf_host_batch {
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     uint32_t count = 0;
+    // staged form: all activations in one device block, all outputs in another, one launch list between the copies
+    tgaf_batch *inner = nullptr;
+    uint8_t *d_x = nullptr, *d_y = nullptr;
 };
 
 struct tgaf_weight {
@@ -528,6 +546,7 @@ int32_t tgaf_ctx_destroy(tgaf_ctx *ctx) {
         ctx->comm = nullptr;
     }
     peer_teardown(ctx);
+    while (!ctx->batches.empty()) tgaf_batch_destroy(ctx, ctx->batches.back());   // launch lists the caller left behind
     if (ctx->scratch.partials) cudaFree(ctx->scratch.partials);
     if (ctx->scratch.counters) cudaFree(ctx->scratch.counters);
     if (ctx->scratch.tagged) cudaFree(ctx->scratch.tagged);
@@ -658,6 +677,10 @@ int32_t tgaf_synchronize(tgaf_ctx *ctx) {
         if (ctx->scratch.tagged) cudaMemset(ctx->scratch.tagged, 0, ctx->scratch.tagged_bytes);  // ... or tags set
         if (ctx->d_grid_bar) cudaMemset(ctx->d_grid_bar, 0, 4 * sizeof(unsigned int));
         if (ctx->gemm_flags) cudaMemset(ctx->gemm_flags, 0, ctx->gemm_flag_count * sizeof(unsigned int));
+        for (tgaf_batch *b : ctx->batches) {
+            if (b->list) gemv_list_reset(b->list);
+            if (b->tagged) cudaMemset(b->tagged, 0, b->tagged_bytes);
+        }
         return fail(ctx, TGAF_ERR_DEVICE_FLAG, "a kernel gave up a bounded wait (code 0x%x)", flag);
     }
     return TGAF_OK;
@@ -677,6 +700,8 @@ int32_t tgaf_ctx_set_option(tgaf_ctx *ctx, const char *name, int64_t value) {
         ctx->tune.pdl = value != 0;
     } else if (!strcmp(name, "force_generic")) {
         ctx->tune.force_generic = value != 0;
+    } else if (!strcmp(name, "imma_small")) {
+        ctx->tune.imma_small = value != 0;
     } else if (!strcmp(name, "no_dp4a")) {
         ctx->tune.no_dp4a = value != 0;
     } else if (!strcmp(name, "peer_allreduce")) {
@@ -997,9 +1022,128 @@ int32_t tgaf_linear_bf16_host_async_batch(tgaf_ctx *ctx, uint32_t count, const t
     return TGAF_OK;
 }
 
-int32_t tgaf_host_batch_create(tgaf_ctx *ctx, uint32_t count, const tgaf_weight *const *weights,
-                               const void *const *xs_bf16_host, const uint32_t *ms, void *const *ys_bf16_host,
-                               tgaf_host_batch **out_batch) {
+namespace {
+
+// Copies `count` buffers between host and the device block, merging neighbours that are adjacent on both sides
+// (a decoder that keeps its activations in one page-locked block pays for one copy, not one per linear).
+cudaError_t copy_runs(uint32_t count, const std::vector<size_t> &dev_off, const std::vector<size_t> &bytes, uint8_t *dev,
+                      const void *const *host, bool to_device, cudaStream_t stream) {
+    uint32_t i = 0;
+    while (i < count) {
+        uint32_t j = i + 1u;
+        size_t run = bytes[i];
+        while (j < count && static_cast<const uint8_t *>(host[j]) == static_cast<const uint8_t *>(host[i]) + run &&
+               dev_off[j] == dev_off[i] + run) {
+            run += bytes[j];
+            ++j;
+        }
+        void *h = const_cast<void *>(host[i]);
+        const cudaError_t e = to_device ? cudaMemcpyAsync(dev + dev_off[i], h, run, cudaMemcpyHostToDevice, stream)
+                                        : cudaMemcpyAsync(h, dev + dev_off[i], run, cudaMemcpyDeviceToHost, stream);
+        if (e != cudaSuccess) return e;
+        i = j;
+    }
+    return cudaSuccess;
+}
+
+void host_batch_free(tgaf_ctx *ctx, tgaf_host_batch *b) {
+    if (b->exec) cudaGraphExecDestroy(b->exec);
+    if (b->graph) cudaGraphDestroy(b->graph);
+    if (b->inner) tgaf_batch_destroy(ctx, b->inner);
+    if (b->d_x) cudaFree(b->d_x);
+    if (b->d_y) cudaFree(b->d_y);
+    delete b;
+}
+
+// The staged form of a recorded host list: x block up, ONE launch list (or, with sums over the ranks on a
+// communicator without peer memory, its calls one after the other), y block down.  Returns TGAF_OK with *out == nullptr
+// when the list is not of that kind (different m per call, or no single launch to gain).
+int32_t host_batch_staged(tgaf_ctx *ctx, uint32_t count, const tgaf_weight *const *weights, const void *const *xs_host,
+                          const uint32_t *ms, void *const *ys_host, const uint8_t *reduce, tgaf_host_batch **out) {
+    *out = nullptr;
+    bool any_reduce = false;
+    for (uint32_t i = 0; i < count; ++i) {
+        if (!weights[i] || !xs_host[i] || !ys_host[i] || ms[i] == 0) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null entry %u or M == 0", i);
+        if (ms[i] != ms[0]) {
+            if (reduce) return fail(ctx, TGAF_ERR_UNSUPPORTED, "a host batch with sums over the ranks needs the same M in every call");
+            return TGAF_OK;
+        }
+        if (reduce && reduce[i]) any_reduce = true;
+    }
+    const uint32_t m = ms[0];
+    std::vector<size_t> xoff(count), yoff(count), xb(count), yb(count);
+    size_t xt = 0, yt = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+        xb[i] = static_cast<size_t>(m) * weights[i]->v.K * 2u, yb[i] = static_cast<size_t>(m) * weights[i]->v.N * 2u;
+        xoff[i] = xt, yoff[i] = yt;
+        xt += (xb[i] + 15u) & ~size_t(15), yt += (yb[i] + 15u) & ~size_t(15);
+    }
+    tgaf_host_batch *b = new (std::nothrow) tgaf_host_batch();
+    if (!b) return fail(ctx, TGAF_ERR_OUT_OF_MEMORY, "host batch");
+    b->count = count;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&b->d_x), xt);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&b->d_y), yt);
+    if (e != cudaSuccess) {
+        host_batch_free(ctx, b);
+        return cuda_fail(ctx, e, "host batch staging");
+    }
+    std::vector<const void *> dx(count);
+    std::vector<void *> dy(count);
+    for (uint32_t i = 0; i < count; ++i) dx[i] = b->d_x + xoff[i], dy[i] = b->d_y + yoff[i];
+    int32_t st = tgaf_batch_create(ctx, count, weights, dx.data(), m, dy.data(), nullptr, any_reduce ? reduce : nullptr, &b->inner);
+    if (st != TGAF_OK) {
+        host_batch_free(ctx, b);
+        return st;
+    }
+    if (!b->inner->list && !any_reduce) {   // nothing to gain: the queued form overlaps its copies with its kernels
+        host_batch_free(ctx, b);
+        return TGAF_OK;
+    }
+    auto enqueue = [&]() -> int32_t {
+        cudaError_t ce = copy_runs(count, xoff, xb, b->d_x, xs_host, true, ctx->stream);
+        if (ce != cudaSuccess) return cuda_fail(ctx, ce, "host batch upload");
+        const int32_t rs = tgaf_batch_run(ctx, b->inner);
+        if (rs != TGAF_OK) return rs;
+        ce = copy_runs(count, yoff, yb, b->d_y, ys_host, false, ctx->stream);
+        if (ce != cudaSuccess) return cuda_fail(ctx, ce, "host batch download");
+        return TGAF_OK;
+    };
+    st = enqueue();   // once for real: scratch, kernel attributes
+    if (st == TGAF_OK) st = tgaf_synchronize(ctx);
+    if (st != TGAF_OK) {
+        host_batch_free(ctx, b);
+        return st;
+    }
+    e = cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) {
+        host_batch_free(ctx, b);
+        return cuda_fail(ctx, e, "cudaStreamBeginCapture");
+    }
+    st = enqueue();
+    cudaGraph_t graph = nullptr;
+    const cudaError_t e_end = cudaStreamEndCapture(ctx->stream, &graph);
+    if (st == TGAF_OK && (e_end != cudaSuccess || !graph)) st = cuda_fail(ctx, e_end, "capturing the host batch");
+    if (st == TGAF_OK) {
+        b->graph = graph;
+        e = cudaGraphInstantiate(&b->exec, graph, 0);
+        if (e != cudaSuccess) st = cuda_fail(ctx, e, "cudaGraphInstantiate");
+    } else if (graph) {
+        cudaGraphDestroy(graph);
+    }
+    if (st != TGAF_OK) {
+        cudaGetLastError();
+        host_batch_free(ctx, b);
+        return st;
+    }
+    *out = b;
+    return TGAF_OK;
+}
+
+}  // namespace
+
+int32_t tgaf_host_batch_create_reduce(tgaf_ctx *ctx, uint32_t count, const tgaf_weight *const *weights,
+                                      const void *const *xs_bf16_host, const uint32_t *ms, void *const *ys_bf16_host,
+                                      const uint8_t *reduce, tgaf_host_batch **out_batch) {
     if (out_batch) *out_batch = nullptr;
     if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
     if (!out_batch || count == 0 || !weights || !xs_bf16_host || !ms || !ys_bf16_host)
@@ -1007,6 +1151,10 @@ int32_t tgaf_host_batch_create(tgaf_ctx *ctx, uint32_t count, const tgaf_weight 
     cudaSetDevice(ctx->device);
     if (ctx->stream == cudaStreamLegacy || ctx->stream == cudaStreamPerThread || ctx->stream == nullptr)
         return fail(ctx, TGAF_ERR_UNSUPPORTED, "recording needs a context on a stream of its own (the default streams cannot be captured)");
+    {
+        const int32_t sst = host_batch_staged(ctx, count, weights, xs_bf16_host, ms, ys_bf16_host, reduce, out_batch);
+        if (sst != TGAF_OK || *out_batch) return sst;
+    }
     // 1. once for real: every staging buffer, scratch area and kernel attribute the list needs exists afterwards
     ctx->pipe_calls = 0;
     int32_t st = tgaf_linear_bf16_host_async_batch(ctx, count, weights, xs_bf16_host, ms, ys_bf16_host);
@@ -1055,6 +1203,14 @@ int32_t tgaf_host_batch_create(tgaf_ctx *ctx, uint32_t count, const tgaf_weight 
     return TGAF_OK;
 }
 
+int32_t tgaf_host_batch_create(tgaf_ctx *ctx, uint32_t count, const tgaf_weight *const *weights,
+                               const void *const *xs_bf16_host, const uint32_t *ms, void *const *ys_bf16_host,
+                               tgaf_host_batch **out_batch) {
+    return tgaf_host_batch_create_reduce(ctx, count, weights, xs_bf16_host, ms, ys_bf16_host, nullptr, out_batch);
+}
+
+int32_t tgaf_host_batch_uses_one_launch(const tgaf_host_batch *batch) { return batch && batch->inner && batch->inner->list ? 1 : 0; }
+
 int32_t tgaf_host_batch_submit(tgaf_ctx *ctx, tgaf_host_batch *batch) {
     if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
     if (!batch || !batch->exec) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null batch");
@@ -1069,8 +1225,100 @@ int32_t tgaf_host_batch_destroy(tgaf_ctx *ctx, tgaf_host_batch *batch) {
         cudaSetDevice(ctx->device);
         cudaStreamSynchronize(ctx->stream);
     }
-    if (batch->exec) cudaGraphExecDestroy(batch->exec);
-    if (batch->graph) cudaGraphDestroy(batch->graph);
+    host_batch_free(ctx, batch);
+    return TGAF_OK;
+}
+
+int32_t tgaf_batch_create(tgaf_ctx *ctx, uint32_t count, const tgaf_weight *const *weights, const void *const *xs_bf16,
+                          uint32_t m, void *const *ys_bf16, const uint8_t *depends, const uint8_t *reduce,
+                          tgaf_batch **out_batch) {
+    if (out_batch) *out_batch = nullptr;
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!out_batch || count == 0 || !weights || !xs_bf16 || !ys_bf16 || m == 0)
+        return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null array, empty list or m == 0");
+    bool any_reduce = false;
+    for (uint32_t i = 0; i < count; ++i) {
+        if (!weights[i] || !xs_bf16[i] || !ys_bf16[i]) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null entry %u", i);
+        if (reduce && reduce[i]) any_reduce = true;
+    }
+    if (depends && depends[0]) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "the first operation has no predecessor to depend on");
+    if (any_reduce && !ctx->comm) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "no communicator: call tgaf_comm_init first");
+    TGAF_CUDA(ctx, cudaSetDevice(ctx->device));
+    tgaf_batch *b = new (std::nothrow) tgaf_batch();
+    if (!b) return fail(ctx, TGAF_ERR_OUT_OF_MEMORY, "batch");
+    b->m = m;
+    std::vector<const WeightView *> views(count);
+    std::vector<const PeerComm *> fuse(count, nullptr);
+    for (uint32_t i = 0; i < count; ++i) {
+        b->weights.push_back(weights[i]);
+        b->xs.push_back(xs_bf16[i]);
+        b->ys.push_back(ys_bf16[i]);
+        b->deps.push_back(depends ? depends[i] : 0);
+        b->reduce.push_back(reduce ? reduce[i] : 0);
+        views[i] = &weights[i]->v;
+        if (b->reduce[i]) fuse[i] = &ctx->peer;
+    }
+    // one launch when every operation is on the M <= 4 kernel's ground (and every sum over the ranks can ride in it)
+    bool one_launch = gemv_list_eligible(views.data(), count, m, ctx->tune);
+    if (any_reduce && !(ctx->peer.ok && ctx->fused_allreduce)) one_launch = false;
+    if (one_launch) {
+        const size_t words = gemv_list_tagged_words(views.data(), count, m, ctx->tune, ctx->sm_count);
+        b->tagged_bytes = words * 8u < 256u ? 256u : words * 8u;
+        cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&b->tagged), b->tagged_bytes);
+        if (e == cudaSuccess) e = cudaMemsetAsync(b->tagged, 0, b->tagged_bytes, ctx->stream);
+        if (e == cudaSuccess)
+            e = gemv_list_create(views.data(), b->xs.data(), b->ys.data(), b->deps.data(), any_reduce ? fuse.data() : nullptr, count, m,
+                                 b->tagged, ctx->tune, ctx->sm_count, ctx->d_error_word, ctx->stream, &b->list);
+        if (e != cudaSuccess && e != cudaErrorNotSupported) {
+            if (b->tagged) cudaFree(b->tagged);
+            delete b;
+            return cuda_fail(ctx, e, "building the launch list");
+        }
+        if (e == cudaErrorNotSupported) {   // e.g. a buffer that is not 16-byte aligned: the calls run one by one
+            cudaGetLastError();
+            if (b->tagged) cudaFree(b->tagged);
+            b->tagged = nullptr, b->tagged_bytes = 0, b->list = nullptr;
+        }
+    }
+    ctx->batches.push_back(b);
+    *out_batch = b;
+    return TGAF_OK;
+}
+
+int32_t tgaf_batch_run(tgaf_ctx *ctx, tgaf_batch *batch) {
+    if (!ctx) return TGAF_ERR_INVALID_ARGUMENT;
+    if (!batch) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "null batch");
+    TGAF_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (batch->list) {
+        ctx->tune.next = nullptr;
+        cudaError_t e = gemv_list_launch(batch->list, ctx->tune, ctx->stream);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "launch list");
+        return TGAF_OK;
+    }
+    const uint32_t n = static_cast<uint32_t>(batch->weights.size());
+    for (uint32_t i = 0; i < n; ++i) {
+        if (i + 1u < n) ctx->tune.next = &batch->weights[i + 1u]->v;   // the list is the call order
+        const int32_t st = linear_device(ctx, batch->weights[i]->v, batch->xs[i], batch->m, batch->ys[i], false, batch->reduce[i] != 0);
+        if (st != TGAF_OK) return st;
+    }
+    return TGAF_OK;
+}
+
+int32_t tgaf_batch_uses_one_launch(const tgaf_batch *batch) { return batch && batch->list ? 1 : 0; }
+
+int32_t tgaf_batch_destroy(tgaf_ctx *ctx, tgaf_batch *batch) {
+    if (!batch) return TGAF_OK;
+    if (ctx) {
+        cudaSetDevice(ctx->device);
+        cudaStreamSynchronize(ctx->stream);
+        for (size_t i = 0; i < ctx->batches.size(); ++i)
+            if (ctx->batches[i] == batch) {
+                ctx->batches.erase(ctx->batches.begin() + static_cast<long>(i));
+                break;
+            }
+    }
+    if (batch->list) gemv_list_destroy(batch->list);
+    if (batch->tagged) cudaFree(batch->tagged);
     delete batch;
     return TGAF_OK;
 }

@@ -59,7 +59,9 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include <cstring>
+#include <new>
 #include <type_traits>
 
 namespace tgaf {
@@ -104,7 +106,18 @@ struct GemvParams {
     uint32_t fuse_rank, fuse_size;        //   fuse_size == 0: plain GEMV
     uint32_t y_f32;          // M <= 4 kernel: write y as fp32 although x is bf16 (first half of the fused FFN)
     uint32_t act;            // M <= 4 kernel: 1 / 2 = x is fp32 [M][2K] and the operand is silu / gelu(x[:, :K]) * x[:, K:]
-    unsigned int *grid_bar;  // M <= 4 kernel, two operations per launch: arrival counters, zero between launches
+    unsigned int *grid_bar;  // M <= 4 kernel, several operations per launch: arrival counters, zero between launches
+    uint32_t dep;            // M <= 4 kernel, several operations per launch: 1 = x of this operation is written by an earlier
+                             // operation of the launch (wait for the grid-wide arrival at the previous operation)
+};
+
+// A launch list for the M <= 4 kernel: operations in order, three tensor maps (packed, scales, biases) per operation,
+// all in device memory (written by the host before the launch).
+struct GemvOpList {
+    const GemvParams *ops;
+    const CUtensorMap *maps;
+    uint32_t count;
+    unsigned int *grid_bar;   // `count` arrival counters, zero between launches
 };
 
 // ---- small PTX wrappers ----------------------------------------------------
@@ -1019,12 +1032,16 @@ struct DpPlan {
 // so the ring never drains between the two; the second operation's warps meet at a grid-wide arrival
 // counter (every CTA's writer arrives when its share of the first output is stored) before they read that
 // output.  In that mode the "next" tensor maps are the second weight's.
+// NOPS = 0 runs a whole launch list (GemvOpList) the same way: the copy warp streams across all the weights of a
+// decoder step without a pause, an operation waits at the arrival counter of its predecessor only when its
+// activations are that predecessor's output (GemvParams::dep), and the per-launch costs (launch gap, ring ramp-up
+// and drain, write-out tail) are paid once per list instead of once per weight.
 template <int GB, int MD, bool XF32, int SD, int NCW, int NST, int BU, int NOPS>
 __global__ void __launch_bounds__((NCW + 2) * 32, 1)
 gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_constant__ CUtensorMap tmap_w,
                      const __grid_constant__ CUtensorMap tmap_s, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap next_w, const __grid_constant__ CUtensorMap next_s,
-                     const __grid_constant__ CUtensorMap next_b) {
+                     const __grid_constant__ CUtensorMap next_b, const GemvOpList list) {
     using Geo = StreamGeom<GB>;
     using Plan = DpPlan<GB, MD, XF32, NST, BU>;
     constexpr int GPS = Geo::GPS, WPG = Plan::WPG;
@@ -1066,18 +1083,22 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
 
     // every CTA has at least one unit of every operation (the host caps the grid at the smallest unit count)
     if (range_begin(blockIdx.x, pa.units, gridDim.x) >= range_begin(blockIdx.x + 1u, pa.units, gridDim.x)) return;
+    const uint32_t nops = NOPS > 0 ? static_cast<uint32_t>(NOPS) : list.count;   // list mode: pa is the first operation
+    unsigned int *const gbar = NOPS > 0 ? pa.grid_bar : list.grid_bar;
 
     if (warp == NCW) {
         // ------------------------- producer warp (one lane works) -------------------------
         if (lane != 0) return;
         uint32_t issued = 0;
         bool ok = true;
-#pragma unroll
-        for (int o = 0; o < NOPS; ++o) {
-            const GemvParams &p = o == 0 ? pa : pb;
-            const CUtensorMap *tw = o == 0 ? &tmap_w : &next_w;
-            const CUtensorMap *ts = o == 0 ? &tmap_s : &next_s;
-            const CUtensorMap *tb = o == 0 ? &tmap_b : &next_b;
+#pragma unroll 1
+        for (uint32_t o = 0; o < nops; ++o) {
+            GemvParams plist;
+            if constexpr (NOPS == 0) plist = list.ops[o];
+            const GemvParams &p = NOPS == 0 ? plist : (o == 0 ? pa : pb);
+            const CUtensorMap *tw = NOPS == 0 ? list.maps + 3u * o : (o == 0 ? &tmap_w : &next_w);
+            const CUtensorMap *ts = NOPS == 0 ? list.maps + 3u * o + 1u : (o == 0 ? &tmap_s : &next_s);
+            const CUtensorMap *tb = NOPS == 0 ? list.maps + 3u * o + 2u : (o == 0 ? &tmap_b : &next_b);
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tw)) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(ts)) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tb)) : "memory");
@@ -1122,9 +1143,15 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         // lane owns rows lane, lane + 32, lane + 64, lane + 96 of the row group
         asm volatile("griddepcontrol.wait;" ::: "memory");
         uint32_t ob = 0, ophase = 0;
-#pragma unroll
-        for (int o = 0; o < NOPS; ++o) {
-        const GemvParams &p = o == 0 ? pa : pb;
+        // fused all-reduce: the exchange epoch of the launch's k-th fused operation is (epoch at launch start) + 1 + k;
+        // the epoch word itself moves once, at the very end of the launch, by the number of fused operations
+        uint32_t fbase = 0u, nfused = 0u;
+        uint32_t *fctl_launch = nullptr;
+#pragma unroll 1
+        for (uint32_t o = 0; o < nops; ++o) {
+        GemvParams plist;
+        if constexpr (NOPS == 0) plist = list.ops[o];
+        const GemvParams &p = NOPS == 0 ? plist : (o == 0 ? pa : pb);
         const uint32_t u_begin = range_begin(blockIdx.x, p.units, gridDim.x);
         const uint32_t u_end = range_begin(blockIdx.x + 1u, p.units, gridDim.x);
         const uint32_t rg_begin = u_begin / p.chunks;
@@ -1140,11 +1167,16 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         uint32_t *fctl = reinterpret_cast<uint32_t *>(my_region + kFusedCtlOff);  // {epoch, done}
         uint32_t fepoch = 0u, fphase = 0u;
         if (fused) {
-            fepoch = __ldcg(fctl) + 1u;  // every CTA of this launch reads the same value: it moves only when all have finished
+            if (fctl_launch == nullptr) {
+                fctl_launch = fctl;
+                fbase = __ldcg(fctl);  // every CTA of this launch reads the same value: it moves only when the whole launch is through
+            }
+            fepoch = fbase + 1u + nfused;
             fphase = fepoch & 1u;
+            ++nfused;
         }
         constexpr uint32_t kPend = 8;
-        uint32_t pend[kPend];
+        uint32_t pend[kPend] = {};
         uint32_t npend = 0u;
         bool peers_ok = true;
 
@@ -1368,31 +1400,33 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         if (fused) {
             for (uint32_t i = 0; i < npend; ++i)
                 if (peers_ok) finish(pend[i]);
-            // the launch's epoch moves once, when its last CTA is through
-            __syncwarp();
-            if (lane == 0) {
-                __threadfence();
-                const uint32_t t = atomicAdd(fctl + 1, 1u);
-                if (t == gridDim.x - 1u) {
-                    fctl[1] = 0u;
-                    __threadfence();
-                    fctl[0] = fepoch;
-                }
-            }
         }
-        if constexpr (NOPS > 1) {
+        if (NOPS != 1) {
             // this CTA's share of operation o's output is stored (or handed to the head owner, who stores it
             // before it arrives here itself): arrive at the operation's grid-wide counter.  After the last
             // operation the counter only finds the last CTA, which zeroes all of them for the next launch.
             __syncwarp();
             if (lane == 0) {
                 unsigned int t;
-                asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(t) : "l"(pa.grid_bar + o) : "memory");
-                if (o == NOPS - 1 && t == gridDim.x - 1u)
-                    for (int i = 0; i < NOPS; ++i) pa.grid_bar[i] = 0u;
+                asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(t) : "l"(gbar + o) : "memory");
+                if (o == nops - 1u && t == gridDim.x - 1u)
+                    for (uint32_t i = 0; i < nops; ++i) gbar[i] = 0u;
             }
         }
         }  // operations
+        if (fctl_launch != nullptr) {
+            // the exchange epoch moves once per launch, when the launch's last CTA is through all its operations
+            __syncwarp();
+            if (lane == 0) {
+                __threadfence();
+                const uint32_t t = atomicAdd(fctl_launch + 1, 1u);
+                if (t == gridDim.x - 1u) {
+                    fctl_launch[1] = 0u;
+                    __threadfence();
+                    fctl_launch[0] = fbase + nfused;
+                }
+            }
+        }
         return;
     }
 
@@ -1442,25 +1476,32 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
     uint32_t stage = 0, phase = 0;   // ring position and out-buffer position run on across operations
     uint32_t ob = 0, ophase = 0;
     bool alive = true;
+    // launch lists: the activations of the NEXT operation's first block, fetched while this operation runs (only
+    // when that operation does not read what this launch writes), so that its start does not wait for memory
+    constexpr int kPreG = GB * 2, kPrePER = kPreG / 32, kPreTPW = (BU * GPS * MD + NCW - 1) / NCW;
+    float xpre[kPreTPW][kPrePER];
+    bool have_pre = false;
     asm volatile("griddepcontrol.wait;" ::: "memory");
-#pragma unroll
-    for (int o = 0; o < NOPS; ++o) {
-    const GemvParams &p = o == 0 ? pa : pb;
+#pragma unroll 1
+    for (uint32_t o = 0; o < nops; ++o) {
+    GemvParams plist;
+    if constexpr (NOPS == 0) plist = list.ops[o];
+    const GemvParams &p = NOPS == 0 ? plist : (o == 0 ? pa : pb);
     const uint8_t *xbase = static_cast<const uint8_t *>(p.x);
     const uint32_t u_begin = range_begin(blockIdx.x, p.units, gridDim.x);
     const uint32_t u_end = range_begin(blockIdx.x + 1u, p.units, gridDim.x);
     const uint32_t rg_begin = u_begin / p.chunks;
     const uint32_t kc_begin = u_begin - rg_begin * p.chunks;
-    if constexpr (NOPS > 1) {
+    if (NOPS != 1) {
         if (o > 0) {
-            // all warps are done reading the previous operation's activation blocks, and the previous
-            // operation's output is complete on every CTA before anybody reads it
+            // all warps are done reading the previous operation's activation blocks, and (when this operation reads
+            // what the previous one wrote) the previous operation's output is complete on every CTA
             asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
-            if (warp == 0 && lane == 0) {
+            if (p.dep != 0u && warp == 0 && lane == 0) {
                 bool ok = false;
                 for (uint32_t it = 0; it < kWaitLimit; ++it) {
                     unsigned int v;
-                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(pa.grid_bar + (o - 1)) : "memory");
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(gbar + (o - 1u)) : "memory");
                     if (v >= gridDim.x) {
                         ok = true;
                         break;
@@ -1479,7 +1520,23 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
 
     // ---- quantised activations for a block of units: (unit, group, activation row) triples over the warps ----
     // Two passes so that all of a warp's global loads are in flight together.
-    auto prep_block = [&](auto act_c, uint32_t kc_first, uint32_t count, uint32_t buf) {
+    // plain bf16 activations of a block of units into registers: (unit, group, activation row) triples over the warps
+    auto load_block = [&](const GemvParams &q, uint32_t kc_first, uint32_t count, float (&xv)[kPreTPW][kPrePER]) {
+        const uint32_t ntask = count * GPS * MD;
+#pragma unroll
+        for (int tk = 0; tk < kPreTPW; ++tk) {
+            const uint32_t pi = warp + tk * NCW;
+            const uint32_t m = pi % MD, gl = (pi / MD) % GPS, ub = pi / (MD * GPS);
+            const uint32_t gi = ((kc_first + ub) % q.chunks) * GPS + gl;
+            const bool live = pi < ntask && m < q.M && gi < q.groups;
+#pragma unroll
+            for (int e = 0; e < kPrePER; ++e) {
+                const size_t idx = static_cast<size_t>(m) * q.K + static_cast<size_t>(gi) * kPreG + lane * kPrePER + e;
+                xv[tk][e] = live ? __bfloat162float(static_cast<const __nv_bfloat16 *>(q.x)[idx]) : 0.f;
+            }
+        }
+    };
+    auto prep_block = [&](auto act_c, uint32_t kc_first, uint32_t count, uint32_t buf, bool use_pre = false) {
         constexpr bool ACT = decltype(act_c)::value;  // compile-time: the plain path keeps its loads branch-free
         if constexpr (IM && !ACT && !XF32) {
             // Four activation rows: a lane takes one packed word's worth (8 consecutive elements, one 16-byte
@@ -1548,8 +1605,15 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         constexpr int G = GB * 2;                          // elements per group (4-bit codes)
         constexpr int PER = G / 32;                        // elements per lane: 1 (G=32), 2, 4
         constexpr int TPW = (BU * GPS * MD + NCW - 1) / NCW;  // triples per warp, at most
+        static_assert(TPW == kPreTPW && PER == kPrePER, "prefetch registers must match the block's shape");
         float xv[TPW][PER];
         const uint32_t ntask = count * GPS * MD;
+        if (use_pre) {
+#pragma unroll
+            for (int tk = 0; tk < TPW; ++tk)
+#pragma unroll
+                for (int e = 0; e < PER; ++e) xv[tk][e] = xpre[tk][e];
+        } else
 #pragma unroll
         for (int tk = 0; tk < TPW; ++tk) {
             const uint32_t pi = warp + tk * NCW;
@@ -1636,15 +1700,29 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         const uint32_t total = u_end - u_begin;
         const uint32_t first = total < block_len ? total : block_len;
         const uint32_t head = first < block_units ? first : block_units;
-        if (NOPS > 1 && p.act != 0u) {
+        if (NOPS != 1 && p.act != 0u) {
             prep_block(std::true_type{}, kc_begin, head, 0u);
             if (first > head) prep_block(std::true_type{}, (kc_begin + head) % p.chunks, first - head, 1u);
         } else {
-            prep_block(std::false_type{}, kc_begin, head, 0u);
+            prep_block(std::false_type{}, kc_begin, head, 0u, have_pre);
             if (first > head) prep_block(std::false_type{}, (kc_begin + head) % p.chunks, first - head, 1u);
         }
+        have_pre = false;
     }
     asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+    if constexpr (NOPS == 0 && !IM && !XF32) {
+        if (o + 1u < nops) {
+            const GemvParams qn = list.ops[o + 1u];
+            if (qn.dep == 0u && qn.act == 0u) {
+                const uint32_t nb = range_begin(blockIdx.x, qn.units, gridDim.x), ne = range_begin(blockIdx.x + 1u, qn.units, gridDim.x);
+                const uint32_t nlen = qn.chunks <= 2u * block_units ? qn.chunks : block_units;
+                uint32_t nhead = ne - nb < nlen ? ne - nb : nlen;
+                if (nhead > block_units) nhead = block_units;
+                load_block(qn, nb % qn.chunks, nhead, xpre);
+                have_pre = true;
+            }
+        }
+    }
 
     uint32_t rg = rg_begin, kc = kc_begin;
     uint32_t ub = 0, buf = 0;
@@ -1793,7 +1871,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
             ub = 0u;
             if (more && !whole_k) {
                 const uint32_t left = u_end - (u + 1u);
-                if (NOPS > 1 && p.act != 0u)
+                if (NOPS != 1 && p.act != 0u)
                     prep_block(std::true_type{}, kc_n, left < block_units ? left : block_units, buf ^ 1u);
                 else
                     prep_block(std::false_type{}, kc_n, left < block_units ? left : block_units, buf ^ 1u);
@@ -1993,7 +2071,7 @@ cudaError_t launch_stream(const GemvParams &p, const WeightView &w, const Weight
 
 template <int GB, int MD, bool XF32, int SD, int NCW, int NST, int BU, int NOPS = 1>
 cudaError_t launch_dp4a(const GemvParams &p, const WeightView &w, const WeightView *next, uint32_t ctas, bool pdl,
-                        cudaStream_t stream, const GemvParams *second = nullptr) {
+                        cudaStream_t stream, const GemvParams *second = nullptr, const GemvOpList *list = nullptr) {
     auto kern = gaf_gemv_dp4a_kernel<GB, MD, XF32, SD, NCW, NST, BU, NOPS>;
     using Plan = DpPlan<GB, MD, XF32, NST, BU>;
     static bool configured[kMaxDevices] = {};
@@ -2010,7 +2088,29 @@ cudaError_t launch_dp4a(const GemvParams &p, const WeightView &w, const WeightVi
     cfg.numAttrs = pdl ? 1 : 0;
     // two operations: `next` is the second weight (its maps travel in the next-weight slots)
     const WeightView &nx = next ? *next : w;
-    return cudaLaunchKernelEx(&cfg, kern, p, second ? *second : p, w.tmap, w.tmap_s, w.tmap_b, nx.tmap, nx.tmap_s, nx.tmap_b);
+    GemvOpList none;
+    memset(&none, 0, sizeof none);
+    return cudaLaunchKernelEx(&cfg, kern, p, second ? *second : p, w.tmap, w.tmap_s, w.tmap_b, nx.tmap, nx.tmap_s, nx.tmap_b,
+                              list ? *list : none);
+}
+
+// a whole launch list in one launch (all operations: gaf4, one group size, one scales dtype, the same M <= 4)
+template <int GB>
+cudaError_t dispatch_list(const GemvParams &first, const WeightView &w0, const GemvOpList &list, uint32_t ctas, uint32_t M,
+                          bool pdl, cudaStream_t stream, bool imma_small) {
+    const bool bf = first.sdtype == 1u;
+    constexpr int NST1 = GB == 16 ? 3 : 4;
+    if (imma_small && M <= 2) M = 4;   // the int8-MMA instance (built for four rows) with fewer rows in use
+    if (M == 1)
+        return bf ? launch_dp4a<GB, 1, false, 1, kConsumerWarps, NST1, 8, 0>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list)
+                  : launch_dp4a<GB, 1, false, 0, kConsumerWarps, NST1, 8, 0>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list);
+    if (M == 2)
+        return bf ? launch_dp4a<GB, 2, false, 1, kConsumerWarps, 3, 8, 0>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list)
+                  : launch_dp4a<GB, 2, false, 0, kConsumerWarps, 3, 8, 0>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list);
+    if (M == 3 || M == 4)
+        return bf ? launch_dp4a<GB, 4, false, 1, kConsumerWarps, 3, (GB == 16 ? 4 : 8), 0>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list)
+                  : launch_dp4a<GB, 4, false, 0, kConsumerWarps, 3, (GB == 16 ? 4 : 8), 0>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list);
+    return cudaErrorNotSupported;
 }
 
 // gate|up then down in one launch (M = 1, both weights of one group size)
@@ -2301,6 +2401,7 @@ cudaError_t gemv_ffn_swiglu(const WeightView &w1, const WeightView &w2, const vo
     GemvParams p2 = base_params(w2, mid, y, M, pl2, d_error_word);
     p2.tagged = scratch.tagged + need1;
     p2.act = act;
+    p2.dep = 1u;
     p2.grid_bar = grid_bar;
     if (tune.fuse && gemv_fused_eligible(w2, M, false, tune)) {  // tensor parallel: the sum over ranks rides in the down projection
         for (int r = 0; r < kPeerMaxRanks; ++r) p2.fuse_region[r] = static_cast<uint8_t *>(tune.fuse->region[r]);
@@ -2315,6 +2416,157 @@ cudaError_t gemv_ffn_swiglu(const WeightView &w1, const WeightView &w2, const vo
     if (gb == 32u) return dispatch_ffn<32>(p1, p2, w1, w2, pl1.ctas, M, pdl, stream);
     if (gb == 64u) return dispatch_ffn<64>(p1, p2, w1, w2, pl1.ctas, M, pdl, stream);
     return cudaErrorNotSupported;
+}
+
+// ---------------------------------------------------------------------------
+// Launch list: several linears (M <= 4, gaf4, one group size and scales dtype) in ONE launch of the M <= 4 kernel.
+// The caller fills `params` / `maps` (host arrays of `count` / 3 * count entries) through gemv_list_plan, copies them
+// to the device once, and launches with gemv_list_launch as often as it likes.
+// ---------------------------------------------------------------------------
+bool gemv_list_eligible(const WeightView *const *ws, uint32_t count, uint32_t M, const GemvTuning &tune) {
+    if (count == 0u || count > 256u || M == 0u || M > 4u || tune.no_dp4a || tune.force_generic) return false;
+    const WeightView &w0 = *ws[0];
+    const uint32_t gb0 = w0.group * w0.bits / 8u;
+    if (gb0 != 16u && gb0 != 32u && gb0 != 64u) return false;
+    for (uint32_t i = 0; i < count; ++i) {
+        const WeightView &w = *ws[i];
+        if (w.bits != 4u || w.group != w0.group || w.sdtype != w0.sdtype || !w.has_tmap) return false;
+        if (w.row_bytes != w.K / 2u) return false;
+    }
+    return true;
+}
+
+uint32_t gemv_list_ctas(const WeightView *const *ws, uint32_t count, const GemvTuning &tune, int sm_count) {
+    uint32_t ctas = 0xFFFFFFFFu;
+    for (uint32_t i = 0; i < count; ++i) {
+        const GemvPlan pl = plan_gemv(*ws[i], tune, sm_count);
+        if (pl.ctas < ctas) ctas = pl.ctas;   // one grid: every CTA has units of every weight
+    }
+    return ctas;
+}
+
+// tagged split-K words the whole list needs (64-bit words), operation by operation
+size_t gemv_list_tagged_words(const WeightView *const *ws, uint32_t count, uint32_t M, const GemvTuning &tune, int sm_count) {
+    GemvTuning t = tune;
+    t.ctas = static_cast<int>(gemv_list_ctas(ws, count, tune, sm_count));
+    const uint32_t md = (M == 1u && !tune.imma_small) ? M : 4u;   // two rows: the int8-MMA instance measured faster in a list
+    size_t words = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+        const GemvPlan pl = plan_gemv(*ws[i], t, sm_count);
+        words += static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * md;
+    }
+    return words;
+}
+
+// A planned launch list: host copy of the first operation's parameters (the kernel takes them by value), the
+// device tables (tensor maps, parameters, arrival counters) in one allocation.
+struct GemvList {
+    GemvParams first;
+    WeightView w0;
+    void *d_blob;
+    const GemvParams *d_params;
+    const CUtensorMap *d_maps;
+    unsigned int *d_bar;
+    size_t bar_bytes;
+    uint32_t count, ctas, M;
+    bool imma_small;   // M <= 2 on the int8-MMA instance (the tagged words are then laid out for four rows)
+};
+
+cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs, void *const *ys, const uint8_t *deps,
+                             const PeerComm *const *fuse, uint32_t count, uint32_t M, unsigned long long *tagged,
+                             const GemvTuning &tune, int sm_count, unsigned int *d_error_word, cudaStream_t stream,
+                             GemvList **out) {
+    *out = nullptr;
+    if (!gemv_list_eligible(ws, count, M, tune)) return cudaErrorNotSupported;
+    GemvTuning t = tune;
+    t.ctas = static_cast<int>(gemv_list_ctas(ws, count, tune, sm_count));
+    const uint32_t md = (M == 1u && !tune.imma_small) ? M : 4u;   // two rows: the int8-MMA instance measured faster in a list
+    const size_t map_bytes = static_cast<size_t>(count) * 3u * sizeof(CUtensorMap);
+    const size_t par_bytes = (static_cast<size_t>(count) * sizeof(GemvParams) + 255u) & ~size_t(255);
+    const size_t bar_bytes = (static_cast<size_t>(count) * sizeof(unsigned int) + 255u) & ~size_t(255);
+    uint8_t *host = static_cast<uint8_t *>(malloc(map_bytes + par_bytes));
+    if (!host) return cudaErrorMemoryAllocation;
+    CUtensorMap *maps = reinterpret_cast<CUtensorMap *>(host);
+    GemvParams *params = reinterpret_cast<GemvParams *>(host + map_bytes);
+    size_t words = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+        const WeightView &w = *ws[i];
+        if (!gemv_mma_eligible(w, xs[i], ys[i], false)) {
+            free(host);
+            return cudaErrorNotSupported;
+        }
+        const GemvPlan pl = plan_gemv(w, t, sm_count);
+        GemvParams q = base_params(w, xs[i], ys[i], M, pl, d_error_word);
+        q.tagged = tagged + words;
+        words += static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * md;
+        q.dep = deps && deps[i] ? 1u : 0u;
+        if (fuse && fuse[i]) {
+            GemvTuning tf = t;
+            tf.fuse = fuse[i];
+            if (!gemv_fused_eligible(w, M, false, tf)) {
+                free(host);
+                return cudaErrorNotSupported;
+            }
+            for (int r = 0; r < kPeerMaxRanks; ++r) q.fuse_region[r] = static_cast<uint8_t *>(fuse[i]->region[r]);
+            q.fuse_rank = fuse[i]->rank;
+            q.fuse_size = fuse[i]->size;
+        }
+        params[i] = q;
+        memcpy(&maps[3u * i], &w.tmap, sizeof(CUtensorMap));
+        memcpy(&maps[3u * i + 1u], &w.tmap_s, sizeof(CUtensorMap));
+        memcpy(&maps[3u * i + 2u], &w.tmap_b, sizeof(CUtensorMap));
+    }
+    GemvList *l = new (std::nothrow) GemvList();
+    if (!l) {
+        free(host);
+        return cudaErrorMemoryAllocation;
+    }
+    cudaError_t e = cudaMalloc(&l->d_blob, map_bytes + par_bytes + bar_bytes);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(l->d_blob, host, map_bytes + par_bytes, cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(static_cast<uint8_t *>(l->d_blob) + map_bytes + par_bytes, 0, bar_bytes, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);   // the host copy goes away below
+    l->first = params[0];
+    l->w0 = *ws[0];
+    free(host);
+    if (e != cudaSuccess) {
+        if (l->d_blob) cudaFree(l->d_blob);
+        delete l;
+        return e;
+    }
+    l->d_maps = static_cast<const CUtensorMap *>(l->d_blob);
+    l->d_params = reinterpret_cast<const GemvParams *>(static_cast<uint8_t *>(l->d_blob) + map_bytes);
+    l->d_bar = reinterpret_cast<unsigned int *>(static_cast<uint8_t *>(l->d_blob) + map_bytes + par_bytes);
+    l->bar_bytes = bar_bytes;
+    l->count = count;
+    l->ctas = static_cast<uint32_t>(t.ctas);
+    l->M = M;
+    l->imma_small = tune.imma_small != 0 || M == 2u;
+    *out = l;
+    return cudaSuccess;
+}
+
+cudaError_t gemv_list_launch(const GemvList *l, const GemvTuning &tune, cudaStream_t stream) {
+    GemvOpList list;
+    list.ops = l->d_params;
+    list.maps = l->d_maps;
+    list.count = l->count;
+    list.grid_bar = l->d_bar;
+    const uint32_t gb = l->w0.group * l->w0.bits / 8u;
+    const bool pdl = tune.pdl != 0;
+    const bool im = l->imma_small;
+    if (gb == 16u) return dispatch_list<16>(l->first, l->w0, list, l->ctas, l->M, pdl, stream, im);
+    if (gb == 32u) return dispatch_list<32>(l->first, l->w0, list, l->ctas, l->M, pdl, stream, im);
+    if (gb == 64u) return dispatch_list<64>(l->first, l->w0, list, l->ctas, l->M, pdl, stream, im);
+    return cudaErrorNotSupported;
+}
+
+// after a launch was abandoned (a bounded wait ran out): the arrival counters may be anywhere
+cudaError_t gemv_list_reset(GemvList *l) { return cudaMemset(l->d_bar, 0, l->bar_bytes); }
+
+void gemv_list_destroy(GemvList *l) {
+    if (!l) return;
+    if (l->d_blob) cudaFree(l->d_blob);
+    delete l;
 }
 
 // ---------------------------------------------------------------------------

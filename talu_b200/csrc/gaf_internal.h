@@ -44,7 +44,7 @@ struct GemvTuning {
     int ctas;           // persistent CTAs of the streaming GEMV (0 = one per SM)
     int pdl;            // launch with programmatic stream serialization
     int force_generic;  // use the shape-agnostic kernel even when the fast path applies
-    int reserved0;      // (was a tuning switch; kept so that the initialiser lists stay put)
+    int imma_small;     // launch lists: M <= 2 on the int8 tensor-core instance instead of the integer dot-product one (A/B aid)
     int no_dp4a;        // keep M <= 2 on the tensor-core formulation (for A/B comparisons)
     int wait_limit;     // polls (with back-off) a device-side wait on another CTA or rank makes before it gives up (0 = default)
     int prefetch_units; // units at the head of each CTA range of the hinted next weight to pull into L2
@@ -83,6 +83,22 @@ size_t gemv_mma_counter_count(const WeightView &w);
 uint32_t gemv_mma_max_rows(const WeightView &w, bool x_f32);
 // bytes of Scratch::tagged the M <= 4 kernel needs for this weight (0 when that kernel does not apply)
 size_t gemv_tagged_bytes(const WeightView &w, uint32_t M, bool x_f32, const GemvTuning &tune, int sm_count);
+
+// Launch list: `count` linears (gaf4 weights of one group size and scales dtype, the same M <= 4 bf16 rows) in ONE
+// launch of the M <= 4 kernel; the copy warps stream across all the weights without a pause.  deps[i] = 1: x of
+// operation i is written by an earlier operation of the list (it then waits for operation i - 1 to be complete on the
+// whole grid); fuse[i] != null: y of operation i is summed over the ranks inside the launch.  `tagged`: zeroed 64-bit
+// words, gemv_list_tagged_words of them, owned by the caller for the life of the list.
+struct GemvList;
+bool gemv_list_eligible(const WeightView *const *ws, uint32_t count, uint32_t M, const GemvTuning &tune);
+size_t gemv_list_tagged_words(const WeightView *const *ws, uint32_t count, uint32_t M, const GemvTuning &tune, int sm_count);
+cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs, void *const *ys, const uint8_t *deps,
+                             const struct PeerComm *const *fuse, uint32_t count, uint32_t M, unsigned long long *tagged,
+                             const GemvTuning &tune, int sm_count, unsigned int *d_error_word, cudaStream_t stream,
+                             GemvList **out);
+cudaError_t gemv_list_launch(const GemvList *l, const GemvTuning &tune, cudaStream_t stream);
+cudaError_t gemv_list_reset(GemvList *l);
+void gemv_list_destroy(GemvList *l);
 
 // Same kernel on the library's fixed device-resident scratch: allocates nothing.
 // cudaErrorMemoryAllocation: the problem needs more scratch than the fixed array holds

@@ -290,12 +290,58 @@ def linear_host(ctx: Context, w: Weight, x: np.ndarray, out: np.ndarray | None =
     return out
 
 
+class Batch:
+    """A launch list of device-buffer linears (tgaf_batch_*): `count` operations y_i = x_i @ W_i^T with the same
+    number of rows, run by ONE call (one kernel launch when every weight is gaf4 of one scheme and M <= 4).
+    depends[i]: x_i is written by an earlier operation of the list; reduce[i]: y_i is summed over the ranks."""
+
+    def __init__(self, ctx: Context, weights, xs, ys, depends=None, reduce=None):
+        import torch
+        n = len(weights)
+        if not (len(xs) == len(ys) == n) or n == 0:
+            raise GafError(_STATUS_INVALID_ARGUMENT, "weights, xs and ys must have one entry per operation")
+        m = xs[0].shape[0]
+        for w, x, y in zip(weights, xs, ys):
+            if x.dtype != torch.bfloat16 or y.dtype != torch.bfloat16 or tuple(x.shape) != (m, w.K) or tuple(y.shape) != (m, w.N):
+                raise GafError(_STATUS_INVALID_ARGUMENT, "x must be bf16 [m, K] and y bf16 [m, N], the same m for all")
+            if not (x.is_contiguous() and y.is_contiguous()):
+                raise GafError(_STATUS_INVALID_ARGUMENT, "buffers must be contiguous")
+        self.ctx, self.n = ctx, n
+        self._keep = (list(weights), list(xs), list(ys))
+        wp = (C.c_void_p * n)(*[w._h.value if isinstance(w._h, C.c_void_p) else w._h for w in weights])
+        xp = (C.c_void_p * n)(*[x.data_ptr() for x in xs])
+        yp = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
+        dep = (C.c_uint8 * n)(*[1 if d else 0 for d in depends]) if depends is not None else None
+        red = (C.c_uint8 * n)(*[1 if r else 0 for r in reduce]) if reduce is not None else None
+        h = C.c_void_p()
+        ctx._check(ctx._lib.tgaf_batch_create(ctx._h, n, wp, xp, m, yp, dep, red, C.byref(h)))
+        self._h = h
+
+    @property
+    def one_launch(self) -> bool:
+        return bool(self.ctx._lib.tgaf_batch_uses_one_launch(self._h))
+
+    def run(self) -> None:
+        self.ctx._check(self.ctx._lib.tgaf_batch_run(self.ctx._h, self._h))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None) and getattr(self.ctx, "_h", None):
+            self.ctx._lib.tgaf_batch_destroy(self.ctx._h, self._h)
+        self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 class HostBatch:
     """A fixed list of (weight, x, out) host-buffer calls, submitted with one crossing of the C ABI
     (tgaf_linear_bf16_host_async_batch).  x / out: uint16 arrays (bf16 bit patterns) in page-locked memory; they
     are read / written when `submit` runs on the GPU, so refill x and read out between ctx.synchronize() calls."""
 
-    def __init__(self, ctx: Context, weights, xs, outs):
+    def __init__(self, ctx: Context, weights, xs, outs, reduce=None):
         n = len(weights)
         if not (len(xs) == len(outs) == n):
             raise GafError(_STATUS_INVALID_ARGUMENT, "weights, xs and outs must have one entry per call")
@@ -310,19 +356,27 @@ class HostBatch:
         self._x = (C.c_void_p * n)(*[x.ctypes.data for x in xs])
         self._y = (C.c_void_p * n)(*[o.ctypes.data for o in outs])
         self._m = (C.c_uint32 * n)(*[x.shape[0] for x in xs])
-
+        self._red = (C.c_uint8 * n)(*[1 if r else 0 for r in reduce]) if reduce is not None else None
         self._g = None
 
     def record(self) -> "HostBatch":
         """Runs the list once and records it as a CUDA graph (tgaf_host_batch_create); `submit` then replays it."""
         h = C.c_void_p()
-        self.ctx._check(self.ctx._lib.tgaf_host_batch_create(self.ctx._h, self.n, self._w, self._x, self._m, self._y, C.byref(h)))
+        self.ctx._check(self.ctx._lib.tgaf_host_batch_create_reduce(self.ctx._h, self.n, self._w, self._x, self._m, self._y,
+                                                                    self._red, C.byref(h)))
         self._g = h
         return self
+
+    @property
+    def one_launch(self) -> bool:
+        """True when the recorded list is two block copies around ONE kernel launch."""
+        return self._g is not None and bool(self.ctx._lib.tgaf_host_batch_uses_one_launch(self._g))
 
     def submit(self) -> None:
         if self._g is not None:
             self.ctx._check(self.ctx._lib.tgaf_host_batch_submit(self.ctx._h, self._g))
+        elif self._red is not None and any(self._red):
+            raise GafError(_STATUS_INVALID_ARGUMENT, "a list with sums over the ranks must be recorded first")
         else:
             self.ctx._check(self.ctx._lib.tgaf_linear_bf16_host_async_batch(self.ctx._h, self.n, self._w, self._x, self._m, self._y))
 
