@@ -1026,14 +1026,38 @@ namespace {
 
 // Copies `count` buffers between host and the device block, merging neighbours that are adjacent on both sides
 // (a decoder that keeps its activations in one page-locked block pays for one copy, not one per linear).
+// The allocation [base, base + size) that holds a page-locked host pointer; false for pageable memory.
+bool host_allocation_of(const void *p, uintptr_t *base, size_t *size) {
+    typedef CUresult (*RangeFn)(CUdeviceptr *, size_t *, CUdeviceptr);
+    static RangeFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &sym, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<RangeFn>(sym);
+    }
+    if (!fn) return false;
+    CUdeviceptr b = 0;
+    size_t n = 0;
+    if (fn(&b, &n, reinterpret_cast<CUdeviceptr>(p)) != CUDA_SUCCESS) return false;
+    *base = static_cast<uintptr_t>(b), *size = n;
+    return true;
+}
+
 cudaError_t copy_runs(uint32_t count, const std::vector<size_t> &dev_off, const std::vector<size_t> &bytes, uint8_t *dev,
                       const void *const *host, bool to_device, cudaStream_t stream) {
     uint32_t i = 0;
     while (i < count) {
         uint32_t j = i + 1u;
         size_t run = bytes[i];
-        while (j < count && static_cast<const uint8_t *>(host[j]) == static_cast<const uint8_t *>(host[i]) + run &&
-               dev_off[j] == dev_off[i] + run) {
+        // neighbours in address space may still be two allocations, which one copy must not span
+        uintptr_t base = 0;
+        size_t span = 0;
+        const bool known = host_allocation_of(host[i], &base, &span);
+        while (known && j < count && static_cast<const uint8_t *>(host[j]) == static_cast<const uint8_t *>(host[i]) + run &&
+               dev_off[j] == dev_off[i] + run && reinterpret_cast<uintptr_t>(host[j]) + bytes[j] <= base + span) {
             run += bytes[j];
             ++j;
         }

@@ -175,7 +175,7 @@ def _time_stack(ctx, torch, dist, world, stream, stack, M, steps, warmup, min_se
     return out
 
 
-def _time_e2e(ctx, torch, dist, world, stack, M, steps):
+def time_e2e(ctx, torch, dist, world, stack, M, steps):
     """End to end on every rank through the recorded host batch: all activations in one page-locked block, all
     outputs in another; per step the x block goes up, the launch list runs (sums over ranks inside), the y block
     comes back, one wait.  Host wall clock per step, max over ranks of the mean."""
@@ -278,7 +278,7 @@ def measure(args, existing_ctx=None, existing_stream=None, M=1, quick=False, par
         r2 = _time_stack(ctx, torch, dist if world > 1 else None, world, stream, stack, m2, steps, warmup, min_seconds, False, False)
         r2["bytes"] = stack_bytes(layers, m2)
         res["also"][m2] = r2
-    res["e2e"] = _time_e2e(ctx, torch, dist, world, stack, M, steps) if (world > 1 and M <= 4) else None
+    res["e2e"] = time_e2e(ctx, torch, dist, world, stack, M, steps) if (world > 1 and M <= 4) else None
     torch.cuda.synchronize()
     stack.free()
     if world > 1:
