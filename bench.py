@@ -280,7 +280,8 @@ def tp_parity_check(ctx, torch, dist, rank, world, stream):
     """Every rank's output of sharded linears against the UNSHARDED CPU oracle, on converter-made weights (the
     oracle's quantizer): a column-parallel -> row-parallel chain (hidden 1024, ffn 2048; M = 1, 2, 4) and one
     full-size Llama-3-70B `down` shard (8192 x 28672, M = 1), the sum over ranks taken by every path the library
-    has.  Raises when any rank is beyond 1e-2 (max relative error); returns the worst figure and the paths."""
+    has.  Raises when any rank is beyond the path's bound (max relative error 1e-2; where every rank's partial
+    sums are rounded to bf16 before the sum, 3e-2); returns the worst figure and the paths."""
     import talu_b200 as gaf
     from talu_b200.tp import SHARD_COL, SHARD_ROW
     from oracle import gaf_oracle as oracle
@@ -294,7 +295,7 @@ def tp_parity_check(ctx, torch, dist, rank, world, stream):
              ("fused into the GEMV write-out", {"fused_allreduce": 1, "peer_allreduce": 1}),
              ("GEMV then the one-shot peer-memory kernel", {"fused_allreduce": 0, "peer_allreduce": 1}),
              ("GEMV then NCCL all-reduce", {"fused_allreduce": 0, "peer_allreduce": 0})]
-    worst, report = 0.0, []
+    worst, report, failed = 0.0, [], False
 
     def to_f32(t):
         return oracle.bf16_to_f32(bits_from_torch_bf16(t))
@@ -338,6 +339,20 @@ def tp_parity_check(ctx, torch, dist, rank, world, stream):
                     stream.synchronize()
                     ctx.synchronize()
                 errs.append(rel_err(to_f32(y), yref))
+                if opts is None:
+                    # operations that do not depend on one another: the wait for the peers' words of a row-parallel
+                    # operation is put off to the end of the following operation
+                    ya, yb = torch.zeros_like(y), torch.zeros_like(y)
+                    h2, h3 = torch.zeros_like(h), torch.zeros_like(h)
+                    b = gaf.Batch(ctx, [w2, w1, w2, w1], [h, x, h, x], [ya, h2, yb, h3], reduce=[1, 0, 1, 0])
+                    for _ in range(3):
+                        b.run()
+                    stream.synchronize()
+                    ctx.synchronize()
+                    b.close()
+                    errs.append(rel_err(to_f32(ya), yref))
+                    errs.append(rel_err(to_f32(yb), yref))
+                    errs.append(0.0 if (torch.equal(h2, h) and torch.equal(h3, h)) else 1.0)
             y3 = torch.empty((1, N3), dtype=torch.bfloat16, device="cuda")
             if opts is None:
                 b = gaf.Batch(ctx, [w3], [x3], [y3], reduce=[1])
@@ -352,15 +367,19 @@ def tp_parity_check(ctx, torch, dist, rank, world, stream):
             errs.append(rel_err(to_f32(y3), ref3))
             e = torch.tensor([max(errs)], dtype=torch.float64)
             dist.all_reduce(e, op=dist.ReduceOp.MAX)            # the worst rank
-            report.append({"path": name, "rel": round(float(e.item()), 6)})
+            # the two-step paths round every rank's partial sums to bf16 before they are added (P + 1 roundings
+            # instead of one, and NCCL rounds again at every hop): their bound is 3e-2; the paths that add fp32 partials keep the 1e-2 of the other tests
+            tol = 3e-2 if (opts and not opts["fused_allreduce"]) else 1e-2
+            report.append({"path": name, "rel": round(float(e.item()), 6), "tolerance": tol})
+            failed = failed or not float(e.item()) <= tol
             worst = max(worst, float(e.item()))
         ctx.set_option("fused_allreduce", 1)
         ctx.set_option("peer_allreduce", 1)
         for w in (w1, w2, w3):
             w.free()
-    if not worst <= 1e-2:
+    if failed:
         raise RuntimeError(f"rank {rank}: sharded linears differ from the unsharded oracle: {report}")
-    return {"rel": round(worst, 6), "tolerance": 1e-2, "peer_memory": bool(peer), "paths": report,
+    return {"rel": round(worst, 6), "peer_memory": bool(peer), "paths": report,
             "cases": "col->row chain 1024/2048 at M = 1, 2, 4; 8192 x 28672 row-parallel shard at M = 1; every rank compared"}
 
 

@@ -117,6 +117,7 @@ struct tgaf_ctx {
     uint32_t comm_rank = 0, comm_size = 1;
     PeerComm peer = {{nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr}, 0, 1, false};
     int peer_allreduce = 1;  // small tiles go through the peer-memory kernel when the mapping exists
+    uint32_t gemm_min_m = 17;  // activation rows from which the tensor-core GEMM takes over from the decode GEMVs
     int fused_allreduce = 1; // tgaf_linear_bf16_allreduce sums inside the GEMV when it can
     int ffn_one_launch = 1;  // tgaf_ffn_swiglu_bf16 runs both linears in one kernel when it can
     int peer_pdl = 0;        // programmatic stream serialization for the all-reduce kernel (measured slower)
@@ -260,7 +261,7 @@ int32_t linear_device(tgaf_ctx *ctx, const WeightView &w, const void *x, uint32_
     const size_t elt = f32 ? 4 : 2;
     TGAF_CUDA(ctx, cudaSetDevice(ctx->device));  // scratch growth and launches below belong to the context's device
 
-    if (!f32 && gemm_tc_eligible(w, M)) {
+    if (!f32 && gemm_tc_eligible(w, M, ctx->gemm_min_m)) {
         if (!ctx->gemm_ws) {
             // first GEMM on this context: the split-tile workspace (38 MB on 148 SMs) and its flags
             const size_t wb = gemm_tc_workspace_bytes(ctx->sm_count), fc = gemm_tc_flag_count(ctx->sm_count);
@@ -704,6 +705,9 @@ int32_t tgaf_ctx_set_option(tgaf_ctx *ctx, const char *name, int64_t value) {
         ctx->tune.imma_small = value != 0;
     } else if (!strcmp(name, "no_dp4a")) {
         ctx->tune.no_dp4a = value != 0;
+    } else if (!strcmp(name, "gemm_min_m")) {
+        if (value < 1 || value > 17) return fail(ctx, TGAF_ERR_INVALID_ARGUMENT, "gemm_min_m must be in [1, 17]");
+        ctx->gemm_min_m = static_cast<uint32_t>(value);
     } else if (!strcmp(name, "peer_allreduce")) {
         ctx->peer_allreduce = value != 0;
     } else if (!strcmp(name, "ffn_one_launch")) {

@@ -57,6 +57,10 @@ constexpr int kFirstDequantWarp = 3;   // warps 0, 1, 2: activation copies, MMA 
 constexpr int kThreadsTc = (kFirstDequantWarp + kDequantWarps) * 32;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kWaitLimitTc = 1u << 22;
+// how long a thread may stay suspended inside one mbarrier.try_wait before it looks again (it is woken at once
+// when the phase completes); an mbarrier wait as a whole gives up after four seconds
+constexpr uint32_t kSuspendHintNs = 20000u;
+constexpr unsigned long long kWaitLimitNs = 4000000000ull;
 constexpr uint32_t kTileFloats = 256 * 256;   // workspace slot of one CTA (fp32 partial tile)
 
 // Optional timeline of one CTA (debug builds with -DTGAF_GEMM_TRACE only): SM clock at the hand-over points of
@@ -120,10 +124,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
         : "memory");
     return ok != 0;
 }
@@ -133,9 +137,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // pipeline (three or four per K block) than it saved in polling traffic.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
                                                unsigned int *error_word, uint32_t code) {
+    unsigned long long t0 = 0ull;
     for (uint32_t it = 0; it < kWaitLimitTc; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 255u) == 255u && *abort_flag) return false;
+        if ((it & 63u) == 63u) {
+            if (*abort_flag) return false;
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0ull) t0 = now;
+            else if (now - t0 > kWaitLimitNs) break;
+        }
     }
     atomicOr(error_word, code);
     *abort_flag = 1u;
@@ -755,8 +766,8 @@ extern "C" int tgaf_debug_gemm_trace(unsigned long long *out) {
 size_t gemm_tc_workspace_bytes(int sm_count) { return static_cast<size_t>(sm_count) * kTileFloats * sizeof(float); }
 size_t gemm_tc_flag_count(int sm_count) { return static_cast<size_t>(sm_count) * kDequantWarps; }
 
-bool gemm_tc_eligible(const WeightView &w, uint32_t M) {
-    if (M <= 16u) return false;                                   // the decode GEMV kernels take M <= 16
+bool gemm_tc_eligible(const WeightView &w, uint32_t M, uint32_t min_m) {
+    if (M < min_m) return false;                                  // the decode GEMV kernels take the rows below
     if (w.bits != 4u && w.bits != 8u) return false;
     if (w.group != 32u && w.group != 64u && w.group != 128u) return false;
     if (w.K % kBK != 0u || w.groups % 8u != 0u) return false;      // whole K blocks; 16-byte loads of scales
@@ -770,7 +781,7 @@ bool gemm_tc_eligible(const WeightView &w, uint32_t M) {
 cudaError_t gemm_tc(const WeightView &w, const void *x_bf16, void *y_bf16, uint32_t M, cudaStream_t stream,
                     int sm_count, unsigned int *d_error_word, float *ws, size_t ws_bytes, unsigned int *flags,
                     size_t flag_count) {
-    if (!gemm_tc_eligible(w, M)) return cudaErrorNotSupported;
+    if (!gemm_tc_eligible(w, M, 1u)) return cudaErrorNotSupported;
     if (reinterpret_cast<uintptr_t>(x_bf16) % 16u != 0 || reinterpret_cast<uintptr_t>(y_bf16) % 16u != 0 ||
         (static_cast<size_t>(w.K) * 2u) % 16u != 0)
         return cudaErrorNotSupported;

@@ -111,6 +111,13 @@ struct GemvParams {
                              // operation of the launch (wait for the grid-wide arrival at the previous operation)
 };
 
+// One operation's exchange as the writer warp needs it to collect the peers' words later on.
+struct FusedOp {
+    void *y;
+    uint8_t *region;   // this rank's exchange region
+    uint32_t N, M, y_f32, size, epoch, phase;
+};
+
 // A launch list for the M <= 4 kernel: operations in order, three tensor maps (packed, scales, biases) per operation,
 // all in device memory (written by the host before the launch).
 struct GemvOpList {
@@ -1147,6 +1154,8 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         // the epoch word itself moves once, at the very end of the launch, by the number of fused operations
         uint32_t fbase = 0u, nfused = 0u;
         uint32_t *fctl_launch = nullptr;
+        FusedOp late = {};                       // an exchange whose wait was put off to the end of the following operation
+        uint32_t late_rg[8] = {}, late_n = 0xFFFFFFFFu;
 #pragma unroll 1
         for (uint32_t o = 0; o < nops; ++o) {
         GemvParams plist;
@@ -1172,7 +1181,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                 fbase = __ldcg(fctl);  // every CTA of this launch reads the same value: it moves only when the whole launch is through
             }
             fepoch = fbase + 1u + nfused;
-            fphase = fepoch & 1u;
+            fphase = fepoch & static_cast<uint32_t>(kFusedPhases - 1);   // four data phases: an exchange may still be read while the next two are written
             ++nfused;
         }
         constexpr uint32_t kPend = 8;
@@ -1192,15 +1201,15 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         // the epoch has the value, so there is no flag, no fence and no second NVLink hop (the same idea as
         // the split-K words above, and as the "LL" protocols of collective libraries).
         // wait for every rank's words of row group rg, add them in rank order, write y
-        auto finish = [&](uint32_t rg) {
+        auto finish = [&](const FusedOp &f, uint32_t rg) {
             const unsigned long long *data = reinterpret_cast<const unsigned long long *>(
-                my_region + kFusedDataOff + static_cast<size_t>(fphase) * kPeerMaxRanks * kPeerSlotBytes);
+                f.region + kFusedDataOff + static_cast<size_t>(f.phase) * kPeerMaxRanks * kPeerSlotBytes);
             float acc[4][MD];
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
                 for (int m = 0; m < MD; ++m) acc[i][m] = 0.f;
-            for (uint32_t r = 0; r < p.fuse_size; ++r) {
+            for (uint32_t r = 0; r < f.size; ++r) {
                 const unsigned long long *src = data + r * (kPeerSlotBytes / 8u);
                 unsigned long long word[4][MD];
                 bool got = false;
@@ -1211,12 +1220,12 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                         const uint32_t n = rg * kRows + lane + 32u * i;
 #pragma unroll
                         for (int m = 0; m < MD; ++m) {
-                            if (static_cast<uint32_t>(m) < p.M && n < p.N) {
+                            if (static_cast<uint32_t>(m) < f.M && n < f.N) {
                                 asm volatile("ld.relaxed.sys.global.u64 %0, [%1];"
                                              : "=l"(word[i][m])
-                                             : "l"(src + static_cast<size_t>(m) * p.N + n)
+                                             : "l"(src + static_cast<size_t>(m) * f.N + n)
                                              : "memory");
-                                all = all && static_cast<uint32_t>(word[i][m] >> 32) == fepoch;
+                                all = all && static_cast<uint32_t>(word[i][m] >> 32) == f.epoch;
                             } else {
                                 word[i][m] = 0ull;
                             }
@@ -1229,7 +1238,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                     if (it > 64) __nanosleep(it > 4096 ? 1000 : 32);
                 }
                 if (!got) {
-                    if (lane == 0) atomicOr(p.error_word, 0x200u);
+                    if (lane == 0) atomicOr(pa.error_word, 0x200u);
                     peers_ok = false;
                     return;
                 }
@@ -1241,8 +1250,17 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int m = 0; m < MD; ++m) store(m, rg * kRows + lane + 32u * i, acc[i][m]);
+                for (int m = 0; m < MD; ++m) {
+                    const uint32_t n = rg * kRows + lane + 32u * i;
+                    if (static_cast<uint32_t>(m) < f.M && n < f.N) {
+                        if (XF32 || f.y_f32)
+                            static_cast<float *>(f.y)[static_cast<size_t>(m) * f.N + n] = acc[i][m];
+                        else
+                            static_cast<__nv_bfloat16 *>(f.y)[static_cast<size_t>(m) * f.N + n] = __float2bfloat16_rn(acc[i][m]);
+                    }
+                }
         };
+        const FusedOp cur = {p.y, my_region, p.N, p.M, p.y_f32, p.fuse_size, fepoch, fphase};
         // final sums of row group rg (this rank's share of K): to y, or to the peers
         auto emit = [&](uint32_t rg, const float (&v)[4][MD]) {
             if (!fused) {
@@ -1271,7 +1289,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                 }
             }
             if (npend == kPend) {  // rare: many short row groups per CTA; settle the oldest first
-                if (peers_ok) finish(pend[0]);
+                if (peers_ok) finish(cur, pend[0]);
 #pragma unroll
                 for (uint32_t i = 0; i + 1u < kPend; ++i) pend[i] = pend[i + 1u];
                 --npend;
@@ -1397,22 +1415,45 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
             ob ^= 1u;
             if (ob == 0u) ophase ^= 1u;
         }
-        if (fused) {
-            for (uint32_t i = 0; i < npend; ++i)
-                if (peers_ok) finish(pend[i]);
+        // this CTA's share of operation `op`'s output is stored (or handed to the head owner, who stores it
+        // before it arrives here itself): arrive at the operation's grid-wide counter.  After the last
+        // operation the counter only finds the last CTA, which zeroes all of them for the next launch.
+        auto arrive_op = [&](uint32_t op) {
+            if (NOPS != 1) {
+                __syncwarp();
+                if (lane == 0) {
+                    unsigned int t;
+                    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(t) : "l"(gbar + op) : "memory");
+                    if (op == nops - 1u && t == gridDim.x - 1u)
+                        for (uint32_t i = 0; i < nops; ++i) gbar[i] = 0u;
+                }
+            }
+        };
+        // an exchange put off at the end of the previous operation: by now its words have had this whole operation's
+        // streaming time to cross NVLink
+        if (late_n != 0xFFFFFFFFu) {
+            for (uint32_t i = 0; i < late_n; ++i)
+                if (peers_ok) finish(late, late_rg[i]);
+            arrive_op(o - 1u);
+            late_n = 0xFFFFFFFFu;
         }
-        if (NOPS != 1) {
-            // this CTA's share of operation o's output is stored (or handed to the head owner, who stores it
-            // before it arrives here itself): arrive at the operation's grid-wide counter.  After the last
-            // operation the counter only finds the last CTA, which zeroes all of them for the next launch.
-            __syncwarp();
-            if (lane == 0) {
-                unsigned int t;
-                asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(t) : "l"(gbar + o) : "memory");
-                if (o == nops - 1u && t == gridDim.x - 1u)
-                    for (uint32_t i = 0; i < nops; ++i) gbar[i] = 0u;
+        bool put_off = false;
+        if (fused) {
+            // Launch lists: when the next operation does not read what this launch writes, this operation's wait for
+            // the peers moves to the end of the next one (and with it the arrival at its counter), so the NVLink
+            // latency hides behind that operation's streaming instead of stalling the write-out here.
+            if constexpr (NOPS == 0) put_off = o + 1u < nops && list.ops[o + 1u].dep == 0u;
+            if (put_off) {
+                late = cur;
+                late_n = npend;
+#pragma unroll
+                for (uint32_t i = 0; i < kPend; ++i) late_rg[i] = pend[i];
+            } else {
+                for (uint32_t i = 0; i < npend; ++i)
+                    if (peers_ok) finish(cur, pend[i]);
             }
         }
+        if (!put_off) arrive_op(o);
         }  // operations
         if (fctl_launch != nullptr) {
             // the exchange epoch moves once per launch, when the launch's last CTA is through all its operations

@@ -126,7 +126,7 @@ cudaError_t gather_dequant_f32(const WeightView &w, const uint32_t *d_ids, uint3
 cudaError_t gemm_tc(const WeightView &w, const void *x_bf16, void *y_bf16, uint32_t M,
                     cudaStream_t stream, int sm_count, unsigned int *d_error_word, float *ws, size_t ws_bytes,
                     unsigned int *flags, size_t flag_count);
-bool gemm_tc_eligible(const WeightView &w, uint32_t M);
+bool gemm_tc_eligible(const WeightView &w, uint32_t M, uint32_t min_m = 17u);
 size_t gemm_tc_workspace_bytes(int sm_count);
 size_t gemm_tc_flag_count(int sm_count);
 
@@ -138,13 +138,14 @@ constexpr size_t kPeerSlotBytes = size_t(1) << 20;    // one rank's tile as 64-b
 
 // Region layout (one cudaMalloc per rank, mapped by every rank of the node):
 //   all-reduce kernel: per-CTA call counters, data [2 phases][ranks][slot] of 64-bit words {fp32 value, epoch}
-//   fused GEMV + all-reduce: {epoch, done} words, data [2 phases][ranks][slot] holding a rank's partial tile as
+//   fused GEMV + all-reduce: {epoch, done} words, data [4 phases][ranks][slot] holding a rank's partial tile as
 //   64-bit words {fp32 value, launch epoch} [activation row][N]
 constexpr size_t kPeerEpochOff = 4096;
 constexpr size_t kFusedCtlOff = size_t(128) << 10;
 constexpr size_t kPeerDataOff = size_t(256) << 10;
 constexpr size_t kFusedDataOff = kPeerDataOff + 2 * size_t(kPeerMaxRanks) * kPeerSlotBytes;
-constexpr size_t kPeerRegionBytes = kFusedDataOff + 2 * size_t(kPeerMaxRanks) * kPeerSlotBytes;
+constexpr int kFusedPhases = 4;                       // data phases of the exchange fused into the GEMV write-out
+constexpr size_t kPeerRegionBytes = kFusedDataOff + kFusedPhases * size_t(kPeerMaxRanks) * kPeerSlotBytes;
 
 struct PeerComm {
     void *region[kPeerMaxRanks];  // every rank's region as mapped into this process; [rank] is cudaMalloc'ed here
