@@ -45,8 +45,8 @@ GROUP, BITS = 64, 4
 NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch list of the --quick case (2 layers = 4 GEMVs,
 # 198,377,472 algorithmic bytes), from the ncu capture summarised in profiles/gemv_list_llama8b_ffn_m1.md,
-# divided by the four GEMVs of the launch (None until that capture exists)
-NCU_TRAFFIC_PER_GEMV = None
+# divided by the four GEMVs of the launch: (198,353,408 read + 5,768,448 written) / 4
+NCU_TRAFFIC_PER_GEMV = 51030464
 
 
 def measured_peak_hbm():
@@ -145,6 +145,9 @@ def run_reference(args):
 
 
 # --------------------------------------------------------------------------- GPU arm
+MIN_SECONDS_SCALE = 1.0   # --min-seconds
+
+
 def time_graph(ctx, torch, stream, launch_step, steps, warmup, min_seconds=1.0, clocks=None):
     """Captures one step into a CUDA graph on `stream` and replays it for at least `min_seconds` (and at least
     `steps` times), an event after every replay.  Returns (mean ms of the last `steps` replays, stats over all,
@@ -164,7 +167,7 @@ def time_graph(ctx, torch, stream, launch_step, steps, warmup, min_seconds=1.0, 
         e1.record(stream)
         stream.synchronize()
         est = max(e0.elapsed_time(e1) / 5, 1e-3)
-        n = int(min(20000, max(steps, min_seconds * 1e3 / est)))
+        n = int(min(20000, max(steps, min_seconds * MIN_SECONDS_SCALE * 1e3 / est)))
         mark = clocks.mark() if clocks else 0
         evs = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
         evs[0].record(stream)
@@ -421,6 +424,8 @@ def run_single(args):
     if args.quick:
         # small case for profilers: one launch list (or the separate launches with --separate), not a bench value
         M = args.m
+        if args.prefetch_units >= 0:
+            ctx.set_option("prefetch_units", args.prefetch_units)
         xs, ys = make_io(M)
         with torch.cuda.stream(stream):
             if args.separate or M > 4:
@@ -595,8 +600,11 @@ def run_single(args):
         "cfg1": cfg1, "cfg3": cfg3,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "frac_of_nominal_8TBs": round(achieved / NOMINAL_HBM_GBS, 4),
-                     "peak_kind": f"of {peak_kind}", "traffic": NCU_TRAFFIC_PER_GEMV,
-                     "note": "achieved = algorithmic bytes of a step / its time (= bytes per GEMV / (launch time / 24)); traffic: ncu dram bytes per GEMV of a launch list"},
+                     "peak_kind": f"of {peak_kind}", "traffic": NCU_TRAFFIC_PER_GEMV * gemvs_per_step,
+                     "algorithmic_bytes": results[1]["bytes"],
+                     "note": "per launch = one list of all the step's GEMVs: achieved = algorithmic bytes of the step / its time; "
+                             "traffic = ncu dram bytes (read + written) of a 4-GEMV list, per GEMV, times the GEMVs of this list "
+                             "(traffic grows in proportion to the weights streamed)"},
         "cpu_baseline": {"value": round(cpu_gbs, 3), "unit": "GB/s", "cores": logical, "kind": "port",
                          "sample": f"{len(t_all)} passes over the first {len(cstack)} matrices of the same stack ({cbytes / 1e6:.0f} MB per pass), M=1, f32 activations",
                          "reference_thread_policy": {"threads": policy, "value": round(cbytes / float(np.mean(t_pol)) / 1e9, 3)}},
@@ -625,9 +633,15 @@ def main():
                     help="with --quick: which kernel the small case runs")
     ap.add_argument("--m", type=int, default=1, help="activation rows of the --quick decode / stack70b case")
     ap.add_argument("--separate", action="store_true", help="with --quick: separate launches instead of one launch list")
+    ap.add_argument("--prefetch-units", type=int, default=-1,
+                    help="with --quick --separate: units per CTA of the next weight a launch pulls into L2 (library default 2)")
+    ap.add_argument("--min-seconds", type=float, default=1.0,
+                    help="length of every timed graph-replay run (shorter only for launch listings under a profiler)")
     ap.add_argument("--quick", action="store_true",
                     help="one configuration only, no end-to-end and no CPU leg (small case for profilers; not a bench value)")
     args = ap.parse_args()
+    global MIN_SECONDS_SCALE
+    MIN_SECONDS_SCALE = args.min_seconds
     if args.impl == "reference":
         run_reference(args)
         return

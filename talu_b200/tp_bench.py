@@ -241,7 +241,7 @@ def measure(args, existing_ctx=None, existing_stream=None, M=1, quick=False, par
     ctx = existing_ctx or gaf.Context(local, stream=stream.cuda_stream)
     layers = 2 if quick else (args.layers if args.layers != 12 else 8)   # 8 layers: 3.85 GB, 481 MB per rank at N = 8
     steps, warmup = args.steps, max(3, args.warmup)
-    min_seconds = 0.0 if quick else 1.0
+    min_seconds = 0.0 if quick else float(getattr(args, "min_seconds", 1.0))
     res = {"layers": layers, "world": world, "rank": rank, "steps": steps, "warmup": warmup, "bytes": stack_bytes(layers, M)}
 
     if world > 1:
