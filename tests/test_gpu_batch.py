@@ -128,3 +128,98 @@ def test_list_that_does_not_qualify_runs_call_by_call(gaf, ctx, oracle):
         gaf.Batch(ctx, [wa, wb], [x, x], [ya, yb], depends=[1, 0])      # the first operation cannot depend on anything
     wa.free()
     wb.free()
+
+
+def test_list_with_sums_over_the_ranks_on_a_one_rank_communicator(gaf, oracle):
+    """reduce flags on a communicator of ONE rank: the exchange code of the launch list runs (push to the own region,
+    wait for the own words, add, write y), including the form in which an operation's wait for its words is put off
+    to the end of the following independent operation, and many replays go round all data phases of the exchange."""
+    import torch
+    c = gaf.Context(0)
+    try:
+        try:
+            c.comm_init(gaf.make_comm_id(), 0, 1)
+        except gaf.GafError as e:
+            pytest.skip(f"no NCCL on this machine: {e}")
+        assert c.uses_peer_memory()
+        G = 64
+        shapes = [(1024, 2048), (2048, 1024), (640, 4096), (1024, 2048), (384, 1024)]
+        reduce = [1, 0, 1, 1, 0]
+        for M in (1, 2):
+            ws, xs, refs = [], [], []
+            for i, (N, K) in enumerate(shapes):
+                p, s, b = make_weights(oracle, N, K, G, 4, seed=300 + i)
+                xb, xf = make_x_bf16(oracle, M, K, seed=400 + i + M)
+                ws.append(gaf.Weight.from_host(c, p, s, b, G, 4))
+                xs.append(torch_bf16_from_bits(xb, "cuda:0"))
+                refs.append(oracle.matmul_f32(xf, p, s, b, G, 4))
+            ys = [torch.full((M, w.N), float("nan"), dtype=torch.bfloat16, device="cuda:0") for w in ws]
+            batch = gaf.Batch(c, ws, xs, ys, reduce=reduce)
+            assert batch.one_launch
+            first = None
+            for rep in range(9):
+                for y in ys:
+                    y.fill_(float("nan"))
+                batch.run()
+                c.synchronize()
+                if first is None:
+                    first = [y.clone() for y in ys]
+                    for y, ref in zip(ys, refs):
+                        assert rel_err(_f32(oracle, y), ref) <= TOL_BF16
+                else:
+                    for y, f in zip(ys, first):
+                        assert torch.equal(y, f), rep
+            batch.close()
+            for w in ws:
+                w.free()
+    finally:
+        c.close()
+
+
+def test_recorded_host_batch_is_two_block_copies_around_one_launch(gaf, oracle):
+    """tgaf_host_batch_create on page-locked buffers: views of ONE block travel as one copy each way around one
+    launch list; separate allocations still work (one copy per buffer).  New activations in the same buffers give
+    new results on the next submit."""
+    import torch
+    stream = torch.cuda.Stream()
+    c = gaf.Context(0, stream=stream.cuda_stream)
+    try:
+        G, M = 64, 1
+        shapes = [(1000, 2048), (2048, 1024), (384, 4096)]
+        ws, prm = [], []
+        for i, (N, K) in enumerate(shapes):
+            p, s, b = make_weights(oracle, N, K, G, 4, seed=500 + i)
+            ws.append(gaf.Weight.from_host(c, p, s, b, G, 4))
+            prm.append((p, s, b))
+        xn, yn = sum(M * w.K for w in ws), sum(M * w.N for w in ws)
+        for one_block in (True, False):
+            if one_block:
+                hx = torch.zeros(xn, dtype=torch.int16).pin_memory().numpy().view(np.uint16)
+                hy = torch.zeros(yn, dtype=torch.int16).pin_memory().numpy().view(np.uint16)
+                xv, yv, xo, yo = [], [], 0, 0
+                for w in ws:
+                    xv.append(hx[xo: xo + M * w.K].reshape(M, w.K))
+                    yv.append(hy[yo: yo + M * w.N].reshape(M, w.N))
+                    xo, yo = xo + M * w.K, yo + M * w.N
+            else:
+                xv = [torch.zeros((M, w.K), dtype=torch.int16).pin_memory().numpy().view(np.uint16) for w in ws]
+                yv = [torch.zeros((M, w.N), dtype=torch.int16).pin_memory().numpy().view(np.uint16) for w in ws]
+            hb = gaf.HostBatch(c, ws, xv, yv).record()
+            assert hb.one_launch
+            for rep in range(3):
+                xfs = []
+                for i, (w, x) in enumerate(zip(ws, xv)):
+                    xb, xf = make_x_bf16(oracle, M, w.K, seed=600 + 10 * rep + i)
+                    x[...] = xb
+                    xfs.append(xf)
+                for y in yv:
+                    y[...] = 0
+                hb.submit()
+                c.synchronize()
+                for (p, s, b), xf, y in zip(prm, xfs, yv):
+                    assert rel_err(oracle.bf16_to_f32(y), oracle.matmul_f32(xf, p, s, b, G, 4)) <= TOL_BF16, (one_block, rep)
+            hb.close()
+        for w in ws:
+            w.free()
+    finally:
+        c.close()

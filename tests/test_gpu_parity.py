@@ -504,6 +504,35 @@ def test_prefill_cfg4_full_size(gaf, ctx, oracle):
     assert rel_err(got, ref) <= TOL_BF16, rel_err(got, ref)
 
 
+def test_gemm_min_m_option_moves_the_hand_over(gaf, oracle):
+    """"gemm_min_m" = the activation rows from which the tensor-core GEMM takes over from the decode GEMVs (default 17).
+    With it lowered, M = 5, 8 and 16 run on the GEMM: same results within the same bound."""
+    import torch
+    c = gaf.Context(0)
+    try:
+        with pytest.raises(gaf.GafError):
+            c.set_option("gemm_min_m", 0)
+        with pytest.raises(gaf.GafError):
+            c.set_option("gemm_min_m", 18)
+        for M, N, K, G in [(5, 300, 1024, 64), (8, 1024, 2048, 32), (16, 512, 4096, 128)]:
+            p, s, b = make_weights(oracle, N, K, G, 4, seed=M)
+            xb, xf = make_x_bf16(oracle, M, K, seed=M + 1)
+            w = gaf.Weight.from_host(c, p, s, b, G, 4)
+            x = torch_bf16_from_bits(xb, "cuda:0")
+            ref = oracle.matmul_f32(xf, p, s, b, G, 4)
+            outs = []
+            for mn in (17, 5):
+                c.set_option("gemm_min_m", mn)
+                y = gaf.linear(c, w, x)
+                c.synchronize()
+                got = oracle.bf16_to_f32(bits_from_torch_bf16(y))
+                assert rel_err(got, ref) <= TOL_BF16, (M, N, K, G, mn)
+                outs.append(y)
+            w.free()
+    finally:
+        c.close()
+
+
 def test_embedding_lookup_and_lm_head(gaf, ctx, oracle):
     """Embedding rows (bit-exact gather-dequant with the multiplier) and the lm_head shape: one GEMV over a
     vocabulary-sized table."""
