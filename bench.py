@@ -318,6 +318,16 @@ def tp_parity_check(ctx, torch, dist, rank, world, stream):
         ref3 = oracle.matmul_f32(xf3, p3, s3, b3, GROUP, BITS)
         k3 = K3 // world
         x3 = torch_bf16_from_bits(np.ascontiguousarray(xb3[:, rank * k3:(rank + 1) * k3]), "cuda")
+        # kernel error apart from reduction error: every rank's own partial output (no sum on the GPU), added over the
+        # ranks on the host in float64, against the oracle; the GPU's sums below are then compared with that sum too
+        part = gaf.linear(ctx, w3, x3)
+        stream.synchronize()
+        ctx.synchronize()
+        psum = torch.from_numpy(to_f32(part).astype(np.float64))
+        dist.all_reduce(psum, op=dist.ReduceOp.SUM)
+        psum = psum.numpy()
+        kernel_rel = rel_err(psum.astype(np.float32), ref3)
+        reduction_rel = 0.0
         for name, opts in paths:
             for k, v in (opts or {}).items():
                 ctx.set_option(k, v)
@@ -368,6 +378,8 @@ def tp_parity_check(ctx, torch, dist, rank, world, stream):
                 stream.synchronize()
                 ctx.synchronize()
             errs.append(rel_err(to_f32(y3), ref3))
+            if opts is None or opts["fused_allreduce"]:
+                reduction_rel = max(reduction_rel, rel_err(to_f32(y3), psum.astype(np.float32)))
             e = torch.tensor([max(errs)], dtype=torch.float64)
             dist.all_reduce(e, op=dist.ReduceOp.MAX)            # the worst rank
             # the two-step paths round every rank's partial sums to bf16 before they are added (P + 1 roundings
@@ -383,6 +395,9 @@ def tp_parity_check(ctx, torch, dist, rank, world, stream):
     if failed:
         raise RuntimeError(f"rank {rank}: sharded linears differ from the unsharded oracle: {report}")
     return {"rel": round(worst, 6), "peer_memory": bool(peer), "paths": report,
+            "down_shard_split": {"kernel_rel": round(float(kernel_rel), 6), "reduction_rel": round(float(reduction_rel), 6),
+                                 "note": "8192 x 28672 shard: float64 host sum of the ranks' own bf16 partial outputs vs the oracle "
+                                         "(kernel error), and the GPU's fp32-partials sum vs that host sum (reduction and rounding)"},
             "cases": "col->row chain 1024/2048 at M = 1, 2, 4; 8192 x 28672 row-parallel shard at M = 1; every rank compared"}
 
 
