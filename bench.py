@@ -631,7 +631,9 @@ def run_single(args):
         "llama3_70b_stack_1gpu": stack70b,
         "gpu_launches": args.steps,
         "gpu_launches_note": "kernel launches inside the timed K steps of the headline: one launch list per step (24 GEMVs each)",
-        "clocks": clocks.summary(),
+        "clocks": {**clocks.summary(), "sm_mhz": (head["clocks"] or {}).get("sm_mhz_median", clocks.summary()["sm_mhz"]),
+                   "sm_mhz_all_cases": clocks.summary()["sm_mhz"],
+                   "note": "sm_mhz = median while the headline case (M = 1 launch list) ran; reasons = seen at any time during the bench"},
     }
     print(json.dumps(out))
 
