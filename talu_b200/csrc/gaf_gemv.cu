@@ -109,6 +109,10 @@ struct GemvParams {
     unsigned int *grid_bar;  // M <= 4 kernel, several operations per launch: arrival counters, zero between launches
     uint32_t dep;            // M <= 4 kernel, several operations per launch: 1 = x of this operation is written by an earlier
                              // operation of the launch (wait for the grid-wide arrival at the previous operation)
+    uint8_t *xq;             // launch lists, one activation row: this operation's quantised activations in global memory,
+                             // [K chunk][quantised unit + {scale, sum} pairs], built once per launch at its very start and
+                             // copied into every ring stage beside the weights (null: each CTA quantises for itself)
+    uint32_t xq_pair0;       //   index of this operation's first (operation, K chunk) pair among all such pairs of the list
 };
 
 // One operation's exchange as the writer warp needs it to collect the peers' words later on.
@@ -124,7 +128,8 @@ struct GemvOpList {
     const GemvParams *ops;
     const CUtensorMap *maps;
     uint32_t count;
-    unsigned int *grid_bar;   // `count` arrival counters, zero between launches
+    unsigned int *grid_bar;   // `count` arrival counters (+ one for the quantised activations), zero between launches
+    uint32_t xq_pairs;        // (operation, K chunk) pairs whose activations are quantised at the start of the launch (0: none)
 };
 
 // ---- small PTX wrappers ----------------------------------------------------
@@ -1017,7 +1022,7 @@ __device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
     return d;
 }
 
-template <int GB, int MD, bool XF32, int NST, int BU>
+template <int GB, int MD, bool XF32, int NST, int BU, bool XQS = false>
 struct DpPlan {
     static constexpr int GPS = kChunkBytes / GB;           // groups per unit
     static constexpr int WPG = GB / 4;                     // packed words per group and row
@@ -1025,7 +1030,10 @@ struct DpPlan {
     static constexpr int XQ_UNIT = GPS * XQ_GROUP;         // 1 KB per activation row for any group size
     static constexpr int XI_UNIT = GPS * MD * 8;           // {2^(E-12), sum x} per group and activation row
     static constexpr int OUT_BUF = GPS * kRows * MD * 4;   // per-group partial sums of one row group
-    static constexpr int OFF_XQ = NST * StreamGeom<GB>::STAGE_BYTES;
+    // XQS: a stage also holds the unit's quantised activations (copied from global memory like the weights)
+    static constexpr int XQS_UNIT = XQ_UNIT + XI_UNIT;     // a multiple of 16 bytes
+    static constexpr int STAGE = XQS ? ((StreamGeom<GB>::STAGE_BYTES + XQS_UNIT + 1023) / 1024) * 1024 : StreamGeom<GB>::STAGE_BYTES;
+    static constexpr int OFF_XQ = NST * STAGE;
     static constexpr int OFF_XI = OFF_XQ + 2 * BU * XQ_UNIT;
     static constexpr int OFF_OUT = OFF_XI + 2 * BU * XI_UNIT;
     static constexpr int TOTAL = OFF_OUT + 2 * OUT_BUF + 1024;
@@ -1050,7 +1058,9 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                      const __grid_constant__ CUtensorMap next_w, const __grid_constant__ CUtensorMap next_s,
                      const __grid_constant__ CUtensorMap next_b, const GemvOpList list) {
     using Geo = StreamGeom<GB>;
-    using Plan = DpPlan<GB, MD, XF32, NST, BU>;
+    // launch lists with one activation row: activations quantised once per launch, streamed into the stages
+    constexpr bool XQS = NOPS == 0 && MD == 1 && !XF32;
+    using Plan = DpPlan<GB, MD, XF32, NST, BU, XQS>;
     constexpr int GPS = Geo::GPS, WPG = Plan::WPG;
     constexpr int RW = kRows * GPS / NCW;  // rows per warp: 128 (G=32), 64 (G=64), 32 (G=128)
     constexpr int R = RW / 32;                        // rows per lane
@@ -1098,6 +1108,37 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         if (lane != 0) return;
         uint32_t issued = 0;
         bool ok = true;
+        bool xq_seen = !XQS || list.xq_pairs == 0u;
+        uint32_t late_dst[NST], late_bar[NST], n_late = 0u;
+        const uint8_t *late_src[NST];
+        auto xq_copy = [&](uint32_t dst, const uint8_t *src, uint32_t bar) {
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                         "l"(src), "n"(Plan::XQS_UNIT), "r"(bar)
+                         : "memory");
+        };
+        // waits (bounded) until every CTA has written its share of the launch's quantised activations, orders the copies
+        // (async proxy) after what was observed, and issues the copies that were put off
+        auto flush_late = [&]() -> bool {
+            bool there = false;
+            for (uint32_t it = 0; it < kWaitLimit; ++it) {
+                unsigned int v;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(gbar + nops) : "memory");
+                if (v >= gridDim.x) {
+                    there = true;
+                    break;
+                }
+                if (it > 32) __nanosleep(it > 4096 ? 256 : 32);
+            }
+            if (!there) {
+                atomicOr(pa.error_word, 0x400u);
+                return false;
+            }
+            asm volatile("fence.proxy.async;" ::: "memory");
+            for (uint32_t i = 0; i < n_late; ++i) xq_copy(late_dst[i], late_src[i], late_bar[i]);
+            n_late = 0u;
+            xq_seen = true;
+            return true;
+        };
 #pragma unroll 1
         for (uint32_t o = 0; o < nops; ++o) {
             GemvParams plist;
@@ -1116,24 +1157,46 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
             for (uint32_t u = u_begin; u < u_end && ok; ++u) {
                 const uint32_t stage = issued % NST;
                 const uint32_t round = issued / NST;
+                if constexpr (XQS) {
+                    // the ring is full of weights whose activations are still missing (or the very first such stage when
+                    // the ring is already turning): now the counter has to be there
+                    if (!xq_seen && (n_late == static_cast<uint32_t>(NST) || (round > 0 && n_late != 0u))) ok = flush_late();
+                    if (!ok) break;
+                }
                 if (round > 0) ok = mbar_wait(smem_u32(&s_empty[stage]), (round - 1u) & 1u, p.error_word, 0x1u);
                 if (!ok) break;
                 const uint32_t full = smem_u32(&s_full[stage]);
                 {
-                    const uint32_t base = ring + stage * Geo::STAGE_BYTES;
-                    mbar_arrive_expect_tx(full, Geo::STAGE_BYTES);
+                    const uint32_t base = ring + stage * Plan::STAGE;
+                    const bool with_x = XQS && p.xq != nullptr;
+                    mbar_arrive_expect_tx(full, Geo::STAGE_BYTES + (with_x ? Plan::XQS_UNIT : 0));
 #pragma unroll
                     for (int pnl = 0; pnl < kPanels; ++pnl)
                         tma_load_2d(base + pnl * kPanelSize, tw, kc * kChunkBytes + pnl * kPanelBytes, rg * kRows, full);
                     const uint32_t sb_col = (kc * GPS * 2u) & ~15u;
                     tma_load_2d(base + kWeightBytes, ts, sb_col, rg * kRows, full);
                     tma_load_2d(base + kWeightBytes + Geo::SB_BYTES, tb, sb_col, rg * kRows, full);
+                    if (with_x) {
+                        const uint8_t *src = p.xq + static_cast<size_t>(kc) * Plan::XQS_UNIT;
+                        if (xq_seen) {
+                            xq_copy(base + Geo::STAGE_BYTES, src, full);
+                        } else {
+                            // the quantised activations are still being written (start of the launch): the weights of
+                            // this stage are on their way; its activations follow once the grid-wide counter is there
+                            late_dst[n_late] = base + Geo::STAGE_BYTES, late_src[n_late] = src, late_bar[n_late] = full;
+                            ++n_late;
+                        }
+                    }
                 }
                 ++issued;
                 if (++kc == p.chunks) kc = 0u, ++rg;
             }
         }
+        if constexpr (XQS) {
+            if (ok && !xq_seen && n_late != 0u) ok = flush_late();
+        }
         if (!ok) {
+            s_abort = 1u;
             const uint32_t pending = issued < static_cast<uint32_t>(NST) ? issued : static_cast<uint32_t>(NST);
             for (uint32_t i = 0; i < pending; ++i) {
                 const uint32_t idx = issued - 1u - i;
@@ -1425,7 +1488,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                     unsigned int t;
                     asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(t) : "l"(gbar + op) : "memory");
                     if (op == nops - 1u && t == gridDim.x - 1u)
-                        for (uint32_t i = 0; i < nops; ++i) gbar[i] = 0u;
+                        for (uint32_t i = 0; i <= nops; ++i) gbar[i] = 0u;   // [nops]: the quantised-activations counter
                 }
             }
         };
@@ -1517,12 +1580,72 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
     uint32_t stage = 0, phase = 0;   // ring position and out-buffer position run on across operations
     uint32_t ob = 0, ophase = 0;
     bool alive = true;
-    // launch lists: the activations of the NEXT operation's first block, fetched while this operation runs (only
-    // when that operation does not read what this launch writes), so that its start does not wait for memory
-    constexpr int kPreG = GB * 2, kPrePER = kPreG / 32, kPreTPW = (BU * GPS * MD + NCW - 1) / NCW;
-    float xpre[kPreTPW][kPrePER];
-    bool have_pre = false;
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if constexpr (XQS) {
+        // ---- the launch's activations, quantised ONCE: the (operation, K chunk) pairs are dealt round-robin to the
+        // CTAs, each writes its pairs' quantised units to global memory, then arrives at a grid-wide counter; the copy
+        // warps wait for that counter before their first copy of such a unit.  Afterwards an operation's activations
+        // arrive with its weights, stage by stage: no per-CTA rebuild, no CTA barrier between operations.
+        if (list.xq_pairs != 0u) {
+            constexpr int G = GB * 2, PER = G / 32;
+            // task = (pair, group of the unit): one warp each, dealt over all consumer warps of the grid
+            const uint32_t ntasks = list.xq_pairs * GPS, stride = gridDim.x * NCW;
+#pragma unroll 1
+            for (uint32_t task = blockIdx.x * NCW + warp; task < ntasks; task += stride) {
+                const uint32_t j = task / GPS, gl = task % GPS;
+                // the operation this pair belongs to (a few dozen operations at most: a linear search)
+                uint8_t *xq_base = nullptr;
+                const __nv_bfloat16 *qx = nullptr;
+                uint32_t kc = 0u, qgroups = 0u;
+                for (uint32_t oo = 0; oo < nops; ++oo) {
+                    const GemvParams *qp = list.ops + oo;
+                    uint8_t *b = qp->xq;
+                    const uint32_t p0 = qp->xq_pair0, ch = qp->chunks;
+                    if (b != nullptr && j >= p0 && j < p0 + ch) {
+                        xq_base = b, kc = j - p0, qgroups = qp->groups;
+                        qx = static_cast<const __nv_bfloat16 *>(qp->x);
+                        break;
+                    }
+                }
+                if (xq_base == nullptr) continue;
+                uint8_t *dst = xq_base + static_cast<size_t>(kc) * Plan::XQS_UNIT;
+                const uint32_t gi = kc * GPS + gl;
+                float xv[PER];
+#pragma unroll
+                for (int e = 0; e < PER; ++e)
+                    xv[e] = gi < qgroups ? __bfloat162float(qx[static_cast<size_t>(gi) * G + lane * PER + e]) : 0.f;
+                uint32_t abits = 0u;
+#pragma unroll
+                for (int e = 0; e < PER; ++e) abits = max(abits, __float_as_uint(xv[e]) & 0x7FFFFFFFu);
+                abits = __reduce_max_sync(0xFFFFFFFFu, abits);
+                const uint32_t eb = abits >> 23;   // same rule as the per-CTA quantiser below
+                const bool nz = eb >= 27u && eb < 255u;
+                const float up = nz ? __uint_as_float((265u - eb) << 23) : 0.f;
+                const float down = nz ? __uint_as_float((eb - 11u) << 23) : 0.f;
+                int isum = 0;
+#pragma unroll
+                for (int e = 0; e < PER; ++e) {
+                    int xi = __float_as_int(fmaf(xv[e], up, 12582912.f)) - 0x4B400000;
+                    xi = max(-4095, min(4095, xi));
+                    isum += xi;
+                    const uint32_t k = lane * PER + e;
+                    const uint32_t wj = k >> 3, odd = k & 1u, bytepos = (k & 7u) >> 1;
+                    uint8_t *a = dst + gl * Plan::XQ_GROUP + wj * 16u + odd * 4u + bytepos;   // {even hi, odd hi, even lo, odd lo} x 4 bytes
+                    a[0] = static_cast<uint8_t>((xi >> 6) & 0xFF);
+                    a[8] = static_cast<uint8_t>(xi & 63);
+                }
+                isum = __reduce_add_sync(0xFFFFFFFFu, isum);
+                if (lane == 0)
+                    *reinterpret_cast<float2 *>(dst + Plan::XQ_UNIT + gl * 8u) = make_float2(down, static_cast<float>(isum) * down);
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
+            if (warp == 0 && lane == 0) {
+                __threadfence();
+                asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(gbar + nops) : "memory");
+            }
+        }
+    }
 #pragma unroll 1
     for (uint32_t o = 0; o < nops; ++o) {
     GemvParams plist;
@@ -1533,7 +1656,10 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
     const uint32_t u_end = range_begin(blockIdx.x + 1u, p.units, gridDim.x);
     const uint32_t rg_begin = u_begin / p.chunks;
     const uint32_t kc_begin = u_begin - rg_begin * p.chunks;
-    if (NOPS != 1) {
+    // opx: this operation's activations were quantised at the start of the launch and arrive with every stage: no
+    // block to build, nothing to wait for between operations
+    const bool opx = XQS && p.xq != nullptr;
+    if (NOPS != 1 && !opx) {
         if (o > 0) {
             // all warps are done reading the previous operation's activation blocks, and (when this operation reads
             // what the previous one wrote) the previous operation's output is complete on every CTA
@@ -1561,23 +1687,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
 
     // ---- quantised activations for a block of units: (unit, group, activation row) triples over the warps ----
     // Two passes so that all of a warp's global loads are in flight together.
-    // plain bf16 activations of a block of units into registers: (unit, group, activation row) triples over the warps
-    auto load_block = [&](const GemvParams &q, uint32_t kc_first, uint32_t count, float (&xv)[kPreTPW][kPrePER]) {
-        const uint32_t ntask = count * GPS * MD;
-#pragma unroll
-        for (int tk = 0; tk < kPreTPW; ++tk) {
-            const uint32_t pi = warp + tk * NCW;
-            const uint32_t m = pi % MD, gl = (pi / MD) % GPS, ub = pi / (MD * GPS);
-            const uint32_t gi = ((kc_first + ub) % q.chunks) * GPS + gl;
-            const bool live = pi < ntask && m < q.M && gi < q.groups;
-#pragma unroll
-            for (int e = 0; e < kPrePER; ++e) {
-                const size_t idx = static_cast<size_t>(m) * q.K + static_cast<size_t>(gi) * kPreG + lane * kPrePER + e;
-                xv[tk][e] = live ? __bfloat162float(static_cast<const __nv_bfloat16 *>(q.x)[idx]) : 0.f;
-            }
-        }
-    };
-    auto prep_block = [&](auto act_c, uint32_t kc_first, uint32_t count, uint32_t buf, bool use_pre = false) {
+    auto prep_block = [&](auto act_c, uint32_t kc_first, uint32_t count, uint32_t buf) {
         constexpr bool ACT = decltype(act_c)::value;  // compile-time: the plain path keeps its loads branch-free
         if constexpr (IM && !ACT && !XF32) {
             // Four activation rows: a lane takes one packed word's worth (8 consecutive elements, one 16-byte
@@ -1646,15 +1756,8 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         constexpr int G = GB * 2;                          // elements per group (4-bit codes)
         constexpr int PER = G / 32;                        // elements per lane: 1 (G=32), 2, 4
         constexpr int TPW = (BU * GPS * MD + NCW - 1) / NCW;  // triples per warp, at most
-        static_assert(TPW == kPreTPW && PER == kPrePER, "prefetch registers must match the block's shape");
         float xv[TPW][PER];
         const uint32_t ntask = count * GPS * MD;
-        if (use_pre) {
-#pragma unroll
-            for (int tk = 0; tk < TPW; ++tk)
-#pragma unroll
-                for (int e = 0; e < PER; ++e) xv[tk][e] = xpre[tk][e];
-        } else
 #pragma unroll
         for (int tk = 0; tk < TPW; ++tk) {
             const uint32_t pi = warp + tk * NCW;
@@ -1735,9 +1838,9 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
 
     // When a row of K fits the two activation buffers taken together (K / 512 <= 2 BU), they are filled here
     // with every K chunk, in the order this CTA meets them; later row groups reuse them and nothing is rebuilt.
-    const bool whole_k = p.chunks <= 2u * block_units;
+    const bool whole_k = opx || p.chunks <= 2u * block_units;
     const uint32_t block_len = whole_k ? p.chunks : block_units;
-    {
+    if (!opx) {
         const uint32_t total = u_end - u_begin;
         const uint32_t first = total < block_len ? total : block_len;
         const uint32_t head = first < block_units ? first : block_units;
@@ -1745,26 +1848,11 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
             prep_block(std::true_type{}, kc_begin, head, 0u);
             if (first > head) prep_block(std::true_type{}, (kc_begin + head) % p.chunks, first - head, 1u);
         } else {
-            prep_block(std::false_type{}, kc_begin, head, 0u, have_pre);
+            prep_block(std::false_type{}, kc_begin, head, 0u);
             if (first > head) prep_block(std::false_type{}, (kc_begin + head) % p.chunks, first - head, 1u);
         }
-        have_pre = false;
+        asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
-    if constexpr (NOPS == 0 && !IM && !XF32) {
-        if (o + 1u < nops) {
-            const GemvParams qn = list.ops[o + 1u];
-            if (qn.dep == 0u && qn.act == 0u) {
-                const uint32_t nb = range_begin(blockIdx.x, qn.units, gridDim.x), ne = range_begin(blockIdx.x + 1u, qn.units, gridDim.x);
-                const uint32_t nlen = qn.chunks <= 2u * block_units ? qn.chunks : block_units;
-                uint32_t nhead = ne - nb < nlen ? ne - nb : nlen;
-                if (nhead > block_units) nhead = block_units;
-                load_block(qn, nb % qn.chunks, nhead, xpre);
-                have_pre = true;
-            }
-        }
-    }
-
     uint32_t rg = rg_begin, kc = kc_begin;
     uint32_t ub = 0, buf = 0;
     for (uint32_t u = u_begin; u < u_end; ++u) {
@@ -1780,7 +1868,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         const bool exists = kc * GPS + gq < p.groups;  // the last K chunk of a row may hold fewer groups
         if constexpr (IM) {
             if (landed && exists) {
-                const uint32_t stage_off = stage * Geo::STAGE_BYTES;
+                const uint32_t stage_off = stage * Plan::STAGE;
                 const uint32_t xq = xq_warp + (buf * BU + ub) * Plan::XQ_UNIT + lane * 8u;
                 uint32_t bfr[WPT][2];  // this group's B registers, kept for all row blocks
 #pragma unroll
@@ -1815,7 +1903,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
             }
         } else
         if (landed && exists) {
-            const uint32_t stage_off = stage * Geo::STAGE_BYTES;
+            const uint32_t stage_off = stage * Plan::STAGE;
             // packed codes of this lane's rows
             uint32_t w[R][WPG];
 #pragma unroll
@@ -1830,7 +1918,9 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
             for (int i = 0; i < R; ++i)
 #pragma unroll
                 for (int m = 0; m < MD; ++m) ahi[i][m] = 0, alo[i][m] = 0;
-            const uint32_t xq = xq_warp + (buf * BU + ub) * Plan::XQ_UNIT;
+            // quantised activations: of this unit, beside its weights in the stage (opx), or of the CTA's current block
+            const uint32_t xq = opx ? ring + stage_off + Geo::STAGE_BYTES + gq * Plan::XQ_GROUP
+                                    : xq_warp + (buf * BU + ub) * Plan::XQ_UNIT;
 #pragma unroll
             for (int j = 0; j < WPG; ++j) {
                 uint32_t xe_hi[MD], xo_hi[MD], xe_lo[MD], xo_lo[MD];
@@ -1852,7 +1942,8 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                 }
             }
             float ex[MD], xs[MD];
-            const uint32_t xi = xi_warp + (buf * BU + ub) * Plan::XI_UNIT;
+            const uint32_t xi = opx ? ring + stage_off + Geo::STAGE_BYTES + Plan::XQ_UNIT + gq * MD * 8u
+                                    : xi_warp + (buf * BU + ub) * Plan::XI_UNIT;
 #pragma unroll
             for (int m = 0; m < MD; ++m)
                 asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(ex[m]), "=f"(xs[m]) : "r"(xi + m * 8u));
@@ -2114,7 +2205,7 @@ template <int GB, int MD, bool XF32, int SD, int NCW, int NST, int BU, int NOPS 
 cudaError_t launch_dp4a(const GemvParams &p, const WeightView &w, const WeightView *next, uint32_t ctas, bool pdl,
                         cudaStream_t stream, const GemvParams *second = nullptr, const GemvOpList *list = nullptr) {
     auto kern = gaf_gemv_dp4a_kernel<GB, MD, XF32, SD, NCW, NST, BU, NOPS>;
-    using Plan = DpPlan<GB, MD, XF32, NST, BU>;
+    using Plan = DpPlan<GB, MD, XF32, NST, BU, (NOPS == 0 && MD == 1 && !XF32)>;
     static bool configured[kMaxDevices] = {};
     if (cudaError_t e = opt_in_shared_memory(kern, Plan::TOTAL, configured); e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
@@ -2510,6 +2601,7 @@ struct GemvList {
     unsigned int *d_bar;
     size_t bar_bytes;
     uint32_t count, ctas, M;
+    uint32_t xq_pairs;  // (operation, K chunk) pairs quantised at the start of every launch
     bool imma_small;   // M <= 2 on the int8-MMA instance (the tagged words are then laid out for four rows)
 };
 
@@ -2524,12 +2616,32 @@ cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs,
     const uint32_t md = (M == 1u && !tune.imma_small) ? M : 4u;   // two rows: the int8-MMA instance measured faster in a list
     const size_t map_bytes = static_cast<size_t>(count) * 3u * sizeof(CUtensorMap);
     const size_t par_bytes = (static_cast<size_t>(count) * sizeof(GemvParams) + 255u) & ~size_t(255);
-    const size_t bar_bytes = (static_cast<size_t>(count) * sizeof(unsigned int) + 255u) & ~size_t(255);
+    const size_t bar_bytes = (static_cast<size_t>(count + 1u) * sizeof(unsigned int) + 255u) & ~size_t(255);   // + the activations counter
+    // One activation row on the integer-dot instance: operations whose activations nothing in this launch writes get them
+    // quantised once per launch into global memory, [K chunk][1 KB of limb bytes + {scale, sum} per group]
+    const uint32_t gb0 = ws[0]->group * ws[0]->bits / 8u;
+    const size_t xqs_unit = 1024u + (gb0 ? (kChunkBytes / gb0) * 8u : 0u);
+    const bool use_xq = md == 1u && gb0 != 0u;
+    size_t xq_bytes = 0;
+    // (only where it measured faster than letting each CTA quantise the block or two it needs: operations that give
+    // every CTA at least eight units, or at least four when a row of K does not fit one CTA's activation buffers, so
+    // that the per-CTA form would rebuild its block, behind a CTA barrier, every eight units)
+    auto wants_xq = [&](uint32_t i, const GemvPlan &pl) {
+        if (!use_xq || (deps && deps[i])) return false;
+        const uint32_t per_cta = pl.units / static_cast<uint32_t>(t.ctas);
+        return per_cta >= 8u || (per_cta >= 4u && pl.chunks > 16u);
+    };
+    for (uint32_t i = 0; i < count; ++i) {
+        const GemvPlan pl = plan_gemv(*ws[i], t, sm_count);
+        if (wants_xq(i, pl)) xq_bytes += static_cast<size_t>(pl.chunks) * xqs_unit;
+    }
+    xq_bytes = (xq_bytes + 255u) & ~size_t(255);
     uint8_t *host = static_cast<uint8_t *>(malloc(map_bytes + par_bytes));
     if (!host) return cudaErrorMemoryAllocation;
     CUtensorMap *maps = reinterpret_cast<CUtensorMap *>(host);
     GemvParams *params = reinterpret_cast<GemvParams *>(host + map_bytes);
-    size_t words = 0;
+    size_t words = 0, xq_off = 0;
+    uint32_t xq_pairs = 0;
     for (uint32_t i = 0; i < count; ++i) {
         const WeightView &w = *ws[i];
         if (!gemv_mma_eligible(w, xs[i], ys[i], false)) {
@@ -2541,6 +2653,13 @@ cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs,
         q.tagged = tagged + words;
         words += static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * md;
         q.dep = deps && deps[i] ? 1u : 0u;
+        if (wants_xq(i, pl)) {
+            // the address is an offset for now: the blob it lives in is allocated below
+            q.xq = reinterpret_cast<uint8_t *>(xq_off + 1u);
+            q.xq_pair0 = xq_pairs;
+            xq_off += static_cast<size_t>(pl.chunks) * xqs_unit;
+            xq_pairs += pl.chunks;
+        }
         if (fuse && fuse[i]) {
             GemvTuning tf = t;
             tf.fuse = fuse[i];
@@ -2562,7 +2681,12 @@ cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs,
         free(host);
         return cudaErrorMemoryAllocation;
     }
-    cudaError_t e = cudaMalloc(&l->d_blob, map_bytes + par_bytes + bar_bytes);
+    cudaError_t e = cudaMalloc(&l->d_blob, map_bytes + par_bytes + bar_bytes + xq_bytes);
+    if (e == cudaSuccess) {
+        uint8_t *xq_base = static_cast<uint8_t *>(l->d_blob) + map_bytes + par_bytes + bar_bytes;
+        for (uint32_t i = 0; i < count; ++i)
+            if (params[i].xq) params[i].xq = xq_base + (reinterpret_cast<uintptr_t>(params[i].xq) - 1u);
+    }
     if (e == cudaSuccess) e = cudaMemcpyAsync(l->d_blob, host, map_bytes + par_bytes, cudaMemcpyHostToDevice, stream);
     if (e == cudaSuccess) e = cudaMemsetAsync(static_cast<uint8_t *>(l->d_blob) + map_bytes + par_bytes, 0, bar_bytes, stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(stream);   // the host copy goes away below
@@ -2581,6 +2705,7 @@ cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs,
     l->count = count;
     l->ctas = static_cast<uint32_t>(t.ctas);
     l->M = M;
+    l->xq_pairs = xq_pairs;
     l->imma_small = tune.imma_small != 0 || M == 2u;
     *out = l;
     return cudaSuccess;
@@ -2592,6 +2717,7 @@ cudaError_t gemv_list_launch(const GemvList *l, const GemvTuning &tune, cudaStre
     list.maps = l->d_maps;
     list.count = l->count;
     list.grid_bar = l->d_bar;
+    list.xq_pairs = l->xq_pairs;
     const uint32_t gb = l->w0.group * l->w0.bits / 8u;
     const bool pdl = tune.pdl != 0;
     const bool im = l->imma_small;
