@@ -1058,8 +1058,9 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                      const __grid_constant__ CUtensorMap next_w, const __grid_constant__ CUtensorMap next_s,
                      const __grid_constant__ CUtensorMap next_b, const GemvOpList list) {
     using Geo = StreamGeom<GB>;
-    // launch lists with one activation row: activations quantised once per launch, streamed into the stages
-    constexpr bool XQS = NOPS == 0 && MD == 1 && !XF32;
+    // launch lists (one activation row on the dp4a instance, up to four on the int8-MMA instance): activations
+    // quantised once per launch, streamed into the stages
+    constexpr bool XQS = NOPS == 0 && (MD == 1 || MD == 4) && !XF32;
     using Plan = DpPlan<GB, MD, XF32, NST, BU, XQS>;
     constexpr int GPS = Geo::GPS, WPG = Plan::WPG;
     constexpr int RW = kRows * GPS / NCW;  // rows per warp: 128 (G=32), 64 (G=64), 32 (G=128)
@@ -1588,21 +1589,21 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         // arrive with its weights, stage by stage: no per-CTA rebuild, no CTA barrier between operations.
         if (list.xq_pairs != 0u) {
             constexpr int G = GB * 2, PER = G / 32;
-            // task = (pair, group of the unit): one warp each, dealt over all consumer warps of the grid
-            const uint32_t ntasks = list.xq_pairs * GPS, stride = gridDim.x * NCW;
+            // task = (pair, group of the unit, activation row): one warp each, dealt over all consumer warps of the grid
+            const uint32_t ntasks = list.xq_pairs * GPS * MD, stride = gridDim.x * NCW;
 #pragma unroll 1
             for (uint32_t task = blockIdx.x * NCW + warp; task < ntasks; task += stride) {
-                const uint32_t j = task / GPS, gl = task % GPS;
+                const uint32_t m = task % MD, gl = (task / MD) % GPS, j = task / (MD * GPS);
                 // the operation this pair belongs to (a few dozen operations at most: a linear search)
                 uint8_t *xq_base = nullptr;
                 const __nv_bfloat16 *qx = nullptr;
-                uint32_t kc = 0u, qgroups = 0u;
+                uint32_t kc = 0u, qgroups = 0u, qK = 0u, qM = 0u;
                 for (uint32_t oo = 0; oo < nops; ++oo) {
                     const GemvParams *qp = list.ops + oo;
                     uint8_t *b = qp->xq;
                     const uint32_t p0 = qp->xq_pair0, ch = qp->chunks;
                     if (b != nullptr && j >= p0 && j < p0 + ch) {
-                        xq_base = b, kc = j - p0, qgroups = qp->groups;
+                        xq_base = b, kc = j - p0, qgroups = qp->groups, qK = qp->K, qM = qp->M;
                         qx = static_cast<const __nv_bfloat16 *>(qp->x);
                         break;
                     }
@@ -1610,10 +1611,11 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                 if (xq_base == nullptr) continue;
                 uint8_t *dst = xq_base + static_cast<size_t>(kc) * Plan::XQS_UNIT;
                 const uint32_t gi = kc * GPS + gl;
+                const bool live = gi < qgroups && m < qM;   // rows the instance has room for but the call does not use: zeros
                 float xv[PER];
 #pragma unroll
                 for (int e = 0; e < PER; ++e)
-                    xv[e] = gi < qgroups ? __bfloat162float(qx[static_cast<size_t>(gi) * G + lane * PER + e]) : 0.f;
+                    xv[e] = live ? __bfloat162float(qx[static_cast<size_t>(m) * qK + static_cast<size_t>(gi) * G + lane * PER + e]) : 0.f;
                 uint32_t abits = 0u;
 #pragma unroll
                 for (int e = 0; e < PER; ++e) abits = max(abits, __float_as_uint(xv[e]) & 0x7FFFFFFFu);
@@ -1630,13 +1632,21 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                     isum += xi;
                     const uint32_t k = lane * PER + e;
                     const uint32_t wj = k >> 3, odd = k & 1u, bytepos = (k & 7u) >> 1;
-                    uint8_t *a = dst + gl * Plan::XQ_GROUP + wj * 16u + odd * 4u + bytepos;   // {even hi, odd hi, even lo, odd lo} x 4 bytes
-                    a[0] = static_cast<uint8_t>((xi >> 6) & 0xFF);
-                    a[8] = static_cast<uint8_t>(xi & 63);
+                    if constexpr (IM) {
+                        // B registers of MMA (wj % WPT) for the quad lane (wj / WPT): 8 bytes {even, odd} per (column, quad
+                        // lane), column 2m = hi limb, 2m + 1 = lo limb (the layout the per-CTA quantiser writes)
+                        uint8_t *a = dst + gl * Plan::XQ_GROUP + (wj % WPT) * 256u + ((2u * m) * 4u + wj / WPT) * 8u + odd * 4u + bytepos;
+                        a[0] = static_cast<uint8_t>((xi >> 6) & 0xFF);
+                        a[32] = static_cast<uint8_t>(xi & 63);
+                    } else {
+                        uint8_t *a = dst + gl * Plan::XQ_GROUP + (wj * MD + m) * 16u + odd * 4u + bytepos;   // {even hi, odd hi, even lo, odd lo} x 4 bytes
+                        a[0] = static_cast<uint8_t>((xi >> 6) & 0xFF);
+                        a[8] = static_cast<uint8_t>(xi & 63);
+                    }
                 }
                 isum = __reduce_add_sync(0xFFFFFFFFu, isum);
                 if (lane == 0)
-                    *reinterpret_cast<float2 *>(dst + Plan::XQ_UNIT + gl * 8u) = make_float2(down, static_cast<float>(isum) * down);
+                    *reinterpret_cast<float2 *>(dst + Plan::XQ_UNIT + (gl * MD + m) * 8u) = make_float2(down, static_cast<float>(isum) * down);
             }
             __threadfence();
             asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory");
@@ -1869,7 +1879,8 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         if constexpr (IM) {
             if (landed && exists) {
                 const uint32_t stage_off = stage * Plan::STAGE;
-                const uint32_t xq = xq_warp + (buf * BU + ub) * Plan::XQ_UNIT + lane * 8u;
+                const uint32_t xq = (opx ? ring + stage_off + Geo::STAGE_BYTES + gq * Plan::XQ_GROUP
+                                         : xq_warp + (buf * BU + ub) * Plan::XQ_UNIT) + lane * 8u;
                 uint32_t bfr[WPT][2];  // this group's B registers, kept for all row blocks
 #pragma unroll
                 for (int j = 0; j < WPT; ++j)
@@ -1877,7 +1888,8 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                 float ex, xs;  // activation row qt
                 asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];"
                              : "=f"(ex), "=f"(xs)
-                             : "r"(xi_warp + (buf * BU + ub) * Plan::XI_UNIT + qt * 8u));
+                             : "r"((opx ? ring + stage_off + Geo::STAGE_BYTES + Plan::XQ_UNIT + gq * MD * 8u
+                                        : xi_warp + (buf * BU + ub) * Plan::XI_UNIT) + qt * 8u));
                 const uint32_t sbo = (kc * GPS * 2u) & 15u;
 #pragma unroll
                 for (int rb = 0; rb < NRB; ++rb) {
@@ -2205,7 +2217,7 @@ template <int GB, int MD, bool XF32, int SD, int NCW, int NST, int BU, int NOPS 
 cudaError_t launch_dp4a(const GemvParams &p, const WeightView &w, const WeightView *next, uint32_t ctas, bool pdl,
                         cudaStream_t stream, const GemvParams *second = nullptr, const GemvOpList *list = nullptr) {
     auto kern = gaf_gemv_dp4a_kernel<GB, MD, XF32, SD, NCW, NST, BU, NOPS>;
-    using Plan = DpPlan<GB, MD, XF32, NST, BU, (NOPS == 0 && MD == 1 && !XF32)>;
+    using Plan = DpPlan<GB, MD, XF32, NST, BU, (NOPS == 0 && (MD == 1 || MD == 4) && !XF32)>;
     static bool configured[kMaxDevices] = {};
     if (cudaError_t e = opt_in_shared_memory(kern, Plan::TOTAL, configured); e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
@@ -2620,8 +2632,8 @@ cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs,
     // One activation row on the integer-dot instance: operations whose activations nothing in this launch writes get them
     // quantised once per launch into global memory, [K chunk][1 KB of limb bytes + {scale, sum} per group]
     const uint32_t gb0 = ws[0]->group * ws[0]->bits / 8u;
-    const size_t xqs_unit = 1024u + (gb0 ? (kChunkBytes / gb0) * 8u : 0u);
-    const bool use_xq = md == 1u && gb0 != 0u;
+    const size_t xqs_unit = (1024u + (gb0 ? (kChunkBytes / gb0) * 8u : 0u)) * md;   // per activation row the instance is built for
+    const bool use_xq = gb0 != 0u;
     size_t xq_bytes = 0;
     // (only where it measured faster than letting each CTA quantise the block or two it needs: operations that give
     // every CTA at least eight units, or at least four when a row of K does not fit one CTA's activation buffers, so
