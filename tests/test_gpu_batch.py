@@ -223,3 +223,40 @@ def test_recorded_host_batch_is_two_block_copies_around_one_launch(gaf, oracle):
             w.free()
     finally:
         c.close()
+
+
+@pytest.mark.parametrize("M", [1, 3])
+def test_full_grid_list_takes_its_activations_through_the_ring(gaf, ctx, oracle, M):
+    """Llama-3-8B FFN shapes on all SMs: every operation gives each CTA dozens of units, so the launch quantises the
+    activations once at its start and the copy warps stream them into the ring stages beside the weights (one
+    activation row: integer-dot instance; three: the int8-MMA instance with an unused fourth row).  Every output
+    against the oracle; same bits on every run."""
+    import torch
+    G = 64
+    shapes = [(28672, 4096), (4096, 14336), (6144, 4608)]
+    ws, xs, refs = [], [], []
+    for i, (N, K) in enumerate(shapes):
+        p, s, b = make_weights(oracle, N, K, G, 4, seed=700 + i)
+        xb, xf = make_x_bf16(oracle, M, K, seed=800 + i + M)
+        ws.append(gaf.Weight.from_host(ctx, p, s, b, G, 4))
+        xs.append(torch_bf16_from_bits(xb, "cuda:0"))
+        refs.append(oracle.matmul_f32(xf, p, s, b, G, 4))
+    ys = [torch.full((M, w.N), float("nan"), dtype=torch.bfloat16, device="cuda:0") for w in ws]
+    batch = gaf.Batch(ctx, ws, xs, ys)
+    assert batch.one_launch
+    first = None
+    for rep in range(4):
+        for y in ys:
+            y.fill_(float("nan"))
+        batch.run()
+        ctx.synchronize()
+        if first is None:
+            first = [y.clone() for y in ys]
+            for y, ref in zip(ys, refs):
+                assert rel_err(_f32(oracle, y), ref) <= TOL_BF16
+        else:
+            for y, f in zip(ys, first):
+                assert torch.equal(y, f), rep
+    batch.close()
+    for w in ws:
+        w.free()
