@@ -443,7 +443,7 @@ def run_single(args):
             ctx.set_option("prefetch_units", args.prefetch_units)
         xs, ys = make_io(M)
         with torch.cuda.stream(stream):
-            if args.separate or M > 4:
+            if args.separate or M > 8:
                 def step():
                     for i, (w, y) in enumerate(zip(wl, ys)):
                         gaf.hint_next_weight(ctx, wl[(i + 1) % len(wl)])
@@ -462,7 +462,7 @@ def run_single(args):
         ctx.synchronize()
         ms = e0.elapsed_time(e1) / args.steps
         nbytes = sum(launch_bytes(w.N, w.K, M) for w in wl)
-        print(json.dumps({"quick": True, "M": M, "mode": "separate" if (args.separate or M > 4) else "launch list",
+        print(json.dumps({"quick": True, "M": M, "mode": "separate" if (args.separate or M > 8) else "launch list",
                           "gbs": round(nbytes / ms / 1e6, 2), "ms_per_step": ms}))
         return
 
@@ -488,7 +488,7 @@ def run_single(args):
 
             ms, st, clk = time_graph(ctx, torch, stream, separate, args.steps, args.warmup, clocks=clocks)
             results[M] = {"ms_per_step": ms, "gbs": nbytes / ms / 1e6, "bytes": nbytes, "stats_ms": st, "clocks": clk}
-            if M <= 4:
+            if M <= 8:
                 b = gaf.Batch(ctx, wl, [xs[w.K] for w in wl], ys)
                 ms, st, clk = time_graph(ctx, torch, stream, b.run, args.steps, args.warmup, clocks=clocks)
                 lists[M] = {"independent": {"ms_per_step": ms, "gbs": nbytes / ms / 1e6, "stats_ms": st, "clocks": clk,

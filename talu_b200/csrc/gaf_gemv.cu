@@ -1030,13 +1030,14 @@ struct DpPlan {
     static constexpr int XQ_UNIT = GPS * XQ_GROUP;         // 1 KB per activation row for any group size
     static constexpr int XI_UNIT = GPS * MD * 8;           // {2^(E-12), sum x} per group and activation row
     static constexpr int OUT_BUF = GPS * kRows * MD * 4;   // per-group partial sums of one row group
+    static constexpr int NOB = MD > 4 ? 1 : 2;             // hand-over buffers to the writer warp (32 KB each at eight rows)
     // XQS: a stage also holds the unit's quantised activations (copied from global memory like the weights)
     static constexpr int XQS_UNIT = XQ_UNIT + XI_UNIT;     // a multiple of 16 bytes
     static constexpr int STAGE = XQS ? ((StreamGeom<GB>::STAGE_BYTES + XQS_UNIT + 1023) / 1024) * 1024 : StreamGeom<GB>::STAGE_BYTES;
     static constexpr int OFF_XQ = NST * STAGE;
     static constexpr int OFF_XI = OFF_XQ + 2 * BU * XQ_UNIT;
     static constexpr int OFF_OUT = OFF_XI + 2 * BU * XI_UNIT;
-    static constexpr int TOTAL = OFF_OUT + 2 * OUT_BUF + 1024;
+    static constexpr int TOTAL = OFF_OUT + NOB * OUT_BUF + 1024;
 };
 
 // NCW consumer warps, NST ring stages, BU units per activation block.  (A configuration with 8 warps and 2
@@ -1060,13 +1061,15 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
     using Geo = StreamGeom<GB>;
     // launch lists (one activation row on the dp4a instance, up to four on the int8-MMA instance): activations
     // quantised once per launch, streamed into the stages
-    constexpr bool XQS = NOPS == 0 && (MD == 1 || MD == 4) && !XF32;
+    constexpr bool XQS = NOPS == 0 && (MD == 1 || MD >= 4) && !XF32;
     using Plan = DpPlan<GB, MD, XF32, NST, BU, XQS>;
     constexpr int GPS = Geo::GPS, WPG = Plan::WPG;
     constexpr int RW = kRows * GPS / NCW;  // rows per warp: 128 (G=32), 64 (G=64), 32 (G=128)
     constexpr int R = RW / 32;                        // rows per lane
     constexpr int CH = GB / 16;                       // 16-byte chunks per group and row
-    constexpr bool IM = MD == 4;                      // three or four activation rows: int8 MMA instead of dp4a
+    constexpr bool IM = MD >= 4;                      // three to eight activation rows: int8 MMA instead of dp4a
+    constexpr int NB = IM ? MD / 4 : 1;               // IM: sets of eight B columns (four activation rows x two limbs each)
+    constexpr int MQ = MD > 4 ? 4 : MD;               // writer: activation rows handled together when it polls for partial sums
     constexpr int WPT = GB / 16;                      // IM: packed words per quad lane, group and row = MMAs per group
     constexpr int NRB = RW / 16;                      // IM: 16-row blocks per warp
     static_assert(R >= 1 && GPS <= NCW && GPS * (kRows / RW) == NCW, "unsupported group size");
@@ -1235,7 +1238,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         // of this CTA's row groups are pushed, it waits for the peers' words of the same row groups, adds the
         // ranks in rank order and writes y.  Early row groups therefore cross NVLink while later ones are
         // still being computed.
-        const bool fused = p.fuse_size != 0u;
+        const bool fused = MD <= 4 && p.fuse_size != 0u;   // (the sum over ranks rides in launches of up to four rows)
         uint8_t *my_region = fused ? p.fuse_region[p.fuse_rank] : nullptr;
         uint32_t *fctl = reinterpret_cast<uint32_t *>(my_region + kFusedCtlOff);  // {epoch, done}
         uint32_t fepoch = 0u, fphase = 0u;
@@ -1266,6 +1269,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         // the split-K words above, and as the "LL" protocols of collective libraries).
         // wait for every rank's words of row group rg, add them in rank order, write y
         auto finish = [&](const FusedOp &f, uint32_t rg) {
+            if constexpr (MD <= 4) {
             const unsigned long long *data = reinterpret_cast<const unsigned long long *>(
                 f.region + kFusedDataOff + static_cast<size_t>(f.phase) * kPeerMaxRanks * kPeerSlotBytes);
             float acc[4][MD];
@@ -1323,6 +1327,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                             static_cast<__nv_bfloat16 *>(f.y)[static_cast<size_t>(m) * f.N + n] = __float2bfloat16_rn(acc[i][m]);
                     }
                 }
+            }
         };
         const FusedOp cur = {p.y, my_region, p.N, p.M, p.y_f32, p.fuse_size, fepoch, fphase};
         // final sums of row group rg (this rank's share of K): to y, or to the peers
@@ -1378,6 +1383,22 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const uint32_t row = lane + 32u * i;
+                if constexpr (MD > 4) {
+                    // four activation rows per load; groups added in the same fixed order
+#pragma unroll
+                    for (int m4 = 0; m4 < MD; m4 += 4) {
+                        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+                        for (int gq = 0; gq < GPS; ++gq) {
+                            float v0, v1, v2, v3;
+                            asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
+                                         : "=f"(v0), "=f"(v1), "=f"(v2), "=f"(v3)
+                                         : "r"(obuf + ((gq * kRows + row) * MD + m4) * 4u));
+                            a0 += v0, a1 += v1, a2 += v2, a3 += v3;
+                        }
+                        sum[i][m4] = a0, sum[i][m4 + 1] = a1, sum[i][m4 + 2] = a2, sum[i][m4 + 3] = a3;
+                    }
+                } else {
 #pragma unroll
                 for (int m = 0; m < MD; ++m) {
                     float a = 0.f;
@@ -1388,6 +1409,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                         a += v;
                     }
                     sum[i][m] = a;
+                }
                 }
             }
             __syncwarp();
@@ -1416,15 +1438,17 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                         bool got = true;
                         for (uint32_t sidx = 1; sidx < slots && got; ++sidx) {  // fixed order: reproducible sums
                             unsigned long long *src = slots_base + static_cast<size_t>(sidx) * (kRows * MD);
-                            unsigned long long word[4][MD];
+#pragma unroll
+                            for (int cb = 0; cb < MD / MQ; ++cb) {   // MQ activation rows at a time (register budget)
+                            unsigned long long word[4][MQ];
                             got = false;
                             for (uint32_t it = 0; it < kWaitLimit; ++it) {
                                 bool all = true;
 #pragma unroll
                                 for (int i = 0; i < 4; ++i)
 #pragma unroll
-                                    for (int m = 0; m < MD; ++m) {
-                                        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(word[i][m]) : "l"(src + (lane + 32u * i) * MD + m) : "memory");
+                                    for (int m = 0; m < MQ; ++m) {
+                                        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(word[i][m]) : "l"(src + (lane + 32u * i) * MD + cb * MQ + m) : "memory");
                                         all = all && static_cast<uint32_t>(word[i][m] >> 32) == kTag;
                                     }
                                 if (__all_sync(0xFFFFFFFFu, all)) {
@@ -1440,10 +1464,11 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
 #pragma unroll
                             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                                for (int m = 0; m < MD; ++m) {
-                                    sum[i][m] += __uint_as_float(static_cast<uint32_t>(word[i][m]));
-                                    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(src + (lane + 32u * i) * MD + m), "l"(0ull) : "memory");
+                                for (int m = 0; m < MQ; ++m) {
+                                    sum[i][cb * MQ + m] += __uint_as_float(static_cast<uint32_t>(word[i][m]));
+                                    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(src + (lane + 32u * i) * MD + cb * MQ + m), "l"(0ull) : "memory");
                                 }
+                            }
                         }
                         if (got) emit(rg, sum);
                     }
@@ -1476,8 +1501,12 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                     }
                 }
             }
-            ob ^= 1u;
-            if (ob == 0u) ophase ^= 1u;
+            if constexpr (Plan::NOB == 2) {
+                ob ^= 1u;
+                if (ob == 0u) ophase ^= 1u;
+            } else {
+                ophase ^= 1u;
+            }
         }
         // this CTA's share of operation `op`'s output is stored (or handed to the head owner, who stores it
         // before it arrives here itself): arrive at the operation's grid-wide counter.  After the last
@@ -1565,7 +1594,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
     const uint32_t qg = lane >> 2, qt = lane & 3;
     const uint32_t wr = rho<GB / 4>(qg);
     uint32_t aoff[IM ? NRB : 1], sbim[IM ? NRB : 1];
-    float yim[IM ? NRB : 1][2];
+    float yim[IM ? NRB : 1][2 * NB];
     if constexpr (IM) {
 #pragma unroll
         for (int rb = 0; rb < NRB; ++rb) {
@@ -1574,7 +1603,8 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
             const uint32_t pnl = obyte / kPanelBytes, inp = obyte % kPanelBytes;
             aoff[rb] = ring + pnl * kPanelSize + row * kPanelBytes + ((((inp >> 4) ^ row) & 7u) << 4) + (inp & 15u);
             sbim[rb] = ring + kWeightBytes + row * Geo::SBOX + gq * 2u;
-            yim[rb][0] = yim[rb][1] = 0.f;
+#pragma unroll
+            for (int c2 = 0; c2 < 2 * NB; ++c2) yim[rb][c2] = 0.f;
         }
     }
 
@@ -1635,7 +1665,8 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                     if constexpr (IM) {
                         // B registers of MMA (wj % WPT) for the quad lane (wj / WPT): 8 bytes {even, odd} per (column, quad
                         // lane), column 2m = hi limb, 2m + 1 = lo limb (the layout the per-CTA quantiser writes)
-                        uint8_t *a = dst + gl * Plan::XQ_GROUP + (wj % WPT) * 256u + ((2u * m) * 4u + wj / WPT) * 8u + odd * 4u + bytepos;
+                        uint8_t *a = dst + gl * Plan::XQ_GROUP + ((wj % WPT) * NB + m / 4u) * 256u + ((2u * (m % 4u)) * 4u + wj / WPT) * 8u +
+                                     odd * 4u + bytepos;
                         a[0] = static_cast<uint8_t>((xi >> 6) & 0xFF);
                         a[32] = static_cast<uint8_t>(xi & 63);
                     } else {
@@ -1752,7 +1783,8 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                 isum = __reduce_add_sync(gmask, isum);
                 if (id < ntask) {
                     const uint32_t qb = ring + Plan::OFF_XQ + (buf * BU + ubk) * Plan::XQ_UNIT + gl * Plan::XQ_GROUP;
-                    const uint32_t a = qb + (wd % WPT) * 256u + ((2u * m) * 4u + wd / WPT) * 8u;
+                    // MMA (wd % WPT), column set m / 4: 256 bytes = 8 columns x 4 quad lanes x {even, odd} words
+                    const uint32_t a = qb + ((wd % WPT) * NB + m / 4u) * 256u + ((2u * (m % 4u)) * 4u + wd / WPT) * 8u;
                     asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a), "r"(ehi), "r"(ohi) : "memory");
                     asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a + 32u), "r"(elo), "r"(olo) : "memory");
                     if (wd == 0u) {
@@ -1826,7 +1858,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                 if constexpr (IM) {
                     // B registers of MMA (wj % WPT) for the quad lane (wj / WPT): 8 bytes {even, odd} per
                     // (column, quad lane), column 2m = hi limb, 2m + 1 = lo limb
-                    const uint32_t a = qb + (wj % WPT) * 256u + ((2u * m) * 4u + wj / WPT) * 8u + odd * 4u + bytepos;
+                    const uint32_t a = qb + ((wj % WPT) * NB + m / 4u) * 256u + ((2u * (m % 4u)) * 4u + wj / WPT) * 8u + odd * 4u + bytepos;
                     asm volatile("st.shared.u8 [%0], %1;" ::"r"(a), "r"(hi & 0xFF) : "memory");
                     asm volatile("st.shared.u8 [%0], %1;" ::"r"(a + 32u), "r"(lo & 0xFF) : "memory");
                 } else {
@@ -1881,26 +1913,35 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                 const uint32_t stage_off = stage * Plan::STAGE;
                 const uint32_t xq = (opx ? ring + stage_off + Geo::STAGE_BYTES + gq * Plan::XQ_GROUP
                                          : xq_warp + (buf * BU + ub) * Plan::XQ_UNIT) + lane * 8u;
-                uint32_t bfr[WPT][2];  // this group's B registers, kept for all row blocks
+                uint32_t bfr[NB][WPT][2];  // this group's B registers, kept for all row blocks
 #pragma unroll
-                for (int j = 0; j < WPT; ++j)
-                    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(bfr[j][0]), "=r"(bfr[j][1]) : "r"(xq + j * 256u));
-                float ex, xs;  // activation row qt
-                asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];"
-                             : "=f"(ex), "=f"(xs)
-                             : "r"((opx ? ring + stage_off + Geo::STAGE_BYTES + Plan::XQ_UNIT + gq * MD * 8u
-                                        : xi_warp + (buf * BU + ub) * Plan::XI_UNIT) + qt * 8u));
+                for (int cs = 0; cs < NB; ++cs)
+#pragma unroll
+                    for (int j = 0; j < WPT; ++j)
+                        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(bfr[cs][j][0]), "=r"(bfr[cs][j][1]) : "r"(xq + (j * NB + cs) * 256u));
+                float ex[NB], xs[NB];  // activation rows 4 cs + qt
+#pragma unroll
+                for (int cs = 0; cs < NB; ++cs)
+                    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];"
+                                 : "=f"(ex[cs]), "=f"(xs[cs])
+                                 : "r"((opx ? ring + stage_off + Geo::STAGE_BYTES + Plan::XQ_UNIT + gq * MD * 8u
+                                            : xi_warp + (buf * BU + ub) * Plan::XI_UNIT) + (cs * 4u + qt) * 8u));
                 const uint32_t sbo = (kc * GPS * 2u) & 15u;
 #pragma unroll
                 for (int rb = 0; rb < NRB; ++rb) {
                     uint32_t wa[WPT], wb[WPT];
                     lds_row<WPT>(stage_off + aoff[rb], wr, wa);
                     lds_row<WPT>(stage_off + aoff[rb] + 8u * kPanelBytes, wr, wb);
-                    int c[4] = {0, 0, 0, 0};
+                    int c[NB][4];
 #pragma unroll
-                    for (int j = 0; j < WPT; ++j)
-                        mma_u8s8_16832(c, wa[j] & 0x0F0F0F0Fu, wb[j] & 0x0F0F0F0Fu, (wa[j] >> 4) & 0x0F0F0F0Fu,
-                                       (wb[j] >> 4) & 0x0F0F0F0Fu, bfr[j][0], bfr[j][1]);
+                    for (int cs = 0; cs < NB; ++cs) c[cs][0] = c[cs][1] = c[cs][2] = c[cs][3] = 0;
+#pragma unroll
+                    for (int j = 0; j < WPT; ++j) {
+                        const uint32_t a0 = wa[j] & 0x0F0F0F0Fu, a1 = wb[j] & 0x0F0F0F0Fu;
+                        const uint32_t a2 = (wa[j] >> 4) & 0x0F0F0F0Fu, a3 = (wb[j] >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+                        for (int cs = 0; cs < NB; ++cs) mma_u8s8_16832(c[cs], a0, a1, a2, a3, bfr[cs][j][0], bfr[cs][j][1]);
+                    }
                     uint16_t s0r, b0r, s1r, b1r;
                     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s0r) : "r"(stage_off + sbim[rb] + sbo));
                     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(b0r) : "r"(stage_off + sbim[rb] + sbo + Geo::SB_BYTES));
@@ -1909,8 +1950,11 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                     const float s0 = sb_half<SD>(s0r, 0), b0 = sb_half<SD>(b0r, 0);
                     const float s1 = sb_half<SD>(s1r, 0), b1 = sb_half<SD>(b1r, 0);
                     // columns 2 qt (hi) and 2 qt + 1 (lo): y += s 2^(E-12) (64 hi + lo) + b 2^(E-12) sum(xi)
-                    yim[rb][0] = fmaf(limbs_to_float(c[0], c[1]), s0 * ex, fmaf(b0, xs, yim[rb][0]));
-                    yim[rb][1] = fmaf(limbs_to_float(c[2], c[3]), s1 * ex, fmaf(b1, xs, yim[rb][1]));
+#pragma unroll
+                    for (int cs = 0; cs < NB; ++cs) {
+                        yim[rb][2 * cs] = fmaf(limbs_to_float(c[cs][0], c[cs][1]), s0 * ex[cs], fmaf(b0, xs[cs], yim[rb][2 * cs]));
+                        yim[rb][2 * cs + 1] = fmaf(limbs_to_float(c[cs][2], c[cs][3]), s1 * ex[cs], fmaf(b1, xs[cs], yim[rb][2 * cs + 1]));
+                    }
                 }
             }
         } else
@@ -1986,9 +2030,12 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
 #pragma unroll
                     for (int rb = 0; rb < NRB; ++rb) {
                         const uint32_t row = rbase + rb * 16u + wr;
-                        asm volatile("st.shared.f32 [%0], %1;" ::"r"(out_warp + ob * Plan::OUT_BUF + (row * MD + qt) * 4u), "f"(yim[rb][0]) : "memory");
-                        asm volatile("st.shared.f32 [%0], %1;" ::"r"(out_warp + ob * Plan::OUT_BUF + ((row + 8u) * MD + qt) * 4u), "f"(yim[rb][1]) : "memory");
-                        yim[rb][0] = yim[rb][1] = 0.f;
+#pragma unroll
+                        for (int cs = 0; cs < NB; ++cs) {
+                            asm volatile("st.shared.f32 [%0], %1;" ::"r"(out_warp + ob * Plan::OUT_BUF + (row * MD + cs * 4u + qt) * 4u), "f"(yim[rb][2 * cs]) : "memory");
+                            asm volatile("st.shared.f32 [%0], %1;" ::"r"(out_warp + ob * Plan::OUT_BUF + ((row + 8u) * MD + cs * 4u + qt) * 4u), "f"(yim[rb][2 * cs + 1]) : "memory");
+                            yim[rb][2 * cs] = yim[rb][2 * cs + 1] = 0.f;
+                        }
                     }
                 } else {
 #pragma unroll
@@ -2003,8 +2050,12 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&s_out_full[ob]));
             }
-            ob ^= 1u;
-            if (ob == 0u) ophase ^= 1u;
+            if constexpr (Plan::NOB == 2) {
+                ob ^= 1u;
+                if (ob == 0u) ophase ^= 1u;
+            } else {
+                ophase ^= 1u;
+            }
 #pragma unroll
             for (int i = 0; i < R; ++i)
 #pragma unroll
@@ -2217,7 +2268,7 @@ template <int GB, int MD, bool XF32, int SD, int NCW, int NST, int BU, int NOPS 
 cudaError_t launch_dp4a(const GemvParams &p, const WeightView &w, const WeightView *next, uint32_t ctas, bool pdl,
                         cudaStream_t stream, const GemvParams *second = nullptr, const GemvOpList *list = nullptr) {
     auto kern = gaf_gemv_dp4a_kernel<GB, MD, XF32, SD, NCW, NST, BU, NOPS>;
-    using Plan = DpPlan<GB, MD, XF32, NST, BU, (NOPS == 0 && (MD == 1 || MD == 4) && !XF32)>;
+    using Plan = DpPlan<GB, MD, XF32, NST, BU, (NOPS == 0 && (MD == 1 || MD >= 4) && !XF32)>;
     static bool configured[kMaxDevices] = {};
     if (cudaError_t e = opt_in_shared_memory(kern, Plan::TOTAL, configured); e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
@@ -2254,6 +2305,13 @@ cudaError_t dispatch_list(const GemvParams &first, const WeightView &w0, const G
     if (M == 3 || M == 4)
         return bf ? launch_dp4a<GB, 4, false, 1, kConsumerWarps, 3, (GB == 16 ? 4 : 8), 0>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list)
                   : launch_dp4a<GB, 4, false, 0, kConsumerWarps, 3, (GB == 16 ? 4 : 8), 0>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list);
+    if constexpr (GB != 16) {
+        // five to eight rows: two sets of MMA columns; activation blocks of two units for the operations that still
+        // quantise per CTA, one hand-over buffer to the writer warp
+        if (M >= 5 && M <= 8)
+            return bf ? launch_dp4a<GB, 8, false, 1, kConsumerWarps, 3, 2, 0>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list)
+                      : launch_dp4a<GB, 8, false, 0, kConsumerWarps, 3, 2, 0>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list);
+    }
     return cudaErrorNotSupported;
 }
 
@@ -2567,11 +2625,19 @@ cudaError_t gemv_ffn_swiglu(const WeightView &w1, const WeightView &w2, const vo
 // The caller fills `params` / `maps` (host arrays of `count` / 3 * count entries) through gemv_list_plan, copies them
 // to the device once, and launches with gemv_list_launch as often as it likes.
 // ---------------------------------------------------------------------------
+// activation rows the list's kernel instance is built for: 1 (integer dot products), 4 or 8 (int8 MMA; two rows run
+// on the four-row instance, which measured faster in a list than the two-row dot-product one)
+static uint32_t list_instance_rows(uint32_t M, const GemvTuning &tune) {
+    if (M == 1u && !tune.imma_small) return 1u;
+    return M <= 4u ? 4u : 8u;
+}
+
 bool gemv_list_eligible(const WeightView *const *ws, uint32_t count, uint32_t M, const GemvTuning &tune) {
-    if (count == 0u || count > 256u || M == 0u || M > 4u || tune.no_dp4a || tune.force_generic) return false;
+    if (count == 0u || count > 256u || M == 0u || M > 8u || tune.no_dp4a || tune.force_generic) return false;
     const WeightView &w0 = *ws[0];
     const uint32_t gb0 = w0.group * w0.bits / 8u;
     if (gb0 != 16u && gb0 != 32u && gb0 != 64u) return false;
+    if (M > 4u && gb0 == 16u) return false;   // five to eight rows: groups of 64 and 128 codes only (shared memory)
     for (uint32_t i = 0; i < count; ++i) {
         const WeightView &w = *ws[i];
         if (w.bits != 4u || w.group != w0.group || w.sdtype != w0.sdtype || !w.has_tmap) return false;
@@ -2593,7 +2659,7 @@ uint32_t gemv_list_ctas(const WeightView *const *ws, uint32_t count, const GemvT
 size_t gemv_list_tagged_words(const WeightView *const *ws, uint32_t count, uint32_t M, const GemvTuning &tune, int sm_count) {
     GemvTuning t = tune;
     t.ctas = static_cast<int>(gemv_list_ctas(ws, count, tune, sm_count));
-    const uint32_t md = (M == 1u && !tune.imma_small) ? M : 4u;   // two rows: the int8-MMA instance measured faster in a list
+    const uint32_t md = list_instance_rows(M, tune);
     size_t words = 0;
     for (uint32_t i = 0; i < count; ++i) {
         const GemvPlan pl = plan_gemv(*ws[i], t, sm_count);
@@ -2625,7 +2691,7 @@ cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs,
     if (!gemv_list_eligible(ws, count, M, tune)) return cudaErrorNotSupported;
     GemvTuning t = tune;
     t.ctas = static_cast<int>(gemv_list_ctas(ws, count, tune, sm_count));
-    const uint32_t md = (M == 1u && !tune.imma_small) ? M : 4u;   // two rows: the int8-MMA instance measured faster in a list
+    const uint32_t md = list_instance_rows(M, tune);
     const size_t map_bytes = static_cast<size_t>(count) * 3u * sizeof(CUtensorMap);
     const size_t par_bytes = (static_cast<size_t>(count) * sizeof(GemvParams) + 255u) & ~size_t(255);
     const size_t bar_bytes = (static_cast<size_t>(count + 1u) * sizeof(unsigned int) + 255u) & ~size_t(255);   // + the activations counter

@@ -153,7 +153,7 @@ def _time_stack(ctx, torch, dist, world, stream, stack, M, steps, warmup, min_se
                 gaf.linear(ctx, w, x, out=y)
 
     out = {"separate": None, "no_reduce_ms": None}
-    if M <= 4:
+    if M <= 4 or (M <= 8 and not any(stack.reduce)):
         batch = gaf.Batch(ctx, ws, xs, ys, reduce=stack.reduce if any(stack.reduce) else None)
         out["submission"] = ("one launch list per step (tgaf_batch_run), one kernel launch" if batch.one_launch
                              else "tgaf_batch_run, its calls one after the other")

@@ -26,7 +26,7 @@ def _f32(oracle, t):
     return oracle.bf16_to_f32(bits_from_torch_bf16(t))
 
 
-@pytest.mark.parametrize("M", [1, 2, 4])
+@pytest.mark.parametrize("M", [1, 2, 4, 5, 8])
 def test_independent_list_in_one_launch(gaf, ctx, oracle, M):
     """Six weights of different shapes (ragged N, K below and above one activation block, a K that is split over many
     CTAs), each with its own activations: one launch, every output against the oracle and the one-by-one calls."""
@@ -225,7 +225,7 @@ def test_recorded_host_batch_is_two_block_copies_around_one_launch(gaf, oracle):
         c.close()
 
 
-@pytest.mark.parametrize("M", [1, 3])
+@pytest.mark.parametrize("M", [1, 3, 7])
 def test_full_grid_list_takes_its_activations_through_the_ring(gaf, ctx, oracle, M):
     """Llama-3-8B FFN shapes on all SMs: every operation gives each CTA dozens of units, so the launch quantises the
     activations once at its start and the copy warps stream them into the ring stages beside the weights (one
