@@ -2689,6 +2689,11 @@ cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs,
                              GemvList **out) {
     *out = nullptr;
     if (!gemv_list_eligible(ws, count, M, tune)) return cudaErrorNotSupported;
+    // five to eight rows: an operation that reads what the launch writes would quantise per CTA in blocks of two units
+    // (that is all the shared memory left beside the eight-row stages), which measured slower than separate launches
+    if (M > 4u && deps)
+        for (uint32_t i = 0; i < count; ++i)
+            if (deps[i]) return cudaErrorNotSupported;
     GemvTuning t = tune;
     t.ctas = static_cast<int>(gemv_list_ctas(ws, count, tune, sm_count));
     const uint32_t md = list_instance_rows(M, tune);
