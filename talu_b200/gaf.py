@@ -293,7 +293,7 @@ def linear_host(ctx: Context, w: Weight, x: np.ndarray, out: np.ndarray | None =
 class Batch:
     """A launch list of device-buffer linears (tgaf_batch_*): `count` operations y_i = x_i @ W_i^T with the same
     number of rows, run by ONE call (one kernel launch when every weight is gaf4 of one scheme and M <= 8; M <= 4 for
-    groups of 32 codes and for lists with sums over the ranks).
+    groups of 32 codes and for lists with sums over the ranks or dependent operations).
     depends[i]: x_i is written by an earlier operation of the list; reduce[i]: y_i is summed over the ranks."""
 
     def __init__(self, ctx: Context, weights, xs, ys, depends=None, reduce=None):
