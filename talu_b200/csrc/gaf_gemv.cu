@@ -180,15 +180,6 @@ __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap *tmap, uint32_
                  : "memory");
 }
 
-// flag words other GPUs write / read (fused all-reduce)
-__device__ __forceinline__ void st_release_sys_u32(uint32_t *p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 constexpr uint32_t kPeerPollLimit = 1u << 23;  // polls with back-off (several seconds) before a rank gives up on a peer
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -2295,13 +2286,10 @@ cudaError_t dispatch_list(const GemvParams &first, const WeightView &w0, const G
                           bool pdl, cudaStream_t stream, bool imma_small) {
     const bool bf = first.sdtype == 1u;
     constexpr int NST1 = GB == 16 ? 3 : 4;
-    if (imma_small && M <= 2) M = 4;   // the int8-MMA instance (built for four rows) with fewer rows in use
+    if ((imma_small && M == 1) || M == 2) M = 4;   // the int8-MMA instance (built for four rows) with fewer rows in use
     if (M == 1)
         return bf ? launch_dp4a<GB, 1, false, 1, kConsumerWarps, NST1, 8, 0>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list)
                   : launch_dp4a<GB, 1, false, 0, kConsumerWarps, NST1, 8, 0>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list);
-    if (M == 2)
-        return bf ? launch_dp4a<GB, 2, false, 1, kConsumerWarps, 3, 8, 0>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list)
-                  : launch_dp4a<GB, 2, false, 0, kConsumerWarps, 3, 8, 0>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list);
     if (M == 3 || M == 4)
         return bf ? launch_dp4a<GB, 4, false, 1, kConsumerWarps, 3, (GB == 16 ? 4 : 8), 0>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list)
                   : launch_dp4a<GB, 4, false, 0, kConsumerWarps, 3, (GB == 16 ? 4 : 8), 0>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list);
