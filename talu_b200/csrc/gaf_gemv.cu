@@ -1013,11 +1013,12 @@ __device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
     return d;
 }
 
-template <int GB, int MD, bool XF32, int NST, int BU, bool XQS = false>
+template <int GB, int MD, bool XF32, int NST, int BU, bool XQS = false, int BITS = 4>
 struct DpPlan {
     static constexpr int GPS = kChunkBytes / GB;           // groups per unit
     static constexpr int WPG = GB / 4;                     // packed words per group and row
-    static constexpr int XQ_GROUP = WPG * MD * 16;         // quantised activations of one group: 16 bytes per word and row
+    // quantised activations of one group: per word and row 16 bytes (eight 4-bit codes x {hi, lo}) or 8 (four 8-bit codes)
+    static constexpr int XQ_GROUP = WPG * MD * (BITS == 4 ? 16 : 8);
     static constexpr int XQ_UNIT = GPS * XQ_GROUP;         // 1 KB per activation row for any group size
     static constexpr int XI_UNIT = GPS * MD * 8;           // {2^(E-12), sum x} per group and activation row
     static constexpr int OUT_BUF = GPS * kRows * MD * 4;   // per-group partial sums of one row group
@@ -1043,7 +1044,7 @@ struct DpPlan {
 // decoder step without a pause, an operation waits at the arrival counter of its predecessor only when its
 // activations are that predecessor's output (GemvParams::dep), and the per-launch costs (launch gap, ring ramp-up
 // and drain, write-out tail) are paid once per list instead of once per weight.
-template <int GB, int MD, bool XF32, int SD, int NCW, int NST, int BU, int NOPS>
+template <int GB, int MD, bool XF32, int SD, int NCW, int NST, int BU, int NOPS, int BITS>
 __global__ void __launch_bounds__((NCW + 2) * 32, 1)
 gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_constant__ CUtensorMap tmap_w,
                      const __grid_constant__ CUtensorMap tmap_s, const __grid_constant__ CUtensorMap tmap_b,
@@ -1053,7 +1054,8 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
     // launch lists (one activation row on the dp4a instance, up to four on the int8-MMA instance): activations
     // quantised once per launch, streamed into the stages
     constexpr bool XQS = NOPS == 0 && (MD == 1 || MD >= 4) && !XF32;
-    using Plan = DpPlan<GB, MD, XF32, NST, BU, XQS>;
+    using Plan = DpPlan<GB, MD, XF32, NST, BU, XQS, BITS>;
+    static_assert(BITS == 4 || (BITS == 8 && MD <= 2), "8-bit codes: the integer dot-product form only (one or two rows)");
     constexpr int GPS = Geo::GPS, WPG = Plan::WPG;
     constexpr int RW = kRows * GPS / NCW;  // rows per warp: 128 (G=32), 64 (G=64), 32 (G=128)
     constexpr int R = RW / 32;                        // rows per lane
@@ -1609,7 +1611,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         // warps wait for that counter before their first copy of such a unit.  Afterwards an operation's activations
         // arrive with its weights, stage by stage: no per-CTA rebuild, no CTA barrier between operations.
         if (list.xq_pairs != 0u) {
-            constexpr int G = GB * 2, PER = G / 32;
+            constexpr int G = GB * 8 / BITS, PER = G / 32;
             // task = (pair, group of the unit, activation row): one warp each, dealt over all consumer warps of the grid
             const uint32_t ntasks = list.xq_pairs * GPS * MD, stride = gridDim.x * NCW;
 #pragma unroll 1
@@ -1660,6 +1662,10 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                                      odd * 4u + bytepos;
                         a[0] = static_cast<uint8_t>((xi >> 6) & 0xFF);
                         a[32] = static_cast<uint8_t>(xi & 63);
+                    } else if constexpr (BITS == 8) {
+                        uint8_t *a = dst + gl * Plan::XQ_GROUP + ((k >> 2) * MD + m) * 8u + (k & 3u);   // {hi, lo} x 4 bytes per word of four codes
+                        a[0] = static_cast<uint8_t>((xi >> 6) & 0xFF);
+                        a[4] = static_cast<uint8_t>(xi & 63);
                     } else {
                         uint8_t *a = dst + gl * Plan::XQ_GROUP + (wj * MD + m) * 16u + odd * 4u + bytepos;   // {even hi, odd hi, even lo, odd lo} x 4 bytes
                         a[0] = static_cast<uint8_t>((xi >> 6) & 0xFF);
@@ -1786,7 +1792,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
             }
             return;
         }
-        constexpr int G = GB * 2;                          // elements per group (4-bit codes)
+        constexpr int G = GB * 8 / BITS;                   // elements per group
         constexpr int PER = G / 32;                        // elements per lane: 1 (G=32), 2, 4
         constexpr int TPW = (BU * GPS * MD + NCW - 1) / NCW;  // triples per warp, at most
         float xv[TPW][PER];
@@ -1852,6 +1858,11 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                     const uint32_t a = qb + ((wj % WPT) * NB + m / 4u) * 256u + ((2u * (m % 4u)) * 4u + wj / WPT) * 8u + odd * 4u + bytepos;
                     asm volatile("st.shared.u8 [%0], %1;" ::"r"(a), "r"(hi & 0xFF) : "memory");
                     asm volatile("st.shared.u8 [%0], %1;" ::"r"(a + 32u), "r"(lo & 0xFF) : "memory");
+                } else if constexpr (BITS == 8) {
+                    // element k of the group -> word k / 4, byte k % 4: 8 bytes per (word, activation row): {hi, lo} x 4
+                    const uint32_t a = qb + ((k >> 2) * MD + m) * 8u + (k & 3u);
+                    asm volatile("st.shared.u8 [%0], %1;" ::"r"(a), "r"(hi & 0xFF) : "memory");
+                    asm volatile("st.shared.u8 [%0], %1;" ::"r"(a + 4u), "r"(lo & 0xFF) : "memory");
                 } else {
                     const uint32_t a = qb + (wj * MD + m) * 16u + odd * 4u + bytepos;
                     asm volatile("st.shared.u8 [%0], %1;" ::"r"(a), "r"(hi & 0xFF) : "memory");
@@ -1970,6 +1981,20 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                                     : xq_warp + (buf * BU + ub) * Plan::XQ_UNIT;
 #pragma unroll
             for (int j = 0; j < WPG; ++j) {
+                if constexpr (BITS == 8) {
+                    // a packed word IS four unsigned bytes: two dot products per word and row, no unpacking at all
+                    uint32_t x_hi[MD], x_lo[MD];
+#pragma unroll
+                    for (int m = 0; m < MD; ++m)
+                        asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(x_hi[m]), "=r"(x_lo[m]) : "r"(xq + (j * MD + m) * 8u));
+#pragma unroll
+                    for (int i = 0; i < R; ++i)
+#pragma unroll
+                        for (int m = 0; m < MD; ++m) {
+                            ahi[i][m] = dp4a_u8s8(w[i][j], x_hi[m], ahi[i][m]);
+                            alo[i][m] = dp4a_u8s8(w[i][j], x_lo[m], alo[i][m]);
+                        }
+                } else {
                 uint32_t xe_hi[MD], xo_hi[MD], xe_lo[MD], xo_lo[MD];
 #pragma unroll
                 for (int m = 0; m < MD; ++m)
@@ -1986,6 +2011,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                         alo[i][m] = dp4a_u8s8(even, xe_lo[m], alo[i][m]);
                         alo[i][m] = dp4a_u8s8(odd, xo_lo[m], alo[i][m]);
                     }
+                }
                 }
             }
             float ex[MD], xs[MD];
@@ -2255,11 +2281,11 @@ cudaError_t launch_stream(const GemvParams &p, const WeightView &w, const Weight
     return cudaLaunchKernelEx(&cfg, kern, p, w.tmap, w.tmap_s, w.tmap_b, nx.tmap, nx.tmap_s, nx.tmap_b);
 }
 
-template <int GB, int MD, bool XF32, int SD, int NCW, int NST, int BU, int NOPS = 1>
+template <int GB, int MD, bool XF32, int SD, int NCW, int NST, int BU, int NOPS = 1, int BITS = 4>
 cudaError_t launch_dp4a(const GemvParams &p, const WeightView &w, const WeightView *next, uint32_t ctas, bool pdl,
                         cudaStream_t stream, const GemvParams *second = nullptr, const GemvOpList *list = nullptr) {
-    auto kern = gaf_gemv_dp4a_kernel<GB, MD, XF32, SD, NCW, NST, BU, NOPS>;
-    using Plan = DpPlan<GB, MD, XF32, NST, BU, (NOPS == 0 && (MD == 1 || MD >= 4) && !XF32)>;
+    auto kern = gaf_gemv_dp4a_kernel<GB, MD, XF32, SD, NCW, NST, BU, NOPS, BITS>;
+    using Plan = DpPlan<GB, MD, XF32, NST, BU, (NOPS == 0 && (MD == 1 || MD >= 4) && !XF32), BITS>;
     static bool configured[kMaxDevices] = {};
     if (cudaError_t e = opt_in_shared_memory(kern, Plan::TOTAL, configured); e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
@@ -2331,6 +2357,21 @@ cudaError_t dispatch_dp4a(const GemvParams &p, const WeightView &w, const Weight
     if (M == 3 || M == 4)  // int8-MMA variant, three stages, activation blocks of eight units (four for 32-element groups)
         return bf ? launch_dp4a<GB, 4, false, 1, kConsumerWarps, 3, (GB == 16 ? 4 : 8)>(p, w, next, ctas, pdl, stream)
                   : launch_dp4a<GB, 4, false, 0, kConsumerWarps, 3, (GB == 16 ? 4 : 8)>(p, w, next, ctas, pdl, stream);
+    return cudaErrorNotSupported;
+}
+
+// 8-bit codes, one or two bf16 activation rows: the integer dot-product kernel on the bytes as they are
+// (groups of 32 and 64 codes: the row split of the kernel needs at least four groups per unit)
+template <int GB>
+cudaError_t dispatch_dp4a8(const GemvParams &p, const WeightView &w, const WeightView *next, uint32_t ctas, uint32_t M,
+                           bool pdl, cudaStream_t stream) {
+    const bool bf = p.sdtype == 1u;
+    if (M == 1)
+        return bf ? launch_dp4a<GB, 1, false, 1, kConsumerWarps, 4, 8, 1, 8>(p, w, next, ctas, pdl, stream)
+                  : launch_dp4a<GB, 1, false, 0, kConsumerWarps, 4, 8, 1, 8>(p, w, next, ctas, pdl, stream);
+    if (M == 2)
+        return bf ? launch_dp4a<GB, 2, false, 1, kConsumerWarps, 3, 8, 1, 8>(p, w, next, ctas, pdl, stream)
+                  : launch_dp4a<GB, 2, false, 0, kConsumerWarps, 3, 8, 1, 8>(p, w, next, ctas, pdl, stream);
     return cudaErrorNotSupported;
 }
 
@@ -2446,7 +2487,8 @@ size_t gemv_tagged_bytes(const WeightView &w, uint32_t M, bool x_f32, const Gemv
     if (M == 0u || M > 16u) return 0;
     const GemvPlan pl = plan_gemv(w, tune, sm_count);
     const uint32_t gb = w.group * w.bits / 8u;
-    const bool integer_path = w.bits == 4u && (M <= 4u) && !x_f32 && !tune.no_dp4a && gb != 0u;
+    const bool integer_path = ((w.bits == 4u && M <= 4u) || (w.bits == 8u && M <= 2u && (gb == 32u || gb == 64u))) && !x_f32 &&
+                              !tune.no_dp4a && gb != 0u;
     const uint32_t cols = integer_path ? (M <= 2u ? M : 4u) : (M <= 8u ? 8u : 16u);
     return static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * cols * 8u;
 }
@@ -2533,6 +2575,12 @@ cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bo
         if (gb == 16u) return dispatch_dp4a<16>(p, w, next, pl.ctas, M, pdl, stream);
         if (gb == 32u) return dispatch_dp4a<32>(p, w, next, pl.ctas, M, pdl, stream);
         if (gb == 64u) return dispatch_dp4a<64>(p, w, next, pl.ctas, M, pdl, stream);
+    }
+    if (w.bits == 8 && M <= 2u && !x_f32 && !tune.no_dp4a && (gb == 32u || gb == 64u)) {
+        if (scratch.tagged && static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * M * 8u <= scratch.tagged_bytes)
+            p.tagged = scratch.tagged;
+        if (gb == 32u) return dispatch_dp4a8<32>(p, w, next, pl.ctas, M, pdl, stream);
+        return dispatch_dp4a8<64>(p, w, next, pl.ctas, M, pdl, stream);
     }
     // tensor-core formulation: tagged partial sums [row group][slot][128][8 or 16] when the scratch has room
     if (scratch.tagged && static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * (mt * 8) * 8u <= scratch.tagged_bytes)

@@ -504,6 +504,28 @@ def test_prefill_cfg4_full_size(gaf, ctx, oracle):
     assert rel_err(got, ref) <= TOL_BF16, rel_err(got, ref)
 
 
+def test_8bit_codes_on_the_integer_dot_product_kernel(gaf, ctx, oracle):
+    """gaf8_32 / gaf8_64 at one and two bf16 activation rows run on the integer dot-product kernel (a packed word IS four
+    unsigned bytes): K split over many CTAs, ragged N, bf16 and f16 scale patterns; gaf8_128 stays on the tensor-core
+    GEMV.  rel <= 1e-2 against the oracle."""
+    rng = np.random.default_rng(5)
+    for N, K, G, M, f16 in [(2048, 4096, 64, 1, False), (1000, 8192, 32, 2, False), (4096, 14336, 64, 1, True),
+                            (520, 2048, 32, 1, True), (384, 1024, 128, 2, False)]:
+        p, s, b = make_weights(oracle, N, K, G, 8, seed=N + M)
+        sd_lib, sd_or = gaf.SCALES_BF16, oracle.SCALES_BF16
+        if f16:
+            s = (oracle.bf16_to_f32(s) * (1 + rng.uniform(0, 2 ** -8, s.shape))).astype(np.float16).view(np.uint16)
+            b = (oracle.bf16_to_f32(b) * (1 + rng.uniform(0, 2 ** -8, b.shape))).astype(np.float16).view(np.uint16)
+            sd_lib, sd_or = gaf.SCALES_F16, oracle.SCALES_F16
+        xb, xf = make_x_bf16(oracle, M, K, seed=M + 3)
+        w = gaf.Weight.from_host(ctx, p, s, b, G, 8, sdtype=sd_lib)
+        y = gaf.linear(ctx, w, torch_bf16_from_bits(xb, "cuda:0"))
+        ctx.synchronize()
+        ref = oracle.matmul_f32(xf, p, s, b, G, 8, sdtype=sd_or)
+        assert rel_err(oracle.bf16_to_f32(bits_from_torch_bf16(y)), ref) <= TOL_BF16, (N, K, G, M, f16)
+        w.free()
+
+
 def test_gemm_min_m_option_moves_the_hand_over(gaf, oracle):
     """"gemm_min_m" = the activation rows from which the tensor-core GEMM takes over from the decode GEMVs (default 17).
     With it lowered, M = 5, 8 and 16 run on the GEMM: same results within the same bound."""
