@@ -541,11 +541,11 @@ def run_single(args):
             ms, st, _ = time_graph(ctx, torch, stream, sep, args.steps, args.warmup, min_seconds=0.3, clocks=clocks)
             out = {"gemvs": n, "ring_gb": round(n * per / 1e9, 3),
                    "separate_launches": {**frac(nb / ms / 1e6), "us_per_gemv": round(ms * 1e3 / n, 3), "stats_ms": st}}
-            if bits == 4 and M <= 4:
-                b_ = gaf.Batch(ctx, ws_, [x] * n, ys_)
+            b_ = gaf.Batch(ctx, ws_, [x] * n, ys_)
+            if b_.one_launch:
                 ms, st, _ = time_graph(ctx, torch, stream, b_.run, args.steps, args.warmup, min_seconds=0.3, clocks=clocks)
                 out["launch_list"] = {**frac(nb / ms / 1e6), "us_per_gemv": round(ms * 1e3 / n, 3), "stats_ms": st}
-                b_.close()
+            b_.close()
             for w in ws_:
                 w.free()
             return out

@@ -211,7 +211,8 @@ int32_t tgaf_host_batch_destroy(tgaf_ctx *ctx, tgaf_host_batch *batch);
  * the same m.  No counterpart in the reference, whose decoder issues each linear on its own
  * (core/src/inference/backend/cuda/engine.zig:4431-4474); it is the device-buffer sibling of tgaf_host_batch.
  * When every weight is gaf4 with one group size and scales dtype and m <= 8 (m <= 4 for groups of 32 codes, and for
- * lists with sums over the ranks or with dependent operations), the whole list runs as ONE kernel
+ * lists with sums over the ranks or with dependent operations), or every weight is gaf8_32 / gaf8_64 of one scheme and
+ * m = 1, the whole list runs as ONE kernel
  * launch: the copy warps stream from one weight straight into the next, so launch gap, ring ramp-up / drain and
  * write-out tail are paid once per list instead of once per weight; otherwise the calls run one after the other.
  *   depends[i] = 1: x_i is written by an earlier operation of the list (as down after gate|up): operation i starts

@@ -2312,6 +2312,13 @@ cudaError_t dispatch_list(const GemvParams &first, const WeightView &w0, const G
                           bool pdl, cudaStream_t stream, bool imma_small) {
     const bool bf = first.sdtype == 1u;
     constexpr int NST1 = GB == 16 ? 3 : 4;
+    if constexpr (GB != 16) {
+        if (w0.bits == 8u) {
+            if (M != 1) return cudaErrorNotSupported;
+            return bf ? launch_dp4a<GB, 1, false, 1, kConsumerWarps, 4, 8, 0, 8>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list)
+                      : launch_dp4a<GB, 1, false, 0, kConsumerWarps, 4, 8, 0, 8>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list);
+        }
+    }
     if ((imma_small && M == 1) || M == 2) M = 4;   // the int8-MMA instance (built for four rows) with fewer rows in use
     if (M == 1)
         return bf ? launch_dp4a<GB, 1, false, 1, kConsumerWarps, NST1, 8, 0>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list)
@@ -2672,12 +2679,17 @@ bool gemv_list_eligible(const WeightView *const *ws, uint32_t count, uint32_t M,
     if (count == 0u || count > 256u || M == 0u || M > 8u || tune.no_dp4a || tune.force_generic) return false;
     const WeightView &w0 = *ws[0];
     const uint32_t gb0 = w0.group * w0.bits / 8u;
-    if (gb0 != 16u && gb0 != 32u && gb0 != 64u) return false;
-    if (M > 4u && gb0 == 16u) return false;   // five to eight rows: groups of 64 and 128 codes only (shared memory)
+    if (w0.bits == 8u) {
+        // 8-bit codes: one activation row, groups of 32 and 64 codes (the integer dot-product instance)
+        if (M != 1u || tune.imma_small || (gb0 != 32u && gb0 != 64u)) return false;
+    } else {
+        if (gb0 != 16u && gb0 != 32u && gb0 != 64u) return false;
+        if (M > 4u && gb0 == 16u) return false;   // five to eight rows: groups of 64 and 128 codes only (shared memory)
+    }
     for (uint32_t i = 0; i < count; ++i) {
         const WeightView &w = *ws[i];
-        if (w.bits != 4u || w.group != w0.group || w.sdtype != w0.sdtype || !w.has_tmap) return false;
-        if (w.row_bytes != w.K / 2u) return false;
+        if ((w.bits != 4u && w.bits != 8u) || w.bits != w0.bits || w.group != w0.group || w.sdtype != w0.sdtype || !w.has_tmap) return false;
+        if (w.row_bytes != w.K * w.bits / 8u) return false;
     }
     return true;
 }
@@ -2739,7 +2751,9 @@ cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs,
     // One activation row on the integer-dot instance: operations whose activations nothing in this launch writes get them
     // quantised once per launch into global memory, [K chunk][1 KB of limb bytes + {scale, sum} per group]
     const uint32_t gb0 = ws[0]->group * ws[0]->bits / 8u;
-    const size_t xqs_unit = (1024u + (gb0 ? (kChunkBytes / gb0) * 8u : 0u)) * md;   // per activation row the instance is built for
+    // per activation row the instance is built for: the limb bytes of a unit's 512 (4-bit) or 256 (8-bit) activations
+    // and a {scale, sum} pair per group
+    const size_t xqs_unit = ((ws[0]->bits == 4u ? 1024u : 512u) + (gb0 ? (kChunkBytes / gb0) * 8u : 0u)) * md;
     const bool use_xq = gb0 != 0u;
     size_t xq_bytes = 0;
     // (only where it measured faster than letting each CTA quantise the block or two it needs: operations that give
