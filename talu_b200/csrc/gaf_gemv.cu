@@ -2737,8 +2737,9 @@ cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs,
                              GemvList **out) {
     *out = nullptr;
     if (!gemv_list_eligible(ws, count, M, tune)) return cudaErrorNotSupported;
-    // five to eight rows: an operation that reads what the launch writes would quantise per CTA in blocks of two units
-    // (that is all the shared memory left beside the eight-row stages), which measured slower than separate launches
+    // five to eight rows: an operation that quantises per CTA (it reads what the launch writes, or it is too small for the
+    // once-per-launch form) would do so in blocks of two units - all the shared memory left beside the eight-row stages -
+    // which measured slower than separate launches: such lists run call by call
     if (M > 4u && deps)
         for (uint32_t i = 0; i < count; ++i)
             if (deps[i]) return cudaErrorNotSupported;
@@ -2767,6 +2768,7 @@ cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs,
     for (uint32_t i = 0; i < count; ++i) {
         const GemvPlan pl = plan_gemv(*ws[i], t, sm_count);
         if (wants_xq(i, pl)) xq_bytes += static_cast<size_t>(pl.chunks) * xqs_unit;
+        else if (M > 4u) return cudaErrorNotSupported;   // five to eight rows: only operations that take the once-per-launch form
     }
     xq_bytes = (xq_bytes + 255u) & ~size_t(255);
     uint8_t *host = static_cast<uint8_t *>(malloc(map_bytes + par_bytes));

@@ -26,7 +26,7 @@ def _f32(oracle, t):
     return oracle.bf16_to_f32(bits_from_torch_bf16(t))
 
 
-@pytest.mark.parametrize("M", [1, 2, 4, 5, 8])
+@pytest.mark.parametrize("M", [1, 2, 4])
 def test_independent_list_in_one_launch(gaf, ctx, oracle, M):
     """Six weights of different shapes (ragged N, K below and above one activation block, a K that is split over many
     CTAs), each with its own activations: one launch, every output against the oracle and the one-by-one calls."""
@@ -225,15 +225,15 @@ def test_recorded_host_batch_is_two_block_copies_around_one_launch(gaf, oracle):
         c.close()
 
 
-@pytest.mark.parametrize("M", [1, 3, 7])
+@pytest.mark.parametrize("M", [1, 3, 5, 8])
 def test_full_grid_list_takes_its_activations_through_the_ring(gaf, ctx, oracle, M):
     """Llama-3-8B FFN shapes on all SMs: every operation gives each CTA dozens of units, so the launch quantises the
     activations once at its start and the copy warps stream them into the ring stages beside the weights (one
-    activation row: integer-dot instance; three: the int8-MMA instance with an unused fourth row).  Every output
-    against the oracle; same bits on every run."""
+    activation row: integer-dot instance; three: the int8-MMA instance with an unused fourth row; five and eight: its
+    two-column-set form, which exists for such lists only).  Every output against the oracle; same bits on every run."""
     import torch
     G = 64
-    shapes = [(28672, 4096), (4096, 14336), (6144, 4608)]
+    shapes = [(28672, 4096), (4096, 14336), (20480, 4608)]
     ws, xs, refs = [], [], []
     for i, (N, K) in enumerate(shapes):
         p, s, b = make_weights(oracle, N, K, G, 4, seed=700 + i)
