@@ -124,12 +124,20 @@ struct FusedOp {
 
 // A launch list for the M <= 4 kernel: operations in order, three tensor maps (packed, scales, biases) per operation,
 // all in device memory (written by the host before the launch).
+// One (operation, K chunk) pair of a launch list whose activations are quantised at the start of the launch.
+struct XqPair {
+    const void *x;     // the operation's bf16 activations [M][K]
+    uint8_t *dst;      // where this chunk's quantised unit goes
+    uint32_t kc, groups, K, M;
+};
+
 struct GemvOpList {
     const GemvParams *ops;
     const CUtensorMap *maps;
     uint32_t count;
     unsigned int *grid_bar;   // `count` arrival counters (+ one for the quantised activations), zero between launches
     uint32_t xq_pairs;        // (operation, K chunk) pairs whose activations are quantised at the start of the launch (0: none)
+    const XqPair *xq_tab;     // one entry per pair
 };
 
 // ---- small PTX wrappers ----------------------------------------------------
@@ -1617,22 +1625,10 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
 #pragma unroll 1
             for (uint32_t task = blockIdx.x * NCW + warp; task < ntasks; task += stride) {
                 const uint32_t m = task % MD, gl = (task / MD) % GPS, j = task / (MD * GPS);
-                // the operation this pair belongs to (a few dozen operations at most: a linear search)
-                uint8_t *xq_base = nullptr;
-                const __nv_bfloat16 *qx = nullptr;
-                uint32_t kc = 0u, qgroups = 0u, qK = 0u, qM = 0u;
-                for (uint32_t oo = 0; oo < nops; ++oo) {
-                    const GemvParams *qp = list.ops + oo;
-                    uint8_t *b = qp->xq;
-                    const uint32_t p0 = qp->xq_pair0, ch = qp->chunks;
-                    if (b != nullptr && j >= p0 && j < p0 + ch) {
-                        xq_base = b, kc = j - p0, qgroups = qp->groups, qK = qp->K, qM = qp->M;
-                        qx = static_cast<const __nv_bfloat16 *>(qp->x);
-                        break;
-                    }
-                }
-                if (xq_base == nullptr) continue;
-                uint8_t *dst = xq_base + static_cast<size_t>(kc) * Plan::XQS_UNIT;
+                const XqPair pr = list.xq_tab[j];
+                const __nv_bfloat16 *qx = static_cast<const __nv_bfloat16 *>(pr.x);
+                uint8_t *dst = pr.dst;
+                const uint32_t kc = pr.kc, qgroups = pr.groups, qK = pr.K, qM = pr.M;
                 const uint32_t gi = kc * GPS + gl;
                 const bool live = gi < qgroups && m < qM;   // rows the instance has room for but the call does not use: zeros
                 float xv[PER];
@@ -2724,6 +2720,7 @@ struct GemvList {
     void *d_blob;
     const GemvParams *d_params;
     const CUtensorMap *d_maps;
+    const XqPair *d_tab;
     unsigned int *d_bar;
     size_t bar_bytes;
     uint32_t count, ctas, M;
@@ -2771,8 +2768,15 @@ cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs,
         else if (M > 4u) return cudaErrorNotSupported;   // five to eight rows: only operations that take the once-per-launch form
     }
     xq_bytes = (xq_bytes + 255u) & ~size_t(255);
-    uint8_t *host = static_cast<uint8_t *>(malloc(map_bytes + par_bytes));
+    uint32_t total_pairs = 0;
+    for (uint32_t i = 0; i < count; ++i) {
+        const GemvPlan pl = plan_gemv(*ws[i], t, sm_count);
+        if (wants_xq(i, pl)) total_pairs += pl.chunks;
+    }
+    const size_t tab_bytes = (static_cast<size_t>(total_pairs) * sizeof(XqPair) + 255u) & ~size_t(255);
+    uint8_t *host = static_cast<uint8_t *>(malloc(map_bytes + par_bytes + tab_bytes));
     if (!host) return cudaErrorMemoryAllocation;
+    XqPair *tab = reinterpret_cast<XqPair *>(host + map_bytes + par_bytes);
     CUtensorMap *maps = reinterpret_cast<CUtensorMap *>(host);
     GemvParams *params = reinterpret_cast<GemvParams *>(host + map_bytes);
     size_t words = 0, xq_off = 0;
@@ -2816,14 +2820,23 @@ cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs,
         free(host);
         return cudaErrorMemoryAllocation;
     }
-    cudaError_t e = cudaMalloc(&l->d_blob, map_bytes + par_bytes + bar_bytes + xq_bytes);
+    // device blob: tensor maps, parameters, pair table, counters, quantised activations
+    cudaError_t e = cudaMalloc(&l->d_blob, map_bytes + par_bytes + tab_bytes + bar_bytes + xq_bytes);
     if (e == cudaSuccess) {
-        uint8_t *xq_base = static_cast<uint8_t *>(l->d_blob) + map_bytes + par_bytes + bar_bytes;
-        for (uint32_t i = 0; i < count; ++i)
-            if (params[i].xq) params[i].xq = xq_base + (reinterpret_cast<uintptr_t>(params[i].xq) - 1u);
+        uint8_t *xq_base = static_cast<uint8_t *>(l->d_blob) + map_bytes + par_bytes + tab_bytes + bar_bytes;
+        uint32_t np = 0;
+        for (uint32_t i = 0; i < count; ++i) {
+            if (!params[i].xq) continue;
+            params[i].xq = xq_base + (reinterpret_cast<uintptr_t>(params[i].xq) - 1u);
+            for (uint32_t kc = 0; kc < params[i].chunks; ++kc, ++np) {
+                tab[np].x = params[i].x;
+                tab[np].dst = params[i].xq + static_cast<size_t>(kc) * xqs_unit;
+                tab[np].kc = kc, tab[np].groups = params[i].groups, tab[np].K = params[i].K, tab[np].M = params[i].M;
+            }
+        }
     }
-    if (e == cudaSuccess) e = cudaMemcpyAsync(l->d_blob, host, map_bytes + par_bytes, cudaMemcpyHostToDevice, stream);
-    if (e == cudaSuccess) e = cudaMemsetAsync(static_cast<uint8_t *>(l->d_blob) + map_bytes + par_bytes, 0, bar_bytes, stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(l->d_blob, host, map_bytes + par_bytes + tab_bytes, cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(static_cast<uint8_t *>(l->d_blob) + map_bytes + par_bytes + tab_bytes, 0, bar_bytes, stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(stream);   // the host copy goes away below
     l->first = params[0];
     l->w0 = *ws[0];
@@ -2835,7 +2848,8 @@ cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs,
     }
     l->d_maps = static_cast<const CUtensorMap *>(l->d_blob);
     l->d_params = reinterpret_cast<const GemvParams *>(static_cast<uint8_t *>(l->d_blob) + map_bytes);
-    l->d_bar = reinterpret_cast<unsigned int *>(static_cast<uint8_t *>(l->d_blob) + map_bytes + par_bytes);
+    l->d_tab = reinterpret_cast<const XqPair *>(static_cast<uint8_t *>(l->d_blob) + map_bytes + par_bytes);
+    l->d_bar = reinterpret_cast<unsigned int *>(static_cast<uint8_t *>(l->d_blob) + map_bytes + par_bytes + tab_bytes);
     l->bar_bytes = bar_bytes;
     l->count = count;
     l->ctas = static_cast<uint32_t>(t.ctas);
@@ -2853,6 +2867,7 @@ cudaError_t gemv_list_launch(const GemvList *l, const GemvTuning &tune, cudaStre
     list.count = l->count;
     list.grid_bar = l->d_bar;
     list.xq_pairs = l->xq_pairs;
+    list.xq_tab = l->d_tab;
     const uint32_t gb = l->w0.group * l->w0.bits / 8u;
     const bool pdl = tune.pdl != 0;
     const bool im = l->imma_small;
