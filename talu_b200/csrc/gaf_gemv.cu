@@ -1063,7 +1063,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
     // quantised once per launch, streamed into the stages
     constexpr bool XQS = NOPS == 0 && (MD == 1 || MD >= 4) && !XF32;
     using Plan = DpPlan<GB, MD, XF32, NST, BU, XQS, BITS>;
-    static_assert(BITS == 4 || (BITS == 8 && MD <= 2), "8-bit codes: the integer dot-product form only (one or two rows)");
+    static_assert(BITS == 4 || (BITS == 8 && MD <= 4), "8-bit codes: up to four rows");
     constexpr int GPS = Geo::GPS, WPG = Plan::WPG;
     constexpr int RW = kRows * GPS / NCW;  // rows per warp: 128 (G=32), 64 (G=64), 32 (G=128)
     constexpr int R = RW / 32;                        // rows per lane
@@ -1651,7 +1651,13 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                     isum += xi;
                     const uint32_t k = lane * PER + e;
                     const uint32_t wj = k >> 3, odd = k & 1u, bytepos = (k & 7u) >> 1;
-                    if constexpr (IM) {
+                    if constexpr (IM && BITS == 8) {
+                        const uint32_t w8 = k >> 2, t8 = w8 / WPT, wl = w8 % WPT;   // (the layout the per-CTA quantiser writes)
+                        uint8_t *a = dst + gl * Plan::XQ_GROUP + ((wl >> 1) * NB + m / 4u) * 256u + ((2u * (m % 4u)) * 4u + t8) * 8u +
+                                     (wl & 1u) * 4u + (k & 3u);
+                        a[0] = static_cast<uint8_t>((xi >> 6) & 0xFF);
+                        a[32] = static_cast<uint8_t>(xi & 63);
+                    } else if constexpr (IM) {
                         // B registers of MMA (wj % WPT) for the quad lane (wj / WPT): 8 bytes {even, odd} per (column, quad
                         // lane), column 2m = hi limb, 2m + 1 = lo limb (the layout the per-CTA quantiser writes)
                         uint8_t *a = dst + gl * Plan::XQ_GROUP + ((wj % WPT) * NB + m / 4u) * 256u + ((2u * (m % 4u)) * 4u + wj / WPT) * 8u +
@@ -1723,7 +1729,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
     // Two passes so that all of a warp's global loads are in flight together.
     auto prep_block = [&](auto act_c, uint32_t kc_first, uint32_t count, uint32_t buf) {
         constexpr bool ACT = decltype(act_c)::value;  // compile-time: the plain path keeps its loads branch-free
-        if constexpr (IM && !ACT && !XF32) {
+        if constexpr (IM && BITS == 4 && !ACT && !XF32) {
             // Four activation rows: a lane takes one packed word's worth (8 consecutive elements, one 16-byte
             // load) of one (unit, group, activation row); the G/8 lanes of a row reduce among themselves.  The
             // word's {even, odd} byte pairs are exactly one lane's B registers of one MMA.
@@ -1848,7 +1854,14 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                 const uint32_t k = lane * PER + e;
                 const uint32_t wj = k >> 3, odd = k & 1u, bytepos = (k & 7u) >> 1;
                 // 16 bytes per (word, activation row): {even hi, odd hi, even lo, odd lo} x 4 bytes
-                if constexpr (IM) {
+                if constexpr (IM && BITS == 8) {
+                    // 8-bit codes: a lane's WPT words of the group row feed WPT / 2 MMAs, two words each (A registers
+                    // {a0, a1} = word 2 jj of rows g / g + 8, {a2, a3} = word 2 jj + 1); element k = byte k % 4 of word k / 4
+                    const uint32_t w8 = k >> 2, t8 = w8 / WPT, wl = w8 % WPT;
+                    const uint32_t a = qb + ((wl >> 1) * NB + m / 4u) * 256u + ((2u * (m % 4u)) * 4u + t8) * 8u + (wl & 1u) * 4u + (k & 3u);
+                    asm volatile("st.shared.u8 [%0], %1;" ::"r"(a), "r"(hi & 0xFF) : "memory");
+                    asm volatile("st.shared.u8 [%0], %1;" ::"r"(a + 32u), "r"(lo & 0xFF) : "memory");
+                } else if constexpr (IM) {
                     // B registers of MMA (wj % WPT) for the quad lane (wj / WPT): 8 bytes {even, odd} per
                     // (column, quad lane), column 2m = hi limb, 2m + 1 = lo limb
                     const uint32_t a = qb + ((wj % WPT) * NB + m / 4u) * 256u + ((2u * (m % 4u)) * 4u + wj / WPT) * 8u + odd * 4u + bytepos;
@@ -1911,11 +1924,12 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                 const uint32_t stage_off = stage * Plan::STAGE;
                 const uint32_t xq = (opx ? ring + stage_off + Geo::STAGE_BYTES + gq * Plan::XQ_GROUP
                                          : xq_warp + (buf * BU + ub) * Plan::XQ_UNIT) + lane * 8u;
-                uint32_t bfr[NB][WPT][2];  // this group's B registers, kept for all row blocks
+                constexpr int NMMA = BITS == 4 ? WPT : WPT / 2;   // MMAs per group: 32 codes each
+                uint32_t bfr[NB][NMMA][2];  // this group's B registers, kept for all row blocks
 #pragma unroll
                 for (int cs = 0; cs < NB; ++cs)
 #pragma unroll
-                    for (int j = 0; j < WPT; ++j)
+                    for (int j = 0; j < NMMA; ++j)
                         asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(bfr[cs][j][0]), "=r"(bfr[cs][j][1]) : "r"(xq + (j * NB + cs) * 256u));
                 float ex[NB], xs[NB];  // activation rows 4 cs + qt
 #pragma unroll
@@ -1933,12 +1947,21 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
                     int c[NB][4];
 #pragma unroll
                     for (int cs = 0; cs < NB; ++cs) c[cs][0] = c[cs][1] = c[cs][2] = c[cs][3] = 0;
+                    if constexpr (BITS == 8) {
+                        // the code bytes ARE the A registers: no unpacking at all
+#pragma unroll
+                        for (int j = 0; j < NMMA; ++j)
+#pragma unroll
+                            for (int cs = 0; cs < NB; ++cs)
+                                mma_u8s8_16832(c[cs], wa[2 * j], wb[2 * j], wa[2 * j + 1], wb[2 * j + 1], bfr[cs][j][0], bfr[cs][j][1]);
+                    } else {
 #pragma unroll
                     for (int j = 0; j < WPT; ++j) {
                         const uint32_t a0 = wa[j] & 0x0F0F0F0Fu, a1 = wb[j] & 0x0F0F0F0Fu;
                         const uint32_t a2 = (wa[j] >> 4) & 0x0F0F0F0Fu, a3 = (wb[j] >> 4) & 0x0F0F0F0Fu;
 #pragma unroll
                         for (int cs = 0; cs < NB; ++cs) mma_u8s8_16832(c[cs], a0, a1, a2, a3, bfr[cs][j][0], bfr[cs][j][1]);
+                    }
                     }
                     uint16_t s0r, b0r, s1r, b1r;
                     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(s0r) : "r"(stage_off + sbim[rb] + sbo));
@@ -2310,9 +2333,13 @@ cudaError_t dispatch_list(const GemvParams &first, const WeightView &w0, const G
     constexpr int NST1 = GB == 16 ? 3 : 4;
     if constexpr (GB != 16) {
         if (w0.bits == 8u) {
-            if (M != 1) return cudaErrorNotSupported;
-            return bf ? launch_dp4a<GB, 1, false, 1, kConsumerWarps, 4, 8, 0, 8>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list)
-                      : launch_dp4a<GB, 1, false, 0, kConsumerWarps, 4, 8, 0, 8>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list);
+            if (M == 1 && !imma_small)
+                return bf ? launch_dp4a<GB, 1, false, 1, kConsumerWarps, 4, 8, 0, 8>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list)
+                          : launch_dp4a<GB, 1, false, 0, kConsumerWarps, 4, 8, 0, 8>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list);
+            if (M <= 4)
+                return bf ? launch_dp4a<GB, 4, false, 1, kConsumerWarps, 3, 8, 0, 8>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list)
+                          : launch_dp4a<GB, 4, false, 0, kConsumerWarps, 3, 8, 0, 8>(first, w0, nullptr, ctas, pdl, stream, nullptr, &list);
+            return cudaErrorNotSupported;
         }
     }
     if ((imma_small && M == 1) || M == 2) M = 4;   // the int8-MMA instance (built for four rows) with fewer rows in use
@@ -2375,6 +2402,9 @@ cudaError_t dispatch_dp4a8(const GemvParams &p, const WeightView &w, const Weigh
     if (M == 2)
         return bf ? launch_dp4a<GB, 2, false, 1, kConsumerWarps, 3, 8, 1, 8>(p, w, next, ctas, pdl, stream)
                   : launch_dp4a<GB, 2, false, 0, kConsumerWarps, 3, 8, 1, 8>(p, w, next, ctas, pdl, stream);
+    if (M == 3 || M == 4)   // int8 MMA on the code bytes as they are
+        return bf ? launch_dp4a<GB, 4, false, 1, kConsumerWarps, 3, 8, 1, 8>(p, w, next, ctas, pdl, stream)
+                  : launch_dp4a<GB, 4, false, 0, kConsumerWarps, 3, 8, 1, 8>(p, w, next, ctas, pdl, stream);
     return cudaErrorNotSupported;
 }
 
@@ -2490,7 +2520,7 @@ size_t gemv_tagged_bytes(const WeightView &w, uint32_t M, bool x_f32, const Gemv
     if (M == 0u || M > 16u) return 0;
     const GemvPlan pl = plan_gemv(w, tune, sm_count);
     const uint32_t gb = w.group * w.bits / 8u;
-    const bool integer_path = ((w.bits == 4u && M <= 4u) || (w.bits == 8u && M <= 2u && (gb == 32u || gb == 64u))) && !x_f32 &&
+    const bool integer_path = ((w.bits == 4u && M <= 4u) || (w.bits == 8u && M <= 4u && (gb == 32u || gb == 64u))) && !x_f32 &&
                               !tune.no_dp4a && gb != 0u;
     const uint32_t cols = integer_path ? (M <= 2u ? M : 4u) : (M <= 8u ? 8u : 16u);
     return static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * cols * 8u;
@@ -2579,8 +2609,9 @@ cudaError_t gemv_mma(const WeightView &w, const void *x, void *y, uint32_t M, bo
         if (gb == 32u) return dispatch_dp4a<32>(p, w, next, pl.ctas, M, pdl, stream);
         if (gb == 64u) return dispatch_dp4a<64>(p, w, next, pl.ctas, M, pdl, stream);
     }
-    if (w.bits == 8 && M <= 2u && !x_f32 && !tune.no_dp4a && (gb == 32u || gb == 64u)) {
-        if (scratch.tagged && static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * M * 8u <= scratch.tagged_bytes)
+    if (w.bits == 8 && M <= 4u && !x_f32 && !tune.no_dp4a && (gb == 32u || gb == 64u)) {
+        const uint32_t md8 = M <= 2u ? M : 4u;
+        if (scratch.tagged && static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * md8 * 8u <= scratch.tagged_bytes)
             p.tagged = scratch.tagged;
         if (gb == 32u) return dispatch_dp4a8<32>(p, w, next, pl.ctas, M, pdl, stream);
         return dispatch_dp4a8<64>(p, w, next, pl.ctas, M, pdl, stream);
@@ -2676,8 +2707,8 @@ bool gemv_list_eligible(const WeightView *const *ws, uint32_t count, uint32_t M,
     const WeightView &w0 = *ws[0];
     const uint32_t gb0 = w0.group * w0.bits / 8u;
     if (w0.bits == 8u) {
-        // 8-bit codes: one activation row, groups of 32 and 64 codes (the integer dot-product instance)
-        if (M != 1u || tune.imma_small || (gb0 != 32u && gb0 != 64u)) return false;
+        // 8-bit codes: up to four activation rows, groups of 32 and 64 codes
+        if (M > 4u || (gb0 != 32u && gb0 != 64u)) return false;
     } else {
         if (gb0 != 16u && gb0 != 32u && gb0 != 64u) return false;
         if (M > 4u && gb0 == 16u) return false;   // five to eight rows: groups of 64 and 128 codes only (shared memory)

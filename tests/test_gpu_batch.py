@@ -262,16 +262,17 @@ def test_full_grid_list_takes_its_activations_through_the_ring(gaf, ctx, oracle,
         w.free()
 
 
-def test_list_of_8bit_weights_at_one_row(gaf, ctx, oracle):
-    """gaf8_64 weights, one activation row: one launch of the integer dot-product instance for 8-bit codes (activations
-    through the ring stages where the operation is large enough); against the oracle and the single calls."""
+@pytest.mark.parametrize("M", [1, 2, 4])
+def test_list_of_8bit_weights(gaf, ctx, oracle, M):
+    """gaf8_64 weights: one launch of the integer kernel's 8-bit instances (dot products at one row, the int8 MMA on the
+    code bytes above; activations through the ring stages where the operation is large enough); against the oracle."""
     import torch
-    G, M = 64, 1
+    G = 64
     shapes = [(4096, 4096), (1000, 2048), (8192, 4096), (512, 14336)]
     ws, xs, refs = [], [], []
     for i, (N, K) in enumerate(shapes):
         p, s, b = make_weights(oracle, N, K, G, 8, seed=900 + i)
-        xb, xf = make_x_bf16(oracle, M, K, seed=950 + i)
+        xb, xf = make_x_bf16(oracle, M, K, seed=950 + i + M)
         ws.append(gaf.Weight.from_host(ctx, p, s, b, G, 8))
         xs.append(torch_bf16_from_bits(xb, "cuda:0"))
         refs.append(oracle.matmul_f32(xf, p, s, b, G, 8))
@@ -286,13 +287,5 @@ def test_list_of_8bit_weights_at_one_row(gaf, ctx, oracle):
         for y, ref in zip(ys, refs):
             assert rel_err(_f32(oracle, y), ref) <= TOL_BF16, rep
     batch.close()
-    # two rows: no 8-bit list instance, the calls run one by one
-    x2 = [torch.zeros((2, w.K), dtype=torch.bfloat16, device="cuda:0") for w in ws]
-    y2 = [torch.zeros((2, w.N), dtype=torch.bfloat16, device="cuda:0") for w in ws]
-    b2 = gaf.Batch(ctx, ws, x2, y2)
-    assert not b2.one_launch
-    b2.run()
-    ctx.synchronize()
-    b2.close()
     for w in ws:
         w.free()

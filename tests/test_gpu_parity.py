@@ -505,12 +505,13 @@ def test_prefill_cfg4_full_size(gaf, ctx, oracle):
 
 
 def test_8bit_codes_on_the_integer_dot_product_kernel(gaf, ctx, oracle):
-    """gaf8_32 / gaf8_64 at one and two bf16 activation rows run on the integer dot-product kernel (a packed word IS four
-    unsigned bytes): K split over many CTAs, ragged N, bf16 and f16 scale patterns; gaf8_128 stays on the tensor-core
-    GEMV.  rel <= 1e-2 against the oracle."""
+    """gaf8_32 / gaf8_64 at one to four bf16 activation rows run on the integer kernel (a packed word IS four unsigned
+    bytes: dot products at one and two rows, the int8 MMA at three and four): K split over many CTAs, ragged N, bf16
+    and f16 scale patterns; gaf8_128 stays on the tensor-core GEMV.  rel <= 1e-2 against the oracle."""
     rng = np.random.default_rng(5)
     for N, K, G, M, f16 in [(2048, 4096, 64, 1, False), (1000, 8192, 32, 2, False), (4096, 14336, 64, 1, True),
-                            (520, 2048, 32, 1, True), (384, 1024, 128, 2, False)]:
+                            (520, 2048, 32, 1, True), (384, 1024, 128, 2, False), (2048, 4096, 64, 4, False),
+                            (1000, 8192, 32, 3, True), (4096, 14336, 64, 4, True), (130, 512, 64, 3, False)]:
         p, s, b = make_weights(oracle, N, K, G, 8, seed=N + M)
         sd_lib, sd_or = gaf.SCALES_BF16, oracle.SCALES_BF16
         if f16:
