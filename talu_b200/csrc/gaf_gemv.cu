@@ -2787,11 +2787,12 @@ cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs,
     size_t xq_bytes = 0;
     // (only where it measured faster than letting each CTA quantise the block or two it needs: operations that give
     // every CTA at least eight units, or at least four when a row of K does not fit one CTA's activation buffers, so
-    // that the per-CTA form would rebuild its block, behind a CTA barrier, every eight units)
+    // that the per-CTA form would rebuild its block, behind a CTA barrier, every eight units - or when there are more
+    // than four rows, whose instance has room for per-CTA blocks of two units only)
     auto wants_xq = [&](uint32_t i, const GemvPlan &pl) {
         if (!use_xq || (deps && deps[i])) return false;
         const uint32_t per_cta = pl.units / static_cast<uint32_t>(t.ctas);
-        return per_cta >= 8u || (per_cta >= 4u && pl.chunks > 16u);
+        return per_cta >= 8u || (per_cta >= 4u && (pl.chunks > 16u || M > 4u));
     };
     for (uint32_t i = 0; i < count; ++i) {
         const GemvPlan pl = plan_gemv(*ws[i], t, sm_count);
