@@ -212,7 +212,7 @@ int32_t tgaf_host_batch_destroy(tgaf_ctx *ctx, tgaf_host_batch *batch);
  * (core/src/inference/backend/cuda/engine.zig:4431-4474); it is the device-buffer sibling of tgaf_host_batch.
  * When every weight is gaf4 with one group size and scales dtype and m <= 8 (m <= 4 for groups of 32 codes, for lists
  * with sums over the ranks or with dependent operations, and for lists with small weights: above four rows every
- * operation must give each CTA eight units of 128 rows x 512 codes, or four when K > 8192), or every weight is gaf8_32 / gaf8_64 of one scheme and
+ * operation must give each CTA four units of 128 rows x 512 codes), or every weight is gaf8_32 / gaf8_64 of one scheme and
  * m <= 4, the whole list runs as ONE kernel
  * launch: the copy warps stream from one weight straight into the next, so launch gap, ring ramp-up / drain and
  * write-out tail are paid once per list instead of once per weight; otherwise the calls run one after the other.
