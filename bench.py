@@ -45,8 +45,8 @@ GROUP, BITS = 64, 4
 NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch list of the --quick case (2 layers = 4 GEMVs,
 # 198,377,472 algorithmic bytes), from the ncu capture summarised in profiles/gemv_list_llama8b_ffn_m1.md,
-# divided by the four GEMVs of the launch: (198,460,672 read + 4,923,648 written) / 4
-NCU_TRAFFIC_PER_GEMV = 50846080
+# divided by the four GEMVs of the launch: (198,450,432 read + 4,838,400 written) / 4
+NCU_TRAFFIC_PER_GEMV = 50822208
 
 
 def measured_peak_hbm():
