@@ -113,6 +113,8 @@ struct GemvParams {
                              // [K chunk][quantised unit + {scale, sum} pairs], built once per launch at its very start and
                              // copied into every ring stage beside the weights (null: each CTA quantises for itself)
     uint32_t xq_pair0;       //   index of this operation's first (operation, K chunk) pair among all such pairs of the list
+    uint32_t rot;            // launch lists: CTA b takes the unit range of index (b + rot) mod grid, so that the CTAs with one
+                             //   unit more than the others are different ones from operation to operation
 };
 
 // One operation's exchange as the writer warp needs it to collect the peers' words later on.
@@ -314,6 +316,11 @@ __device__ __forceinline__ void load_x_frags(const void *xrow, uint32_t kx, bool
 __device__ __host__ __forceinline__ uint32_t range_begin(uint32_t cta, uint32_t units, uint32_t ctas) {
     const uint32_t q = units / ctas, rem = units % ctas;
     return cta * q + (cta < rem ? cta : rem);
+}
+// launch lists: the range index of CTA `cta` in an operation whose ranges are dealt from CTA (grid - rot) on
+__device__ __forceinline__ uint32_t range_index(uint32_t cta, uint32_t rot, uint32_t ctas) {
+    const uint32_t v = cta + rot;
+    return v >= ctas ? v - ctas : v;
 }
 __device__ __host__ __forceinline__ uint32_t unit_owner(uint32_t u, uint32_t units, uint32_t ctas) {
     const uint32_t q = units / ctas, rem = units % ctas;
@@ -1103,8 +1110,9 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
     __syncthreads();
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    // every CTA has at least one unit of every operation (the host caps the grid at the smallest unit count)
-    if (range_begin(blockIdx.x, pa.units, gridDim.x) >= range_begin(blockIdx.x + 1u, pa.units, gridDim.x)) return;
+    // one or two operations: every CTA has at least one unit of each (the host caps the grid at the smallest unit count).
+    // A launch list may hold operations with fewer units than CTAs: a CTA without units of one still arrives at its counter
+    if (NOPS != 0 && range_begin(blockIdx.x, pa.units, gridDim.x) >= range_begin(blockIdx.x + 1u, pa.units, gridDim.x)) return;
     const uint32_t nops = NOPS > 0 ? static_cast<uint32_t>(NOPS) : list.count;   // list mode: pa is the first operation
     unsigned int *const gbar = NOPS > 0 ? pa.grid_bar : list.grid_bar;
 
@@ -1155,8 +1163,9 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tw)) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(ts)) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tb)) : "memory");
-            const uint32_t u_begin = range_begin(blockIdx.x, p.units, gridDim.x);
-            const uint32_t u_end = range_begin(blockIdx.x + 1u, p.units, gridDim.x);
+            const uint32_t vcta = NOPS == 0 ? range_index(blockIdx.x, p.rot, gridDim.x) : blockIdx.x;
+            const uint32_t u_begin = range_begin(vcta, p.units, gridDim.x);
+            const uint32_t u_end = range_begin(vcta + 1u, p.units, gridDim.x);
             uint32_t rg = u_begin / p.chunks;
             uint32_t kc = u_begin - rg * p.chunks;
             for (uint32_t u = u_begin; u < u_end && ok; ++u) {
@@ -1229,9 +1238,11 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
         GemvParams plist;
         if constexpr (NOPS == 0) plist = list.ops[o];
         const GemvParams &p = NOPS == 0 ? plist : (o == 0 ? pa : pb);
-        const uint32_t u_begin = range_begin(blockIdx.x, p.units, gridDim.x);
-        const uint32_t u_end = range_begin(blockIdx.x + 1u, p.units, gridDim.x);
+        const uint32_t vcta = NOPS == 0 ? range_index(blockIdx.x, p.rot, gridDim.x) : blockIdx.x;
+        const uint32_t u_begin = range_begin(vcta, p.units, gridDim.x);
+        const uint32_t u_end = range_begin(vcta + 1u, p.units, gridDim.x);
         const uint32_t rg_begin = u_begin / p.chunks;
+        // (a CTA without units of this operation: u_begin = u_end = units, the loop below is empty)
         const uint32_t rg_last_touched = (u_end - 1u) / p.chunks;
 
         // Fused all-reduce (row-parallel weight under tensor parallelism): the final sums of a row group are
@@ -1375,7 +1386,7 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
             if (!whole) {
                 const uint32_t first_cta = unit_owner(rg_first, p.units, gridDim.x);
                 slots = unit_owner(rg_last, p.units, gridDim.x) - first_cta + 1u;
-                slot = blockIdx.x - first_cta;
+                slot = vcta - first_cta;
             }
             // scratch slot layout [128 rows][8]: the same footprint as the tensor-core kernel's single tile
             float *mine = p.partials + (static_cast<size_t>(rg) * p.max_slots + slot) * (kRows * 8);
@@ -1692,8 +1703,9 @@ gaf_gemv_dp4a_kernel(const GemvParams pa, const GemvParams pb, const __grid_cons
     if constexpr (NOPS == 0) plist = list.ops[o];
     const GemvParams &p = NOPS == 0 ? plist : (o == 0 ? pa : pb);
     const uint8_t *xbase = static_cast<const uint8_t *>(p.x);
-    const uint32_t u_begin = range_begin(blockIdx.x, p.units, gridDim.x);
-    const uint32_t u_end = range_begin(blockIdx.x + 1u, p.units, gridDim.x);
+    const uint32_t vcta = NOPS == 0 ? range_index(blockIdx.x, p.rot, gridDim.x) : blockIdx.x;
+    const uint32_t u_begin = range_begin(vcta, p.units, gridDim.x);
+    const uint32_t u_end = range_begin(vcta + 1u, p.units, gridDim.x);
     const uint32_t rg_begin = u_begin / p.chunks;
     const uint32_t kc_begin = u_begin - rg_begin * p.chunks;
     // opx: this operation's activations were quantised at the start of the launch and arrive with every stage: no
@@ -2721,19 +2733,23 @@ bool gemv_list_eligible(const WeightView *const *ws, uint32_t count, uint32_t M,
     return true;
 }
 
-uint32_t gemv_list_ctas(const WeightView *const *ws, uint32_t count, const GemvTuning &tune, int sm_count) {
-    uint32_t ctas = 0xFFFFFFFFu;
+// One grid for the whole list.  Up to four rows: as many CTAs as the largest operation can use; in an operation with
+// fewer units than that some CTAs have none (they pass straight on to the next one).  Five to eight rows: the
+// smallest unit count, so that every operation keeps the units per CTA the once-per-launch activations want.
+uint32_t gemv_list_ctas(const WeightView *const *ws, uint32_t count, uint32_t M, const GemvTuning &tune, int sm_count) {
+    uint32_t lo = 0xFFFFFFFFu, hi = 1u;
     for (uint32_t i = 0; i < count; ++i) {
         const GemvPlan pl = plan_gemv(*ws[i], tune, sm_count);
-        if (pl.ctas < ctas) ctas = pl.ctas;   // one grid: every CTA has units of every weight
+        if (pl.ctas < lo) lo = pl.ctas;
+        if (pl.ctas > hi) hi = pl.ctas;
     }
-    return ctas;
+    return M <= 4u ? hi : lo;
 }
 
 // tagged split-K words the whole list needs (64-bit words), operation by operation
 size_t gemv_list_tagged_words(const WeightView *const *ws, uint32_t count, uint32_t M, const GemvTuning &tune, int sm_count) {
     GemvTuning t = tune;
-    t.ctas = static_cast<int>(gemv_list_ctas(ws, count, tune, sm_count));
+    t.ctas = static_cast<int>(gemv_list_ctas(ws, count, M, tune, sm_count));
     const uint32_t md = list_instance_rows(M, tune);
     size_t words = 0;
     for (uint32_t i = 0; i < count; ++i) {
@@ -2772,7 +2788,7 @@ cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs,
         for (uint32_t i = 0; i < count; ++i)
             if (deps[i]) return cudaErrorNotSupported;
     GemvTuning t = tune;
-    t.ctas = static_cast<int>(gemv_list_ctas(ws, count, tune, sm_count));
+    t.ctas = static_cast<int>(gemv_list_ctas(ws, count, M, tune, sm_count));
     const uint32_t md = list_instance_rows(M, tune);
     const size_t map_bytes = static_cast<size_t>(count) * 3u * sizeof(CUtensorMap);
     const size_t par_bytes = (static_cast<size_t>(count) * sizeof(GemvParams) + 255u) & ~size_t(255);
@@ -2812,7 +2828,7 @@ cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs,
     CUtensorMap *maps = reinterpret_cast<CUtensorMap *>(host);
     GemvParams *params = reinterpret_cast<GemvParams *>(host + map_bytes);
     size_t words = 0, xq_off = 0;
-    uint32_t xq_pairs = 0;
+    uint32_t xq_pairs = 0, rot = 0;
     for (uint32_t i = 0; i < count; ++i) {
         const WeightView &w = *ws[i];
         if (!gemv_mma_eligible(w, xs[i], ys[i], false)) {
@@ -2824,6 +2840,9 @@ cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs,
         q.tagged = tagged + words;
         words += static_cast<size_t>(pl.rgs) * pl.max_slots * kRows * md;
         q.dep = deps && deps[i] ? 1u : 0u;
+        // the ranges with one unit more start where the previous operation's stopped
+        q.rot = rot;
+        rot = (rot + static_cast<uint32_t>(t.ctas) - pl.units % static_cast<uint32_t>(t.ctas)) % static_cast<uint32_t>(t.ctas);
         if (wants_xq(i, pl)) {
             // the address is an offset for now: the blob it lives in is allocated below
             q.xq = reinterpret_cast<uint8_t *>(xq_off + 1u);

@@ -262,6 +262,70 @@ def test_full_grid_list_takes_its_activations_through_the_ring(gaf, ctx, oracle,
         w.free()
 
 
+@pytest.mark.parametrize("M", [1, 3])
+def test_list_whose_operations_have_fewer_units_than_the_grid(gaf, ctx, oracle, M):
+    """One grid serves the whole list, sized for its largest operation: in the small operations (4, 32 and 128 units of
+    128 rows x 256 packed bytes against a grid of 148 CTAs) some CTAs have no units and pass straight on, and the
+    ranges with one unit more rotate from operation to operation.  The second half repeats the list with the second
+    operation reading the first one's output (the grid-wide counter between them is reached by every CTA, with or
+    without units).  Every output against the oracle; same bits on every run."""
+    import torch
+    G = 64
+    shapes = [(8192, 8192), (256, 1024), (1024, 2048), (8192, 1024), (20480, 4608)]
+    ws, xs, refs = [], [], []
+    for i, (N, K) in enumerate(shapes):
+        p, s, b = make_weights(oracle, N, K, G, 4, seed=1100 + i)
+        xb, xf = make_x_bf16(oracle, M, K, seed=1200 + i + M)
+        ws.append(gaf.Weight.from_host(ctx, p, s, b, G, 4))
+        xs.append(torch_bf16_from_bits(xb, "cuda:0"))
+        refs.append(oracle.matmul_f32(xf, p, s, b, G, 4))
+    ys = [torch.full((M, w.N), float("nan"), dtype=torch.bfloat16, device="cuda:0") for w in ws]
+    batch = gaf.Batch(ctx, ws, xs, ys)
+    assert batch.one_launch
+    first = None
+    for rep in range(4):
+        for y in ys:
+            y.fill_(float("nan"))
+        batch.run()
+        ctx.synchronize()
+        if first is None:
+            first = [y.clone() for y in ys]
+            for y, ref in zip(ys, refs):
+                assert rel_err(_f32(oracle, y), ref) <= TOL_BF16
+        else:
+            for y, f in zip(ys, first):
+                assert torch.equal(y, f), rep
+    batch.close()
+    # a chain through small operations: y0 = W[8192 x 1024] x0 (128 units), y1 = W[2048 x 8192] y0, y2 = W[1024 x 2048] y1 (32 units)
+    pm, sm, bm = make_weights(oracle, 2048, 8192, G, 4, seed=1300)
+    mid_w = gaf.Weight.from_host(ctx, pm, sm, bm, G, 4)
+    y0 = torch.full((M, 8192), float("nan"), dtype=torch.bfloat16, device="cuda:0")
+    y1 = torch.full((M, 2048), float("nan"), dtype=torch.bfloat16, device="cuda:0")
+    y2 = torch.full((M, 1024), float("nan"), dtype=torch.bfloat16, device="cuda:0")
+    chain = gaf.Batch(ctx, [ws[3], mid_w, ws[2]], [xs[3], y0, y1], [y0, y1, y2], depends=[0, 1, 1])
+    assert chain.one_launch
+    p2, s2, b2 = make_weights(oracle, 1024, 2048, G, 4, seed=1100 + 2)
+    kept = None
+    for rep in range(3):
+        for y in (y0, y1, y2):
+            y.fill_(float("nan"))
+        chain.run()
+        ctx.synchronize()
+        if kept is None:
+            kept = [y.clone() for y in (y0, y1, y2)]
+            assert rel_err(_f32(oracle, y0), refs[3]) <= TOL_BF16
+            # each link from the GPU's own input: one linear's budget
+            assert rel_err(_f32(oracle, y1), oracle.matmul_f32(_f32(oracle, y0), pm, sm, bm, G, 4)) <= TOL_BF16
+            assert rel_err(_f32(oracle, y2), oracle.matmul_f32(_f32(oracle, y1), p2, s2, b2, G, 4)) <= TOL_BF16
+        else:
+            for y, f in zip((y0, y1, y2), kept):
+                assert torch.equal(y, f), rep
+    chain.close()
+    mid_w.free()
+    for w in ws:
+        w.free()
+
+
 @pytest.mark.parametrize("M", [1, 2, 4])
 def test_list_of_8bit_weights(gaf, ctx, oracle, M):
     """gaf8_64 weights: one launch of the integer kernel's 8-bit instances (dot products at one row, the int8 MMA on the
