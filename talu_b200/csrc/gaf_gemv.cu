@@ -2801,14 +2801,14 @@ cudaError_t gemv_list_create(const WeightView *const *ws, const void *const *xs,
     const size_t xqs_unit = ((ws[0]->bits == 4u ? 1024u : 512u) + (gb0 ? (kChunkBytes / gb0) * 8u : 0u)) * md;
     const bool use_xq = gb0 != 0u;
     size_t xq_bytes = 0;
-    // (only where it measured faster than letting each CTA quantise the block or two it needs: operations that give
-    // every CTA at least eight units, or at least four when a row of K does not fit one CTA's activation buffers, so
-    // that the per-CTA form would rebuild its block, behind a CTA barrier, every eight units - or when there are more
-    // than four rows, whose instance has room for per-CTA blocks of two units only)
+    // (operations that give every CTA at least two units - with the unit ranges rotating and the launch-start
+    // quantisation dealt over the whole grid that measured faster than, or as fast as, letting each CTA quantise the
+    // block or two it needs, down to the shards of eight tensor-parallel ranks; above four rows, whose instance has room
+    // for per-CTA blocks of two units only, at least four units)
     auto wants_xq = [&](uint32_t i, const GemvPlan &pl) {
         if (!use_xq || (deps && deps[i])) return false;
         const uint32_t per_cta = pl.units / static_cast<uint32_t>(t.ctas);
-        return per_cta >= 8u || (per_cta >= 4u && (pl.chunks > 16u || M > 4u));
+        return per_cta >= (M <= 4u ? 2u : 4u);
     };
     for (uint32_t i = 0; i < count; ++i) {
         const GemvPlan pl = plan_gemv(*ws[i], t, sm_count);
