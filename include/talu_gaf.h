@@ -216,6 +216,8 @@ int32_t tgaf_host_batch_destroy(tgaf_ctx *ctx, tgaf_host_batch *batch);
  * m <= 4, the whole list runs as ONE kernel
  * launch: the copy warps stream from one weight straight into the next, so launch gap, ring ramp-up / drain and
  * write-out tail are paid once per list instead of once per weight; otherwise the calls run one after the other.
+ * Weights of any sizes may share a list (up to four rows the launch is sized for the largest; the unit ranges are dealt
+ * so that over the whole list every CTA streams the same number of units to within one).
  *   depends[i] = 1: x_i is written by an earlier operation of the list (as down after gate|up): operation i starts
  *                   on its activations only when operation i - 1 is complete on the whole GPU.  0 (or depends ==
  *                   NULL): the caller promises that x_i is written by no operation of this list.
